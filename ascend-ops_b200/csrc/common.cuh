@@ -1,0 +1,97 @@
+// Shared host/device helpers for the sm_100a decode operator kernels.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <cstdarg>
+#include <cstdio>
+
+#include "b200ops.h"
+
+namespace b200ops {
+
+// ---- host-side error reporting -------------------------------------------------------
+// One message buffer per host thread; b200ops_last_error() returns it.
+char* last_error_buffer();
+constexpr size_t kLastErrorLen = 512;
+
+inline int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(last_error_buffer(), kLastErrorLen, fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+#define B200OPS_REQUIRE(cond, ...)                         \
+  do {                                                     \
+    if (!(cond)) return ::b200ops::fail(B200OPS_EINVAL, __VA_ARGS__); \
+  } while (0)
+
+#define B200OPS_CUDA(expr)                                                          \
+  do {                                                                              \
+    cudaError_t err__ = (expr);                                                     \
+    if (err__ != cudaSuccess)                                                       \
+      return ::b200ops::fail(B200OPS_ECUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
+  } while (0)
+
+// Launch check: reports configuration errors of the launch just made without
+// synchronising (asynchronous faults surface at the caller's next sync, as with any stream work).
+#define B200OPS_LAUNCH_CHECK(name)                                                        \
+  do {                                                                                    \
+    cudaError_t err__ = cudaGetLastError();                                               \
+    if (err__ != cudaSuccess)                                                             \
+      return ::b200ops::fail(B200OPS_ECUDA, "%s launch failed: %s", name, cudaGetErrorString(err__)); \
+  } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Number of SMs of the current device (cached per device).
+int sm_count();
+
+// ---- device helpers --------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// 128-bit global loads/stores with cache hints.  Streaming data that is touched once is
+// loaded without L1 allocation and stored with an evict-first policy so that it does not
+// push reusable lines (weights, cos/sin rows) out of L2.
+__device__ __forceinline__ uint4 ld_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void st_stream(void* p, const uint4& v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__device__ __forceinline__ float2 h2_to_f2(uint32_t u) {
+  return __half22float2(*reinterpret_cast<const __half2*>(&u));
+}
+
+__device__ __forceinline__ uint32_t f2_to_h2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+#endif  // __CUDACC__
+
+}  // namespace b200ops

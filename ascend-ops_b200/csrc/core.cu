@@ -1,0 +1,60 @@
+// Library-wide pieces of the C ABI: version, per-thread error text, device report.
+#include "common.cuh"
+
+#include <cstring>
+
+namespace b200ops {
+
+char* last_error_buffer() {
+  static thread_local char buf[kLastErrorLen] = {0};
+  return buf;
+}
+
+int sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace b200ops
+
+extern "C" int b200ops_version(void) { return 100; }
+
+extern "C" const char* b200ops_last_error(void) { return b200ops::last_error_buffer(); }
+
+// Replaces native::print_info (csrc/ffi/bind.cpp:26-51), which prints the Ascend core counts
+// and the sizes / bandwidths of its on-chip memories; the CUDA counterpart of those figures
+// is what cudaDeviceProp and the device attributes report.
+extern "C" int b200ops_print_info(int device_id, char* buf, size_t buf_len) {
+  using namespace b200ops;
+  cudaDeviceProp prop;
+  B200OPS_CUDA(cudaGetDeviceProperties(&prop, device_id));
+  int mem_clock_khz = 0, bus_bits = 0, smem_optin = 0;
+  B200OPS_CUDA(cudaDeviceGetAttribute(&mem_clock_khz, cudaDevAttrMemoryClockRate, device_id));
+  B200OPS_CUDA(cudaDeviceGetAttribute(&bus_bits, cudaDevAttrGlobalMemoryBusWidth, device_id));
+  B200OPS_CUDA(cudaDeviceGetAttribute(&smem_optin, cudaDevAttrMaxSharedMemoryPerBlockOptin, device_id));
+  char text[1024];
+  snprintf(text, sizeof(text),
+           "device %d: %s (sm_%d%d)\n"
+           "SMs: %d, max threads/SM: %d, registers/SM: %d\n"
+           "shared memory/SM: %zu, shared memory/block (opt-in): %d, L2: %d, HBM: %zu\n"
+           "memory clock kHz: %d, memory bus bits: %d, nominal HBM GB/s: %.0f\n",
+           device_id, prop.name, prop.major, prop.minor, prop.multiProcessorCount,
+           prop.maxThreadsPerMultiProcessor, prop.regsPerMultiprocessor,
+           prop.sharedMemPerMultiprocessor, smem_optin, prop.l2CacheSize, prop.totalGlobalMem,
+           mem_clock_khz, bus_bits, 2.0 * mem_clock_khz * 1e3 * (bus_bits / 8.0) / 1e9);
+  fputs(text, stdout);
+  fflush(stdout);
+  if (buf != nullptr && buf_len > 0) {
+    strncpy(buf, text, buf_len - 1);
+    buf[buf_len - 1] = '\0';
+  }
+  return B200OPS_OK;
+}

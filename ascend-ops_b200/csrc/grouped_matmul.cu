@@ -1,0 +1,347 @@
+// Grouped (per-expert) NT GEMM for sm_100a on the 5th-generation tensor cores.
+//
+//   y[gl[e-1]:gl[e], :] = x[gl[e-1]:gl[e], :] @ w[e],   w[e] stored [N, K] (K contiguous)
+//
+// Semantics follow the reference kernel (csrc/opdev/op_kernel/grouped_mat_mul_ex.cpp:29-44:
+// inclusive cumulative ends, empty groups skipped) and its tile engine MatMulNT
+// (csrc/opdev/op_kernel/matmul_core.h:43-68: fp16 operands, fp32 accumulation, fp16 result).
+// The reference gives one core per expert and walks 64x64x64 tiles serially; this kernel
+// is a persistent, warp-specialised pipeline over all SMs:
+//
+//   warp 0      TMA producer: x tile [128 x 64] and w tile [256 x 64] per k-block into a
+//               4-stage ring of 128B-swizzled shared memory (48 KB per stage)
+//   warp 1      MMA issuer: tcgen05.mma 128x256x16 (kind::f16), fp32 accumulators in TMEM,
+//               two accumulator buffers (2 x 256 columns) so the epilogue of tile i overlaps
+//               the main loop of tile i+1
+//   warps 2-5   epilogue: tcgen05.ld of their TMEM lane quarter, fp32 -> fp16 (RNE), stores
+//               predicated on the group's row end (an M-tail tile never writes into the next
+//               group's rows; reading them is harmless)
+//
+// Tiles are enumerated group by group, m-tile fastest, so that CTAs running at the same
+// time share the same w tile (read from HBM once, then from L2) while the group's x rows
+// stay L2-resident.  Work is 2*M*K*N flops; at the sizes of interest the kernel is bound by
+// the tensor pipe, at decode sizes (few rows per expert) by streaming w from HBM.
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+#include "tma_host.cuh"
+
+namespace b200ops {
+namespace gmm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kThreads = 192;
+constexpr int kMaxExperts = 1024;
+constexpr int kTmemCols = 512;  // two fp32 accumulators of BN columns
+
+constexpr int kABytes = BM * BK * 2;
+constexpr int kBBytes = BN * BK * 2;
+constexpr int kStageBytes = kABytes + kBBytes;
+
+// Error codes left in the device status word.
+constexpr int kErrProducerWait = 1;
+constexpr int kErrMmaWaitFull = 2;
+constexpr int kErrMmaWaitTmem = 3;
+constexpr int kErrEpilogueWait = 4;
+
+struct Control {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int tile_prefix[kMaxExperts + 1];  // first tile id of each group; [E] = total tiles
+  int row_start[kMaxExperts];
+  int row_end[kMaxExperts];
+};
+
+constexpr size_t kSmemBytes = 1024 /* alignment slack */ + kStages * kStageBytes + sizeof(Control);
+
+// Sticky per-device status of the pipeline kernels (0 = no failure).
+__device__ int g_pipeline_status = 0;
+
+struct TileCoord {
+  int group, row0, row_end, n0;
+};
+
+// Tiles of one group are numbered m-fastest.  `g` is carried between calls: tile ids only
+// grow within a CTA, so the search is amortised O(1).
+__device__ __forceinline__ TileCoord locate_tile(const Control* c, int tile, int& g) {
+  while (tile >= c->tile_prefix[g + 1]) ++g;
+  const int local = tile - c->tile_prefix[g];
+  const int rows = c->row_end[g] - c->row_start[g];
+  const int m_tiles = (rows + BM - 1) / BM;
+  const int n_tile = local / m_tiles;
+  const int m_tile = local - n_tile * m_tiles;
+  TileCoord t;
+  t.group = g;
+  t.row0 = c->row_start[g] + m_tile * BM;
+  t.row_end = c->row_end[g];
+  t.n0 = n_tile * BN;
+  return t;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
+                      const __grid_constant__ CUtensorMap map_w,
+                      const int64_t* __restrict__ group_list, __half* __restrict__ y, int M, int N,
+                      int K, int E) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* a_tiles = smem;
+  uint8_t* b_tiles = smem + kStages * kABytes;
+  Control* ctl = reinterpret_cast<Control*>(smem + kStages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int n_tiles = (N + BN - 1) / BN;
+  const int k_blocks = K / BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&ctl->full[s], 1);
+      ptx::mbar_init(&ctl->empty[s], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      ptx::mbar_init(&ctl->tmem_full[i], 1);
+      ptx::mbar_init(&ctl->tmem_empty[i], 4);  // one arrival per epilogue warp
+    }
+    ctl->abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_x);
+    ptx::prefetch_tensormap(&map_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
+    ptx::tmem_relinquish_alloc_permit();
+  }
+  // Group table: clamp the cumulative ends into [0, M] and count m-tiles per group.
+  for (int e = threadIdx.x; e < E; e += kThreads) {
+    long long s = e ? group_list[e - 1] : 0;
+    long long t = group_list[e];
+    s = s < 0 ? 0 : (s > M ? M : s);
+    t = t < s ? s : (t > M ? M : t);
+    ctl->row_start[e] = static_cast<int>(s);
+    ctl->row_end[e] = static_cast<int>(t);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    ctl->tile_prefix[0] = 0;
+    for (int e = 0; e < E; ++e) {
+      const int rows = ctl->row_end[e] - ctl->row_start[e];
+      acc += ((rows + BM - 1) / BM) * n_tiles;
+      ctl->tile_prefix[e + 1] = acc;
+    }
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+
+  const int total_tiles = ctl->tile_prefix[E];
+  const uint32_t tmem_base = ctl->tmem_base;
+  volatile int* abort_flag = &ctl->abort_flag;
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    if (lane == 0) {
+      int stage = 0, g = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        const TileCoord tc = locate_tile(ctl, tile, g);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(&g_pipeline_status, 0, kErrProducerWait);
+            ok = false;
+            break;
+          }
+          ptx::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
+          ptx::tma_load_2d(a_tiles + stage * kABytes, &map_x, &ctl->full[stage], kb * BK, tc.row0);
+          ptx::tma_load_3d(b_tiles + stage * kBBytes, &map_w, &ctl->full[stage], kb * BK, tc.n0,
+                           tc.group);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = ptx::make_f16_idesc(BM, BN);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      int iter = 0;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (iter >> 1) & 1;
+        if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
+          *abort_flag = 1;
+          atomicCAS(&g_pipeline_status, 0, kErrMmaWaitTmem);
+          break;
+        }
+        ptx::tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!ptx::mbar_wait(&ctl->full[stage], phase, abort_flag)) {
+            *abort_flag = 1;
+            atomicCAS(&g_pipeline_status, 0, kErrMmaWaitFull);
+            ok = false;
+            break;
+          }
+          ptx::tcgen05_fence_after();
+          const uint32_t a_addr = ptx::smem_u32(a_tiles + stage * kABytes);
+          const uint32_t b_addr = ptx::smem_u32(b_tiles + stage * kBBytes);
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            // Inside a 128-byte swizzle row the k-th 16-element slice starts 32 bytes on.
+            const uint64_t a_desc = ptx::make_sw128_kmajor_desc(a_addr + k * UMMA_K * 2);
+            const uint64_t b_desc = ptx::make_sw128_kmajor_desc(b_addr + k * UMMA_K * 2);
+            ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(&ctl->empty[stage]);  // frees the stage once these MMAs retire
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) ptx::umma_commit(&ctl->tmem_full[acc]);
+      }
+    }
+  } else {
+    // ---------------- epilogue (warps 2..5) ----------------
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
+    int g = 0, iter = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
+      const TileCoord tc = locate_tile(ctl, tile, g);
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (iter >> 1) & 1;
+      if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) {
+        *abort_flag = 1;
+        atomicCAS(&g_pipeline_status, 0, kErrEpilogueWait);
+        break;
+      }
+      ptx::tcgen05_fence_after();
+      const int row = tc.row0 + quarter * 32 + lane;
+      const bool row_ok = row < tc.row_end;
+      __half* yrow = y + static_cast<size_t>(row) * N + tc.n0;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        if (tc.n0 + c * 32 >= N) break;  // N is a multiple of 64, so chunks are all-or-nothing
+        uint32_t r[32];
+        ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+        ptx::tmem_ld_wait();
+        if (row_ok) {
+          uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+#pragma unroll
+          for (int v = 0; v < 4; ++v) {
+            uint4 o;
+            o.x = f2_to_h2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+            o.y = f2_to_h2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+            o.z = f2_to_h2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+            o.w = f2_to_h2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+            dst[v] = o;
+          }
+        }
+      }
+      ptx::tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+    }
+  }
+
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tcgen05_fence_after();
+    ptx::tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+}  // namespace gmm
+}  // namespace b200ops
+
+extern "C" size_t b200ops_grouped_matmul_workspace_size(int64_t, int64_t, int64_t, int64_t) {
+  return 0;
+}
+
+extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_t* group_list,
+                                      void* y, int64_t num_tokens, int64_t k, int64_t num_experts,
+                                      int64_t n, void* /*workspace*/, size_t /*workspace_size*/,
+                                      void* stream) {
+  using namespace b200ops;
+  B200OPS_REQUIRE(num_tokens >= 0 && k > 0 && n > 0 && num_experts > 0,
+                  "grouped_matmul: bad shape tokens=%lld k=%lld experts=%lld n=%lld",
+                  (long long)num_tokens, (long long)k, (long long)num_experts, (long long)n);
+  B200OPS_REQUIRE(k % 64 == 0 && n % 64 == 0,
+                  "grouped_matmul: second and third dimensions of w must be multiples of 64, got %lld and %lld",
+                  (long long)k, (long long)n);
+  B200OPS_REQUIRE(num_experts <= gmm::kMaxExperts, "grouped_matmul: at most %d experts, got %lld",
+                  gmm::kMaxExperts, (long long)num_experts);
+  B200OPS_REQUIRE(num_tokens < (1LL << 30) && k < (1LL << 30) && n < (1LL << 30),
+                  "grouped_matmul: dimension too large");
+  if (num_tokens == 0) return B200OPS_OK;
+  B200OPS_REQUIRE(x && w && group_list && y, "grouped_matmul: null pointer");
+  B200OPS_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y),
+                  "grouped_matmul: pointers must be 16-byte aligned");
+
+  CUtensorMap map_x, map_w;
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(num_tokens)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
+    const uint32_t box[2] = {gmm::BK, gmm::BM};
+    const int rc = encode_f16_map(&map_x, x, 2, dims, strides, box, "grouped_matmul(x)");
+    if (rc != B200OPS_OK) return rc;
+  }
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                              static_cast<uint64_t>(num_experts)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(k) * n * 2};
+    const uint32_t box[3] = {gmm::BK, gmm::BN, 1};
+    const int rc = encode_f16_map(&map_w, w, 3, dims, strides, box, "grouped_matmul(w)");
+    if (rc != B200OPS_OK) return rc;
+  }
+
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  B200OPS_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    B200OPS_CUDA(cudaFuncSetAttribute(gmm::grouped_matmul_kernel,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(gmm::kSmemBytes)));
+    attr_set[dev] = true;
+  }
+  const int64_t n_tiles = (n + gmm::BN - 1) / gmm::BN;
+  const int64_t max_tiles = ((num_tokens + gmm::BM - 1) / gmm::BM + num_experts) * n_tiles;
+  const int grid = static_cast<int>(max_tiles < sm_count() ? max_tiles : sm_count());
+  gmm::grouped_matmul_kernel<<<grid, gmm::kThreads, gmm::kSmemBytes,
+                               static_cast<cudaStream_t>(stream)>>>(
+      map_x, map_w, group_list, static_cast<__half*>(y), static_cast<int>(num_tokens),
+      static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts));
+  B200OPS_LAUNCH_CHECK("grouped_matmul");
+  return B200OPS_OK;
+}
+
+extern "C" int b200ops_pipeline_status(int* status) {
+  using namespace b200ops;
+  B200OPS_REQUIRE(status != nullptr, "pipeline_status: null pointer");
+  B200OPS_CUDA(cudaDeviceSynchronize());
+  int v = 0;
+  B200OPS_CUDA(cudaMemcpyFromSymbol(&v, gmm::g_pipeline_status, sizeof(int)));
+  if (v != 0) {
+    const int zero = 0;
+    B200OPS_CUDA(cudaMemcpyToSymbol(gmm::g_pipeline_status, &zero, sizeof(int)));
+  }
+  *status = v;
+  return B200OPS_OK;
+}

@@ -1,0 +1,351 @@
+// Paged-attention decode for sm_100a: C-ABI entry, split-context plan, the general kernel
+// (any cache layout, head_dim in {32,64,128,256}, any GQA ratio) and the combine kernel.
+//
+// Semantics (the reference's kernel is unfinished, so these come from its interface and
+// tiling code): one query token per sequence; query head h reads kv head h / (Hq/Hkv)
+// (csrc/opdev/op_kernel/paged_attention_ex.cpp:91-95); scale = 1/sqrt(head_dim) and the
+// exponentials are taken base 2 with scale*log2(e) folded in
+// (csrc/opdev/op_host/paged_attention_ex.cpp:26-27); pages are found through
+// block_tables[b, i] (paged_attention_ex.cpp:129-137); only the first context_lens[b]
+// tokens count.  Scores, softmax and the PV sum are fp32; the output is rounded once.
+#include "paged_attention.cuh"
+
+#include <cmath>
+#include <cstdlib>
+
+namespace b200ops {
+namespace pa {
+namespace {
+
+constexpr int kWarps = 4;
+constexpr int kHeadTile = 8;   // query heads of one kv head handled per CTA
+constexpr int kTokUnroll = 4;  // tokens whose K/V loads are in flight per warp
+
+template <int N>
+struct HalfVec;
+template <>
+struct HalfVec<1> { unsigned short v; };
+template <>
+struct HalfVec<2> { uint32_t v; };
+template <>
+struct HalfVec<4> { uint2 v; };
+template <>
+struct HalfVec<8> { uint4 v; };
+
+template <int DPL>
+__device__ __forceinline__ void unpack(const HalfVec<DPL>& in, float* out) {
+  const __half* h = reinterpret_cast<const __half*>(&in);
+#pragma unroll
+  for (int i = 0; i < DPL; ++i) out[i] = __half2float(h[i]);
+}
+
+// Element offset of (page, off, kv head, d) in either cache layout.
+__device__ __forceinline__ size_t kv_offset(int layout, int page, int off, int head, int d,
+                                            int page_size, int num_kv_heads, int head_dim) {
+  if (layout == B200OPS_KV_LAYOUT_NHD) {
+    return ((static_cast<size_t>(page) * page_size + off) * num_kv_heads + head) * head_dim + d;
+  }
+  const int e = head * head_dim + d;
+  const size_t chunks = static_cast<size_t>(num_kv_heads) * head_dim / 16;
+  return ((static_cast<size_t>(page) * chunks + (e >> 4)) * page_size + off) * 16 + (e & 15);
+}
+
+// General kernel: a warp owns whole tokens, lane i owns DPL = head_dim/32 consecutive
+// channels.  grid = (max_chunks, num_kv_heads * head_tiles, bs).
+template <int DPL>
+__global__ void __launch_bounds__(kWarps * 32) paged_attention_general_kernel(Args a) {
+  extern __shared__ float smem[];
+  const int D = a.head_dim;
+  const int chunk = blockIdx.x;
+  const int group = a.num_heads / a.num_kv_heads;
+  const int head_tiles = (group + kHeadTile - 1) / kHeadTile;
+  const int kvh = blockIdx.y / head_tiles;
+  const int tile = blockIdx.y - kvh * head_tiles;
+  const int b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  int L = a.context_lens[b];
+  const int cap = a.max_pages_per_seq * a.page_size;
+  if (L > cap) L = cap;
+  const int h0 = kvh * group + tile * kHeadTile;           // first query head of this CTA
+  const int nh = min(kHeadTile, group - tile * kHeadTile);  // query heads of this CTA
+  if (L <= 0) {
+    if (chunk == 0)
+      for (int i = threadIdx.x; i < nh * D; i += blockDim.x)
+        a.out[(static_cast<size_t>(b) * a.num_heads + h0) * D + i] = __float2half(0.f);
+    return;
+  }
+  const int start = chunk * a.chunk_tokens;
+  if (start >= L) return;
+  const int end = min(L, start + a.chunk_tokens);
+  const int n_chunks = (L + a.chunk_tokens - 1) / a.chunk_tokens;
+
+  float qf[kHeadTile][DPL];
+#pragma unroll
+  for (int g = 0; g < kHeadTile; ++g) {
+#pragma unroll
+    for (int i = 0; i < DPL; ++i)
+      qf[g][i] = (g < nh) ? __half2float(a.q[(static_cast<size_t>(b) * a.num_heads + h0 + g) * D +
+                                              lane * DPL + i]) * a.scale_log2
+                          : 0.f;
+  }
+  float m[kHeadTile], l[kHeadTile], acc[kHeadTile][DPL];
+#pragma unroll
+  for (int g = 0; g < kHeadTile; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) acc[g][i] = 0.f;
+  }
+
+  const int32_t* table = a.block_tables + static_cast<size_t>(b) * a.max_pages_per_seq;
+  for (int t0 = start + warp * kTokUnroll; t0 < end; t0 += kWarps * kTokUnroll) {
+    HalfVec<DPL> kv[kTokUnroll], vv[kTokUnroll];
+    bool ok[kTokUnroll];
+#pragma unroll
+    for (int j = 0; j < kTokUnroll; ++j) {
+      const int t = t0 + j;
+      ok[j] = t < end;
+      if (ok[j]) {
+        const int page = table[t / a.page_size];
+        ok[j] = page >= 0 && page < a.num_pages;
+        if (ok[j]) {
+          const size_t o = kv_offset(a.layout, page, t % a.page_size, kvh, lane * DPL,
+                                     a.page_size, a.num_kv_heads, D);
+          kv[j] = *reinterpret_cast<const HalfVec<DPL>*>(a.k_cache + o);
+          vv[j] = *reinterpret_cast<const HalfVec<DPL>*>(a.v_cache + o);
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kTokUnroll; ++j) {
+      if (!ok[j]) continue;  // warp-uniform
+      float kf[DPL], vf[DPL];
+      unpack<DPL>(kv[j], kf);
+      unpack<DPL>(vv[j], vf);
+#pragma unroll
+      for (int g = 0; g < kHeadTile; ++g) {
+        if (g >= nh) break;
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) s = fmaf(qf[g][i], kf[i], s);
+        s = warp_sum(s);
+        const float m_new = fmaxf(m[g], s);
+        const float alpha = exp2f(m[g] - m_new);  // exp2(-inf) = 0 on the first token
+        const float p = exp2f(s - m_new);
+        l[g] = l[g] * alpha + p;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) acc[g][i] = fmaf(p, vf[i], acc[g][i] * alpha);
+        m[g] = m_new;
+      }
+    }
+  }
+
+  // Merge the four warps through shared memory: [warp][head][D + 2].
+  const int rec = D + 2;
+#pragma unroll
+  for (int g = 0; g < kHeadTile; ++g) {
+    float* r = smem + (warp * kHeadTile + g) * rec;
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) r[lane * DPL + i] = acc[g][i];
+    if (lane == 0) {
+      r[D] = m[g];
+      r[D + 1] = l[g];
+    }
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < nh * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx - g * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) mm = fmaxf(mm, smem[(w * kHeadTile + g) * rec + D]);
+    float o = 0.f, ll = 0.f;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) {
+      const float* r = smem + (w * kHeadTile + g) * rec;
+      const float f = (r[D] == -INFINITY) ? 0.f : exp2f(r[D] - mm);
+      o += r[d] * f;
+      ll += r[D + 1] * f;
+    }
+    const int h = h0 + g;
+    if (n_chunks == 1) {
+      a.out[(static_cast<size_t>(b) * a.num_heads + h) * D + d] =
+          __float2half(ll > 0.f ? o / ll : 0.f);
+    } else {
+      float* pr = a.partials +
+                  ((static_cast<size_t>(b) * a.num_heads + h) * a.max_chunks + chunk) * rec;
+      pr[d] = o;
+      if (d == 0) {
+        pr[D] = mm;
+        pr[D + 1] = ll;
+      }
+    }
+  }
+}
+
+// Combine: grid = (num_heads, bs).  Merges the chunk partials of sequences that were split.
+__global__ void __launch_bounds__(128) paged_attention_combine_kernel(Args a) {
+  const int h = blockIdx.x, b = blockIdx.y;
+  int L = a.context_lens[b];
+  const int cap = a.max_pages_per_seq * a.page_size;
+  if (L > cap) L = cap;
+  if (L <= 0) return;
+  const int n_chunks = (L + a.chunk_tokens - 1) / a.chunk_tokens;
+  if (n_chunks <= 1) return;
+  const int D = a.head_dim;
+  const size_t rec = partial_stride(D);
+  const float* base = a.partials + (static_cast<size_t>(b) * a.num_heads + h) * a.max_chunks * rec;
+  float mm = -INFINITY;
+  for (int c = 0; c < n_chunks; ++c) mm = fmaxf(mm, base[c * rec + D]);
+  float ll = 0.f;
+  for (int c = 0; c < n_chunks; ++c) {
+    const float mc = base[c * rec + D];
+    if (mc != -INFINITY) ll += base[c * rec + D + 1] * exp2f(mc - mm);
+  }
+  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float o = 0.f;
+    for (int c = 0; c < n_chunks; ++c) {
+      const float mc = base[c * rec + D];
+      if (mc != -INFINITY) o += base[c * rec + d] * exp2f(mc - mm);
+    }
+    a.out[(static_cast<size_t>(b) * a.num_heads + h) * D + d] = __float2half(o * inv);
+  }
+}
+
+}  // namespace
+
+Plan make_plan(int64_t bs, int64_t num_kv_heads, int64_t page_size, int64_t max_pages_per_seq) {
+  // Chunk length: enough chunks to spread ragged lengths over the SMs, few enough that
+  // the partial records stay a small fraction of the KV bytes.  More (sequence, kv head)
+  // pairs -> longer chunks.
+  const int64_t pairs = bs * num_kv_heads;
+  int64_t chunk = pairs >= 1024 ? 1024 : 512;
+  if (const char* s = std::getenv("B200OPS_PA_CHUNK_TOKENS")) {
+    const long v = std::atol(s);
+    if (v > 0) chunk = v;
+  }
+  // Round up to whole pages so that a chunk never starts inside a page.
+  chunk = (chunk + page_size - 1) / page_size * page_size;
+  const int64_t cap = max_pages_per_seq * page_size;
+  if (chunk > cap && cap > 0) chunk = cap;
+  Plan p;
+  p.chunk_tokens = static_cast<int>(chunk);
+  p.max_chunks = static_cast<int>(cap > 0 ? (cap + chunk - 1) / chunk : 1);
+  return p;
+}
+
+int launch_general(const Args& a, cudaStream_t st) {
+  const int group = a.num_heads / a.num_kv_heads;
+  const int head_tiles = (group + kHeadTile - 1) / kHeadTile;
+  const dim3 grid(a.max_chunks, a.num_kv_heads * head_tiles, a.bs);
+  const size_t smem = static_cast<size_t>(kWarps) * kHeadTile * (a.head_dim + 2) * sizeof(float);
+  B200OPS_REQUIRE(grid.y <= 65535 && grid.z <= 65535,
+                  "paged_attention: batch or head count too large for one launch");
+  switch (a.head_dim / 32) {
+    case 1: paged_attention_general_kernel<1><<<grid, kWarps * 32, smem, st>>>(a); break;
+    case 2: paged_attention_general_kernel<2><<<grid, kWarps * 32, smem, st>>>(a); break;
+    case 4: paged_attention_general_kernel<4><<<grid, kWarps * 32, smem, st>>>(a); break;
+    case 8: paged_attention_general_kernel<8><<<grid, kWarps * 32, smem, st>>>(a); break;
+    default:
+      return fail(B200OPS_EUNSUPPORTED, "paged_attention: head_dim %d not in {32,64,128,256}",
+                  a.head_dim);
+  }
+  B200OPS_LAUNCH_CHECK("paged_attention");
+  return B200OPS_OK;
+}
+
+int launch_combine(const Args& a, cudaStream_t st) {
+  if (a.max_chunks <= 1) return B200OPS_OK;
+  const dim3 grid(a.num_heads, a.bs);
+  paged_attention_combine_kernel<<<grid, 128, 0, st>>>(a);
+  B200OPS_LAUNCH_CHECK("paged_attention combine");
+  return B200OPS_OK;
+}
+
+}  // namespace pa
+}  // namespace b200ops
+
+extern "C" size_t b200ops_paged_attention_workspace_size(int64_t bs, int64_t num_heads,
+                                                         int64_t num_kv_heads, int64_t head_dim,
+                                                         int64_t page_size,
+                                                         int64_t max_pages_per_seq) {
+  using namespace b200ops;
+  if (bs <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || page_size <= 0 ||
+      max_pages_per_seq <= 0)
+    return 0;
+  const pa::Plan p = pa::make_plan(bs, num_kv_heads, page_size, max_pages_per_seq);
+  if (p.max_chunks <= 1) return 0;
+  return static_cast<size_t>(bs) * num_heads * p.max_chunks * pa::partial_stride((int)head_dim) *
+         sizeof(float);
+}
+
+extern "C" int b200ops_paged_attention(const void* q, const void* key_cache,
+                                       const void* value_cache, const int32_t* block_tables,
+                                       const int32_t* context_lens, void* out, int64_t bs,
+                                       int64_t num_heads, int64_t num_kv_heads, int64_t head_dim,
+                                       int64_t num_pages, int64_t page_size,
+                                       int64_t max_pages_per_seq, int layout, void* workspace,
+                                       size_t workspace_size, void* stream) {
+  using namespace b200ops;
+  B200OPS_REQUIRE(bs >= 0 && num_heads > 0 && num_kv_heads > 0 && head_dim > 0,
+                  "paged_attention: bad q shape [%lld, %lld, %lld]", (long long)bs,
+                  (long long)num_heads, (long long)head_dim);
+  B200OPS_REQUIRE(num_heads % num_kv_heads == 0,
+                  "paged_attention: num_heads %lld is not a multiple of num_kv_heads %lld",
+                  (long long)num_heads, (long long)num_kv_heads);
+  B200OPS_REQUIRE(num_pages > 0 && page_size > 0 && max_pages_per_seq > 0,
+                  "paged_attention: bad cache shape pages=%lld page_size=%lld max_pages_per_seq=%lld",
+                  (long long)num_pages, (long long)page_size, (long long)max_pages_per_seq);
+  B200OPS_REQUIRE(layout == B200OPS_KV_LAYOUT_NZ || layout == B200OPS_KV_LAYOUT_NHD,
+                  "paged_attention: unknown cache layout %d", layout);
+  B200OPS_REQUIRE(head_dim % 32 == 0 && head_dim <= 256,
+                  "paged_attention: head_dim must be 32, 64, 128 or 256, got %lld",
+                  (long long)head_dim);
+  B200OPS_REQUIRE(bs <= 65535 && num_heads <= 4096 && num_pages <= 0x7fffffffLL &&
+                      page_size <= (1 << 20) && max_pages_per_seq <= (1 << 24) &&
+                      max_pages_per_seq * page_size <= 0x7fffffffLL,
+                  "paged_attention: shape too large");
+  if (bs == 0) return B200OPS_OK;
+  B200OPS_REQUIRE(q && key_cache && value_cache && block_tables && context_lens && out,
+                  "paged_attention: null pointer");
+  B200OPS_REQUIRE(aligned16(q) && aligned16(key_cache) && aligned16(value_cache) && aligned16(out),
+                  "paged_attention: pointers must be 16-byte aligned");
+
+  const pa::Plan plan = pa::make_plan(bs, num_kv_heads, page_size, max_pages_per_seq);
+  const size_t need = b200ops_paged_attention_workspace_size(bs, num_heads, num_kv_heads,
+                                                             head_dim, page_size,
+                                                             max_pages_per_seq);
+  if (need > 0 && (workspace == nullptr || workspace_size < need))
+    return fail(B200OPS_EWORKSPACE, "paged_attention: workspace of %zu bytes needed, got %zu",
+                need, workspace ? workspace_size : (size_t)0);
+
+  pa::Args a;
+  a.q = static_cast<const __half*>(q);
+  a.k_cache = static_cast<const __half*>(key_cache);
+  a.v_cache = static_cast<const __half*>(value_cache);
+  a.block_tables = block_tables;
+  a.context_lens = context_lens;
+  a.out = static_cast<__half*>(out);
+  a.partials = static_cast<float*>(workspace);
+  a.bs = (int)bs;
+  a.num_heads = (int)num_heads;
+  a.num_kv_heads = (int)num_kv_heads;
+  a.head_dim = (int)head_dim;
+  a.num_pages = (int)num_pages;
+  a.page_size = (int)page_size;
+  a.max_pages_per_seq = (int)max_pages_per_seq;
+  a.layout = layout;
+  a.chunk_tokens = plan.chunk_tokens;
+  a.max_chunks = plan.max_chunks;
+  a.scale_log2 = (1.0f / std::sqrt(static_cast<float>(head_dim))) * 1.44269504088896340736f;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int rc;
+  if (pa::fast_path_supported(a))
+    rc = pa::launch_fast(a, st);
+  else
+    rc = pa::launch_general(a, st);
+  if (rc != B200OPS_OK) return rc;
+  return pa::launch_combine(a, st);
+}

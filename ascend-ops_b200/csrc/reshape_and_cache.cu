@@ -1,0 +1,178 @@
+// reshape_and_cache for sm_100a: scatter this step's K/V rows into the paged KV cache.
+//
+// Pure address arithmetic plus 128-bit copies; results are bit-exact.  Two cache layouts:
+//   NZ  [pages, C, P, 16] : cache[s/P, c, s%P, j] = flat(key[t])[c*16 + j]   (reference-native;
+//        golden benchmark/test_reshape_and_cache.py:6-25, kernel
+//        csrc/opdev/op_kernel/reshape_and_cache_ex.cpp:47-69)
+//   NHD [pages, P, Hkv, D]: cache[s/P, s%P, h, d] = key[t, h, d]             (vLLM standard)
+// Slots outside [0, pages*P) are skipped, as the reference kernel does (:50).  Where the
+// reference lets every core copy all tokens element by element, here each thread moves one
+// 16-byte vector of K and the matching vector of V.  If two tokens name the same slot the
+// reference keeps the later token; here the winner is unspecified (callers never do this:
+// a slot is one cache position).
+#include "common.cuh"
+
+namespace b200ops {
+namespace {
+
+constexpr int kThreads = 256;
+
+struct ScatterParams {
+  const __half* key;
+  const __half* value;
+  __half* key_cache;
+  __half* value_cache;
+  const int32_t* slots;
+  uint32_t num_tokens;
+  uint32_t row_elems;   // Hkv * D
+  uint32_t items_per_token;
+  int64_t num_slots;    // pages * P
+  uint32_t page_size;   // P
+  uint32_t chunks;      // NZ: C
+};
+
+// NHD: a token's destination is one contiguous row of row_elems halfs at slot * row_elems.
+__global__ void __launch_bounds__(kThreads) scatter_nhd_vec_kernel(ScatterParams p) {
+  const uint32_t item = blockIdx.x * kThreads + threadIdx.x;
+  const uint32_t token = item / p.items_per_token;
+  if (token >= p.num_tokens) return;
+  const uint32_t v = item - token * p.items_per_token;
+  const int64_t slot = p.slots[token];
+  if (slot < 0 || slot >= p.num_slots) return;
+  const size_t src = static_cast<size_t>(token) * p.items_per_token + v;
+  const size_t dst = static_cast<size_t>(slot) * p.items_per_token + v;
+  const uint4 kv = ld_stream(reinterpret_cast<const uint4*>(p.key) + src);
+  if (p.value != nullptr) {
+    const uint4 vv = ld_stream(reinterpret_cast<const uint4*>(p.value) + src);
+    reinterpret_cast<uint4*>(p.value_cache)[dst] = vv;
+  }
+  reinterpret_cast<uint4*>(p.key_cache)[dst] = kv;
+}
+
+// NZ: vector v of the flat row belongs to chunk c = v/2 (16 halfs = two vectors per chunk).
+__global__ void __launch_bounds__(kThreads) scatter_nz_vec_kernel(ScatterParams p) {
+  const uint32_t item = blockIdx.x * kThreads + threadIdx.x;
+  const uint32_t token = item / p.items_per_token;
+  if (token >= p.num_tokens) return;
+  const uint32_t v = item - token * p.items_per_token;
+  const uint32_t c = v >> 1;
+  if (c >= p.chunks) return;
+  const int64_t slot = p.slots[token];
+  if (slot < 0 || slot >= p.num_slots) return;
+  const uint32_t page = static_cast<uint32_t>(slot / p.page_size);
+  const uint32_t off = static_cast<uint32_t>(slot - static_cast<int64_t>(page) * p.page_size);
+  const size_t src = static_cast<size_t>(token) * p.items_per_token + v;
+  const size_t dst =
+      ((static_cast<size_t>(page) * p.chunks + c) * p.page_size + off) * 2 + (v & 1u);
+  const uint4 kv = ld_stream(reinterpret_cast<const uint4*>(p.key) + src);
+  if (p.value != nullptr) {
+    const uint4 vv = ld_stream(reinterpret_cast<const uint4*>(p.value) + src);
+    reinterpret_cast<uint4*>(p.value_cache)[dst] = vv;
+  }
+  reinterpret_cast<uint4*>(p.key_cache)[dst] = kv;
+}
+
+// Any shape / alignment: one 16-bit element per item.
+template <bool kNz>
+__global__ void __launch_bounds__(kThreads) scatter_scalar_kernel(ScatterParams p) {
+  const uint64_t item = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  const uint64_t token = item / p.row_elems;
+  if (token >= p.num_tokens) return;
+  const uint32_t e = static_cast<uint32_t>(item - token * p.row_elems);
+  const int64_t slot = p.slots[token];
+  if (slot < 0 || slot >= p.num_slots) return;
+  size_t dst;
+  if (kNz) {
+    const uint32_t c = e >> 4;
+    if (c >= p.chunks) return;
+    const uint64_t page = static_cast<uint64_t>(slot) / p.page_size;
+    const uint64_t off = static_cast<uint64_t>(slot) - page * p.page_size;
+    dst = ((page * p.chunks + c) * p.page_size + off) * 16 + (e & 15u);
+  } else {
+    dst = static_cast<size_t>(slot) * p.row_elems + e;
+  }
+  const unsigned short* ks = reinterpret_cast<const unsigned short*>(p.key);
+  reinterpret_cast<unsigned short*>(p.key_cache)[dst] = ks[item];
+  if (p.value != nullptr) {
+    const unsigned short* vs = reinterpret_cast<const unsigned short*>(p.value);
+    reinterpret_cast<unsigned short*>(p.value_cache)[dst] = vs[item];
+  }
+}
+
+}  // namespace
+}  // namespace b200ops
+
+extern "C" int b200ops_reshape_and_cache(const void* key, const void* value, void* key_cache,
+                                         void* value_cache, const int32_t* slot_indices,
+                                         int64_t num_tokens, int64_t num_kv_heads,
+                                         int64_t head_size, const int64_t cache_dims[4],
+                                         int layout, void* stream) {
+  using namespace b200ops;
+  B200OPS_REQUIRE(num_tokens >= 0 && num_kv_heads > 0 && head_size > 0,
+                  "reshape_and_cache: bad key shape [%lld, %lld, %lld]", (long long)num_tokens,
+                  (long long)num_kv_heads, (long long)head_size);
+  B200OPS_REQUIRE(cache_dims != nullptr, "reshape_and_cache: cache_dims is null");
+  B200OPS_REQUIRE(layout == B200OPS_KV_LAYOUT_NZ || layout == B200OPS_KV_LAYOUT_NHD,
+                  "reshape_and_cache: unknown cache layout %d", layout);
+  for (int i = 0; i < 4; ++i)
+    B200OPS_REQUIRE(cache_dims[i] > 0, "reshape_and_cache: key_cache must be 4D with positive sizes");
+  const int64_t row_elems = num_kv_heads * head_size;
+  B200OPS_REQUIRE(row_elems <= 0x7fffffffLL && num_tokens <= 0x7fffffffLL,
+                  "reshape_and_cache: key too large");
+
+  ScatterParams p;
+  int64_t pages = cache_dims[0], page_size, chunks = 0;
+  if (layout == B200OPS_KV_LAYOUT_NZ) {
+    B200OPS_REQUIRE(cache_dims[3] == 16,
+                    "reshape_and_cache: NZ cache must be [pages, chunks, page_size, 16], last size is %lld",
+                    (long long)cache_dims[3]);
+    chunks = cache_dims[1];
+    page_size = cache_dims[2];
+  } else {
+    page_size = cache_dims[1];
+    B200OPS_REQUIRE(cache_dims[2] == num_kv_heads && cache_dims[3] == head_size,
+                    "reshape_and_cache: NHD cache must be [pages, page_size, %lld, %lld], got [.., .., %lld, %lld]",
+                    (long long)num_kv_heads, (long long)head_size, (long long)cache_dims[2],
+                    (long long)cache_dims[3]);
+  }
+  B200OPS_REQUIRE(page_size <= 0x7fffffffLL && chunks <= 0x7fffffffLL,
+                  "reshape_and_cache: cache too large");
+  if (num_tokens == 0) return B200OPS_OK;
+  B200OPS_REQUIRE(key && key_cache && slot_indices, "reshape_and_cache: null pointer");
+
+  const bool with_value = value != nullptr && value_cache != nullptr;
+  p.key = static_cast<const __half*>(key);
+  p.value = with_value ? static_cast<const __half*>(value) : nullptr;
+  p.key_cache = static_cast<__half*>(key_cache);
+  p.value_cache = with_value ? static_cast<__half*>(value_cache) : nullptr;
+  p.slots = slot_indices;
+  p.num_tokens = static_cast<uint32_t>(num_tokens);
+  p.row_elems = static_cast<uint32_t>(row_elems);
+  p.num_slots = pages * page_size;
+  p.page_size = static_cast<uint32_t>(page_size);
+  p.chunks = static_cast<uint32_t>(chunks);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+
+  const bool vec_ok = row_elems % 8 == 0 && aligned16(key) && aligned16(key_cache) &&
+                      (!with_value || (aligned16(value) && aligned16(value_cache)));
+  const int64_t vec_items = num_tokens * (row_elems / 8);
+  if (vec_ok && vec_items < 0x7fffff00LL) {
+    p.items_per_token = static_cast<uint32_t>(row_elems / 8);
+    const unsigned grid = static_cast<unsigned>((vec_items + kThreads - 1) / kThreads);
+    if (layout == B200OPS_KV_LAYOUT_NZ)
+      scatter_nz_vec_kernel<<<grid, kThreads, 0, st>>>(p);
+    else
+      scatter_nhd_vec_kernel<<<grid, kThreads, 0, st>>>(p);
+  } else {
+    p.items_per_token = 0;
+    const int64_t items = num_tokens * row_elems;
+    const int64_t grid = (items + kThreads - 1) / kThreads;
+    B200OPS_REQUIRE(grid <= 0x7fffffffLL, "reshape_and_cache: key too large");
+    if (layout == B200OPS_KV_LAYOUT_NZ)
+      scatter_scalar_kernel<true><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(p);
+    else
+      scatter_scalar_kernel<false><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(p);
+  }
+  B200OPS_LAUNCH_CHECK("reshape_and_cache");
+  return B200OPS_OK;
+}

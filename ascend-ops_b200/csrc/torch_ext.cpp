@@ -1,0 +1,309 @@
+// Torch-facing layer: module `ascend910a_extras_C` with the same layout as the reference's
+// pybind module (csrc/ffi/bind.cpp:56-61): `print_info` plus submodule `ops` holding
+// rope, swiglu, grouped_matmul, add_rms_norm, reshape_and_cache, paged_attention
+// (csrc/ffi/ops.cpp:484-491).  Each function checks its arguments under the same
+// conditions as the reference FFI, allocates the outputs and the scratch tensor, and
+// calls the C ABI of libb200ops.so on the current CUDA stream.  Nothing here computes.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <tuple>
+#include <vector>
+
+#include "b200ops.h"
+
+namespace native {
+
+namespace {
+
+void check_status(int rc, const char* op) {
+  if (rc == B200OPS_OK) return;
+  if (rc == B200OPS_EINVAL) {
+    TORCH_CHECK(false, b200ops_last_error());
+  }
+  throw std::runtime_error(std::string("Failed to execute ") + op + ": " + b200ops_last_error());
+}
+
+void check_f16_cuda(const at::Tensor& t, const char* op, const char* name) {
+  TORCH_CHECK(t.is_cuda(), op, ": ", name, " must be a CUDA tensor (there is no CPU path)");
+  TORCH_CHECK(t.scalar_type() == at::kHalf, op, ": ", name, " must be float16, got ", t.scalar_type());
+}
+
+void check_same_device(const at::Tensor& a, const at::Tensor& b, const char* op) {
+  TORCH_CHECK(a.device() == b.device(), op, ": all tensors must be on the same device");
+}
+
+void* current_stream() { return static_cast<void*>(at::cuda::getCurrentCUDAStream().stream()); }
+
+}  // namespace
+
+// Mirrors native::rope (csrc/ffi/ops.cpp:13-108).
+std::vector<at::Tensor> rope(at::Tensor q, at::Tensor k, at::Tensor position_ids,
+                             at::Tensor cos_cache, at::Tensor sin_cache) {
+  TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && position_ids.dim() == 1 && cos_cache.dim() == 2 &&
+                  sin_cache.dim() == 2,
+              "rope: input tensors must be 3D, 3D, 1D, 2D, and 2D, got ", q.dim(), "D, ", k.dim(),
+              "D, ", position_ids.dim(), "D, ", cos_cache.dim(), "D, ", sin_cache.dim(), "D");
+  TORCH_CHECK(position_ids.size(0) == q.size(0),
+              "rope: position_ids must have the same batch size as q, got ", position_ids.size(0),
+              " and ", q.size(0));
+  TORCH_CHECK(q.is_contiguous() && k.is_contiguous() && position_ids.is_contiguous() &&
+                  cos_cache.is_contiguous() && sin_cache.is_contiguous(),
+              "rope: all input tensors must be contiguous");
+  check_f16_cuda(q, "rope", "q");
+  check_f16_cuda(k, "rope", "k");
+  check_f16_cuda(cos_cache, "rope", "cos_cache");
+  check_f16_cuda(sin_cache, "rope", "sin_cache");
+  TORCH_CHECK(position_ids.is_cuda() && position_ids.scalar_type() == at::kInt,
+              "rope: position_ids must be a CUDA int32 tensor, got ", position_ids.scalar_type());
+  check_same_device(q, k, "rope");
+  check_same_device(q, position_ids, "rope");
+  check_same_device(q, cos_cache, "rope");
+  check_same_device(q, sin_cache, "rope");
+  TORCH_CHECK(k.size(0) == q.size(0) && k.size(2) == q.size(2),
+              "rope: q and k must agree in batch size and head_dim, got ", q.sizes(), " and ", k.sizes());
+  TORCH_CHECK(cos_cache.size(1) * 2 == q.size(2) && sin_cache.sizes() == cos_cache.sizes(),
+              "rope: cos_cache and sin_cache must be [max_pos, head_dim/2], got ", cos_cache.sizes(),
+              " and ", sin_cache.sizes(), " for head_dim ", q.size(2));
+
+  const c10::cuda::CUDAGuard guard(q.device());
+  at::Tensor out_q = at::empty_like(q);
+  at::Tensor out_k = at::empty_like(k);
+  check_status(b200ops_rope(q.data_ptr(), k.data_ptr(), position_ids.data_ptr<int32_t>(),
+                            cos_cache.data_ptr(), sin_cache.data_ptr(), out_q.data_ptr(),
+                            out_k.data_ptr(), q.size(0), q.size(1), k.size(1), q.size(2),
+                            cos_cache.size(0), current_stream()),
+               "rope");
+  return {out_q, out_k};
+}
+
+// Mirrors native::swiglu (csrc/ffi/ops.cpp:110-154).
+at::Tensor swiglu(at::Tensor x) {
+  TORCH_CHECK(x.dim() == 2, "swiglu: input tensor must be 2D, got ", x.dim(), "D tensor");
+  TORCH_CHECK(x.size(-1) >= 64 && x.size(-1) % 64 == 0,
+              "swiglu: last dimension must be a multiple of 64, got ", x.size(-1));
+  TORCH_CHECK(x.is_contiguous(), "swiglu: input tensor must be contiguous");
+  check_f16_cuda(x, "swiglu", "x");
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty({x.size(0), x.size(1) / 2}, x.options());
+  check_status(b200ops_swiglu(x.data_ptr(), y.data_ptr(), x.size(0), x.size(1), current_stream()),
+               "swiglu");
+  return y;
+}
+
+// Mirrors native::grouped_matmul (csrc/ffi/ops.cpp:157-233).
+at::Tensor grouped_matmul(at::Tensor x, at::Tensor w, at::Tensor group_list) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && group_list.dim() == 1,
+              "grouped_matmul: input tensors must be 2D and group_list must be 1D");
+  const int64_t num_tokens = x.size(0);
+  const int64_t dim = x.size(1);
+  const int64_t num_experts = w.size(0);
+  const int64_t inner_dim = w.size(2);
+  TORCH_CHECK(dim == w.size(1),
+              "grouped_matmul: last dimension of x must match second dimension of w, got ", dim,
+              " and ", w.size(1));
+  TORCH_CHECK(x.is_contiguous() && group_list.is_contiguous(),
+              "grouped_matmul: x and group_list must be contiguous tensors");
+  TORCH_CHECK(w.stride(1) == 1 && w.stride(2) == dim,
+              "grouped_matmul: w must be K-major order, got strides ", w.strides());
+  TORCH_CHECK(w.size(1) % 64 == 0 && w.size(2) % 64 == 0,
+              "grouped_matmul: second and third dimensions of w must be multiples of 64, got ",
+              w.size(1), " and ", w.size(2));
+  TORCH_CHECK(num_experts <= 1 || w.stride(0) == dim * inner_dim,
+              "grouped_matmul: experts of w must be densely packed, got strides ", w.strides());
+  TORCH_CHECK(group_list.size(0) == num_experts,
+              "grouped_matmul: group_list must have one entry per expert, got ", group_list.size(0),
+              " and ", num_experts);
+  check_f16_cuda(x, "grouped_matmul", "x");
+  check_f16_cuda(w, "grouped_matmul", "w");
+  TORCH_CHECK(group_list.is_cuda() && group_list.scalar_type() == at::kLong,
+              "grouped_matmul: group_list must be a CUDA int64 tensor, got ", group_list.scalar_type());
+  check_same_device(x, w, "grouped_matmul");
+  check_same_device(x, group_list, "grouped_matmul");
+
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty({num_tokens, inner_dim}, x.options());
+  const size_t ws = b200ops_grouped_matmul_workspace_size(num_tokens, dim, num_experts, inner_dim);
+  at::Tensor workspace = at::empty({static_cast<int64_t>(ws)}, x.options().dtype(at::kByte));
+  check_status(b200ops_grouped_matmul(x.data_ptr(), w.data_ptr(), group_list.data_ptr<int64_t>(),
+                                      y.data_ptr(), num_tokens, dim, num_experts, inner_dim,
+                                      ws ? workspace.data_ptr() : nullptr, ws, current_stream()),
+               "grouped_matmul");
+  return y;
+}
+
+// Mirrors native::add_rms_norm (csrc/ffi/ops.cpp:236-333).
+std::tuple<at::Tensor, at::Tensor> add_rms_norm(at::Tensor x, at::Tensor residual,
+                                                at::Tensor weight, float epsilon) {
+  TORCH_CHECK(x.dim() == 2 && residual.dim() == 2 && weight.dim() == 1,
+              "add_rms_norm: x and residual must be 2D, weight must be 1D");
+  TORCH_CHECK(x.size(1) == weight.size(0),
+              "add_rms_norm: last dimension of x must match weight size, got ", x.size(1), " and ",
+              weight.size(0));
+  TORCH_CHECK(x.size(0) == residual.size(0) && x.size(1) == residual.size(1),
+              "add_rms_norm: x and residual must have the same shape, got ", x.sizes(), " and ",
+              residual.sizes());
+  TORCH_CHECK(x.is_contiguous() && residual.is_contiguous() && weight.is_contiguous(),
+              "add_rms_norm: all input tensors must be contiguous");
+  TORCH_CHECK(x.size(1) % 64 == 0, "add_rms_norm: last dimension must be a multiple of 64, got ",
+              x.size(1));
+  check_f16_cuda(x, "add_rms_norm", "x");
+  check_f16_cuda(residual, "add_rms_norm", "residual");
+  check_f16_cuda(weight, "add_rms_norm", "weight");
+  check_same_device(x, residual, "add_rms_norm");
+  check_same_device(x, weight, "add_rms_norm");
+
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty({x.size(0), x.size(1)}, x.options());
+  at::Tensor residual_output = at::empty({x.size(0), x.size(1)}, x.options());
+  check_status(b200ops_add_rms_norm(x.data_ptr(), residual.data_ptr(), weight.data_ptr(), epsilon,
+                                    y.data_ptr(), residual_output.data_ptr(), x.size(0), x.size(1),
+                                    current_stream()),
+               "add_rms_norm");
+  return std::make_tuple(y, residual_output);
+}
+
+namespace {
+
+// NHD if the cache's trailing sizes repeat the key's [Hkv, D]; else NZ if the last size is 16.
+int cache_layout_for_key(const at::Tensor& cache, int64_t num_kv_heads, int64_t head_size,
+                         const char* op) {
+  if (cache.size(2) == num_kv_heads && cache.size(3) == head_size) return B200OPS_KV_LAYOUT_NHD;
+  TORCH_CHECK(cache.size(3) == 16, op,
+              ": cache must be [pages, Hkv*D/16, page_size, 16] or [pages, page_size, Hkv, D], got ",
+              cache.sizes());
+  return B200OPS_KV_LAYOUT_NZ;
+}
+
+}  // namespace
+
+// Mirrors native::reshape_and_cache (csrc/ffi/ops.cpp:336-405).
+void reshape_and_cache(at::Tensor key, at::Tensor value, at::Tensor key_cache,
+                       at::Tensor value_cache, at::Tensor slot_indices) {
+  TORCH_CHECK(key.dim() == 3 && key_cache.dim() == 4 && slot_indices.dim() == 1,
+              "reshape_and_cache: key must be 3D, key_cache must be 4D, slot_indices must be 1D");
+  TORCH_CHECK(key.is_contiguous() && key_cache.is_contiguous() && slot_indices.is_contiguous(),
+              "reshape_and_cache: key, key_cache, slot_indices must be contiguous tensors");
+  if (value.numel() > 0) {
+    TORCH_CHECK(value.dim() == 3 && value.is_contiguous(),
+                "reshape_and_cache: value must be 3D and contiguous if not None");
+    TORCH_CHECK(value.sizes() == key.sizes(), "reshape_and_cache: value must have key's shape, got ",
+                value.sizes(), " and ", key.sizes());
+    check_f16_cuda(value, "reshape_and_cache", "value");
+  }
+  if (value_cache.numel() > 0) {
+    TORCH_CHECK(value_cache.dim() == 4 && value_cache.is_contiguous(),
+                "reshape_and_cache: value_cache must be 4D and contiguous if not None");
+    TORCH_CHECK(value_cache.sizes() == key_cache.sizes(),
+                "reshape_and_cache: value_cache must have key_cache's shape, got ",
+                value_cache.sizes(), " and ", key_cache.sizes());
+    check_f16_cuda(value_cache, "reshape_and_cache", "value_cache");
+  }
+  // The reference's host tiling fails the launch when the lengths differ
+  // (csrc/opdev/op_host/reshape_and_cache_ex.cpp:33-36).
+  TORCH_CHECK(slot_indices.size(0) == key.size(0),
+              "reshape_and_cache: slot_indices must have one entry per token, got ",
+              slot_indices.size(0), " and ", key.size(0));
+  check_f16_cuda(key, "reshape_and_cache", "key");
+  check_f16_cuda(key_cache, "reshape_and_cache", "key_cache");
+  TORCH_CHECK(slot_indices.is_cuda() && slot_indices.scalar_type() == at::kInt,
+              "reshape_and_cache: slot_indices must be a CUDA int32 tensor, got ",
+              slot_indices.scalar_type());
+  check_same_device(key, key_cache, "reshape_and_cache");
+  check_same_device(key, slot_indices, "reshape_and_cache");
+
+  const int layout = cache_layout_for_key(key_cache, key.size(1), key.size(2), "reshape_and_cache");
+  const int64_t dims[4] = {key_cache.size(0), key_cache.size(1), key_cache.size(2), key_cache.size(3)};
+  const c10::cuda::CUDAGuard guard(key.device());
+  check_status(b200ops_reshape_and_cache(
+                   key.data_ptr(), value.numel() > 0 ? value.data_ptr() : nullptr,
+                   key_cache.data_ptr(), value_cache.numel() > 0 ? value_cache.data_ptr() : nullptr,
+                   slot_indices.data_ptr<int32_t>(), key.size(0), key.size(1), key.size(2), dims,
+                   layout, current_stream()),
+               "reshape_and_cache");
+}
+
+// Mirrors native::paged_attention (csrc/ffi/ops.cpp:408-482).  The reference validates
+// nothing here; these checks are what the kernels rely on.
+at::Tensor paged_attention(at::Tensor q, at::Tensor key_cache, at::Tensor value_cache,
+                           at::Tensor block_tables, at::Tensor context_lens) {
+  TORCH_CHECK(q.dim() == 3 && key_cache.dim() == 4 && value_cache.dim() == 4 &&
+                  block_tables.dim() == 2 && context_lens.dim() == 1,
+              "paged_attention: q must be 3D, caches 4D, block_tables 2D, context_lens 1D");
+  TORCH_CHECK(q.is_contiguous() && key_cache.is_contiguous() && value_cache.is_contiguous() &&
+                  block_tables.is_contiguous() && context_lens.is_contiguous(),
+              "paged_attention: all input tensors must be contiguous");
+  check_f16_cuda(q, "paged_attention", "q");
+  check_f16_cuda(key_cache, "paged_attention", "key_cache");
+  check_f16_cuda(value_cache, "paged_attention", "value_cache");
+  TORCH_CHECK(block_tables.is_cuda() && block_tables.scalar_type() == at::kInt &&
+                  context_lens.is_cuda() && context_lens.scalar_type() == at::kInt,
+              "paged_attention: block_tables and context_lens must be CUDA int32 tensors");
+  TORCH_CHECK(value_cache.sizes() == key_cache.sizes(),
+              "paged_attention: key_cache and value_cache must have the same shape, got ",
+              key_cache.sizes(), " and ", value_cache.sizes());
+  TORCH_CHECK(block_tables.size(0) == q.size(0) && context_lens.size(0) == q.size(0),
+              "paged_attention: block_tables and context_lens must have one row per sequence");
+  check_same_device(q, key_cache, "paged_attention");
+  check_same_device(q, value_cache, "paged_attention");
+  check_same_device(q, block_tables, "paged_attention");
+  check_same_device(q, context_lens, "paged_attention");
+
+  const int64_t bs = q.size(0), num_heads = q.size(1), head_dim = q.size(2);
+  int layout;
+  int64_t num_kv_heads, page_size;
+  if (key_cache.size(3) == head_dim) {
+    // [pages, page_size, num_kv_heads, head_dim]
+    layout = B200OPS_KV_LAYOUT_NHD;
+    page_size = key_cache.size(1);
+    num_kv_heads = key_cache.size(2);
+  } else {
+    // kvcache: [num_pages, num_kv_heads * head_dim / 16, page_size, 16] (csrc/ffi/ops.cpp:412-415)
+    TORCH_CHECK(key_cache.size(3) == 16 && (key_cache.size(1) * 16) % head_dim == 0,
+                "paged_attention: cache must be [pages, Hkv*D/16, page_size, 16] or "
+                "[pages, page_size, Hkv, D], got ", key_cache.sizes());
+    layout = B200OPS_KV_LAYOUT_NZ;
+    num_kv_heads = key_cache.size(1) * 16 / head_dim;
+    page_size = key_cache.size(2);
+  }
+  TORCH_CHECK(num_kv_heads > 0 && num_heads % num_kv_heads == 0,
+              "paged_attention: num_heads ", num_heads, " is not a multiple of num_kv_heads ",
+              num_kv_heads);
+
+  const c10::cuda::CUDAGuard guard(q.device());
+  at::Tensor y = at::empty_like(q);
+  if (bs == 0) return y;
+  const size_t ws = b200ops_paged_attention_workspace_size(bs, num_heads, num_kv_heads, head_dim,
+                                                           page_size, block_tables.size(1));
+  at::Tensor workspace = at::empty({static_cast<int64_t>(ws)}, q.options().dtype(at::kByte));
+  check_status(b200ops_paged_attention(q.data_ptr(), key_cache.data_ptr(), value_cache.data_ptr(),
+                                       block_tables.data_ptr<int32_t>(),
+                                       context_lens.data_ptr<int32_t>(), y.data_ptr(), bs, num_heads,
+                                       num_kv_heads, head_dim, key_cache.size(0), page_size,
+                                       block_tables.size(1), layout,
+                                       ws ? workspace.data_ptr() : nullptr, ws, current_stream()),
+               "paged_attention");
+  return y;
+}
+
+int print_info(int device_id) {
+  check_status(b200ops_print_info(device_id, nullptr, 0), "print_info");
+  return 0;
+}
+
+void init_ffi_ops(py::module_&& m) {
+  m.def("rope", &rope, "Rope");
+  m.def("swiglu", &swiglu, "Swiglu");
+  m.def("grouped_matmul", &grouped_matmul, "GroupedMatMul");
+  m.def("add_rms_norm", &add_rms_norm, "AddRMSNorm");
+  m.def("reshape_and_cache", &reshape_and_cache, "ReshapeAndCache");
+  m.def("paged_attention", &paged_attention, "PagedAttention");
+}
+
+}  // namespace native
+
+PYBIND11_MODULE(ascend910a_extras_C, m) {
+  m.def("print_info", &native::print_info, "Print info about the device");
+  native::init_ffi_ops(m.def_submodule("ops"));
+}

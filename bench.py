@@ -1,0 +1,345 @@
+"""Benchmark of the B200 decode operator set.
+
+    python bench.py --gpus N --steps K --warmup W          this implementation (GPU)
+    python bench.py --impl reference ...                    the CPU golden path, for the ratio
+
+Prints ONE JSON line on rank 0.  See DESIGN.md for what each field means; in short
+`value` is device-timed with inputs resident in HBM, `e2e` goes through the public
+`ascend910a_extras.ops` API from pinned host buffers with the copies inside the timed
+region, `roofline` is the dominant kernel against the measured peak, `per_op` lists every
+operator of the path, and `cpu_baseline` times the CPU oracle on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+REPO = Path(__file__).resolve().parent
+sys.path.insert(0, str(REPO / "ascend-ops_b200"))
+sys.path.insert(0, str(REPO))
+
+import torch  # noqa: E402
+
+import decode_workloads as wl  # noqa: E402
+
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+L2_BYTES = 126 * 1024 * 1024
+
+
+def load_peaks():
+    p = REPO / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            d = json.loads(p.read_text())
+            return {k: float(d[k]) for k in FALLBACK_PEAKS if k in d} | {"source": "measured"}
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS) | {"source": "fallback"}
+
+
+# --------------------------------------------------------------------------- clocks
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index=0):
+        self.index = index
+        self.proc = None
+        self.lines = []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [c.strip() for c in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# --------------------------------------------------------------------------- timing
+def time_launches(launch, n_sets, steps, warmup, device):
+    """Device time of one launch, in microseconds.
+
+    `launch(i)` enqueues the operator on buffer set i (0 <= i < n_sets).  The sets rotate so
+    that consecutive launches touch different memory (the caller sizes n_sets so that the
+    sets together exceed L2, or the operator's own footprint does).  Each timed step is
+    bracketed by CUDA events on the launching stream; the median over steps is returned
+    together with the raw list.
+    """
+    stream = torch.cuda.current_stream(device)
+    for i in range(warmup):
+        launch(i % n_sets)
+    torch.cuda.synchronize(device)
+    times = []
+    for i in range(steps):
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        launch((warmup + i) % n_sets)
+        e1.record(stream)
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3)
+    return statistics.median(times), times
+
+
+def time_graph(launch, n_sets, reps, steps, warmup, device):
+    """For kernels of a few microseconds: capture `reps` launches over rotating buffer sets in
+    one CUDA graph so that CPU launch gaps do not dominate, and time graph replays.
+    Returns microseconds per launch."""
+    g = torch.cuda.CUDAGraph()
+    s = torch.cuda.Stream(device)
+    with torch.cuda.stream(s):
+        for i in range(min(n_sets, 3)):
+            launch(i)
+        s.synchronize()
+        with torch.cuda.graph(g, stream=s):
+            for i in range(reps):
+                launch(i % n_sets)
+    torch.cuda.synchronize(device)
+    for _ in range(warmup):
+        g.replay()
+    torch.cuda.synchronize(device)
+    times = []
+    stream = torch.cuda.current_stream(device)
+    for _ in range(steps):
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        g.replay()
+        e1.record(stream)
+        e1.synchronize()
+        times.append(e0.elapsed_time(e1) * 1e3 / reps)
+    return statistics.median(times), times
+
+
+def sets_for(bytes_per_set, minimum=2, maximum=16):
+    """How many rotating buffer sets make the combined footprint exceed twice the L2."""
+    n = max(minimum, -(-2 * L2_BYTES // max(bytes_per_set, 1)))
+    return int(min(n, maximum))
+
+
+# --------------------------------------------------------------------------- per-op cases
+def case_add_rms_norm(ops, dev, steps, warmup, peaks):
+    d = wl.add_rms_norm_inputs()
+    t, h = d["x"].shape
+    nbytes = 8 * t * h + 2 * h
+    n = sets_for(nbytes)
+    xs = [d["x"].to(dev).clone() for _ in range(n)]
+    rs = [d["residual"].to(dev).clone() for _ in range(n)]
+    w = d["weight"].to(dev)
+    us, _ = time_graph(lambda i: ops.add_rms_norm(xs[i], rs[i], w, d["eps"]), n, 2 * n, steps, warmup, dev)
+    return op_record("add_rms_norm", f"[{t},{h}] f16", nbytes, us, peaks, "hbm", launches=1)
+
+
+def case_swiglu(ops, dev, steps, warmup, peaks):
+    t, dd = 8192, 14336
+    x = wl.swiglu_inputs(t, dd)["x"].to(dev)
+    nbytes = 6 * t * dd
+    us, _ = time_launches(lambda i: ops.swiglu(x), 1, steps, warmup, dev)
+    return op_record("swiglu", f"[{t},{2 * dd}] f16", nbytes, us, peaks, "hbm", launches=1)
+
+
+def case_rope(ops, dev, steps, warmup, peaks):
+    r = wl.rope_inputs()
+    t, hq, d = r["q"].shape
+    hkv = r["k"].shape[1]
+    nbytes = 2 * t * (hq + hkv) * d * 2 + t * d * 2 + 4 * t
+    n = sets_for(nbytes)
+    qs = [r["q"].to(dev).clone() for _ in range(n)]
+    ks = [r["k"].to(dev).clone() for _ in range(n)]
+    pos, cos, sin = r["position_ids"].to(dev), r["cos_cache"].to(dev), r["sin_cache"].to(dev)
+    us, _ = time_graph(lambda i: ops.rope(qs[i], ks[i], pos, cos, sin), n, 2 * n, steps, warmup, dev)
+    return op_record("rope", f"q[{t},{hq},{d}] k[{t},{hkv},{d}] f16", nbytes, us, peaks, "hbm", launches=1)
+
+
+def case_reshape_and_cache(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_NHD):
+    c = wl.reshape_and_cache_inputs(layout=layout)
+    t, hkv, d = c["key"].shape
+    nbytes = 2 * (t * hkv * d * 2) * 2 + 4 * t
+    n = 16
+    g = torch.Generator().manual_seed(77)
+    keys = [c["key"].to(dev).clone() for _ in range(n)]
+    vals = [c["value"].to(dev).clone() for _ in range(n)]
+    total_slots = c["cache_shape"][0] * (c["cache_shape"][1] if layout == wl.KV_LAYOUT_NHD else c["cache_shape"][2])
+    slots = [torch.randperm(total_slots, generator=g)[:t].int().to(dev) for _ in range(n)]
+    kc = torch.zeros(c["cache_shape"], dtype=torch.float16, device=dev)
+    vc = torch.zeros(c["cache_shape"], dtype=torch.float16, device=dev)
+    us, _ = time_graph(lambda i: ops.reshape_and_cache(keys[i], vals[i], kc, vc, slots[i]), n, 2 * n,
+                       steps, warmup, dev)
+    name = "reshape_and_cache" + ("" if layout == wl.KV_LAYOUT_NHD else "_nz")
+    return op_record(name, f"{t} tokens -> cache {list(c['cache_shape'])} f16", nbytes, us, peaks, "hbm",
+                     launches=1)
+
+
+def case_paged_attention(ops, dev, steps, warmup, peaks):
+    a = wl.paged_attention_inputs()
+    nbytes = wl.paged_attention_bytes(a["context_lens"], 4, 128, 28, 128)
+    q, kc, vc = a["q"].to(dev), a["key_cache"].to(dev), a["value_cache"].to(dev)
+    bt, cl = a["block_tables"].to(dev), a["context_lens"].to(dev)
+    us, _ = time_launches(lambda i: ops.paged_attention(q, kc, vc, bt, cl), 1, steps, warmup, dev)
+    rec = op_record("paged_attention", "B=64 28q/4kv D=128 L~U[512,8192] page 128", nbytes, us, peaks,
+                    "hbm", launches=2)
+    rec["sum_context"] = int(a["context_lens"].sum())
+    return rec
+
+
+def case_grouped_matmul(ops, dev, steps, warmup, peaks, which="gate_up"):
+    k, n = (4096, 28672) if which == "gate_up" else (14336, 4096)
+    w = wl.grouped_matmul_inputs(rows=8192, k=k, n=n, seed=4 if which == "gate_up" else 5)
+    x, ws, gl = w["x"].to(dev), w["w_storage"].to(dev), w["group_list"].to(dev)
+    wv = ws.transpose(1, 2)
+    flops = 2 * 8192 * k * n
+    us, _ = time_launches(lambda i: ops.grouped_matmul(x, wv, gl), 1, steps, warmup, dev)
+    tf = flops / us / 1e6
+    peak = peaks["bf16_tflops"]
+    return {"op": f"grouped_matmul_{which}", "shape": f"8 experts, 8192 rows, {k}->{n} f16",
+            "flops": flops, "us": round(us, 2), "achieved": round(tf, 1), "unit": "TFLOP/s",
+            "peak": peak, "frac": round(tf / peak, 4), "bound": "tensor", "launches": 1,
+            "group_rows": torch.diff(w["group_list"], prepend=torch.zeros(1, dtype=torch.int64)).tolist()}
+
+
+def op_record(name, shape, nbytes, us, peaks, bound, launches):
+    gbs = nbytes / us / 1e3
+    return {"op": name, "shape": shape, "bytes": int(nbytes), "us": round(us, 3),
+            "achieved": round(gbs, 1), "unit": "GB/s", "peak": peaks["hbm_gbs"],
+            "frac": round(gbs / peaks["hbm_gbs"], 4), "bound": bound, "launches": launches}
+
+
+# --------------------------------------------------------------------------- CPU baseline
+def cpu_paged_attention_sample(seqs=8):
+    """The oracle on the first `seqs` sequences of the benchmark's attention batch."""
+    from oracle import decode_ops_oracle as oracle
+
+    a = wl.paged_attention_inputs(bs=seqs, blocks=seqs * 64, seed=3)
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
+    t0 = time.perf_counter()
+    oracle.paged_attention(a["q"], a["key_cache"], a["value_cache"], a["block_tables"], a["context_lens"])
+    dt = time.perf_counter() - t0
+    nbytes = wl.paged_attention_bytes(a["context_lens"], 4, 128, 28, 128)
+    return nbytes / dt / 1e9, dt, seqs
+
+
+# --------------------------------------------------------------------------- main
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--ops", default="all", help="comma list of per-op cases, or 'all' / 'none'")
+    ns = ap.parse_args()
+    ns.warmup = max(ns.warmup, 3)
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    peaks = load_peaks()
+    cores = len(os.sched_getaffinity(0))
+
+    if ns.impl == "reference":
+        if rank != 0:
+            return
+        gbs, dt, seqs = cpu_paged_attention_sample(8)
+        print(json.dumps({
+            "impl": "reference", "metric": "paged_attention_hbm_gbs", "value": round(gbs, 3),
+            "unit": "GB/s", "n_gpus": ns.gpus, "steps": 1, "warmup": 0, "ms_per_step": round(dt * 1e3, 2),
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+            "data": "synthetic", "config": {"workload": "paged_attention decode B=64 28q/4kv D=128 L~U[512,8192]"},
+            "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
+                             "sample": f"first {seqs} of 64 sequences, one pass"},
+            "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        }))
+        return
+
+    import ascend910a_extras.ops as ops
+
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    cases = {
+        "add_rms_norm": case_add_rms_norm, "reshape_and_cache": case_reshape_and_cache,
+        "reshape_and_cache_nz": lambda *a: case_reshape_and_cache(*a, layout=wl.KV_LAYOUT_NZ),
+        "rope": case_rope, "swiglu": case_swiglu, "paged_attention": case_paged_attention,
+        "grouped_matmul_gate_up": lambda *a: case_grouped_matmul(*a, which="gate_up"),
+        "grouped_matmul_down": lambda *a: case_grouped_matmul(*a, which="down"),
+    }
+    want = list(cases) if ns.ops == "all" else [c for c in ns.ops.split(",") if c and c != "none"]
+    per_op = []
+    for name in want:
+        rec = cases[name](ops, dev, ns.steps, ns.warmup, peaks)
+        per_op.append(rec)
+        torch.cuda.empty_cache()
+    clocks = sampler.stop() if rank == 0 else None
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
+    if rank != 0:
+        return
+    head = next((r for r in per_op if r["op"] == "paged_attention"), per_op[0] if per_op else None)
+    gbs_cpu, dt_cpu, seqs = cpu_paged_attention_sample(8)
+    line = {
+        "metric": "paged_attention_hbm_gbs", "value": head["achieved"] if head else None, "unit": "GB/s",
+        "n_gpus": ns.gpus, "steps": ns.steps, "warmup": ns.warmup,
+        "ms_per_step": round(head["us"] / 1e3, 4) if head else None, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": head["shape"] if head else None, "l2": "inputs larger than L2 or rotating buffer sets"},
+        "roofline": ({"bound": "hbm", "achieved": head["achieved"], "peak": head["peak"], "unit": "GB/s",
+                      "frac": head["frac"], "traffic": None, "peak_source": peaks["source"]} if head else None),
+        "cpu_baseline": {"value": round(gbs_cpu, 3), "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"first {seqs} of 64 sequences, one pass ({dt_cpu:.1f} s)"},
+        "gpu_launches": sum(r["launches"] for r in per_op),
+        "clocks": clocks, "per_op": per_op,
+    }
+    print(json.dumps(line))
+
+
+if __name__ == "__main__":
+    main()

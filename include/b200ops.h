@@ -1,0 +1,161 @@
+/*
+ * b200ops.h -- C ABI of the B200 (sm_100a) decode operator library, libb200ops.so.
+ *
+ * One entry point per operator of the reference's `ascend910a_extras.ops` API.  Each
+ * replaces the two-phase CANN pair the reference FFI calls for the same operator,
+ *     aclnn<Op>GetWorkspaceSize(tensors..., &workspaceSize, &executor)
+ *     aclnn<Op>(workspace, workspaceSize, executor, stream)
+ * (call sites are cited per function below, by path inside the reference project).
+ *
+ * Conventions
+ *   - All data pointers are DEVICE pointers of the current CUDA device; tensors are dense,
+ *     row-major ("contiguous") with the shapes written beside each argument.
+ *   - "f16" = IEEE binary16.  Accumulation is always fp32; results are rounded once (RNE).
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).  Every
+ *     call only enqueues work; nothing synchronises.  No call allocates device memory unless
+ *     its comment says so: operators that need scratch take a caller-owned `workspace` whose
+ *     minimum size comes from the matching *_workspace_size() query (the same split the
+ *     reference makes between GetWorkspaceSize and the launch).
+ *   - Return value: 0 on success, a negative B200OPS_E* code otherwise.  The failing
+ *     thread can read a message with b200ops_last_error().  Argument violations that the
+ *     reference reports through TORCH_CHECK are reported as B200OPS_EINVAL with the same
+ *     condition.
+ *   - There is no CPU path: without a CUDA device every launch returns B200OPS_ECUDA.
+ */
+#ifndef B200OPS_H_
+#define B200OPS_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200OPS_OK 0
+#define B200OPS_EINVAL (-1)   /* argument check failed                       */
+#define B200OPS_ECUDA (-2)    /* a CUDA runtime / driver call failed         */
+#define B200OPS_EWORKSPACE (-3) /* workspace pointer null or too small       */
+#define B200OPS_EUNSUPPORTED (-4) /* shape outside what the kernels implement */
+
+/* KV-cache layouts understood by reshape_and_cache and paged_attention. */
+#define B200OPS_KV_LAYOUT_NZ 0  /* [num_pages, num_kv_heads*head_dim/16, page_size, 16]  (reference-native) */
+#define B200OPS_KV_LAYOUT_NHD 1 /* [num_pages, page_size, num_kv_heads, head_dim]        (vLLM standard)    */
+
+/* Library version (major*10000 + minor*100 + patch). */
+int b200ops_version(void);
+
+/* Message of the last failure on the calling thread ("" if none). Never NULL. */
+const char* b200ops_last_error(void);
+
+/*
+ * Device report: SM count, shared memory, L2, memory size/clock/bus, printed to stdout.
+ * Replaces native::print_info (csrc/ffi/bind.cpp:26-51).  If `buf` is non-NULL the same
+ * text is also copied there (truncated to buf_len, always NUL-terminated).
+ */
+int b200ops_print_info(int device_id, char* buf, size_t buf_len);
+
+/*
+ * Fused residual add + RMSNorm.
+ * Replaces aclnnAddRMSNormExGetWorkspaceSize / aclnnAddRMSNormEx (csrc/ffi/ops.cpp:303,308;
+ * kernel csrc/opdev/op_kernel/add_rms_norm_ex.cpp:3-123).
+ *   s = f16(x + residual); y = f16(s / sqrt(mean(s^2) + eps) * weight); residual_out = s
+ *   x, residual, y, residual_out : f16 [num_tokens, dim];  weight : f16 [dim]
+ * Requires dim % 64 == 0 (csrc/ffi/ops.cpp:245).  No workspace.
+ */
+int b200ops_add_rms_norm(const void* x, const void* residual, const void* weight, float eps,
+                         void* y, void* residual_out, int64_t num_tokens, int64_t dim,
+                         void* stream);
+
+/*
+ * SwiGLU: y[t, j] = silu(x[t, j]) * x[t, d + j],  x : f16 [num_tokens, 2*d], y : f16 [num_tokens, d].
+ * Replaces aclnnSwiGluExGetWorkspaceSize / aclnnSwiGluEx (csrc/ffi/ops.cpp:138,143; kernel
+ * csrc/opdev/op_kernel/swi_glu_ex.cpp:3-68).  `two_d` is x's last dimension; requires
+ * two_d >= 64 and two_d % 64 == 0 (csrc/ffi/ops.cpp:113).  No workspace.
+ */
+int b200ops_swiglu(const void* x, void* y, int64_t num_tokens, int64_t two_d, void* stream);
+
+/*
+ * Rotary embedding, half-split ("neox") form, out of place, on q and k in one launch.
+ * Replaces aclnnRopeExGetWorkspaceSize / aclnnRopeEx (csrc/ffi/ops.cpp:76,81; kernel
+ * csrc/opdev/op_kernel/rope_ex.cpp:3-122).
+ *   q, out_q : f16 [bs, num_heads, head_dim];  k, out_k : f16 [bs, num_kv_heads, head_dim]
+ *   position_ids : int32 [bs];  cos_cache, sin_cache : f16 [max_pos, head_dim/2]
+ *   out[..., :h] = x[..., :h]*cos - x[..., h:]*sin;  out[..., h:] = x[..., h:]*cos + x[..., :h]*sin
+ * A position outside [0, max_pos) is an error the device cannot report; rows with such a
+ * position are written as zeros and the call still returns 0.  Requires head_dim % 16 == 0.
+ */
+int b200ops_rope(const void* q, const void* k, const int32_t* position_ids,
+                 const void* cos_cache, const void* sin_cache, void* out_q, void* out_k,
+                 int64_t bs, int64_t num_heads, int64_t num_kv_heads, int64_t head_dim,
+                 int64_t max_pos, void* stream);
+
+/*
+ * Scatter this step's K (and optionally V) rows into the paged KV cache, in place.
+ * Replaces aclnnReshapeAndCacheExGetWorkspaceSize / aclnnReshapeAndCacheEx
+ * (csrc/ffi/ops.cpp:387,394; kernel csrc/opdev/op_kernel/reshape_and_cache_ex.cpp:3-71).
+ *   key, value : f16 [num_tokens, num_kv_heads, head_size];  slot_indices : int32 [num_tokens]
+ *   cache_dims = the four sizes of key_cache (value_cache has the same shape)
+ *   layout NZ  [pages, C, P, 16]:  cache[s/P, c, s%P, j] = flat(key[t])[c*16 + j]  for c*16+j < Hkv*D, c < C
+ *   layout NHD [pages, P, Hkv, D]: cache[s/P, s%P, h, d] = key[t, h, d]
+ * Slots < 0 or >= pages*P are skipped (reshape_and_cache_ex.cpp:50).  `value` and
+ * `value_cache` may both be NULL (key-only form, ascend910a_extras/ops.py:40-43); if only
+ * one of them is NULL values are not written, as in the reference kernel (:24-25,62-64).
+ * Bit-exact copy.  No workspace.
+ */
+int b200ops_reshape_and_cache(const void* key, const void* value, void* key_cache,
+                              void* value_cache, const int32_t* slot_indices,
+                              int64_t num_tokens, int64_t num_kv_heads, int64_t head_size,
+                              const int64_t cache_dims[4], int layout, void* stream);
+
+/*
+ * Decode attention over the paged KV cache (one query token per sequence, GQA).
+ * Replaces aclnnPagedAttentionExGetWorkspaceSize / aclnnPagedAttentionEx
+ * (csrc/ffi/ops.cpp:454,459; tiling csrc/opdev/op_host/paged_attention_ex.cpp:8-59; kernel
+ * csrc/opdev/op_kernel/paged_attention_ex.cpp:3-471).
+ *   q, out : f16 [bs, num_heads, head_dim];  block_tables : int32 [bs, max_pages_per_seq]
+ *   context_lens : int32 [bs];  caches in `layout` with `num_pages` pages of `page_size` tokens
+ *   out[b,h] = softmax(q[b,h] . K[b, h/(Hq/Hkv), :L_b]^T / sqrt(head_dim)) . V[b, h/(Hq/Hkv), :L_b]
+ * A sequence with context_len <= 0 gets zeros.  Scratch (split-context partials) lives in
+ * `workspace`; ask b200ops_paged_attention_workspace_size() for the minimum size.
+ */
+size_t b200ops_paged_attention_workspace_size(int64_t bs, int64_t num_heads,
+                                              int64_t num_kv_heads, int64_t head_dim,
+                                              int64_t page_size, int64_t max_pages_per_seq);
+int b200ops_paged_attention(const void* q, const void* key_cache, const void* value_cache,
+                            const int32_t* block_tables, const int32_t* context_lens, void* out,
+                            int64_t bs, int64_t num_heads, int64_t num_kv_heads,
+                            int64_t head_dim, int64_t num_pages, int64_t page_size,
+                            int64_t max_pages_per_seq, int layout, void* workspace,
+                            size_t workspace_size, void* stream);
+
+/*
+ * Grouped (per-expert) NT GEMM: y[gl[e-1]:gl[e], :] = x[gl[e-1]:gl[e], :] @ w[e]  (gl[-1] = 0).
+ * Replaces aclnnGroupedMatMulExGetWorkspaceSize / aclnnGroupedMatMulEx
+ * (csrc/ffi/ops.cpp:211,216; kernel csrc/opdev/op_kernel/grouped_mat_mul_ex.cpp:5-45 and
+ * csrc/opdev/op_kernel/matmul_core.h:7-221).
+ *   x : f16 [num_tokens, k];  w : f16, STORAGE [num_experts, n, k] (k contiguous; the torch
+ *   view is [E, k, n] with strides (n*k, 1, k), csrc/ffi/ops.cpp:171-172);
+ *   group_list : int64 [num_experts], inclusive cumulative row ends;  y : f16 [num_tokens, n]
+ * Requires k % 64 == 0 and n % 64 == 0 (csrc/ffi/ops.cpp:173).  Rows past gl[E-1] are not
+ * written.  Empty groups are skipped (grouped_mat_mul_ex.cpp:40).  No workspace is needed
+ * today; the query exists so that callers can keep the two-phase shape.
+ */
+size_t b200ops_grouped_matmul_workspace_size(int64_t num_tokens, int64_t k, int64_t num_experts,
+                                             int64_t n);
+int b200ops_grouped_matmul(const void* x, const void* w, const int64_t* group_list, void* y,
+                           int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n,
+                           void* workspace, size_t workspace_size, void* stream);
+
+/*
+ * Health word of the pipelined kernels (grouped_matmul, paged_attention's TMA path).  Their
+ * producer/consumer waits are bounded; a wait that runs out ends the kernel and leaves a
+ * non-zero code here.  This call synchronises the device, returns the code in *status
+ * (0 = healthy) and clears it.  Diagnostic only; it has no counterpart in the reference.
+ */
+int b200ops_pipeline_status(int* status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200OPS_H_ */

@@ -1,0 +1,333 @@
+"""GPU parity tests: every operator through the C ABI (raw pointers, caller-allocated
+outputs) against the CPU oracle and the reference-made golden fixtures.
+
+Tolerances: reshape_and_cache and add_rms_norm's residual output are bit-exact; the other
+fp16 results are within rtol 1e-2 / atol 1e-3 of the fp32-accumulating golden.
+"""
+import numpy as np
+import pytest
+import torch
+
+import decode_workloads as wl
+from conftest import bits, f16
+from oracle import decode_ops_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+RTOL, ATOL = 1e-2, 1e-3
+
+
+def close(got, want, rtol=RTOL, atol=ATOL):
+    torch.testing.assert_close(got.cpu().float(), want.float(), rtol=rtol, atol=atol)
+
+
+# ------------------------------------------------------------------ add_rms_norm
+def run_add_rms_norm(cabi, x, r, w, eps):
+    xd, rd, wd = x.to(DEV), r.to(DEV), w.to(DEV)
+    y = torch.full_like(xd, float("nan"))
+    s = torch.full_like(xd, float("nan"))
+    cabi.add_rms_norm(xd, rd, wd, eps, y, s)
+    torch.cuda.synchronize()
+    return y.cpu(), s.cpu()
+
+
+def test_add_rms_norm_golden(cabi, golden):
+    z = golden("add_rms_norm")
+    for i in range(int(z["n"])):
+        y, s = run_add_rms_norm(cabi, f16(z[f"x{i}"]), f16(z[f"r{i}"]), f16(z[f"w{i}"]), float(z[f"eps{i}"]))
+        assert np.array_equal(bits(s), z[f"s{i}"])
+        close(y, f16(z[f"y{i}"]))
+
+
+@pytest.mark.parametrize("tokens,hidden", [(1, 64), (7, 128), (33, 1088), (257, 4096), (5, 8192),
+                                           (3, 16384), (2, 65536), (2, 65600)])
+def test_add_rms_norm_shapes(cabi, tokens, hidden):
+    d = wl.add_rms_norm_inputs(tokens, hidden, seed=tokens + hidden)
+    y, s = run_add_rms_norm(cabi, d["x"], d["residual"], d["weight"], d["eps"])
+    ey, es = oracle.add_rms_norm(d["x"], d["residual"], d["weight"], d["eps"])
+    assert torch.equal(s, es)
+    close(y, ey)
+
+
+def test_add_rms_norm_benchmark_size_and_api(cabi, ops):
+    d = wl.add_rms_norm_inputs()
+    ey, es = oracle.add_rms_norm(d["x"], d["residual"], d["weight"], d["eps"])
+    y, s = ops.add_rms_norm(d["x"].to(DEV), d["residual"].to(DEV), d["weight"].to(DEV), d["eps"])
+    assert torch.equal(s.cpu(), es)
+    close(y, ey)
+    # large-magnitude rows must not overflow the fp32 sum of squares
+    big = (d["x"][:4] * 200).half()
+    y, s = run_add_rms_norm(cabi, big, big, d["weight"], 1e-6)
+    ey, es = oracle.add_rms_norm(big, big, d["weight"], 1e-6)
+    assert torch.equal(s, es)
+    close(y, ey)
+
+
+# ------------------------------------------------------------------ swiglu
+def run_swiglu(cabi, x):
+    xd = x.to(DEV)
+    y = torch.full((x.shape[0], x.shape[1] // 2), float("nan"), dtype=torch.float16, device=DEV)
+    cabi.swiglu(xd, y)
+    torch.cuda.synchronize()
+    return y.cpu()
+
+
+def test_swiglu_golden(cabi, golden):
+    z = golden("swiglu")
+    for i in range(int(z["n"])):
+        close(run_swiglu(cabi, f16(z[f"x{i}"])), f16(z[f"y{i}"]))
+
+
+@pytest.mark.parametrize("tokens,d", [(1, 32), (5, 96), (1031, 192), (64, 14336), (3, 100000 * 32 // 32)])
+def test_swiglu_shapes(cabi, tokens, d):
+    if d % 32:
+        d = d // 32 * 32
+    x = (torch.randn(tokens, 2 * d, generator=torch.Generator().manual_seed(d)) * 4).half()
+    close(run_swiglu(cabi, x), oracle.swiglu(x))
+
+
+def test_swiglu_extreme_values_and_api(ops):
+    x = torch.tensor([[-65504.0, -30.0, -1.0, 0.0, 1.0, 30.0, 200.0, 65504.0] * 8] * 2).half()
+    x = torch.cat([x, torch.ones_like(x)], dim=1)  # gate = values, up = 1
+    y = ops.swiglu(x.to(DEV)).cpu()
+    close(y, oracle.swiglu(x))
+    assert torch.isfinite(y[:, :-1].float()).all()
+
+
+# ------------------------------------------------------------------ rope
+def run_rope(cabi, q, k, pos, cos, sin):
+    oq = torch.full_like(q, float("nan"), device=DEV)
+    ok = torch.full_like(k, float("nan"), device=DEV)
+    cabi.rope(q.to(DEV), k.to(DEV), pos.to(DEV), cos.to(DEV), sin.to(DEV), oq, ok)
+    torch.cuda.synchronize()
+    return oq.cpu(), ok.cpu()
+
+
+def test_rope_golden(cabi, golden):
+    z = golden("rope")
+    for i in range(int(z["n"])):
+        oq, ok = run_rope(cabi, f16(z[f"q{i}"]), f16(z[f"k{i}"]), torch.from_numpy(z[f"pos{i}"]),
+                          f16(z[f"cos{i}"]), f16(z[f"sin{i}"]))
+        # fp32 evaluation of the reference's fn_naive, one rounding
+        close(oq, torch.from_numpy(z[f"oq32_{i}"]))
+        close(ok, torch.from_numpy(z[f"ok32_{i}"]))
+        # and the fp16 evaluation the reference itself runs
+        close(oq, f16(z[f"oq{i}"]))
+        close(ok, f16(z[f"ok{i}"]))
+
+
+@pytest.mark.parametrize("tokens,hq,hkv,d", [(1, 1, 1, 16), (9, 4, 4, 64), (256, 32, 8, 128), (17, 28, 4, 256)])
+def test_rope_shapes(cabi, ops, tokens, hq, hkv, d):
+    w = wl.rope_inputs(tokens, hq, hkv, d, min_pos=0, max_pos=300, seed=tokens)
+    eq, ek = oracle.rope(w["q"], w["k"], w["position_ids"], w["cos_cache"], w["sin_cache"])
+    oq, ok = run_rope(cabi, w["q"], w["k"], w["position_ids"], w["cos_cache"], w["sin_cache"])
+    close(oq, eq)
+    close(ok, ek)
+    aq, ak = ops.rope(*(w[n].to(DEV) for n in ("q", "k", "position_ids", "cos_cache", "sin_cache")))
+    assert torch.equal(aq.cpu(), oq) and torch.equal(ak.cpu(), ok)
+
+
+# ------------------------------------------------------------------ reshape_and_cache
+def test_reshape_and_cache_reference_case(cabi, ops, golden):
+    z = golden("reshape_and_cache")
+    shape = tuple(int(v) for v in z["shape0"])
+    kc = torch.zeros(shape, dtype=torch.float16, device=DEV)
+    vc = torch.zeros(shape, dtype=torch.float16, device=DEV)
+    cabi.reshape_and_cache(f16(z["key0"]).to(DEV), f16(z["value0"]).to(DEV), kc, vc,
+                           torch.from_numpy(z["slots0"]).to(DEV), cabi.KV_LAYOUT_NZ)
+    torch.cuda.synchronize()
+    for cache, vals in ((kc, z["kc0"]), (vc, z["vc0"])):
+        flat = bits(cache).reshape(-1)
+        assert np.array_equal(flat[z["idx0"]], vals)
+        assert np.count_nonzero(flat) == np.count_nonzero(vals)
+    # key-only form through the Python API: value cache must stay zero
+    kc.zero_()
+    vc.zero_()
+    ops.reshape_and_cache(f16(z["key1"]).to(DEV), None, kc, None, torch.from_numpy(z["slots1"]).to(DEV))
+    torch.cuda.synchronize()
+    flat = bits(kc).reshape(-1)
+    assert np.array_equal(flat[z["idx1"]], z["kc1"]) and np.count_nonzero(flat) == np.count_nonzero(z["kc1"])
+    assert not vc.any()
+
+
+def test_reshape_and_cache_small_dense_golden(cabi, golden):
+    z = golden("reshape_and_cache")
+    shape = tuple(int(v) for v in z["shape2"])
+    kc = torch.zeros(shape, dtype=torch.float16, device=DEV)
+    vc = torch.zeros(shape, dtype=torch.float16, device=DEV)
+    cabi.reshape_and_cache(f16(z["key2"]).to(DEV), f16(z["value2"]).to(DEV), kc, vc,
+                           torch.from_numpy(z["slots2"]).to(DEV), cabi.KV_LAYOUT_NZ)
+    assert np.array_equal(bits(kc), z["kc2_dense"]) and np.array_equal(bits(vc), z["vc2_dense"])
+
+
+@pytest.mark.parametrize("layout", [wl.KV_LAYOUT_NHD, wl.KV_LAYOUT_NZ])
+@pytest.mark.parametrize("tokens,hkv,d,blocks,p", [(2048, 8, 128, 4096, 128), (37, 2, 64, 9, 16),
+                                                   (5, 1, 24, 4, 8), (64, 3, 40, 16, 32)])
+def test_reshape_and_cache_vs_oracle(cabi, layout, tokens, hkv, d, blocks, p):
+    if layout == wl.KV_LAYOUT_NZ and (hkv * d) % 16:
+        pytest.skip("NZ layout needs a row that is a multiple of 16")
+    w = wl.reshape_and_cache_inputs(tokens, hkv, d, blocks, p, layout, seed=tokens)
+    slots = w["slot_indices"].clone()
+    if tokens > 4:  # some slots the kernel must skip
+        slots[1] = -1
+        slots[3] = blocks * p
+        slots[4] = -7
+    pattern = (torch.arange(int(np.prod(w["cache_shape"])), dtype=torch.int32) % 1021).short()
+    kc_cpu = pattern.view(torch.float16).view(w["cache_shape"]).clone()
+    vc_cpu = (pattern + 1).view(torch.float16).view(w["cache_shape"]).clone()
+    kc, vc = kc_cpu.to(DEV), vc_cpu.to(DEV)
+    cabi.reshape_and_cache(w["key"].to(DEV), w["value"].to(DEV), kc, vc, slots.to(DEV), layout)
+    torch.cuda.synchronize()
+    oracle.reshape_and_cache(w["key"], kc_cpu, slots, w["value"], vc_cpu, layout)
+    assert np.array_equal(bits(kc), bits(kc_cpu))
+    assert np.array_equal(bits(vc), bits(vc_cpu))
+
+
+# ------------------------------------------------------------------ paged_attention
+def run_paged_attention(cabi, w):
+    q = w["q"].to(DEV)
+    kc, vc = w["key_cache"].to(DEV), w["value_cache"].to(DEV)
+    out = torch.full_like(q, float("nan"))
+    n = cabi.paged_attention_workspace_size(q.shape[0], q.shape[1], w["kv_heads"], q.shape[2],
+                                            w["block_size"], w["block_tables"].shape[1])
+    ws = torch.empty(max(n, 1), dtype=torch.uint8, device=DEV)
+    cabi.paged_attention(q, kc, vc, w["block_tables"].to(DEV), w["context_lens"].to(DEV), out,
+                         w["kv_heads"], w["block_size"], w["layout"], ws if n else None)
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    return out.cpu()
+
+
+@pytest.mark.parametrize("layout", [wl.KV_LAYOUT_NHD, wl.KV_LAYOUT_NZ])
+@pytest.mark.parametrize("heads,kv_heads,d,p", [(28, 4, 128, 128), (32, 8, 128, 128), (8, 8, 64, 16),
+                                                (16, 1, 128, 32), (12, 4, 256, 16), (4, 2, 32, 8),
+                                                (40, 2, 128, 64)])
+def test_paged_attention_ragged(cabi, layout, heads, kv_heads, d, p):
+    lens = [1, 0, p, p + 1, 3 * p - 1, 517, 1300, 2048, 5]
+    blocks = sum((l + p - 1) // p for l in lens) + 3
+    w = wl.paged_attention_inputs(heads=heads, kv_heads=kv_heads, head_dim=d, block_size=p,
+                                  blocks=blocks, layout=layout, context_lens=lens, seed=heads + d)
+    # poison every cache position beyond each sequence's length: a correct kernel never lets
+    # them reach the output
+    w = poison_unused(w)
+    want = oracle.paged_attention(clean(w["q"]), w["key_cache_clean"], w["value_cache_clean"],
+                                  w["block_tables"], w["context_lens"], layout)
+    got = run_paged_attention(cabi, w)
+    close(got, want)
+    assert not got[1].any()  # context_len 0 -> zeros
+
+
+def clean(t):
+    return t
+
+
+def poison_unused(w):
+    """NaN-fill all cache tokens that no sequence owns (tails of last pages, spare pages)."""
+    layout, p = w["layout"], w["block_size"]
+    kc, vc = w["key_cache"], w["value_cache"]
+    pages = kc.shape[0]
+    used = torch.zeros(pages, p, dtype=torch.bool)
+    for b, L in enumerate(w["context_lens"].tolist()):
+        for i in range((L + p - 1) // p):
+            pg = int(w["block_tables"][b, i])
+            used[pg, : min(p, L - i * p)] = True
+    w = dict(w)
+    w["key_cache_clean"], w["value_cache_clean"] = kc, vc
+    kp, vp = kc.clone(), vc.clone()
+    if layout == wl.KV_LAYOUT_NHD:
+        kp[~used] = float("nan")
+        vp[~used] = float("nan")
+    else:
+        m = (~used)[:, None, :, None].expand_as(kp)
+        kp[m] = float("nan")
+        vp[m] = float("nan")
+    w["key_cache"], w["value_cache"] = kp, vp
+    return w
+
+
+def test_paged_attention_benchmark_shape_reduced(cabi, ops):
+    """The benchmark's GQA configuration (28 q / 4 kv heads, D 128, pages of 128) on 12 sequences."""
+    w = wl.paged_attention_inputs(bs=12, blocks=12 * 64, seed=33)
+    want = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
+                                  w["context_lens"])
+    got = run_paged_attention(cabi, w)
+    close(got, want)
+    api = ops.paged_attention(w["q"].to(DEV), w["key_cache"].to(DEV), w["value_cache"].to(DEV),
+                              w["block_tables"].to(DEV), w["context_lens"].to(DEV))
+    assert torch.equal(api.cpu(), got)
+
+
+def test_paged_attention_long_context_split(cabi):
+    """One long sequence next to short ones: many chunks for one, a single chunk for others."""
+    w = wl.paged_attention_inputs(heads=32, kv_heads=8, context_lens=[16385, 7, 129, 4096],
+                                  blocks=200, seed=9)
+    want = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
+                                  w["context_lens"])
+    close(run_paged_attention(cabi, w), want)
+
+
+def test_paged_attention_workspace_too_small(cabi):
+    w = wl.paged_attention_inputs(bs=2, blocks=200, seed=1)
+    q = w["q"].to(DEV)
+    with pytest.raises(cabi.B200OpsError) as e:
+        cabi.paged_attention(q, w["key_cache"].to(DEV), w["value_cache"].to(DEV),
+                             w["block_tables"].to(DEV), w["context_lens"].to(DEV),
+                             torch.empty_like(q), 4, 128, wl.KV_LAYOUT_NHD,
+                             torch.empty(16, dtype=torch.uint8, device=DEV))
+    assert e.value.code == cabi.EWORKSPACE
+
+
+# ------------------------------------------------------------------ grouped_matmul
+def run_grouped_matmul(cabi, x, w_storage, gl, fill=float("nan")):
+    y = torch.full((x.shape[0], w_storage.shape[1]), fill, dtype=torch.float16, device=DEV)
+    cabi.grouped_matmul(x.to(DEV), w_storage.to(DEV), gl.to(DEV), y)
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    return y.cpu()
+
+
+def test_grouped_matmul_golden(cabi, golden):
+    z = golden("grouped_matmul")
+    for i in range(int(z["n"])):
+        y = run_grouped_matmul(cabi, f16(z[f"x{i}"]), f16(z[f"w{i}"]), torch.from_numpy(z[f"gl{i}"]))
+        close(y, f16(z[f"y{i}"]))
+
+
+@pytest.mark.parametrize("counts,k,n", [
+    ([128], 64, 64),                       # one exact tile
+    ([1], 64, 64),                         # a single row
+    ([300, 0, 1, 129, 70], 256, 320),      # M tails, an empty group, N tail (320 = 256 + 64)
+    ([5, 250, 3, 0, 0, 77, 128, 256], 512, 1024),
+    ([1000], 1024, 768),                   # plain NT GEMM (one group)
+    ([17] * 128, 128, 192),                # many experts, uniform
+    ([0, 0, 40], 64, 128),                 # leading empty groups
+])
+def test_grouped_matmul_vs_oracle(cabi, counts, k, n):
+    g = torch.Generator().manual_seed(sum(counts) + k + n)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half()
+    w_storage = (torch.randn(len(counts), n, k, generator=g) * 0.05).half()
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64)
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    close(run_grouped_matmul(cabi, x, w_storage, gl), want)
+
+
+def test_grouped_matmul_rows_past_last_group_untouched_and_api(cabi, ops):
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(200, 128, generator=g).half()
+    w_storage = (torch.randn(3, 192, 128, generator=g) * 0.05).half()
+    gl = torch.tensor([50, 50, 130], dtype=torch.int64)  # rows 130..199 belong to no group
+    y = run_grouped_matmul(cabi, x, w_storage, gl, fill=7.0)
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    close(y[:130], want[:130])
+    assert (y[130:] == 7.0).all()
+    api = ops.grouped_matmul(x.to(DEV), w_storage.to(DEV).transpose(1, 2), gl.to(DEV)).cpu()
+    assert torch.equal(api[:130], y[:130])
+
+
+def test_grouped_matmul_moe_shape_sampled_rows(cabi):
+    """Expert count, hidden size and routing skew of the MoE benchmark at a reduced row
+    count and N; all rows are checked."""
+    w = wl.grouped_matmul_inputs(rows=1536, k=4096, n=1024, experts=8, seed=11)
+    want = oracle.grouped_matmul(w["x"], w["w_storage"].transpose(1, 2), w["group_list"])
+    close(run_grouped_matmul(cabi, w["x"], w["w_storage"], w["group_list"]), want)

@@ -58,3 +58,20 @@ extern "C" int b200ops_print_info(int device_id, char* buf, size_t buf_len) {
   }
   return B200OPS_OK;
 }
+
+namespace b200ops {
+namespace gmm { int status_take(); }
+namespace pa { int fast_path_status_take(); }
+}  // namespace b200ops
+
+// Codes 1-9 come from grouped_matmul's pipeline, 11-19 from paged_attention's TMA path.
+extern "C" int b200ops_pipeline_status(int* status) {
+  using namespace b200ops;
+  B200OPS_REQUIRE(status != nullptr, "pipeline_status: null pointer");
+  B200OPS_CUDA(cudaDeviceSynchronize());
+  const int g = gmm::status_take();
+  const int p = pa::fast_path_status_take();
+  if (g < 0 || p < 0) return fail(B200OPS_ECUDA, "pipeline_status: could not read the status words");
+  *status = g != 0 ? g : p;
+  return B200OPS_OK;
+}

@@ -332,16 +332,17 @@ extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_
   return B200OPS_OK;
 }
 
-extern "C" int b200ops_pipeline_status(int* status) {
-  using namespace b200ops;
-  B200OPS_REQUIRE(status != nullptr, "pipeline_status: null pointer");
-  B200OPS_CUDA(cudaDeviceSynchronize());
+namespace b200ops {
+namespace gmm {
+// Reads and clears this translation unit's status word (the device must be idle).
+int status_take() {
   int v = 0;
-  B200OPS_CUDA(cudaMemcpyFromSymbol(&v, gmm::g_pipeline_status, sizeof(int)));
+  if (cudaMemcpyFromSymbol(&v, g_pipeline_status, sizeof(int)) != cudaSuccess) return -1;
   if (v != 0) {
     const int zero = 0;
-    B200OPS_CUDA(cudaMemcpyToSymbol(gmm::g_pipeline_status, &zero, sizeof(int)));
+    cudaMemcpyToSymbol(g_pipeline_status, &zero, sizeof(int));
   }
-  *status = v;
-  return B200OPS_OK;
+  return v;
 }
+}  // namespace gmm
+}  // namespace b200ops

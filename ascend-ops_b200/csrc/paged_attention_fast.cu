@@ -1,6 +1,417 @@
-// Placeholder translation unit: the TMA/mma fast path is not wired yet.
+// Paged-attention decode, fast path for sm_100a: [pages, P, Hkv, 128] caches, P % 64 == 0,
+// GQA group <= 16.
+//
+// One CTA = one (sequence, kv head, context chunk).  A producer warp walks the chunk's pages
+// through the block table and streams 64-token K and V tiles into a ring of 128B-swizzled
+// shared-memory stages with TMA (cp.async.bulk.tensor.4d over the cache viewed as
+// [pages][P][Hkv][D]; two 64-wide boxes per tile and tensor).  Four consumer warps each own
+// 16 tokens of every tile: S = Q.K^T and O += P.V run on warp-level tensor-core MMAs
+// (m16n8k16, query heads padded to the 16-row operand, fp32 accumulation), the online
+// softmax is fp32 with exp2 and scale*log2(e) folded in.  Every K/V byte crosses HBM -> smem
+// once and is shared by all query heads of the group; the kernel is HBM-bound (about 28
+// flop per KV byte at group 7).  Warps merge their (max, sum, O) through shared memory and
+// the CTA writes either the final fp16 rows (single-chunk sequence) or a partial record.
+//
+// Cache bytes past a sequence's length are never trusted: scores of such tokens are
+// replaced by -inf and their V rows are zeroed in shared memory before the PV product, so
+// uninitialised cache memory (NaN patterns) cannot leak into the output.
 #include "paged_attention.cuh"
-namespace b200ops { namespace pa {
-bool fast_path_supported(const Args&) { return false; }
-int launch_fast(const Args&, cudaStream_t) { return fail(B200OPS_EUNSUPPORTED, "paged_attention: fast path not built"); }
-}}
+#include "sm100_ptx.cuh"
+#include "tma_host.cuh"
+
+#include <cstdlib>
+
+namespace b200ops {
+namespace pa {
+namespace {
+
+constexpr int kD = 128;
+constexpr int kTile = 64;             // tokens per pipeline stage
+constexpr int kConsumerWarps = 4;     // each owns 16 tokens of a tile
+constexpr int kThreads = (kConsumerWarps + 1) * 32;
+constexpr int kSubTileBytes = kTile * 128;        // 64 tokens x 64 halfs
+constexpr int kTensorTileBytes = 2 * kSubTileBytes;  // both halves of D
+constexpr int kStageBytes = 2 * kTensorTileBytes;    // K and V
+constexpr int kMaxPagesPerChunk = 64;
+constexpr int kErrProducerWait = 11;
+constexpr int kErrConsumerWait = 12;
+
+template <int kStages>
+struct Smem {
+  static constexpr size_t kTiles = static_cast<size_t>(kStages) * kStageBytes;
+  static constexpr size_t kMerge = static_cast<size_t>(kConsumerWarps) * 16 * (kD + 2) * 4;
+  static constexpr size_t kData = kTiles > kMerge ? kTiles : kMerge;
+  static constexpr size_t kBytes = 1024 + kData + 2 * kStages * 8 + kMaxPagesPerChunk * 4 + 16;
+};
+
+__device__ int g_pa_status = 0;
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
+                                          uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// Byte offset of 16-byte chunk `c` (0..7) of row `r` inside a 128B-swizzled sub-tile.
+__device__ __forceinline__ uint32_t swz(int r, int c) {
+  return static_cast<uint32_t>(r * 128 + ((c ^ (r & 7)) << 4));
+}
+
+// kUpper: the GQA group has more than 8 query heads, so MMA rows 8..15 carry data.
+template <int kStages, bool kUpper>
+__global__ void __launch_bounds__(kThreads)
+paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
+                            const __grid_constant__ CUtensorMap map_v, Args a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + Smem<kStages>::kData);
+  uint64_t* empty = full + kStages;
+  int* page_ids = reinterpret_cast<int*>(empty + kStages);
+  int* abort_flag = page_ids + kMaxPagesPerChunk;
+
+  const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int group = a.num_heads / a.num_kv_heads;
+  const int h0 = kvh * group;
+
+  int L = a.context_lens[b];
+  const int cap = a.max_pages_per_seq * a.page_size;
+  if (L > cap) L = cap;
+  if (L <= 0) {
+    if (chunk == 0)
+      for (int i = threadIdx.x; i < group * kD; i += kThreads)
+        a.out[(static_cast<size_t>(b) * a.num_heads + h0) * kD + i] = __float2half(0.f);
+    return;
+  }
+  const int start = chunk * a.chunk_tokens;
+  if (start >= L) return;
+  const int end = min(L, start + a.chunk_tokens);
+  const int n_tiles = (end - start + kTile - 1) / kTile;
+  const int n_chunks = (L + a.chunk_tokens - 1) / a.chunk_tokens;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&empty[s], kConsumerWarps);
+    }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+
+  if (warp == kConsumerWarps) {
+    // ---------------- producer warp ----------------
+    const int first_page = start / a.page_size;
+    const int n_pages = (end - start + a.page_size - 1) / a.page_size;
+    const int32_t* table = a.block_tables + static_cast<size_t>(b) * a.max_pages_per_seq;
+    for (int i = lane; i < n_pages; i += 32) {
+      int pg = table[first_page + i];
+      pg = pg < 0 ? 0 : (pg >= a.num_pages ? a.num_pages - 1 : pg);
+      page_ids[i] = pg;
+    }
+    __syncwarp();
+    if (lane == 0) {
+      ptx::prefetch_tensormap(&map_k);
+      ptx::prefetch_tensormap(&map_v);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int t = 0; t < n_tiles; ++t) {
+        if (!ptx::mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
+          *abort_flag = 1;
+          atomicCAS(&g_pa_status, 0, kErrProducerWait);
+          break;
+        }
+        const int tok = t * kTile;  // relative to the chunk start (a page boundary)
+        const int pg = page_ids[tok / a.page_size];
+        const int off = tok % a.page_size;
+        uint8_t* st = smem + stage * kStageBytes;
+        ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
+        ptx::tma_load_4d(st, &map_k, &full[stage], 0, kvh, off, pg);
+        ptx::tma_load_4d(st + kSubTileBytes, &map_k, &full[stage], 64, kvh, off, pg);
+        ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, kvh, off, pg);
+        ptx::tma_load_4d(st + kTensorTileBytes + kSubTileBytes, &map_v, &full[stage], 64, kvh, off, pg);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else {
+    // ---------------- consumer warps ----------------
+    const int g = lane >> 2, t4 = lane & 3;
+    // Q fragments (A operand, 16 heads x 16 channels per k-step), loaded once.
+    uint32_t qa[kD / 16][4];
+    {
+      const __half* qb = a.q + (static_cast<size_t>(b) * a.num_heads + h0) * kD;
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ++ks) {
+        const int c = ks * 16 + 2 * t4;
+        qa[ks][0] = (g < group) ? *reinterpret_cast<const uint32_t*>(qb + g * kD + c) : 0u;
+        qa[ks][2] = (g < group) ? *reinterpret_cast<const uint32_t*>(qb + g * kD + c + 8) : 0u;
+        if (kUpper) {
+          qa[ks][1] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * kD + c) : 0u;
+          qa[ks][3] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * kD + c + 8) : 0u;
+        } else {
+          qa[ks][1] = 0u;
+          qa[ks][3] = 0u;
+        }
+      }
+    }
+    float o[kD / 8][4];
+#pragma unroll
+    for (int i = 0; i < kD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+    int stage = 0;
+    uint32_t phase = 0;
+    const int row0 = warp * 16;  // this warp's token rows inside a tile
+    // ldmatrix row/chunk selectors of this lane
+    const int k_row = row0 + ((lane >> 4) << 3) + (lane & 7);  // K: matrices 2,3 are tokens +8
+    const int k_csel = (lane >> 3) & 1;                        //    matrices 1,3 are chunk +1
+    const int v_row = row0 + (((lane >> 3) & 1) << 3) + (lane & 7);  // V: matrices 1,3 tokens +8
+    const int v_csel = lane >> 4;                                    //    matrices 2,3 chunk +1
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      if (!ptx::mbar_wait(&full[stage], phase, abort_flag)) {
+        *abort_flag = 1;
+        atomicCAS(&g_pa_status, 0, kErrConsumerWait);
+        ok = false;
+        break;
+      }
+      const uint32_t kbase = ptx::smem_u32(smem + stage * kStageBytes);
+      const uint32_t vbase = kbase + kTensorTileBytes;
+      const int tok0 = start + t * kTile + row0;  // first token of this warp's slice
+      const bool tail = tok0 + 16 > end;          // warp-uniform
+      if (tail) {
+        // Zero the V rows of tokens past the end so that 0 * garbage cannot become NaN.
+        uint8_t* vt = smem + stage * kStageBytes + kTensorTileBytes;
+        for (int i = lane; i < 16 * 16; i += 32) {
+          const int r = row0 + (i >> 4), c = i & 15;
+          if (start + t * kTile + r >= end)
+            *reinterpret_cast<uint4*>(vt + (c >> 3) * kSubTileBytes + r * 128 + ((c & 7) << 4)) =
+                make_uint4(0, 0, 0, 0);
+        }
+        __syncwarp();
+      }
+
+      // ---- S = Q . K^T for 16 tokens (two n-blocks of 8) ----
+      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+      for (int ks = 0; ks < kD / 16; ++ks) {
+        uint32_t kb[4];
+        const int chunk_in_sub = (ks & 3) * 2 + k_csel;
+        ldmatrix_x4(kb, kbase + (ks >> 2) * kSubTileBytes + swz(k_row, chunk_in_sub));
+        mma_16816(s[0], qa[ks], kb[0], kb[1]);
+        mma_16816(s[1], qa[ks], kb[2], kb[3]);
+      }
+      // ---- online softmax (rows g and g+8; columns 2*t4, 2*t4+1 of each n-block) ----
+#pragma unroll
+      for (int nb = 0; nb < 2; ++nb) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int tok = tok0 + nb * 8 + 2 * t4 + (j & 1);
+          s[nb][j] = (!tail || tok < end) ? s[nb][j] * a.scale_log2 : -INFINITY;
+        }
+      }
+      uint32_t pa_frag[4];
+      {
+        float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_lo, mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(m_lo - m_use);
+        const float p0 = exp2f(s[0][0] - m_use), p1 = exp2f(s[0][1] - m_use);
+        const float p2 = exp2f(s[1][0] - m_use), p3 = exp2f(s[1][1] - m_use);
+        l_lo = l_lo * alpha + (p0 + p1 + p2 + p3);
+        m_lo = m_new;
+        pa_frag[0] = f2_to_h2(p0, p1);
+        pa_frag[2] = f2_to_h2(p2, p3);
+#pragma unroll
+        for (int i = 0; i < kD / 8; ++i) {
+          o[i][0] *= alpha;
+          o[i][1] *= alpha;
+        }
+      }
+      if (kUpper) {
+        float mx = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_hi, mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = exp2f(m_hi - m_use);
+        const float p0 = exp2f(s[0][2] - m_use), p1 = exp2f(s[0][3] - m_use);
+        const float p2 = exp2f(s[1][2] - m_use), p3 = exp2f(s[1][3] - m_use);
+        l_hi = l_hi * alpha + (p0 + p1 + p2 + p3);
+        m_hi = m_new;
+        pa_frag[1] = f2_to_h2(p0, p1);
+        pa_frag[3] = f2_to_h2(p2, p3);
+#pragma unroll
+        for (int i = 0; i < kD / 8; ++i) {
+          o[i][2] *= alpha;
+          o[i][3] *= alpha;
+        }
+      } else {
+        pa_frag[1] = 0u;
+        pa_frag[3] = 0u;
+      }
+      // ---- O += P . V (16 tokens x 128 channels) ----
+#pragma unroll
+      for (int cc = 0; cc < kD / 8; cc += 2) {
+        uint32_t vb[4];
+        const int c = cc + v_csel;
+        ldmatrix_x4_trans(vb, vbase + (c >> 3) * kSubTileBytes + swz(v_row, c & 7));
+        mma_16816(o[cc], pa_frag, vb[0], vb[1]);
+        mma_16816(o[cc + 1], pa_frag, vb[2], vb[3]);
+      }
+      if (tail) ptx::fence_proxy_async();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(&empty[stage]);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+    (void)ok;
+    // Row sums were kept per thread; finish them across the quad.
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+
+    // All tiles of this CTA have landed and been read: reuse the stage memory for the merge.
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32));
+    float* rec = reinterpret_cast<float*>(smem) + static_cast<size_t>(warp) * 16 * (kD + 2);
+#pragma unroll
+    for (int i = 0; i < kD / 8; ++i) {
+      const int d = i * 8 + 2 * t4;
+      *reinterpret_cast<float2*>(rec + g * (kD + 2) + d) = make_float2(o[i][0], o[i][1]);
+      if (kUpper)
+        *reinterpret_cast<float2*>(rec + (g + 8) * (kD + 2) + d) = make_float2(o[i][2], o[i][3]);
+    }
+    if (t4 == 0) {
+      rec[g * (kD + 2) + kD] = m_lo;
+      rec[g * (kD + 2) + kD + 1] = l_lo;
+      if (kUpper) {
+        rec[(g + 8) * (kD + 2) + kD] = m_hi;
+        rec[(g + 8) * (kD + 2) + kD + 1] = l_hi;
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32));
+    const float* all = reinterpret_cast<const float*>(smem);
+    for (int idx = threadIdx.x; idx < group * kD; idx += kConsumerWarps * 32) {
+      const int r = idx >> 7, d = idx & (kD - 1);
+      float mm = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w)
+        mm = fmaxf(mm, all[(w * 16 + r) * (kD + 2) + kD]);
+      float acc = 0.f, ll = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumerWarps; ++w) {
+        const float* rr = all + (w * 16 + r) * (kD + 2);
+        const float f = (rr[kD] == -INFINITY) ? 0.f : exp2f(rr[kD] - mm);
+        acc += rr[d] * f;
+        ll += rr[kD + 1] * f;
+      }
+      const int h = h0 + r;
+      if (n_chunks == 1) {
+        a.out[(static_cast<size_t>(b) * a.num_heads + h) * kD + d] =
+            __float2half(ll > 0.f ? acc / ll : 0.f);
+      } else {
+        float* pr = a.partials +
+                    ((static_cast<size_t>(b) * a.num_heads + h) * a.max_chunks + chunk) * (kD + 2);
+        pr[d] = acc;
+        if (d == 0) {
+          pr[kD] = mm;
+          pr[kD + 1] = ll;
+        }
+      }
+    }
+  }
+}
+
+int env_int(const char* name, int fallback) {
+  const char* s = std::getenv(name);
+  return (s && *s) ? std::atoi(s) : fallback;
+}
+
+template <int kStages>
+int launch_with_stages(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid,
+                       cudaStream_t st) {
+  const bool upper = a.num_heads / a.num_kv_heads > 8;
+  auto kern = upper ? paged_attention_fast_kernel<kStages, true>
+                    : paged_attention_fast_kernel<kStages, false>;
+  static bool attr_set[2][64] = {{false}};
+  int dev = 0;
+  B200OPS_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[upper][dev]) {
+    B200OPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(Smem<kStages>::kBytes)));
+    attr_set[upper][dev] = true;
+  }
+  kern<<<grid, kThreads, Smem<kStages>::kBytes, st>>>(mk, mv, a);
+  B200OPS_LAUNCH_CHECK("paged_attention");
+  return B200OPS_OK;
+}
+
+}  // namespace
+
+bool fast_path_supported(const Args& a) {
+  if (env_int("B200OPS_PA_FORCE_GENERAL", 0)) return false;
+  const int group = a.num_heads / a.num_kv_heads;
+  return a.layout == B200OPS_KV_LAYOUT_NHD && a.head_dim == kD && a.page_size % kTile == 0 &&
+         group <= 16 && a.chunk_tokens % a.page_size == 0 &&
+         a.chunk_tokens / a.page_size <= kMaxPagesPerChunk && a.page_size <= 256 * kTile;
+}
+
+int launch_fast(const Args& a, cudaStream_t st) {
+  CUtensorMap mk, mv;
+  const uint64_t dims[4] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(a.num_kv_heads),
+                            static_cast<uint64_t>(a.page_size), static_cast<uint64_t>(a.num_pages)};
+  const uint64_t strides[3] = {static_cast<uint64_t>(kD) * 2,
+                               static_cast<uint64_t>(a.num_kv_heads) * kD * 2,
+                               static_cast<uint64_t>(a.page_size) * a.num_kv_heads * kD * 2};
+  const uint32_t box[4] = {64, 1, kTile, 1};
+  int rc = encode_f16_map(&mk, a.k_cache, 4, dims, strides, box, "paged_attention(key_cache)");
+  if (rc != B200OPS_OK) return rc;
+  rc = encode_f16_map(&mv, a.v_cache, 4, dims, strides, box, "paged_attention(value_cache)");
+  if (rc != B200OPS_OK) return rc;
+  const dim3 grid(a.max_chunks, a.num_kv_heads, a.bs);
+  B200OPS_REQUIRE(grid.y <= 65535 && grid.z <= 65535,
+                  "paged_attention: batch or head count too large for one launch");
+  switch (env_int("B200OPS_PA_STAGES", 3)) {
+    case 2: return launch_with_stages<2>(mk, mv, a, grid, st);
+    case 4: return launch_with_stages<4>(mk, mv, a, grid, st);
+    case 6: return launch_with_stages<6>(mk, mv, a, grid, st);
+    default: return launch_with_stages<3>(mk, mv, a, grid, st);
+  }
+}
+
+int fast_path_status_take() {
+  int v = 0;
+  if (cudaMemcpyFromSymbol(&v, g_pa_status, sizeof(int)) != cudaSuccess) return -1;
+  if (v != 0) {
+    const int zero = 0;
+    cudaMemcpyToSymbol(g_pa_status, &zero, sizeof(int));
+  }
+  return v;
+}
+
+}  // namespace pa
+}  // namespace b200ops

@@ -331,3 +331,30 @@ def test_grouped_matmul_moe_shape_sampled_rows(cabi):
     w = wl.grouped_matmul_inputs(rows=1536, k=4096, n=1024, experts=8, seed=11)
     want = oracle.grouped_matmul(w["x"], w["w_storage"].transpose(1, 2), w["group_list"])
     close(run_grouped_matmul(cabi, w["x"], w["w_storage"], w["group_list"]), want)
+
+
+def test_paged_attention_benchmark_size_fast_path_vs_general_and_oracle(cabi, monkeypatch):
+    """Full benchmark batch (64 sequences, lengths U[512, 8192], 8192 pages): the TMA/tensor-core
+    path, the general path and the CPU oracle must agree."""
+    w = wl.paged_attention_inputs()
+    fast = run_paged_attention(cabi, w)
+    monkeypatch.setenv("B200OPS_PA_FORCE_GENERAL", "1")
+    general = run_paged_attention(cabi, w)
+    monkeypatch.delenv("B200OPS_PA_FORCE_GENERAL")
+    close(fast, general)
+    want = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
+                                  w["context_lens"])
+    close(fast, want)
+
+
+@pytest.mark.parametrize("stages", ["2", "4", "6"])
+@pytest.mark.parametrize("chunk", ["128", "2048"])
+def test_paged_attention_fast_path_pipeline_depths(cabi, monkeypatch, stages, chunk):
+    monkeypatch.setenv("B200OPS_PA_STAGES", stages)
+    monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", chunk)
+    lens = [1, 63, 64, 65, 127, 128, 129, 1000, 4097, 0, 2048]
+    w = wl.paged_attention_inputs(heads=32, kv_heads=4, context_lens=lens, blocks=80, seed=int(stages))
+    w = poison_unused(w)
+    want = oracle.paged_attention(w["q"], w["key_cache_clean"], w["value_cache_clean"],
+                                  w["block_tables"], w["context_lens"])
+    close(run_paged_attention(cabi, w), want)

@@ -39,6 +39,7 @@ SIGNATURES = {
     "b200ops_paged_attention_workspace_size": (c_size_t, [c_int64] * 6),
     "b200ops_paged_attention": (c_int, [c_void_p] * 6 + [c_int64] * 7 + [c_int, c_void_p,
                                                                          c_size_t, c_void_p]),
+    "b200ops_paged_attention_static": (c_int, [c_void_p] * 6 + [c_int64] * 7 + [c_int, c_void_p]),
     "b200ops_grouped_matmul_workspace_size": (c_size_t, [c_int64] * 4),
     "b200ops_grouped_matmul": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p, c_size_t,
                                                                         c_void_p]),
@@ -130,6 +131,16 @@ def paged_attention(q, key_cache, value_cache, block_tables, context_lens, out, 
                                          q.shape[0], q.shape[1], num_kv_heads, q.shape[2],
                                          key_cache.shape[0], page_size, block_tables.shape[1],
                                          layout, _ptr(workspace), ws_size, _stream(stream)))
+
+
+def paged_attention_static(q, key_cache, value_cache, block_tables, context_lens, out, num_kv_heads,
+                           page_size, layout, stream=None):
+    """Same as paged_attention, with the scratch inside the library (nothing is allocated)."""
+    check(load().b200ops_paged_attention_static(_ptr(q), _ptr(key_cache), _ptr(value_cache),
+                                                _ptr(block_tables), _ptr(context_lens), _ptr(out),
+                                                q.shape[0], q.shape[1], num_kv_heads, q.shape[2],
+                                                key_cache.shape[0], page_size,
+                                                block_tables.shape[1], layout, _stream(stream)))
 
 
 def grouped_matmul(x, w_storage, group_list, y, stream=None):

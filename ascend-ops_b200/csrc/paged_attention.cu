@@ -354,3 +354,70 @@ extern "C" int b200ops_paged_attention(const void* q, const void* key_cache,
   if (rc != B200OPS_OK) return rc;
   return pa::launch_combine(a, st);
 }
+
+// ---------------------------------------------------------------------------------------
+// Decode attention for hosts that cannot allocate device memory.
+//
+// Some embedders hand every byte of HBM to their own arena at start-up (a serving engine
+// that sizes its KV cache to "whatever is left after the weights"), or forbid cudaMalloc on
+// the request path because it synchronises the device and may fail once memory is
+// exhausted.  Such a host has nowhere to get the split-context scratch that
+// b200ops_paged_attention() asks for.  This entry point takes the same inputs and outputs
+// but keeps the scratch in an array that is part of the library image itself.
+namespace b200ops {
+namespace pa {
+namespace {
+
+constexpr size_t kStaticScratchBytes = B200OPS_PAGED_ATTENTION_STATIC_SCRATCH_BYTES;
+
+// Lives in every CUDA context that loads this library, from load until the process exits.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// `g_static_scratch` named in host code is only the host-side handle of the symbol, never
+// a device address; the address on the current device comes from the runtime, once.
+int static_scratch_address(void** out) {
+  static void* address[64] = {nullptr};
+  int dev = -1;
+  B200OPS_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(B200OPS_EUNSUPPORTED, "paged_attention_static: device index %d", dev);
+  if (address[dev] == nullptr) {
+    void* p = nullptr;
+    B200OPS_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    if (p == nullptr) return fail(B200OPS_ECUDA, "paged_attention_static: scratch symbol has no device address");
+    address[dev] = p;
+  }
+  *out = address[dev];
+  return B200OPS_OK;
+}
+
+}  // namespace
+}  // namespace pa
+}  // namespace b200ops
+
+extern "C" int b200ops_paged_attention_static(const void* q, const void* key_cache,
+                                              const void* value_cache, const int32_t* block_tables,
+                                              const int32_t* context_lens, void* out, int64_t bs,
+                                              int64_t num_heads, int64_t num_kv_heads,
+                                              int64_t head_dim, int64_t num_pages,
+                                              int64_t page_size, int64_t max_pages_per_seq,
+                                              int layout, void* stream) {
+  using namespace b200ops;
+  const size_t need = b200ops_paged_attention_workspace_size(bs, num_heads, num_kv_heads, head_dim,
+                                                             page_size, max_pages_per_seq);
+  if (need > pa::kStaticScratchBytes)
+    return fail(B200OPS_EWORKSPACE,
+                "paged_attention_static: this shape needs %zu bytes of scratch but the built-in "
+                "array holds %zu; use b200ops_paged_attention with a caller-owned workspace",
+                need, pa::kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (need > 0) {
+    const int rc = pa::static_scratch_address(&scratch);
+    if (rc != B200OPS_OK) return rc;
+  }
+  // The partial records are fully written by the attention kernel before the combine
+  // kernel reads them, so nothing in the array has to start at zero.
+  return b200ops_paged_attention(q, key_cache, value_cache, block_tables, context_lens, out, bs,
+                                 num_heads, num_kv_heads, head_dim, num_pages, page_size,
+                                 max_pages_per_seq, layout, scratch, need > 0 ? pa::kStaticScratchBytes : 0,
+                                 stream);
+}

@@ -130,6 +130,29 @@ int b200ops_paged_attention(const void* q, const void* key_cache, const void* va
                             size_t workspace_size, void* stream);
 
 /*
+ * Decode attention that allocates nothing (no counterpart in the reference).
+ *
+ * For hosts that cannot obtain device memory at call time: an engine that has already
+ * handed all free HBM to its own arena, or a request path on which cudaMalloc is banned
+ * because it synchronises the device and can fail.  Same arguments as
+ * b200ops_paged_attention() without the workspace: the split-context scratch is a fixed
+ * array of B200OPS_PAGED_ATTENTION_STATIC_SCRATCH_BYTES inside the library image, present
+ * on every GPU that loads the library until the process exits.  Shapes whose
+ * b200ops_paged_attention_workspace_size() exceeds that return B200OPS_EWORKSPACE.
+ * The first call on each device looks up the array's device address (with that device
+ * current); make that first call before starting any stream capture.  All calls share the
+ * one array, which keeps whatever the previous call left in it: two calls whose kernels
+ * overlap on the GPU (different streams, no ordering) race on it -- order them on one
+ * stream or with events.  Calls no cudaMalloc/cudaFree and no allocating library routine.
+ */
+#define B200OPS_PAGED_ATTENTION_STATIC_SCRATCH_BYTES (32u << 20)
+int b200ops_paged_attention_static(const void* q, const void* key_cache, const void* value_cache,
+                                   const int32_t* block_tables, const int32_t* context_lens,
+                                   void* out, int64_t bs, int64_t num_heads, int64_t num_kv_heads,
+                                   int64_t head_dim, int64_t num_pages, int64_t page_size,
+                                   int64_t max_pages_per_seq, int layout, void* stream);
+
+/*
  * Grouped (per-expert) NT GEMM: y[gl[e-1]:gl[e], :] = x[gl[e-1]:gl[e], :] @ w[e]  (gl[-1] = 0).
  * Replaces aclnnGroupedMatMulExGetWorkspaceSize / aclnnGroupedMatMulEx
  * (csrc/ffi/ops.cpp:211,216; kernel csrc/opdev/op_kernel/grouped_mat_mul_ex.cpp:5-45 and

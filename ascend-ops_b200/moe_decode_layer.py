@@ -1,0 +1,206 @@
+"""One MoE decoder layer, decode step, composed from the `ascend910a_extras.ops` operators.
+
+Operator order follows the decoder layer the reference assembles in its graph builder
+(csrc/ffi/graph.cpp:145-283: norm+residual -> QKV linear -> split -> rope -> reshape_and_cache
+-> paged attention -> output linear -> norm+residual -> MLP), with the dense MLP replaced by
+a top-2-of-E routed expert MLP (grouped_matmul gate_up -> swiglu -> grouped_matmul down) and
+without Qwen3's per-head q/k norms:
+
+    add_rms_norm -> QKV GEMM -> rope -> reshape_and_cache -> paged_attention -> o_proj
+    -> add_rms_norm -> router top-k -> [dispatch] grouped_matmul -> swiglu -> grouped_matmul
+    [combine] -> weighted sum
+
+The dense projections run on the same tcgen05 grouped GEMM with a single group (an NT GEMM,
+like the reference's legacy `matmul`, _csrc/kernels/matmul.cpp:3-28).  Router softmax/top-k,
+the token permutation and the weighted sum are small torch index ops.  Sequences (and their
+KV pages) are sharded over ranks with no collective; only the expert MLP exchanges rows
+(moe_parallel.py).
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import torch
+
+import moe_parallel
+
+
+@dataclass
+class LayerConfig:
+    hidden: int = 4096
+    heads: int = 32
+    kv_heads: int = 8
+    head_dim: int = 128
+    intermediate: int = 14336
+    experts: int = 8
+    top_k: int = 2
+    rope_theta: float = 1e6
+    eps: float = 1e-6
+    block_size: int = 128
+
+
+def make_weights(cfg: LayerConfig, seed=7, experts=None, std=0.02, device="cpu"):
+    """Random-init fp16 weights ~ N(0, std); norm weights ~ N(1, 0.1).  All matrices are
+    stored [out, in] (K contiguous), the layout the grouped GEMM reads.  `experts` selects
+    which expert matrices to materialise (all by default; a rank's own under EP).  Each
+    expert draws from its own seeded stream, so a rank that holds a subset sees the same
+    values as a rank that holds all.  `device` chooses where the numbers are drawn (CPU for
+    parity tests, the GPU for full-size benchmark weights)."""
+    def gen(s):
+        return torch.Generator(device=device).manual_seed(s)
+
+    def mat(n, k, g):
+        return (std * torch.randn(n, k, generator=g, device=device)).half()
+
+    g = gen(seed)
+    qkv_out = (cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim
+    w = {
+        "ln1": (1 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).half(),
+        "ln2": (1 + 0.1 * torch.randn(cfg.hidden, generator=g, device=device)).half(),
+        "wqkv": mat(qkv_out, cfg.hidden, g),
+        "wo": mat(cfg.hidden, cfg.heads * cfg.head_dim, g),
+        "wrouter": mat(cfg.experts, cfg.hidden, g),
+    }
+    keep = list(range(cfg.experts)) if experts is None else [int(e) for e in experts]
+    gu = torch.empty(len(keep), 2 * cfg.intermediate, cfg.hidden, dtype=torch.float16, device=device)
+    dn = torch.empty(len(keep), cfg.hidden, cfg.intermediate, dtype=torch.float16, device=device)
+    for i, e in enumerate(keep):
+        ge = gen(seed * 1000 + e)
+        gu[i] = mat(2 * cfg.intermediate, cfg.hidden, ge)
+        dn[i] = mat(cfg.hidden, cfg.intermediate, ge)
+    w["w_gate_up"], w["w_down"], w["experts"] = gu, dn, keep
+    return w
+
+
+def route(logits: torch.Tensor, top_k: int):
+    """softmax over experts in fp32, then top-k (weights not renormalised)."""
+    p = torch.softmax(logits.float(), dim=-1)
+    wts, ids = torch.topk(p, top_k, dim=-1)
+    return ids, wts
+
+
+class MoEDecodeLayer:
+    """Device-resident weights + the decode-step forward.  `ops` is ascend910a_extras.ops."""
+
+    def __init__(self, cfg: LayerConfig, weights: dict, device, ops, group=None):
+        self.cfg, self.ops, self.device, self.group = cfg, ops, device, group
+        d = lambda t: t.to(device)
+        self.ln1, self.ln2 = d(weights["ln1"]), d(weights["ln2"])
+        # NT-GEMM weights as single-group stacks [1, N, K]; the op takes the [1, K, N] view.
+        self.wqkv = d(weights["wqkv"])[None].transpose(1, 2)
+        self.wo = d(weights["wo"])[None].transpose(1, 2)
+        router = torch.zeros(64, cfg.hidden, dtype=torch.float16, device=device)  # N % 64 == 0
+        router[: cfg.experts] = d(weights["wrouter"])
+        self.wrouter = router[None].transpose(1, 2)
+        self.w_gate_up = d(weights["w_gate_up"]).transpose(1, 2)
+        self.w_down = d(weights["w_down"]).transpose(1, 2)
+        max_pos = 16385
+        inv_freq = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2).float() / cfg.head_dim))
+        freqs = torch.einsum("i,j->ij", torch.arange(max_pos, dtype=torch.float), inv_freq)
+        self.cos, self.sin = d(freqs.cos().half().contiguous()), d(freqs.sin().half().contiguous())
+        self._one_group = {}
+
+    def _dense(self, x, w):
+        """x [T, K] @ w^T as a one-group grouped GEMM."""
+        t = x.shape[0]
+        gl = self._one_group.get(t)
+        if gl is None:
+            gl = torch.tensor([t], dtype=torch.int64, device=self.device)
+            self._one_group[t] = gl
+        return self.ops.grouped_matmul(x, w, gl)
+
+    def _local_mlp(self, rows, group_list):
+        if rows.shape[0] == 0:
+            return rows.new_zeros(0, self.cfg.hidden)
+        gu = self.ops.grouped_matmul(rows, self.w_gate_up, group_list)
+        act = self.ops.swiglu(gu)
+        return self.ops.grouped_matmul(act, self.w_down, group_list)
+
+    def forward(self, x, residual, positions, slots, block_tables, context_lens, k_cache, v_cache,
+                return_routing=False, attention_events=None):
+        """`attention_events`, if given, is a pair of CUDA events recorded right before and
+        after the attention operator on the current stream (used by the benchmark to time the
+        dominant kernel inside the step)."""
+        cfg, ops = self.cfg, self.ops
+        t = x.shape[0]
+        h1, res1 = ops.add_rms_norm(x, residual, self.ln1, cfg.eps)
+        qkv = self._dense(h1, self.wqkv)
+        nq, nkv = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
+        q = qkv[:, :nq].contiguous().view(t, cfg.heads, cfg.head_dim)
+        k = qkv[:, nq:nq + nkv].contiguous().view(t, cfg.kv_heads, cfg.head_dim)
+        v = qkv[:, nq + nkv:].contiguous().view(t, cfg.kv_heads, cfg.head_dim)
+        q, k = ops.rope(q, k, positions, self.cos, self.sin)
+        ops.reshape_and_cache(k, v, k_cache, v_cache, slots)
+        if attention_events is not None:
+            attention_events[0].record()
+        attn = ops.paged_attention(q, k_cache, v_cache, block_tables, context_lens)
+        if attention_events is not None:
+            attention_events[1].record()
+        o = self._dense(attn.view(t, nq), self.wo)
+        h2, res2 = ops.add_rms_norm(o, res1, self.ln2, cfg.eps)
+        logits = self._dense(h2, self.wrouter)[:, : cfg.experts]
+        ids, wts = route(logits, cfg.top_k)
+        y = moe_parallel.expert_parallel_mlp(h2, ids, wts, cfg.experts, self._local_mlp, self.group)
+        if return_routing:
+            return y, res2, ids, wts
+        return y, res2
+
+    # number of this library's kernels one forward launches (for the benchmark's accounting):
+    # 2 add_rms_norm, 3 dense GEMMs, rope, reshape_and_cache, attention + combine,
+    # 2 grouped GEMMs, swiglu
+    KERNEL_LAUNCHES = 12
+
+
+def draw_positions(batch=256, min_pos=1024, max_pos=16384, seed=8):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(min_pos, max_pos + 1, (batch,), generator=g, dtype=torch.int32)
+
+
+def make_decode_batch(cfg: LayerConfig, batch=256, min_pos=1024, max_pos=16384, seed=8,
+                      spare_blocks=8, positions=None):
+    """Decode-step inputs: hidden states ~ N(0,1), positions uniform in [min_pos, max_pos],
+    context_len = position + 1, distinct random physical blocks per sequence, the new token's
+    slot = its position inside its last block.  The KV cache itself (shape returned) is
+    filled on the device by the caller.  `positions` overrides the draw (a rank's share of a
+    global batch from draw_positions)."""
+    g = torch.Generator().manual_seed(seed)
+    if positions is not None:  # a rank's slice of a global batch
+        pos = torch.as_tensor(positions, dtype=torch.int32)
+        batch = pos.numel()
+    x = torch.randn(batch, cfg.hidden, generator=g).half()
+    residual = torch.randn(batch, cfg.hidden, generator=g).half()
+    if positions is None:
+        pos = torch.randint(min_pos, max_pos + 1, (batch,), generator=g, dtype=torch.int32)
+    lens = pos + 1
+    bs = cfg.block_size
+    pages = (lens.long() + bs - 1) // bs
+    total = int(pages.sum())
+    blocks = total + spare_blocks
+    ids = torch.randperm(blocks, generator=g)[:total].int()
+    max_pages = int(pages.max())
+    table = torch.zeros(batch, max_pages, dtype=torch.int32)
+    slots = torch.empty(batch, dtype=torch.int32)
+    o = 0
+    for b in range(batch):
+        n = int(pages[b])
+        table[b, :n] = ids[o:o + n]
+        o += n
+        slots[b] = int(table[b, int(pos[b]) // bs]) * bs + int(pos[b]) % bs
+    return {"x": x, "residual": residual, "positions": pos, "context_lens": lens.int(),
+            "block_tables": table, "slots": slots, "num_blocks": blocks,
+            "cache_shape": (blocks, bs, cfg.kv_heads, cfg.head_dim)}
+
+
+def layer_floor_bytes(cfg: LayerConfig, context_lens, experts_touched=None):
+    """HBM bytes one decode step cannot avoid: the KV of every context token and every
+    weight matrix once (activations are negligible)."""
+    kv = int(torch.as_tensor(context_lens).long().sum()) * cfg.kv_heads * cfg.head_dim * 2 * 2
+    dense = ((cfg.heads + 2 * cfg.kv_heads) * cfg.head_dim * cfg.hidden + cfg.hidden * cfg.heads * cfg.head_dim) * 2
+    e = cfg.experts if experts_touched is None else experts_touched
+    experts = e * 3 * cfg.intermediate * cfg.hidden * 2
+    return kv, dense + experts
+
+
+def attention_scale(cfg):
+    return 1.0 / math.sqrt(cfg.head_dim)

@@ -1,0 +1,131 @@
+"""Expert-parallel token exchange for the MoE grouped GEMM (host-side index logic).
+
+The reference has no multi-device code; its grouped_matmul expects rows already sorted by
+expert with cumulative group ends (csrc/opdev/op_kernel/grouped_mat_mul_ex.cpp:29-38).
+Sharding that op over G GPUs therefore needs exactly one exchange before it (send each
+routed row to the rank that owns its expert) and one after it (send results back):
+
+    route (local)  ->  dispatch all-to-all  ->  local grouped GEMMs  ->  combine all-to-all
+                                                                     ->  weighted sum (local)
+
+Every function here works on index tensors only and runs on CPU (gloo) as well as CUDA
+(NCCL), which is how the world_size-2 tests exercise it without GPUs.  The exchange itself
+is `torch.distributed.all_to_all_single` with split sizes derived from one all-gather of
+the per-expert counts; payload rows land in local memory before any kernel reads them.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+
+def expert_owner(num_experts: int, world: int) -> torch.Tensor:
+    """Contiguous placement: expert e lives on rank e // ceil(E / world)."""
+    per = -(-num_experts // world)
+    return torch.arange(num_experts) // per
+
+
+def local_experts(num_experts: int, world: int, rank: int) -> torch.Tensor:
+    return torch.nonzero(expert_owner(num_experts, world) == rank).flatten()
+
+
+def sort_by_expert(expert_ids: torch.Tensor, num_experts: int):
+    """Routing on one rank: flat (token, k) slots sorted by expert, stable.
+
+    Returns (order, counts): `order[i]` = flat slot that supplies sorted row i (its token is
+    order[i] // top_k); counts[e] = rows routed to expert e.
+    """
+    flat = expert_ids.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=num_experts)
+    return order, counts
+
+
+@dataclass
+class ExchangePlan:
+    send_splits: list          # rows this rank sends to each rank (sorted-by-expert order)
+    recv_splits: list          # rows this rank receives from each rank
+    recv_to_grouped: torch.Tensor  # gather index: grouped row i comes from received row [i]
+    group_list: torch.Tensor   # int64 cumulative ends over this rank's experts
+    num_local_rows: int
+
+
+def make_exchange_plan(all_counts: torch.Tensor, rank: int, owner: torch.Tensor) -> ExchangePlan:
+    """all_counts[r, e] = rows rank r routes to expert e (identical on every rank).
+
+    Rows travel sorted by expert, and experts are placed contiguously, so the rows a rank
+    sends to one peer are a contiguous slice.  Received rows arrive ordered (source rank,
+    expert); the grouped GEMM wants (expert, source rank): `recv_to_grouped` is that
+    permutation.
+    """
+    world, num_experts = all_counts.shape
+    owner = owner.to(all_counts.device)
+    mine = torch.nonzero(owner == rank).flatten()
+    send_splits = [int(all_counts[rank, owner == r].sum()) for r in range(world)]
+    recv_mat = all_counts[:, mine]  # [world, local experts]
+    recv_splits = [int(v) for v in recv_mat.sum(1)]
+    # offset of block (source r, local expert j) in the receive buffer (source-major)
+    flat = recv_mat.reshape(-1)
+    starts = torch.cumsum(flat, 0) - flat
+    starts = starts.reshape(world, -1)
+    pieces = []
+    for j in range(mine.numel()):
+        for r in range(world):
+            n = int(recv_mat[r, j])
+            if n:
+                s = int(starts[r, j])
+                pieces.append(torch.arange(s, s + n, device=all_counts.device))
+    total = int(flat.sum())
+    recv_to_grouped = (torch.cat(pieces) if pieces else
+                       torch.zeros(0, dtype=torch.long, device=all_counts.device))
+    group_list = torch.cumsum(recv_mat.sum(0), 0).to(torch.int64)
+    return ExchangePlan(send_splits, recv_splits, recv_to_grouped, group_list, total)
+
+
+def gather_counts(counts: torch.Tensor, group=None) -> torch.Tensor:
+    """All-gather the per-expert counts of every rank -> [world, E]."""
+    world = dist.get_world_size(group)
+    out = torch.empty(world * counts.numel(), dtype=counts.dtype, device=counts.device)
+    dist.all_gather_into_tensor(out, counts.contiguous(), group=group)
+    return out.view(world, counts.numel())
+
+
+def exchange(rows: torch.Tensor, send_splits, recv_splits, group=None) -> torch.Tensor:
+    out = rows.new_empty((sum(recv_splits),) + tuple(rows.shape[1:]))
+    dist.all_to_all_single(out, rows.contiguous(), output_split_sizes=list(recv_splits),
+                           input_split_sizes=list(send_splits), group=group)
+    return out
+
+
+def expert_parallel_mlp(x, expert_ids, expert_weights, num_experts, local_mlp, group=None):
+    """Run the routed expert MLP for this rank's tokens with experts sharded over the group.
+
+    x [T, H]; expert_ids, expert_weights [T, top_k]; local_mlp(rows [R, H], group_list) ->
+    [R, H_out] applies this rank's experts to rows sorted by (local) expert.  Returns
+    y [T, H_out] = sum_k weight[t, k] * expert_{ids[t, k]}(x[t]).
+    With no process group (single GPU) the exchange steps vanish.
+    """
+    top_k = expert_ids.shape[1]
+    order, counts = sort_by_expert(expert_ids, num_experts)
+    tokens = order // top_k
+    rows = x.index_select(0, tokens)
+    distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    if not distributed:
+        out_rows = local_mlp(rows, torch.cumsum(counts, 0).to(torch.int64))
+    else:
+        rank, world = dist.get_rank(group), dist.get_world_size(group)
+        all_counts = gather_counts(counts, group).cpu()  # split sizes are host integers
+        plan = make_exchange_plan(all_counts, rank, expert_owner(num_experts, world))
+        recv = exchange(rows, plan.send_splits, plan.recv_splits, group)
+        idx = plan.recv_to_grouped.to(recv.device)
+        grouped = recv.index_select(0, idx)
+        res = local_mlp(grouped, plan.group_list.to(recv.device))
+        back = torch.empty_like(res)
+        back.index_copy_(0, idx, res)  # back to (source rank, expert) order
+        out_rows = exchange(back, plan.recv_splits, plan.send_splits, group)
+    w = expert_weights.reshape(-1).index_select(0, order).to(torch.float32)
+    y = torch.zeros(x.shape[0], out_rows.shape[1], dtype=torch.float32, device=x.device)
+    y.index_add_(0, tokens, out_rows.to(torch.float32) * w[:, None])
+    return y.to(x.dtype)

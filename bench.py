@@ -247,18 +247,128 @@ def op_record(name, shape, nbytes, us, peaks, bound, launches):
             "frac": round(gbs / peaks["hbm_gbs"], 4), "bound": bound, "launches": launches}
 
 
+# --------------------------------------------------------------------------- the layer step
+LAYER_WORKLOAD = ("MoE decoder layer, decode step: batch 256, hidden 4096, 32q/8kv heads, D 128, "
+                  "positions U[1024,16384], block 128, 8 experts top-2, intermediate 14336")
+
+
+def build_layer(ops, dev, rank, world, group):
+    """This rank's share of the layer: all dense weights, its experts, its sequences and
+    their KV pages (filled with N(0,1) on the device)."""
+    import moe_decode_layer as mdl
+    import moe_parallel
+
+    cfg = mdl.LayerConfig()
+    mine = moe_parallel.local_experts(cfg.experts, world, rank).tolist()
+    weights = mdl.make_weights(cfg, seed=7, experts=mine, device=dev)
+    layer = mdl.MoEDecodeLayer(cfg, weights, dev, ops, group)
+    pos = mdl.draw_positions(256)
+    per = 256 // world
+    batch = mdl.make_decode_batch(cfg, positions=pos[rank * per:(rank + 1) * per], seed=80 + rank)
+    g = torch.Generator(device=dev).manual_seed(90 + rank)
+    k_cache = torch.randn(batch["cache_shape"], generator=g, device=dev, dtype=torch.float16)
+    v_cache = torch.randn(batch["cache_shape"], generator=g, device=dev, dtype=torch.float16)
+    return cfg, layer, batch, k_cache, v_cache, int(pos.long().sum()) + 256
+
+
+def run_layer(ops, dev, rank, world, group, steps, warmup, peaks):
+    import moe_decode_layer as mdl
+
+    cfg, layer, batch, k_cache, v_cache, total_context = build_layer(ops, dev, rank, world, group)
+    names = ("x", "residual", "positions", "slots", "block_tables", "context_lens")
+    host = {n: batch[n].pin_memory() for n in names}
+    devt = {n: batch[n].to(dev) for n in names}
+    h2d = sum(host[n].numel() * host[n].element_size() for n in names)
+
+    def step(inp, events=None):
+        return layer.forward(inp["x"], inp["residual"], inp["positions"], inp["slots"],
+                             inp["block_tables"], inp["context_lens"], k_cache, v_cache,
+                             attention_events=events)
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            torch.distributed.barrier(group)
+            torch.cuda.synchronize(dev)
+
+    # ---- device-resident timing (`value`) ----
+    for _ in range(warmup):
+        step(devt)
+    sync_all()
+    ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for i in range(steps):
+        step(devt, ev[i])
+    t1.record()
+    sync_all()
+    total_ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
+    attn_us = statistics.mean(a.elapsed_time(b) for a, b in ev) * 1e3
+    if world > 1:
+        torch.distributed.all_reduce(total_ms, op=torch.distributed.ReduceOp.MAX, group=group)
+    layer_us = float(total_ms) * 1e3 / steps
+
+    # ---- end to end: host buffers in, result out, copies inside the timed region ----
+    out_host = torch.empty(batch["x"].shape, dtype=torch.float16).pin_memory()
+    res_host = torch.empty(batch["x"].shape, dtype=torch.float16).pin_memory()
+    d2h = 2 * out_host.numel() * 2
+
+    def e2e_step():
+        inp = {n: host[n].to(dev, non_blocking=True) for n in names}
+        y, res = step(inp)
+        out_host.copy_(y, non_blocking=True)
+        res_host.copy_(res, non_blocking=True)
+
+    for _ in range(warmup):
+        e2e_step()
+    sync_all()
+    t0.record()
+    for _ in range(steps):
+        e2e_step()
+    t1.record()
+    sync_all()
+    e2e_ms = torch.tensor([t0.elapsed_time(t1)], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(e2e_ms, op=torch.distributed.ReduceOp.MAX, group=group)
+    e2e_us = float(e2e_ms) * 1e3 / steps
+
+    local_ctx = int(batch["context_lens"].long().sum())
+    attn_bytes = wl.paged_attention_bytes(batch["context_lens"], cfg.kv_heads, cfg.head_dim, cfg.heads,
+                                          cfg.block_size)
+    gbs = attn_bytes / attn_us / 1e3
+    return {
+        "layer_us": layer_us, "e2e_us": e2e_us, "h2d": h2d, "d2h": d2h,
+        "attention": {"us": attn_us, "bytes": attn_bytes, "gbs": gbs, "local_context": local_ctx},
+        "launches": steps * layer.KERNEL_LAUNCHES, "total_context": total_context,
+    }
+
+
 # --------------------------------------------------------------------------- CPU baseline
-def cpu_paged_attention_sample(seqs=8):
-    """The oracle on the first `seqs` sequences of the benchmark's attention batch."""
+def cpu_layer_sample(seqs=32, repeats=1):
+    """The CPU oracle's layer on a bounded sample: the first `seqs` of the 256 sequences with
+    the full weights.  Returns (microseconds scaled to 256 sequences, seconds measured)."""
+    import moe_decode_layer as mdl
     from oracle import decode_ops_oracle as oracle
 
-    a = wl.paged_attention_inputs(bs=seqs, blocks=seqs * 64, seed=3)
     torch.set_num_threads(len(os.sched_getaffinity(0)))
-    t0 = time.perf_counter()
-    oracle.paged_attention(a["q"], a["key_cache"], a["value_cache"], a["block_tables"], a["context_lens"])
-    dt = time.perf_counter() - t0
-    nbytes = wl.paged_attention_bytes(a["context_lens"], 4, 128, 28, 128)
-    return nbytes / dt / 1e9, dt, seqs
+    cfg = mdl.LayerConfig()
+    w = mdl.make_weights(cfg, seed=7)
+    pos = mdl.draw_positions(256)[:seqs]
+    batch = mdl.make_decode_batch(cfg, positions=pos, seed=80)
+    block = torch.randn(64, *batch["cache_shape"][1:], generator=torch.Generator().manual_seed(1)).half()
+    reps = -(-batch["cache_shape"][0] // 64)
+    k_cache = block.repeat(reps, 1, 1, 1)[: batch["cache_shape"][0]].contiguous()
+    v_cache = k_cache.flip(0).contiguous()
+    cos, sin = oracle.cos_sin_cache(16385, cfg.head_dim, cfg.rope_theta)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        oracle.moe_decode_layer(w, batch, k_cache, v_cache, heads=cfg.heads, kv_heads=cfg.kv_heads,
+                                head_dim=cfg.head_dim, experts=cfg.experts, top_k=cfg.top_k, eps=cfg.eps,
+                                cos_cache=cos, sin_cache=sin)
+        times.append(time.perf_counter() - t0)
+    dt = statistics.median(times)
+    return dt * 1e6 * (256 / seqs), dt, seqs
 
 
 # --------------------------------------------------------------------------- main
@@ -268,7 +378,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--ops", default="all", help="comma list of per-op cases, or 'all' / 'none'")
+    ap.add_argument("--ops", default="auto",
+                    help="per-op cases: comma list, 'all', 'none', or 'auto' (all at 1 GPU, none otherwise)")
+    ap.add_argument("--no-layer", action="store_true", help="skip the layer step (per-op cases only)")
+    ap.add_argument("--cpu-seqs", type=int, default=32, help="sequences in the CPU-baseline sample")
     ns = ap.parse_args()
     ns.warmup = max(ns.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
@@ -276,20 +389,29 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     peaks = load_peaks()
     cores = len(os.sched_getaffinity(0))
+    base = {
+        "metric": "moe_decode_layer_latency", "unit": "us", "n_gpus": ns.gpus, "higher_is_better": False,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": LAYER_WORKLOAD, "parallelism": f"ep{ns.gpus}+batch-sharded attention",
+                   "l2": "inputs larger than L2 (the step streams GBs of KV cache and expert weights)"},
+    }
 
     if ns.impl == "reference":
+        # The reference's kernels need Ascend hardware and the CANN toolchain; what can run
+        # here is the CPU golden path, timed with every host thread on a bounded sample.
         if rank != 0:
             return
-        gbs, dt, seqs = cpu_paged_attention_sample(8)
-        print(json.dumps({
-            "impl": "reference", "metric": "paged_attention_hbm_gbs", "value": round(gbs, 3),
-            "unit": "GB/s", "n_gpus": ns.gpus, "steps": 1, "warmup": 0, "ms_per_step": round(dt * 1e3, 2),
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
-            "data": "synthetic", "config": {"workload": "paged_attention decode B=64 28q/4kv D=128 L~U[512,8192]"},
-            "cpu_baseline": {"value": round(gbs, 3), "unit": "GB/s", "cores": cores, "kind": "port",
-                             "sample": f"first {seqs} of 64 sequences, one pass"},
-            "e2e": {"value": round(gbs, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        }))
+        us, dt, seqs = cpu_layer_sample(ns.cpu_seqs, repeats=max(1, min(ns.steps, 3)))
+        line = dict(base)
+        line.update({
+            "impl": "reference", "value": round(us, 1), "steps": max(1, min(ns.steps, 3)), "warmup": 0,
+            "ms_per_step": round(us / 1e3, 3),
+            "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
+                             "sample": f"first {seqs} of 256 sequences with all weights; "
+                                       f"{dt:.2f} s per pass, scaled x{256 // seqs} to the full batch"},
+            "e2e": {"value": round(us, 1), "unit": "us", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        })
+        print(json.dumps(line))
         return
 
     import ascend910a_extras.ops as ops
@@ -297,13 +419,19 @@ def main():
     assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path"
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
+    group = None
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
+        group = dist.group.WORLD
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
+    layer = None if ns.no_layer else run_layer(ops, dev, rank, world, group, ns.steps, ns.warmup, peaks)
+    clocks = sampler.stop() if rank == 0 else None
+    torch.cuda.empty_cache()
+
     cases = {
         "add_rms_norm": case_add_rms_norm, "reshape_and_cache": case_reshape_and_cache,
         "reshape_and_cache_nz": lambda *a: case_reshape_and_cache(*a, layout=wl.KV_LAYOUT_NZ),
@@ -311,33 +439,45 @@ def main():
         "grouped_matmul_gate_up": lambda *a: case_grouped_matmul(*a, which="gate_up"),
         "grouped_matmul_down": lambda *a: case_grouped_matmul(*a, which="down"),
     }
-    want = list(cases) if ns.ops == "all" else [c for c in ns.ops.split(",") if c and c != "none"]
+    if ns.ops == "auto":
+        want = list(cases) if world == 1 else []
+    elif ns.ops == "all":
+        want = list(cases)
+    else:
+        want = [c for c in ns.ops.split(",") if c and c != "none"]
     per_op = []
-    for name in want:
-        rec = cases[name](ops, dev, ns.steps, ns.warmup, peaks)
-        per_op.append(rec)
-        torch.cuda.empty_cache()
-    clocks = sampler.stop() if rank == 0 else None
+    if rank == 0:
+        for name in want:
+            per_op.append(cases[name](ops, dev, max(5, ns.steps // 2), ns.warmup, peaks))
+            torch.cuda.empty_cache()
     if world > 1:
         torch.distributed.barrier()
         torch.distributed.destroy_process_group()
     if rank != 0:
         return
-    head = next((r for r in per_op if r["op"] == "paged_attention"), per_op[0] if per_op else None)
-    gbs_cpu, dt_cpu, seqs = cpu_paged_attention_sample(8)
-    line = {
-        "metric": "paged_attention_hbm_gbs", "value": head["achieved"] if head else None, "unit": "GB/s",
-        "n_gpus": ns.gpus, "steps": ns.steps, "warmup": ns.warmup,
-        "ms_per_step": round(head["us"] / 1e3, 4) if head else None, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": head["shape"] if head else None, "l2": "inputs larger than L2 or rotating buffer sets"},
-        "roofline": ({"bound": "hbm", "achieved": head["achieved"], "peak": head["peak"], "unit": "GB/s",
-                      "frac": head["frac"], "traffic": None, "peak_source": peaks["source"]} if head else None),
-        "cpu_baseline": {"value": round(gbs_cpu, 3), "unit": "GB/s", "cores": cores, "kind": "port",
-                         "sample": f"first {seqs} of 64 sequences, one pass ({dt_cpu:.1f} s)"},
-        "gpu_launches": sum(r["launches"] for r in per_op),
-        "clocks": clocks, "per_op": per_op,
-    }
+
+    line = dict(base)
+    line.update({"steps": ns.steps, "warmup": ns.warmup, "clocks": clocks, "per_op": per_op})
+    launches = sum(r["launches"] * max(5, ns.steps // 2) for r in per_op)
+    if layer is not None:
+        att = layer["attention"]
+        line.update({
+            "value": round(layer["layer_us"], 1), "ms_per_step": round(layer["layer_us"] / 1e3, 4),
+            "tokens_per_s": round(256 / layer["layer_us"] * 1e6, 1),
+            "e2e": {"value": round(layer["e2e_us"], 1), "unit": "us",
+                    "h2d_bytes_per_step": layer["h2d"], "d2h_bytes_per_step": layer["d2h"]},
+            "roofline": {"bound": "hbm", "kernel": "paged_attention (fast kernel + combine) inside the step",
+                         "achieved": round(att["gbs"], 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(att["gbs"] / peaks["hbm_gbs"], 4), "traffic": None,
+                         "us": round(att["us"], 1), "bytes": att["bytes"], "peak_source": peaks["source"]},
+        })
+        launches += layer["launches"]
+        if world == 1:
+            us, dt, seqs = cpu_layer_sample(ns.cpu_seqs)
+            line["cpu_baseline"] = {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
+                                    "sample": f"first {seqs} of 256 sequences with all weights; {dt:.2f} s, "
+                                              f"scaled x{256 // seqs} to the full batch"}
+    line["gpu_launches"] = launches
     print(json.dumps(line))
 
 

@@ -168,3 +168,49 @@ def paged_attention(q, key_cache, value_cache, block_tables, context_lens, layou
             p = torch.softmax(qh @ k.T * scale, dim=-1)
             out[b, h * group : (h + 1) * group] = (p @ v).to(q.dtype)
     return out
+
+
+def moe_decode_layer(w, batch, k_cache, v_cache, *, heads, kv_heads, head_dim, experts, top_k, eps,
+                     cos_cache, sin_cache, expert_ids=None, expert_weights=None):
+    """One MoE decoder layer (decode step) from the operator goldens above, in the operator
+    order of the reference's decoder layer (csrc/ffi/graph.cpp:145-283) with a routed expert
+    MLP in place of the dense one.  Dense projections use fp32 accumulation and one rounding,
+    like grouped_matmul.  `w` holds [out, in] matrices: wqkv, wo, wrouter, w_gate_up [E, 2I, H],
+    w_down [E, H, I], and the two norm weights.  The caches are updated in place.
+    If `expert_ids`/`expert_weights` are given they replace the oracle's own routing (used to
+    compare outputs when a near-tie in the router flips between fp16 implementations).
+    Returns (y, residual_out, ids, weights, stages) where `stages` keeps intermediates.
+    """
+    x, residual = batch["x"], batch["residual"]
+    t = x.shape[0]
+    lin = lambda a, m: (a.float() @ m.float().T).to(a.dtype)
+    h1, res1 = add_rms_norm(x, residual, w["ln1"], eps)
+    qkv = lin(h1, w["wqkv"])
+    nq, nkv = heads * head_dim, kv_heads * head_dim
+    q = qkv[:, :nq].reshape(t, heads, head_dim)
+    k = qkv[:, nq:nq + nkv].reshape(t, kv_heads, head_dim)
+    v = qkv[:, nq + nkv:].reshape(t, kv_heads, head_dim)
+    q, k = rope(q, k, batch["positions"], cos_cache, sin_cache)
+    reshape_and_cache(k, k_cache, batch["slots"], v, v_cache)
+    attn = paged_attention(q, k_cache, v_cache, batch["block_tables"], batch["context_lens"])
+    o = lin(attn.reshape(t, nq), w["wo"])
+    h2, res2 = add_rms_norm(o, res1, w["ln2"], eps)
+    logits = lin(h2, w["wrouter"])
+    p = torch.softmax(logits.float(), dim=-1)
+    own_w, own_ids = torch.topk(p, top_k, dim=-1)
+    ids = own_ids if expert_ids is None else expert_ids
+    wts = own_w if expert_weights is None else expert_weights
+    flat = ids.reshape(-1)
+    order = torch.argsort(flat, stable=True)
+    counts = torch.bincount(flat, minlength=experts)
+    tokens = order // top_k
+    rows = h2[tokens]
+    gl = counts.cumsum(0).to(torch.int64)
+    gu = grouped_matmul(rows, w["w_gate_up"].transpose(1, 2), gl)
+    act = swiglu(gu)
+    dn = grouped_matmul(act, w["w_down"].transpose(1, 2), gl)
+    y = torch.zeros(t, dn.shape[1], dtype=torch.float32)
+    y.index_add_(0, tokens, dn.float() * wts.reshape(-1)[order].float()[:, None])
+    stages = {"h1": h1, "qkv": qkv, "q_rot": q, "k_rot": k, "attn": attn, "o": o, "h2": h2,
+              "logits": logits, "own_ids": own_ids, "own_weights": own_w}
+    return y.to(x.dtype), res2, ids, wts, stages

@@ -1,0 +1,79 @@
+"""The MoE decoder layer (decode step) on the GPU against the CPU oracle's layer, stage by
+stage, at a reduced size; and the expert-parallel path on two GPUs when two are present."""
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+import moe_decode_layer as mdl
+from oracle import decode_ops_oracle as oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+REPO = Path(__file__).resolve().parent.parent
+
+
+def small_case(batch=12, seed=3):
+    cfg = mdl.LayerConfig(hidden=512, heads=8, kv_heads=2, head_dim=128, intermediate=256, experts=4)
+    w = mdl.make_weights(cfg, seed=seed, std=0.05)
+    b = mdl.make_decode_batch(cfg, batch=batch, min_pos=3, max_pos=900, seed=seed + 1)
+    g = torch.Generator().manual_seed(seed + 2)
+    kc = torch.randn(b["cache_shape"], generator=g).half()
+    vc = torch.randn(b["cache_shape"], generator=g).half()
+    return cfg, w, b, kc, vc
+
+
+def test_layer_matches_oracle_stage_by_stage(ops):
+    cfg, w, b, kc, vc = small_case()
+    layer = mdl.MoEDecodeLayer(cfg, w, DEV, ops)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    y, res, ids, wts = layer.forward(*(b[n].to(DEV) for n in ("x", "residual", "positions", "slots",
+                                                              "block_tables", "context_lens")),
+                                     kd, vd, return_routing=True)
+    torch.cuda.synchronize()
+    cos, sin = oracle.cos_sin_cache(16385, cfg.head_dim, cfg.rope_theta)
+    kw = dict(heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim, experts=cfg.experts,
+              top_k=cfg.top_k, eps=cfg.eps, cos_cache=cos, sin_cache=sin)
+    kc_o, vc_o = kc.clone(), vc.clone()
+    ey, eres, eids, ewts, st = oracle.moe_decode_layer(w, b, kc_o, vc_o, expert_ids=ids.cpu(),
+                                                       expert_weights=wts.cpu(), **kw)
+    # the scatter touched exactly the slots of the new tokens, with the rotated keys
+    slots = b["slots"].long()
+    flat_k = kd.cpu().view(-1, cfg.kv_heads, cfg.head_dim)
+    torch.testing.assert_close(flat_k[slots].float(), st["k_rot"].float(), rtol=1e-2, atol=2e-3)
+    untouched = torch.ones(flat_k.shape[0], dtype=torch.bool)
+    untouched[slots] = False
+    assert torch.equal(flat_k[untouched], kc.view(-1, cfg.kv_heads, cfg.head_dim)[untouched])
+    # routing agrees except where the router's top-2 is a near tie
+    same = (ids.cpu().sort(1).values == st["own_ids"].sort(1).values).all(1).float().mean()
+    assert same >= 0.9
+    torch.testing.assert_close(res.cpu().float(), eres.float(), rtol=1e-2, atol=2e-3)
+    torch.testing.assert_close(y.cpu().float(), ey.float(), rtol=2e-2, atol=3e-3)
+
+
+def test_layer_is_deterministic_and_cache_update_is_idempotent(ops):
+    cfg, w, b, kc, vc = small_case(batch=5, seed=11)
+    layer = mdl.MoEDecodeLayer(cfg, w, DEV, ops)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    args = [b[n].to(DEV) for n in ("x", "residual", "positions", "slots", "block_tables", "context_lens")]
+    y1, r1 = layer.forward(*args, kd, vd)
+    k_after = kd.clone()
+    y2, r2 = layer.forward(*args, kd, vd)
+    torch.cuda.synchronize()
+    assert torch.equal(y1, y2) and torch.equal(r1, r2) and torch.equal(k_after, kd)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_expert_parallel_two_gpus_matches_single_gpu(tmp_path):
+    """Two ranks, experts split 2+2, sequences split 6+6: each rank's output rows must equal
+    the single-GPU layer's rows for the same sequences."""
+    script = Path(__file__).with_name("ep_two_rank_check.py")
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29611", str(script)],
+                       env=env, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    assert "EP_CHECK_OK" in r.stdout

@@ -1,0 +1,365 @@
+// MoE routing glue for sm_100a: the steps on either side of grouped_matmul.
+//
+// The reference's grouped_matmul takes rows already sorted by expert plus cumulative group
+// ends (csrc/opdev/op_kernel/grouped_mat_mul_ex.cpp:29-38); producing that order, and
+// undoing it afterwards, is left to its caller (the companion vLLM plugin named in the
+// reference's README.md:3, not part of its tree).  These kernels are that caller's work,
+// written so that a decode step needs no host synchronisation:
+//
+//   moe_route_topk     logits = x . Wr^T (fp32 accumulate, rounded to fp16 like a GEMM output),
+//                      softmax in fp32, top-k experts and their probabilities per token
+//   moe_permute        stable counting sort of the (token, k) slots by expert: destination row
+//                      of every slot, per-expert counts, cumulative group ends.  With
+//                      `world` > 1 the destination is laid out as one fixed-capacity segment
+//                      per destination rank (experts placed contiguously on ranks), the form
+//                      an equal-split all-to-all sends
+//   moe_ep_plan        on the receiving rank: from every rank's counts, the map from grouped
+//                      (expert-major) rows to rows of the received segments, and the local
+//                      cumulative group ends
+//   moe_copy_rows      dst[di(i)] = src[si(i)] for i < n, the row gather/scatter all of the
+//                      above feed
+//   moe_finalize       y[t] = sum_k weight[t,k] * rows[pos[t,k]]  (fp32 accumulate, no atomics)
+//
+// All are bandwidth- or latency-trivial next to the GEMMs; the point is launch count (four
+// launches replace about twenty framework index kernels) and device-resident metadata.
+#include "common.cuh"
+
+namespace b200ops {
+namespace moe {
+namespace {
+
+constexpr int kRouteWarps = 4;
+constexpr int kMaxExperts = 256;
+constexpr int kMaxTopK = 8;
+
+// One warp per token.  The token's row is staged in shared memory once and reused for
+// every expert; lanes stride the hidden dimension with 128-bit loads.
+__global__ void __launch_bounds__(kRouteWarps * 32)
+route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, int32_t* __restrict__ ids,
+                  float* __restrict__ weights, int num_tokens, int hidden, int num_experts, int top_k) {
+  extern __shared__ uint4 smem_rows[];
+  __shared__ float logits_s[kRouteWarps][kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int token = blockIdx.x * kRouteWarps + warp;
+  if (token >= num_tokens) return;
+  const int vecs = hidden >> 3;
+  uint4* row = smem_rows + static_cast<size_t>(warp) * vecs;
+  const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(token) * hidden);
+  for (int v = lane; v < vecs; v += 32) row[v] = xr[v];
+  __syncwarp();
+  float* logits = logits_s[warp];
+  for (int e = 0; e < num_experts; ++e) {
+    const uint4* w = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * hidden);
+    float acc = 0.f;
+    for (int v = lane; v < vecs; v += 32) {
+      const uint4 a = row[v];
+      const uint4 b = __ldg(w + v);
+      const uint32_t* as = reinterpret_cast<const uint32_t*>(&a);
+      const uint32_t* bs = reinterpret_cast<const uint32_t*>(&b);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 fa = h2_to_f2(as[j]);
+        const float2 fb = h2_to_f2(bs[j]);
+        acc = fmaf(fa.x, fb.x, acc);
+        acc = fmaf(fa.y, fb.y, acc);
+      }
+    }
+    acc = warp_sum(acc);
+    if (lane == 0) logits[e] = __half2float(__float2half_rn(acc));
+  }
+  __syncwarp();
+  // softmax over experts in fp32
+  float mx = -INFINITY;
+  for (int e = lane; e < num_experts; e += 32) mx = fmaxf(mx, logits[e]);
+  mx = warp_max(mx);
+  float sum = 0.f;
+  for (int e = lane; e < num_experts; e += 32) sum += expf(logits[e] - mx);
+  sum = warp_sum(sum);
+  const float inv = 1.0f / sum;
+  __syncwarp();
+  for (int e = lane; e < num_experts; e += 32) logits[e] = expf(logits[e] - mx) * inv;
+  __syncwarp();
+  // top-k by repeated arg-max; ties go to the lower expert index
+  for (int k = 0; k < top_k; ++k) {
+    float best = -1.f;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < num_experts; e += 32) {
+      const float p = logits[e];
+      if (p > best) {
+        best = p;
+        best_e = e;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) {
+        best = ob;
+        best_e = oe;
+      }
+    }
+    if (lane == 0) {
+      ids[static_cast<size_t>(token) * top_k + k] = best_e;
+      weights[static_cast<size_t>(token) * top_k + k] = best;
+      logits[best_e] = -2.f;  // remove from the next round
+    }
+    __syncwarp();
+  }
+}
+
+// Single CTA.  Warps own contiguous slices of the flat slot array; a slot's rank inside its
+// expert is (slots of lower warps) + (earlier slots of this warp), so the order is the
+// stable sort order and does not depend on scheduling.
+constexpr int kPermuteThreads = 1024;
+constexpr int kPermuteWarps = kPermuteThreads / 32;
+
+__global__ void __launch_bounds__(kPermuteThreads)
+permute_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ pos, int32_t* __restrict__ counts,
+               int64_t* __restrict__ group_list, int num_slots, int num_experts, int experts_per_rank,
+               int segment_rows) {
+  extern __shared__ int hist[];  // [kPermuteWarps][num_experts], then base[num_experts]
+  int* base = hist + kPermuteWarps * num_experts;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int i = threadIdx.x; i < kPermuteWarps * num_experts; i += kPermuteThreads) hist[i] = 0;
+  __syncthreads();
+  const int per_warp = (num_slots + kPermuteWarps - 1) / kPermuteWarps;
+  const int lo = min(num_slots, warp * per_warp), hi = min(num_slots, lo + per_warp);
+  int* my = hist + warp * num_experts;
+  for (int s = lo + lane; s < hi; s += 32) {
+    const int e = ids[s];
+    if (e >= 0 && e < num_experts) atomicAdd(&my[e], 1);
+  }
+  __syncthreads();
+  // per expert: exclusive scan over warps; totals; segment bases
+  for (int e = threadIdx.x; e < num_experts; e += kPermuteThreads) {
+    int run = 0;
+    for (int w = 0; w < kPermuteWarps; ++w) {
+      const int c = hist[w * num_experts + e];
+      hist[w * num_experts + e] = run;
+      run += c;
+    }
+    base[e] = run;  // total of expert e for now
+    counts[e] = run;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    long long cum = 0;
+    int in_segment = 0;
+    for (int e = 0; e < num_experts; ++e) {
+      const int c = base[e];
+      if (e % experts_per_rank == 0) in_segment = 0;
+      base[e] = (e / experts_per_rank) * segment_rows + in_segment;
+      in_segment += c;
+      cum += c;
+      group_list[e] = cum;
+    }
+  }
+  __syncthreads();
+  for (int s0 = lo; s0 < hi; s0 += 32) {
+    const int s = s0 + lane;
+    const bool ok = s < hi;
+    int e = ok ? ids[s] : -1;
+    if (e < 0 || e >= num_experts) e = -1;
+    const unsigned peers = __match_any_sync(0xffffffffu, e);
+    const int before = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0) {
+      pos[s] = base[e] + my[e] + before;
+    } else if (ok) {
+      pos[s] = -1;
+    }
+    __syncwarp();
+    if (e >= 0 && before == 0) my[e] += __popc(peers);  // leader advances the warp's cursor
+    __syncwarp();
+  }
+}
+
+// Receiving side of the fixed-capacity exchange.  all_counts[r][e] = rows rank r routed to
+// expert e.  Rows from rank r arrive in segment r, sorted by (local) expert.  The grouped GEMM
+// wants expert-major order: map[d] = received row that supplies grouped row d.
+__global__ void __launch_bounds__(256)
+ep_plan_kernel(const int32_t* __restrict__ all_counts, int32_t* __restrict__ map,
+               int64_t* __restrict__ group_list, int32_t* __restrict__ total_rows, int world,
+               int num_experts, int first_expert, int local_experts, int segment_rows) {
+  __shared__ int dst_base[64 * 64];  // [local expert][source rank] start in grouped order
+  __shared__ int src_base[64 * 64];  // same block's start inside the received buffer
+  if (threadIdx.x == 0) {
+    int d = 0;
+    for (int j = 0; j < local_experts; ++j) {
+      for (int r = 0; r < world; ++r) {
+        dst_base[j * world + r] = d;
+        d += all_counts[r * num_experts + first_expert + j];
+      }
+      group_list[j] = d;
+    }
+    *total_rows = d;
+    for (int r = 0; r < world; ++r) {
+      int s = r * segment_rows;
+      for (int j = 0; j < local_experts; ++j) {
+        src_base[j * world + r] = s;
+        s += all_counts[r * num_experts + first_expert + j];
+      }
+    }
+  }
+  __syncthreads();
+  for (int blk = 0; blk < local_experts * world; ++blk) {
+    const int j = blk / world, r = blk - j * world;
+    const int n = all_counts[r * num_experts + first_expert + j];
+    for (int i = threadIdx.x; i < n; i += blockDim.x) map[dst_base[blk] + i] = src_base[blk] + i;
+  }
+}
+
+// dst[di] = src[si] for logical rows i < *n_valid (or n_max if n_valid is null), where
+//   si = src_index ? src_index[i] : i, divided by src_div (token = slot / top_k)
+//   di = dst_index ? dst_index[i] : i
+// Negative indices skip the row.  One CTA per row, 128-bit copies.
+__global__ void __launch_bounds__(128)
+copy_rows_kernel(__half* __restrict__ dst, const __half* __restrict__ src,
+                 const int32_t* __restrict__ dst_index, const int32_t* __restrict__ src_index,
+                 int src_div, const int32_t* __restrict__ n_valid, int row_vecs) {
+  const int i = blockIdx.x;
+  if (n_valid != nullptr && i >= *n_valid) return;
+  int si = src_index ? src_index[i] : i;
+  const int di = dst_index ? dst_index[i] : i;
+  if (si < 0 || di < 0) return;
+  si /= src_div;
+  const uint4* s = reinterpret_cast<const uint4*>(src) + static_cast<size_t>(si) * row_vecs;
+  uint4* d = reinterpret_cast<uint4*>(dst) + static_cast<size_t>(di) * row_vecs;
+  for (int v = threadIdx.x; v < row_vecs; v += blockDim.x) d[v] = s[v];
+}
+
+__global__ void __launch_bounds__(128)
+finalize_kernel(const __half* __restrict__ rows, const int32_t* __restrict__ pos,
+                const float* __restrict__ weights, __half* __restrict__ y, int top_k, int row_vecs) {
+  const int t = blockIdx.x;
+  for (int v = threadIdx.x; v < row_vecs; v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < top_k; ++k) {
+      const int p = pos[t * top_k + k];
+      if (p < 0) continue;
+      const float w = weights[t * top_k + k];
+      const uint4 r = reinterpret_cast<const uint4*>(rows)[static_cast<size_t>(p) * row_vecs + v];
+      const uint32_t* rs = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = h2_to_f2(rs[j]);
+        acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
+      }
+    }
+    uint4 o;
+    o.x = f2_to_h2(acc[0], acc[1]);
+    o.y = f2_to_h2(acc[2], acc[3]);
+    o.z = f2_to_h2(acc[4], acc[5]);
+    o.w = f2_to_h2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(y)[static_cast<size_t>(t) * row_vecs + v] = o;
+  }
+}
+
+}  // namespace
+}  // namespace moe
+}  // namespace b200ops
+
+using namespace b200ops;
+
+extern "C" int b200ops_moe_route_topk(const void* x, const void* router_weight, int32_t* expert_ids,
+                                      float* expert_weights, int64_t num_tokens, int64_t hidden,
+                                      int64_t num_experts, int64_t top_k, void* stream) {
+  B200OPS_REQUIRE(num_tokens >= 0 && hidden > 0 && hidden % 8 == 0, "moe_route_topk: bad shape [%lld, %lld]",
+                  (long long)num_tokens, (long long)hidden);
+  B200OPS_REQUIRE(num_experts >= 1 && num_experts <= moe::kMaxExperts, "moe_route_topk: 1..%d experts, got %lld",
+                  moe::kMaxExperts, (long long)num_experts);
+  B200OPS_REQUIRE(top_k >= 1 && top_k <= moe::kMaxTopK && top_k <= num_experts,
+                  "moe_route_topk: top_k must be in 1..min(%d, experts), got %lld", moe::kMaxTopK, (long long)top_k);
+  B200OPS_REQUIRE(hidden * 2 * moe::kRouteWarps <= 200 * 1024, "moe_route_topk: hidden size %lld too large",
+                  (long long)hidden);
+  if (num_tokens == 0) return B200OPS_OK;
+  B200OPS_REQUIRE(x && router_weight && expert_ids && expert_weights, "moe_route_topk: null pointer");
+  B200OPS_REQUIRE(aligned16(x) && aligned16(router_weight), "moe_route_topk: pointers must be 16-byte aligned");
+  const size_t smem = static_cast<size_t>(moe::kRouteWarps) * hidden * 2;
+  if (smem > 48 * 1024) {
+    static bool set[64] = {false};
+    int dev = 0;
+    B200OPS_CUDA(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && !set[dev]) {
+      B200OPS_CUDA(cudaFuncSetAttribute(moe::route_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        200 * 1024));
+      set[dev] = true;
+    }
+  }
+  const unsigned grid = static_cast<unsigned>((num_tokens + moe::kRouteWarps - 1) / moe::kRouteWarps);
+  moe::route_topk_kernel<<<grid, moe::kRouteWarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(x), static_cast<const __half*>(router_weight), expert_ids, expert_weights,
+      static_cast<int>(num_tokens), static_cast<int>(hidden), static_cast<int>(num_experts),
+      static_cast<int>(top_k));
+  B200OPS_LAUNCH_CHECK("moe_route_topk");
+  return B200OPS_OK;
+}
+
+extern "C" int b200ops_moe_permute(const int32_t* expert_ids, int32_t* slot_to_row, int32_t* counts,
+                                   int64_t* group_list, int64_t num_slots, int64_t num_experts,
+                                   int64_t world, int64_t segment_rows, void* stream) {
+  B200OPS_REQUIRE(num_slots >= 0 && num_slots < (1LL << 30), "moe_permute: bad slot count %lld", (long long)num_slots);
+  B200OPS_REQUIRE(num_experts >= 1 && num_experts <= moe::kMaxExperts, "moe_permute: 1..%d experts, got %lld",
+                  moe::kMaxExperts, (long long)num_experts);
+  B200OPS_REQUIRE(world >= 1 && num_experts % world == 0,
+                  "moe_permute: experts (%lld) must divide evenly over ranks (%lld)", (long long)num_experts,
+                  (long long)world);
+  B200OPS_REQUIRE(segment_rows >= num_slots || world == 1,
+                  "moe_permute: a rank's segment (%lld rows) must hold all %lld slots", (long long)segment_rows,
+                  (long long)num_slots);
+  B200OPS_REQUIRE(slot_to_row && counts && group_list && (expert_ids || num_slots == 0), "moe_permute: null pointer");
+  const size_t smem = (static_cast<size_t>(moe::kPermuteWarps) + 1) * num_experts * sizeof(int);
+  moe::permute_kernel<<<1, moe::kPermuteThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      expert_ids, slot_to_row, counts, group_list, static_cast<int>(num_slots), static_cast<int>(num_experts),
+      static_cast<int>(num_experts / world), static_cast<int>(world == 1 ? 0 : segment_rows));
+  B200OPS_LAUNCH_CHECK("moe_permute");
+  return B200OPS_OK;
+}
+
+extern "C" int b200ops_moe_ep_plan(const int32_t* all_counts, int32_t* grouped_to_received,
+                                   int64_t* group_list, int32_t* total_rows, int64_t world,
+                                   int64_t num_experts, int64_t rank, int64_t segment_rows, void* stream) {
+  B200OPS_REQUIRE(world >= 1 && world <= 64 && num_experts >= 1 && num_experts % world == 0 &&
+                      num_experts / world <= 64 && rank >= 0 && rank < world,
+                  "moe_ep_plan: bad geometry world=%lld experts=%lld rank=%lld", (long long)world,
+                  (long long)num_experts, (long long)rank);
+  B200OPS_REQUIRE(all_counts && grouped_to_received && group_list && total_rows, "moe_ep_plan: null pointer");
+  const int local = static_cast<int>(num_experts / world);
+  moe::ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      all_counts, grouped_to_received, group_list, total_rows, static_cast<int>(world),
+      static_cast<int>(num_experts), static_cast<int>(rank) * local, local, static_cast<int>(segment_rows));
+  B200OPS_LAUNCH_CHECK("moe_ep_plan");
+  return B200OPS_OK;
+}
+
+extern "C" int b200ops_moe_copy_rows(void* dst, const void* src, const int32_t* dst_index,
+                                     const int32_t* src_index, int64_t src_div, const int32_t* n_valid,
+                                     int64_t n_max, int64_t row_elems, void* stream) {
+  B200OPS_REQUIRE(n_max >= 0 && n_max < (1LL << 31) && row_elems > 0 && row_elems % 8 == 0 && src_div >= 1,
+                  "moe_copy_rows: bad shape n=%lld row=%lld div=%lld", (long long)n_max, (long long)row_elems,
+                  (long long)src_div);
+  if (n_max == 0) return B200OPS_OK;
+  B200OPS_REQUIRE(dst && src && aligned16(dst) && aligned16(src), "moe_copy_rows: null or misaligned pointer");
+  moe::copy_rows_kernel<<<static_cast<unsigned>(n_max), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__half*>(dst), static_cast<const __half*>(src), dst_index, src_index, static_cast<int>(src_div),
+      n_valid, static_cast<int>(row_elems / 8));
+  B200OPS_LAUNCH_CHECK("moe_copy_rows");
+  return B200OPS_OK;
+}
+
+extern "C" int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row, const float* expert_weights,
+                                    void* y, int64_t num_tokens, int64_t top_k, int64_t row_elems,
+                                    void* stream) {
+  B200OPS_REQUIRE(num_tokens >= 0 && num_tokens < (1LL << 31) && top_k >= 1 && row_elems > 0 && row_elems % 8 == 0,
+                  "moe_finalize: bad shape tokens=%lld top_k=%lld row=%lld", (long long)num_tokens,
+                  (long long)top_k, (long long)row_elems);
+  if (num_tokens == 0) return B200OPS_OK;
+  B200OPS_REQUIRE(rows && slot_to_row && expert_weights && y && aligned16(rows) && aligned16(y),
+                  "moe_finalize: null or misaligned pointer");
+  moe::finalize_kernel<<<static_cast<unsigned>(num_tokens), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(rows), slot_to_row, expert_weights, static_cast<__half*>(y),
+      static_cast<int>(top_k), static_cast<int>(row_elems / 8));
+  B200OPS_LAUNCH_CHECK("moe_finalize");
+  return B200OPS_OK;
+}

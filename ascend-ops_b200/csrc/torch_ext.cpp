@@ -292,6 +292,113 @@ int print_info(int device_id) {
   return 0;
 }
 
+// ---- MoE routing glue (no counterpart in the reference FFI; see include/b200ops.h) ----
+namespace {
+void check_i32_cuda(const at::Tensor& t, const char* op, const char* name) {
+  TORCH_CHECK(t.is_cuda() && t.scalar_type() == at::kInt && t.is_contiguous(), op, ": ", name,
+              " must be a contiguous CUDA int32 tensor");
+}
+}  // namespace
+
+std::tuple<at::Tensor, at::Tensor> moe_route_topk(at::Tensor x, at::Tensor router_weight, int64_t top_k) {
+  TORCH_CHECK(x.dim() == 2 && router_weight.dim() == 2 && x.size(1) == router_weight.size(1),
+              "moe_route_topk: x must be [T, H] and router_weight [E, H], got ", x.sizes(), " and ",
+              router_weight.sizes());
+  TORCH_CHECK(x.is_contiguous() && router_weight.is_contiguous(), "moe_route_topk: tensors must be contiguous");
+  check_f16_cuda(x, "moe_route_topk", "x");
+  check_f16_cuda(router_weight, "moe_route_topk", "router_weight");
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor ids = at::empty({x.size(0), top_k}, x.options().dtype(at::kInt));
+  at::Tensor wts = at::empty({x.size(0), top_k}, x.options().dtype(at::kFloat));
+  check_status(b200ops_moe_route_topk(x.data_ptr(), router_weight.data_ptr(), ids.data_ptr<int32_t>(),
+                                      wts.data_ptr<float>(), x.size(0), x.size(1), router_weight.size(0),
+                                      top_k, current_stream()),
+               "moe_route_topk");
+  return {ids, wts};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_permute(at::Tensor expert_ids, int64_t num_experts,
+                                                           int64_t world, int64_t segment_rows) {
+  check_i32_cuda(expert_ids, "moe_permute", "expert_ids");
+  const c10::cuda::CUDAGuard guard(expert_ids.device());
+  const int64_t slots = expert_ids.numel();
+  at::Tensor pos = at::empty({slots}, expert_ids.options());
+  at::Tensor counts = at::empty({num_experts}, expert_ids.options());
+  at::Tensor gl = at::empty({num_experts}, expert_ids.options().dtype(at::kLong));
+  check_status(b200ops_moe_permute(expert_ids.data_ptr<int32_t>(), pos.data_ptr<int32_t>(),
+                                   counts.data_ptr<int32_t>(), gl.data_ptr<int64_t>(), slots, num_experts,
+                                   world, segment_rows, current_stream()),
+               "moe_permute");
+  return {pos, counts, gl};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_ep_plan(at::Tensor all_counts, int64_t rank,
+                                                           int64_t segment_rows) {
+  check_i32_cuda(all_counts, "moe_ep_plan", "all_counts");
+  TORCH_CHECK(all_counts.dim() == 2, "moe_ep_plan: all_counts must be [world, experts]");
+  const c10::cuda::CUDAGuard guard(all_counts.device());
+  const int64_t world = all_counts.size(0), experts = all_counts.size(1);
+  at::Tensor map = at::empty({world * segment_rows}, all_counts.options());
+  at::Tensor gl = at::empty({experts / std::max<int64_t>(world, 1)}, all_counts.options().dtype(at::kLong));
+  at::Tensor total = at::empty({1}, all_counts.options());
+  check_status(b200ops_moe_ep_plan(all_counts.data_ptr<int32_t>(), map.data_ptr<int32_t>(),
+                                   gl.data_ptr<int64_t>(), total.data_ptr<int32_t>(), world, experts, rank,
+                                   segment_rows, current_stream()),
+               "moe_ep_plan");
+  return {map, gl, total};
+}
+
+void moe_copy_rows(at::Tensor dst, at::Tensor src, c10::optional<at::Tensor> dst_index,
+                   c10::optional<at::Tensor> src_index, int64_t src_div, c10::optional<at::Tensor> n_valid,
+                   int64_t n_max) {
+  TORCH_CHECK(dst.dim() == 2 && src.dim() == 2 && dst.size(1) == src.size(1) && dst.is_contiguous() &&
+                  src.is_contiguous(),
+              "moe_copy_rows: dst and src must be contiguous [rows, H] with the same H");
+  check_f16_cuda(dst, "moe_copy_rows", "dst");
+  check_f16_cuda(src, "moe_copy_rows", "src");
+  if (dst_index) check_i32_cuda(*dst_index, "moe_copy_rows", "dst_index");
+  if (src_index) check_i32_cuda(*src_index, "moe_copy_rows", "src_index");
+  if (n_valid) check_i32_cuda(*n_valid, "moe_copy_rows", "n_valid");
+  TORCH_CHECK((!dst_index || dst_index->numel() >= n_max) && (!src_index || src_index->numel() >= n_max),
+              "moe_copy_rows: index tensors shorter than n_max");
+  TORCH_CHECK((dst_index || n_max <= dst.size(0)) && (src_index || n_max <= src.size(0) * src_div),
+              "moe_copy_rows: n_max exceeds the tensor rows");
+  const c10::cuda::CUDAGuard guard(dst.device());
+  check_status(b200ops_moe_copy_rows(dst.data_ptr(), src.data_ptr(),
+                                     dst_index ? dst_index->data_ptr<int32_t>() : nullptr,
+                                     src_index ? src_index->data_ptr<int32_t>() : nullptr, src_div,
+                                     n_valid ? n_valid->data_ptr<int32_t>() : nullptr, n_max, dst.size(1),
+                                     current_stream()),
+               "moe_copy_rows");
+}
+
+at::Tensor moe_finalize(at::Tensor rows, at::Tensor slot_to_row, at::Tensor expert_weights) {
+  TORCH_CHECK(rows.dim() == 2 && rows.is_contiguous() && expert_weights.dim() == 2 &&
+                  expert_weights.is_contiguous() && slot_to_row.numel() == expert_weights.numel(),
+              "moe_finalize: rows [R, H], expert_weights [T, k], slot_to_row [T*k]");
+  check_f16_cuda(rows, "moe_finalize", "rows");
+  check_i32_cuda(slot_to_row, "moe_finalize", "slot_to_row");
+  TORCH_CHECK(expert_weights.is_cuda() && expert_weights.scalar_type() == at::kFloat,
+              "moe_finalize: expert_weights must be a CUDA float32 tensor");
+  const c10::cuda::CUDAGuard guard(rows.device());
+  at::Tensor y = at::empty({expert_weights.size(0), rows.size(1)}, rows.options());
+  check_status(b200ops_moe_finalize(rows.data_ptr(), slot_to_row.data_ptr<int32_t>(),
+                                    expert_weights.data_ptr<float>(), y.data_ptr(), expert_weights.size(0),
+                                    expert_weights.size(1), rows.size(1), current_stream()),
+               "moe_finalize");
+  return y;
+}
+
+void init_ffi_moe(py::module_&& m) {
+  m.def("route_topk", &moe_route_topk);
+  m.def("permute", &moe_permute);
+  m.def("ep_plan", &moe_ep_plan);
+  m.def("copy_rows", &moe_copy_rows, py::arg("dst"), py::arg("src"), py::arg("dst_index") = py::none(),
+        py::arg("src_index") = py::none(), py::arg("src_div") = 1, py::arg("n_valid") = py::none(),
+        py::arg("n_max") = 0);
+  m.def("finalize", &moe_finalize);
+}
+
 void init_ffi_ops(py::module_&& m) {
   m.def("rope", &rope, "Rope");
   m.def("swiglu", &swiglu, "Swiglu");
@@ -306,4 +413,5 @@ void init_ffi_ops(py::module_&& m) {
 PYBIND11_MODULE(ascend910a_extras_C, m) {
   m.def("print_info", &native::print_info, "Print info about the device");
   native::init_ffi_ops(m.def_submodule("ops"));
+  native::init_ffi_moe(m.def_submodule("moe"));
 }

@@ -11,8 +11,9 @@ without Qwen3's per-head q/k norms:
     [combine] -> weighted sum
 
 The dense projections run on the same tcgen05 grouped GEMM with a single group (an NT GEMM,
-like the reference's legacy `matmul`, _csrc/kernels/matmul.cpp:3-28).  Router softmax/top-k,
-the token permutation and the weighted sum are small torch index ops.  Sequences (and their
+like the reference's legacy `matmul`, _csrc/kernels/matmul.cpp:3-28).  Router top-k, the
+token permutation and the weighted sum are the library's MoE glue kernels
+(`ascend910a_extras.moe`).  Sequences (and their
 KV pages) are sharded over ranks with no collective; only the expert MLP exchanges rows
 (moe_parallel.py).
 """
@@ -83,16 +84,17 @@ def route(logits: torch.Tensor, top_k: int):
 class MoEDecodeLayer:
     """Device-resident weights + the decode-step forward.  `ops` is ascend910a_extras.ops."""
 
-    def __init__(self, cfg: LayerConfig, weights: dict, device, ops, group=None):
-        self.cfg, self.ops, self.device, self.group = cfg, ops, device, group
+    def __init__(self, cfg: LayerConfig, weights: dict, device, ops, group=None, segment_rows=None):
+        import ascend910a_extras.moe as moe
+
+        self.cfg, self.ops, self.device, self.group, self.moe = cfg, ops, device, group, moe
+        self.segment_rows = segment_rows  # rows each rank sends each peer under expert parallelism
         d = lambda t: t.to(device)
         self.ln1, self.ln2 = d(weights["ln1"]), d(weights["ln2"])
         # NT-GEMM weights as single-group stacks [1, N, K]; the op takes the [1, K, N] view.
         self.wqkv = d(weights["wqkv"])[None].transpose(1, 2)
         self.wo = d(weights["wo"])[None].transpose(1, 2)
-        router = torch.zeros(64, cfg.hidden, dtype=torch.float16, device=device)  # N % 64 == 0
-        router[: cfg.experts] = d(weights["wrouter"])
-        self.wrouter = router[None].transpose(1, 2)
+        self.wrouter = d(weights["wrouter"]).contiguous()
         self.w_gate_up = d(weights["w_gate_up"]).transpose(1, 2)
         self.w_down = d(weights["w_down"]).transpose(1, 2)
         max_pos = 16385
@@ -139,17 +141,19 @@ class MoEDecodeLayer:
             attention_events[1].record()
         o = self._dense(attn.view(t, nq), self.wo)
         h2, res2 = ops.add_rms_norm(o, res1, self.ln2, cfg.eps)
-        logits = self._dense(h2, self.wrouter)[:, : cfg.experts]
-        ids, wts = route(logits, cfg.top_k)
-        y = moe_parallel.expert_parallel_mlp(h2, ids, wts, cfg.experts, self._local_mlp, self.group)
+        ids, wts = self.moe.route_topk(h2, self.wrouter, cfg.top_k)
+        y = moe_parallel.expert_parallel_mlp_device(self.moe, h2, ids, wts, cfg.experts, self._local_mlp,
+                                                    self.group, self.segment_rows)
         if return_routing:
             return y, res2, ids, wts
         return y, res2
 
-    # number of this library's kernels one forward launches (for the benchmark's accounting):
-    # 2 add_rms_norm, 3 dense GEMMs, rope, reshape_and_cache, attention + combine,
-    # 2 grouped GEMMs, swiglu
-    KERNEL_LAUNCHES = 12
+    # number of this library's kernels one single-GPU forward launches (for the benchmark's
+    # accounting): 2 add_rms_norm, 2 dense GEMMs, rope, reshape_and_cache, attention + combine,
+    # route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Expert parallelism adds
+    # ep_plan and two more copy_rows.
+    KERNEL_LAUNCHES = 15
+    KERNEL_LAUNCHES_EP = 18
 
 
 def draw_positions(batch=256, min_pos=1024, max_pos=16384, seed=8):

@@ -129,3 +129,45 @@ def expert_parallel_mlp(x, expert_ids, expert_weights, num_experts, local_mlp, g
     y = torch.zeros(x.shape[0], out_rows.shape[1], dtype=torch.float32, device=x.device)
     y.index_add_(0, tokens, out_rows.to(torch.float32) * w[:, None])
     return y.to(x.dtype)
+
+
+def expert_parallel_mlp_device(moe, x, expert_ids, expert_weights, num_experts, local_mlp, group=None,
+                               segment_rows=None):
+    """Same contract as expert_parallel_mlp, built from the library's own glue kernels
+    (`ascend910a_extras.moe`) with every piece of metadata on the device: no host
+    synchronisation anywhere in the step.
+
+    expert_ids int32 [T, top_k], expert_weights float32 [T, top_k] (from moe.route_topk).
+    Across ranks the exchange is an equal-split all-to-all of fixed-capacity segments:
+    every rank sends `segment_rows` rows to every peer (default T*top_k, the most one peer
+    can be owed), of which only the leading rows are meaningful; the per-expert counts
+    travel in a small all-gather and stay on the device, where `moe.ep_plan` turns them into
+    the grouped order and the group ends grouped_matmul reads.  All ranks must pass the same
+    `segment_rows`.
+    """
+    t, top_k = expert_ids.shape
+    slots, hidden = t * top_k, x.shape[1]
+    distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    if not distributed:
+        pos, _, group_list = moe.permute(expert_ids, num_experts, 1, 0)
+        rows = x.new_empty(slots, hidden)
+        moe.copy_rows(rows, x, dst_index=pos, src_div=top_k, n_max=slots)
+        return moe.finalize(local_mlp(rows, group_list), pos, expert_weights)
+    rank, world = dist.get_rank(group), dist.get_world_size(group)
+    cap = slots if segment_rows is None else int(segment_rows)
+    pos, counts, _ = moe.permute(expert_ids, num_experts, world, cap)
+    send = x.new_empty(world * cap, hidden)
+    moe.copy_rows(send, x, dst_index=pos, src_div=top_k, n_max=slots)
+    all_counts = counts.new_empty(world * num_experts)
+    dist.all_gather_into_tensor(all_counts, counts, group=group)
+    recv = torch.empty_like(send)
+    dist.all_to_all_single(recv, send, group=group)
+    grouped_to_received, group_list, total = moe.ep_plan(all_counts.view(world, num_experts), rank, cap)
+    grouped = x.new_empty(world * cap, hidden)
+    moe.copy_rows(grouped, recv, src_index=grouped_to_received, n_valid=total, n_max=world * cap)
+    res = local_mlp(grouped, group_list)
+    back = res.new_empty(world * cap, res.shape[1])
+    moe.copy_rows(back, res, dst_index=grouped_to_received, n_valid=total, n_max=world * cap)
+    returned = torch.empty_like(back)
+    dist.all_to_all_single(returned, back, group=group)
+    return moe.finalize(returned, pos, expert_weights)

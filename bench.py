@@ -266,9 +266,9 @@ def build_layer(ops, dev, rank, world, group):
     cfg = mdl.LayerConfig()
     mine = moe_parallel.local_experts(cfg.experts, world, rank).tolist()
     weights = mdl.make_weights(cfg, seed=7, experts=mine, device=dev)
-    layer = mdl.MoEDecodeLayer(cfg, weights, dev, ops, group)
-    pos = mdl.draw_positions(256)
     per = 256 // world
+    layer = mdl.MoEDecodeLayer(cfg, weights, dev, ops, group, segment_rows=per * cfg.top_k)
+    pos = mdl.draw_positions(256)
     batch = mdl.make_decode_batch(cfg, positions=pos[rank * per:(rank + 1) * per], seed=80 + rank)
     g = torch.Generator(device=dev).manual_seed(90 + rank)
     k_cache = torch.randn(batch["cache_shape"], generator=g, device=dev, dtype=torch.float16)
@@ -344,7 +344,7 @@ def run_layer(ops, dev, rank, world, group, steps, warmup, peaks):
     return {
         "layer_us": layer_us, "e2e_us": e2e_us, "h2d": h2d, "d2h": d2h,
         "attention": {"us": attn_us, "bytes": attn_bytes, "gbs": gbs, "local_context": local_ctx},
-        "launches": steps * layer.KERNEL_LAUNCHES, "total_context": total_context,
+        "launches": steps * (layer.KERNEL_LAUNCHES if world == 1 else layer.KERNEL_LAUNCHES_EP), "total_context": total_context,
     }
 
 

@@ -171,6 +171,47 @@ int b200ops_grouped_matmul(const void* x, const void* w, const int64_t* group_li
                            void* workspace, size_t workspace_size, void* stream);
 
 /*
+ * MoE routing glue: the steps around grouped_matmul that the reference leaves to its caller
+ * (its grouped_matmul expects rows pre-sorted by expert and cumulative group ends,
+ * csrc/opdev/op_kernel/grouped_mat_mul_ex.cpp:29-38; the sorting lives in the companion
+ * plugin named in the reference's README.md:3).  None of these has a counterpart in the
+ * reference's FFI.  All metadata stays on the device, so a decode step needs no host sync.
+ *
+ * route_topk: logits = x . router_weight^T (fp32 accumulate, rounded to f16), softmax over
+ *   experts in fp32, the top_k experts per token (ties to the lower index) and their
+ *   probabilities.  x f16 [num_tokens, hidden]; router_weight f16 [num_experts, hidden];
+ *   expert_ids int32 [num_tokens, top_k]; expert_weights f32 [num_tokens, top_k].
+ * permute: stable counting sort of the num_slots = num_tokens*top_k routed slots by expert.
+ *   slot_to_row[s] = destination row of slot s; counts[e] = rows of expert e (int32);
+ *   group_list[e] = inclusive cumulative ends (int64), the form grouped_matmul takes.
+ *   world == 1: rows are packed expert-major from row 0.  world > 1 (experts placed
+ *   contiguously, num_experts/world per rank): rows for rank r start at r*segment_rows and are
+ *   packed by expert inside that segment -- the layout an equal-split all-to-all sends.
+ * ep_plan: on the receiving rank.  all_counts int32 [world, num_experts] (every rank's
+ *   `counts`, all-gathered).  grouped_to_received[d] = row of the received buffer
+ *   ([world segments of segment_rows]) that supplies grouped (expert-major) row d;
+ *   group_list int64 [num_experts/world] local cumulative ends; total_rows int32 [1].
+ * copy_rows: for i < *n_valid (n_max if n_valid is NULL):
+ *   dst[dst_index ? dst_index[i] : i] = src[(src_index ? src_index[i] : i) / src_div];
+ *   rows of row_elems f16; negative indices skip the row.
+ * finalize: y[t] = sum_k expert_weights[t,k] * rows[slot_to_row[t*top_k+k]], fp32 accumulate.
+ */
+int b200ops_moe_route_topk(const void* x, const void* router_weight, int32_t* expert_ids,
+                           float* expert_weights, int64_t num_tokens, int64_t hidden,
+                           int64_t num_experts, int64_t top_k, void* stream);
+int b200ops_moe_permute(const int32_t* expert_ids, int32_t* slot_to_row, int32_t* counts,
+                        int64_t* group_list, int64_t num_slots, int64_t num_experts, int64_t world,
+                        int64_t segment_rows, void* stream);
+int b200ops_moe_ep_plan(const int32_t* all_counts, int32_t* grouped_to_received, int64_t* group_list,
+                        int32_t* total_rows, int64_t world, int64_t num_experts, int64_t rank,
+                        int64_t segment_rows, void* stream);
+int b200ops_moe_copy_rows(void* dst, const void* src, const int32_t* dst_index, const int32_t* src_index,
+                          int64_t src_div, const int32_t* n_valid, int64_t n_max, int64_t row_elems,
+                          void* stream);
+int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row, const float* expert_weights,
+                         void* y, int64_t num_tokens, int64_t top_k, int64_t row_elems, void* stream);
+
+/*
  * Health word of the pipelined kernels (grouped_matmul, paged_attention's TMA path).  Their
  * producer/consumer waits are bounded; a wait that runs out ends the kernel and leaves a
  * non-zero code here.  This call synchronises the device, returns the code in *status

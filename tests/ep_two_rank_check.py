@@ -34,7 +34,7 @@ def main():
     h_y, h_res, ids, wts = None, None, None, None
     mine = moe_parallel.local_experts(cfg.experts, world, rank).tolist()
     part = mdl.make_weights(cfg, seed=3, std=0.05, experts=mine)
-    ep = mdl.MoEDecodeLayer(cfg, part, dev, ops, group=dist.group.WORLD)
+    ep = mdl.MoEDecodeLayer(cfg, part, dev, ops, group=dist.group.WORLD, segment_rows=per * cfg.top_k)
     y_ep, res_ep = ep.forward(*args, kc.to(dev), vc.to(dev))
     torch.cuda.synchronize()
     dist.barrier()

@@ -1,0 +1,135 @@
+"""MoE glue kernels through the C ABI against straightforward torch formulations."""
+import ctypes
+
+import pytest
+import torch
+
+import moe_parallel
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def p(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+@pytest.mark.parametrize("tokens,hidden,experts,top_k", [(256, 4096, 8, 2), (7, 512, 64, 4), (1, 64, 3, 1),
+                                                         (33, 1024, 256, 8)])
+def test_route_topk(cabi, tokens, hidden, experts, top_k):
+    g = torch.Generator().manual_seed(tokens + experts)
+    x = torch.randn(tokens, hidden, generator=g).half()
+    w = (torch.randn(experts, hidden, generator=g) * 0.05).half()
+    ids = torch.full((tokens, top_k), -1, dtype=torch.int32, device=DEV)
+    wts = torch.zeros(tokens, top_k, device=DEV)
+    xd, wd = x.to(DEV), w.to(DEV)
+    cabi.check(cabi.load().b200ops_moe_route_topk(p(xd), p(wd), p(ids), p(wts), tokens, hidden, experts, top_k,
+                                                  stream()))
+    torch.cuda.synchronize()
+    logits = (x.float() @ w.float().T).half().float()
+    prob = torch.softmax(logits, -1)
+    ew, ei = torch.topk(prob, top_k, -1)
+    got_w, got_i = wts.cpu(), ids.cpu().long()
+    torch.testing.assert_close(got_w, ew, rtol=2e-3, atol=1e-5)
+    # expert choices may differ only where two probabilities are within rounding of each other
+    differs = got_i != ei
+    if differs.any():
+        gap = (prob.gather(1, got_i) - prob.gather(1, ei)).abs()
+        assert float(gap[differs].max()) < 2e-3
+    assert (got_i.sort(1).values[:, 1:] != got_i.sort(1).values[:, :-1]).all() or top_k == 1
+
+
+@pytest.mark.parametrize("tokens,top_k,experts,world", [(256, 2, 8, 1), (256, 2, 8, 4), (1000, 4, 64, 8),
+                                                        (3, 1, 5, 1), (40000, 2, 16, 2)])
+def test_permute_is_the_stable_sort(cabi, tokens, top_k, experts, world):
+    g = torch.Generator().manual_seed(tokens)
+    ids = torch.randint(0, experts, (tokens, top_k), generator=g, dtype=torch.int32)
+    slots = tokens * top_k
+    cap = slots
+    idd = ids.to(DEV)
+    pos = torch.full((slots,), -5, dtype=torch.int32, device=DEV)
+    counts = torch.zeros(experts, dtype=torch.int32, device=DEV)
+    gl = torch.zeros(experts, dtype=torch.int64, device=DEV)
+    cabi.check(cabi.load().b200ops_moe_permute(p(idd), p(pos), p(counts), p(gl), slots, experts, world, cap,
+                                               stream()))
+    torch.cuda.synchronize()
+    flat = ids.reshape(-1).long()
+    want_counts = torch.bincount(flat, minlength=experts)
+    assert counts.cpu().tolist() == want_counts.tolist()
+    assert gl.cpu().tolist() == want_counts.cumsum(0).tolist()
+    order = torch.argsort(flat, stable=True)
+    want_pos = torch.empty(slots, dtype=torch.long)
+    if world == 1:
+        want_pos[order] = torch.arange(slots)
+    else:
+        per = experts // world
+        dest = flat[order] // per
+        start_of_dest = torch.zeros(world, dtype=torch.long)
+        cnt_dest = torch.bincount(dest, minlength=world)
+        start_sorted = torch.cumsum(cnt_dest, 0) - cnt_dest
+        want_pos[order] = dest * cap + (torch.arange(slots) - start_sorted[dest])
+    assert torch.equal(pos.cpu().long(), want_pos)
+
+
+@pytest.mark.parametrize("world,experts", [(2, 8), (8, 8), (4, 64)])
+def test_ep_plan_matches_host_plan(cabi, world, experts):
+    g = torch.Generator().manual_seed(world * experts)
+    cap = 64
+    all_counts = torch.randint(0, 9, (world, experts), generator=g, dtype=torch.int32)
+    all_counts[:, 1] = 0
+    local = experts // world
+    owner = moe_parallel.expert_owner(experts, world)
+    for rank in (0, world - 1):
+        host = moe_parallel.make_exchange_plan(all_counts.long(), rank, owner)
+        m = torch.full((world * cap,), -1, dtype=torch.int32, device=DEV)
+        gl = torch.zeros(local, dtype=torch.int64, device=DEV)
+        total = torch.zeros(1, dtype=torch.int32, device=DEV)
+        acd = all_counts.to(DEV)
+        cabi.check(cabi.load().b200ops_moe_ep_plan(p(acd), p(m), p(gl), p(total), world, experts, rank, cap,
+                                                   stream()))
+        torch.cuda.synchronize()
+        n = int(total)
+        assert n == host.num_local_rows and gl.cpu().tolist() == host.group_list.tolist()
+        # host plan indexes a densely packed receive buffer; the device plan indexes fixed segments
+        recv_counts = all_counts[:, rank * local:(rank + 1) * local].sum(1).long()
+        dense_start = torch.cumsum(recv_counts, 0) - recv_counts
+        src_rank = torch.bucketize(host.recv_to_grouped, torch.cumsum(recv_counts, 0), right=True)
+        want = src_rank * cap + (host.recv_to_grouped - dense_start[src_rank])
+        assert torch.equal(m[:n].cpu().long(), want)
+
+
+def test_copy_rows_and_finalize(cabi):
+    g = torch.Generator().manual_seed(9)
+    t, k, h = 50, 2, 256
+    x = torch.randn(t, h, generator=g).half().to(DEV)
+    ids = torch.randint(0, 4, (t, k), generator=g, dtype=torch.int32).to(DEV)
+    wts = torch.rand(t, k, generator=g).to(DEV)
+    lib = cabi.load()
+    pos = torch.empty(t * k, dtype=torch.int32, device=DEV)
+    counts = torch.empty(4, dtype=torch.int32, device=DEV)
+    gl = torch.empty(4, dtype=torch.int64, device=DEV)
+    cabi.check(lib.b200ops_moe_permute(p(ids), p(pos), p(counts), p(gl), t * k, 4, 1, 0, stream()))
+    rows = torch.zeros(t * k, h, dtype=torch.float16, device=DEV)
+    cabi.check(lib.b200ops_moe_copy_rows(p(rows), p(x), p(pos), None, k, None, t * k, h, stream()))
+    torch.cuda.synchronize()
+    want_rows = torch.empty_like(rows)
+    want_rows[pos.long()] = x.repeat_interleave(k, 0)
+    assert torch.equal(rows, want_rows)
+    # n_valid limits the copy; a negative index skips its row
+    idx = torch.arange(t * k, dtype=torch.int32, device=DEV)
+    idx[3] = -1
+    dst = torch.zeros_like(rows)
+    nvalid = torch.tensor([10], dtype=torch.int32, device=DEV)
+    cabi.check(lib.b200ops_moe_copy_rows(p(dst), p(rows), None, p(idx), 1, p(nvalid), t * k, h, stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(dst[:3], rows[:3]) and not dst[3].any() and torch.equal(dst[4:10], rows[4:10])
+    assert not dst[10:].any()
+    y = torch.empty(t, h, dtype=torch.float16, device=DEV)
+    cabi.check(lib.b200ops_moe_finalize(p(rows), p(pos), p(wts), p(y), t, k, h, stream()))
+    torch.cuda.synchronize()
+    want = (rows[pos.long()].float().view(t, k, h) * wts[:, :, None]).sum(1)
+    torch.testing.assert_close(y.float(), want, rtol=1e-2, atol=1e-3)

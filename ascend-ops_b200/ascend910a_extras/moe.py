@@ -1,4 +1,4 @@
-"""MoE routing glue around `ops.grouped_matmul`: router top-k, permutation by expert, the
+"""Decode-layer glue around the six operators: fused split+rope+cache, and MoE routing glue around `ops.grouped_matmul`: router top-k, permutation by expert, the
 plan of the expert-parallel exchange, row gather/scatter and the weighted recombination.
 
 The reference's operator API stops at grouped_matmul (rows must arrive sorted by expert,
@@ -13,3 +13,4 @@ permute = _C.moe.permute
 ep_plan = _C.moe.ep_plan
 copy_rows = _C.moe.copy_rows
 finalize = _C.moe.finalize
+fused_qkv_rope_cache = _C.moe.fused_qkv_rope_cache

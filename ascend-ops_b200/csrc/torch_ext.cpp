@@ -389,7 +389,44 @@ at::Tensor moe_finalize(at::Tensor rows, at::Tensor slot_to_row, at::Tensor expe
   return y;
 }
 
+// q_out = rope(q part of qkv); rope(k) and v go into the caches.  See b200ops_fused_qkv_rope_cache.
+at::Tensor fused_qkv_rope_cache(at::Tensor qkv, at::Tensor position_ids, at::Tensor cos_cache,
+                                at::Tensor sin_cache, at::Tensor slot_indices, at::Tensor key_cache,
+                                at::Tensor value_cache, int64_t num_heads, int64_t num_kv_heads) {
+  TORCH_CHECK(qkv.dim() == 2 && qkv.is_contiguous() && qkv.size(1) % (num_heads + 2 * num_kv_heads) == 0,
+              "fused_qkv_rope_cache: qkv must be contiguous [T, (Hq + 2*Hkv) * D], got ", qkv.sizes());
+  const int64_t head_dim = qkv.size(1) / (num_heads + 2 * num_kv_heads);
+  TORCH_CHECK(key_cache.dim() == 4 && key_cache.is_contiguous() && value_cache.is_contiguous() &&
+                  value_cache.sizes() == key_cache.sizes(),
+              "fused_qkv_rope_cache: caches must be contiguous 4D tensors of the same shape");
+  TORCH_CHECK(cos_cache.dim() == 2 && cos_cache.size(1) * 2 == head_dim && cos_cache.is_contiguous() &&
+                  sin_cache.is_contiguous() && sin_cache.sizes() == cos_cache.sizes(),
+              "fused_qkv_rope_cache: cos_cache and sin_cache must be [max_pos, head_dim/2]");
+  TORCH_CHECK(position_ids.numel() == qkv.size(0) && slot_indices.numel() == qkv.size(0),
+              "fused_qkv_rope_cache: one position and one slot per token");
+  check_f16_cuda(qkv, "fused_qkv_rope_cache", "qkv");
+  check_f16_cuda(key_cache, "fused_qkv_rope_cache", "key_cache");
+  check_f16_cuda(value_cache, "fused_qkv_rope_cache", "value_cache");
+  check_f16_cuda(cos_cache, "fused_qkv_rope_cache", "cos_cache");
+  check_f16_cuda(sin_cache, "fused_qkv_rope_cache", "sin_cache");
+  check_i32_cuda(position_ids, "fused_qkv_rope_cache", "position_ids");
+  check_i32_cuda(slot_indices, "fused_qkv_rope_cache", "slot_indices");
+  const int layout = cache_layout_for_key(key_cache, num_kv_heads, head_dim, "fused_qkv_rope_cache");
+  const int64_t dims[4] = {key_cache.size(0), key_cache.size(1), key_cache.size(2), key_cache.size(3)};
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  at::Tensor q_out = at::empty({qkv.size(0), num_heads, head_dim}, qkv.options());
+  check_status(b200ops_fused_qkv_rope_cache(qkv.data_ptr(), position_ids.data_ptr<int32_t>(),
+                                            cos_cache.data_ptr(), sin_cache.data_ptr(),
+                                            slot_indices.data_ptr<int32_t>(), q_out.data_ptr(),
+                                            key_cache.data_ptr(), value_cache.data_ptr(), qkv.size(0),
+                                            num_heads, num_kv_heads, head_dim, cos_cache.size(0), dims,
+                                            layout, current_stream()),
+               "fused_qkv_rope_cache");
+  return q_out;
+}
+
 void init_ffi_moe(py::module_&& m) {
+  m.def("fused_qkv_rope_cache", &fused_qkv_rope_cache);
   m.def("route_topk", &moe_route_topk);
   m.def("permute", &moe_permute);
   m.def("ep_plan", &moe_ep_plan);

@@ -89,6 +89,7 @@ class MoEDecodeLayer:
 
         self.cfg, self.ops, self.device, self.group, self.moe = cfg, ops, device, group, moe
         self.segment_rows = segment_rows  # rows each rank sends each peer under expert parallelism
+        self.fuse_rope_cache = True  # False: split + ops.rope + ops.reshape_and_cache separately
         d = lambda t: t.to(device)
         self.ln1, self.ln2 = d(weights["ln1"]), d(weights["ln2"])
         # NT-GEMM weights as single-group stacks [1, N, K]; the op takes the [1, K, N] view.
@@ -128,12 +129,17 @@ class MoEDecodeLayer:
         t = x.shape[0]
         h1, res1 = ops.add_rms_norm(x, residual, self.ln1, cfg.eps)
         qkv = self._dense(h1, self.wqkv)
-        nq, nkv = cfg.heads * cfg.head_dim, cfg.kv_heads * cfg.head_dim
-        q = qkv[:, :nq].contiguous().view(t, cfg.heads, cfg.head_dim)
-        k = qkv[:, nq:nq + nkv].contiguous().view(t, cfg.kv_heads, cfg.head_dim)
-        v = qkv[:, nq + nkv:].contiguous().view(t, cfg.kv_heads, cfg.head_dim)
-        q, k = ops.rope(q, k, positions, self.cos, self.sin)
-        ops.reshape_and_cache(k, v, k_cache, v_cache, slots)
+        nq = cfg.heads * cfg.head_dim
+        if self.fuse_rope_cache:
+            q = self.moe.fused_qkv_rope_cache(qkv, positions, self.cos, self.sin, slots, k_cache, v_cache,
+                                              cfg.heads, cfg.kv_heads)
+        else:
+            nkv = cfg.kv_heads * cfg.head_dim
+            q = qkv[:, :nq].contiguous().view(t, cfg.heads, cfg.head_dim)
+            k = qkv[:, nq:nq + nkv].contiguous().view(t, cfg.kv_heads, cfg.head_dim)
+            v = qkv[:, nq + nkv:].contiguous().view(t, cfg.kv_heads, cfg.head_dim)
+            q, k = ops.rope(q, k, positions, self.cos, self.sin)
+            ops.reshape_and_cache(k, v, k_cache, v_cache, slots)
         if attention_events is not None:
             attention_events[0].record()
         attn = ops.paged_attention(q, k_cache, v_cache, block_tables, context_lens)
@@ -149,11 +155,56 @@ class MoEDecodeLayer:
         return y, res2
 
     # number of this library's kernels one single-GPU forward launches (for the benchmark's
-    # accounting): 2 add_rms_norm, 2 dense GEMMs, rope, reshape_and_cache, attention + combine,
+    # accounting): 2 add_rms_norm, 2 dense GEMMs, fused rope+cache, attention + combine,
     # route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Expert parallelism adds
     # ep_plan and two more copy_rows.
-    KERNEL_LAUNCHES = 15
-    KERNEL_LAUNCHES_EP = 18
+    KERNEL_LAUNCHES = 14
+    KERNEL_LAUNCHES_EP = 17
+
+
+class CapturedDecodeStep:
+    """The layer's decode step recorded once into a CUDA graph and replayed.
+
+    Counterpart of the reference's two-phase graph execution (csrc/ffi/adaptor.h:57-89 `Setup`
+    then `Execute`; csrc/ffi/graph.cpp `Context.setup` / `Context.run`): set-up fixes shapes,
+    allocates every intermediate once and records the launches; a run only refreshes the
+    input buffers and replays.  Possible because no step of the layer synchronises with the
+    host (routing metadata stays on the device, the expert-parallel exchange has fixed
+    shapes).  Under expert parallelism every rank must construct and run it together.
+    """
+
+    NAMES = ("x", "residual", "positions", "slots", "block_tables", "context_lens")
+
+    def __init__(self, layer: MoEDecodeLayer, example: dict, k_cache, v_cache, warmup=3):
+        self.layer, self.k_cache, self.v_cache = layer, k_cache, v_cache
+        dev = layer.device
+        self.inputs = {n: example[n].to(dev).clone() for n in self.NAMES}
+        self.stream = torch.cuda.Stream(dev)
+        self.stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(self.stream):
+            for _ in range(warmup):  # first-call set-up (function attributes, NCCL channels) happens here
+                self._forward()
+        self.stream.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=self.stream):
+            self.y, self.res = self._forward()
+        torch.cuda.current_stream(dev).wait_stream(self.stream)
+
+    def _forward(self):
+        i = self.inputs
+        return self.layer.forward(i["x"], i["residual"], i["positions"], i["slots"], i["block_tables"],
+                                  i["context_lens"], self.k_cache, self.v_cache)
+
+    def load(self, batch: dict, non_blocking=True):
+        """Copy a step's inputs (host or device tensors) into the graph's input buffers."""
+        for n in self.NAMES:
+            self.inputs[n].copy_(batch[n], non_blocking=non_blocking)
+
+    def run(self):
+        """Replay on the current stream; returns the graph's output tensors (overwritten by the
+        next run)."""
+        self.graph.replay()
+        return self.y, self.res
 
 
 def draw_positions(batch=256, min_pos=1024, max_pos=16384, seed=8):

@@ -171,6 +171,22 @@ int b200ops_grouped_matmul(const void* x, const void* w, const int64_t* group_li
                            void* workspace, size_t workspace_size, void* stream);
 
 /*
+ * Split + rotary embedding + KV-cache scatter in one launch, for the decode step
+ * (the reference runs them as three graph nodes after the QKV projection,
+ * csrc/ffi/graph.cpp:207-283; no single FFI call of the reference corresponds to this).
+ *   qkv f16 [num_tokens, (num_heads + 2*num_kv_heads) * head_dim] (q heads, then k, then v)
+ *   q_out f16 [num_tokens, num_heads, head_dim] = rope(q);  rope(k) and v are written into
+ *   key_cache / value_cache at slot_indices[t] (layout and cache_dims as in
+ *   b200ops_reshape_and_cache).  Bit-identical to b200ops_rope followed by
+ *   b200ops_reshape_and_cache on the split tensors.
+ */
+int b200ops_fused_qkv_rope_cache(const void* qkv, const int32_t* position_ids, const void* cos_cache,
+                                 const void* sin_cache, const int32_t* slot_indices, void* q_out,
+                                 void* key_cache, void* value_cache, int64_t num_tokens,
+                                 int64_t num_heads, int64_t num_kv_heads, int64_t head_dim,
+                                 int64_t max_pos, const int64_t cache_dims[4], int layout, void* stream);
+
+/*
  * MoE routing glue: the steps around grouped_matmul that the reference leaves to its caller
  * (its grouped_matmul expects rows pre-sorted by expert and cumulative group ends,
  * csrc/opdev/op_kernel/grouped_mat_mul_ex.cpp:29-38; the sorting lives in the companion

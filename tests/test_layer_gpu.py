@@ -77,3 +77,51 @@ def test_expert_parallel_two_gpus_matches_single_gpu(tmp_path):
                        env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
     assert "EP_CHECK_OK" in r.stdout
+
+
+@pytest.mark.parametrize("nz", [False, True])
+def test_fused_rope_cache_equals_the_two_operators(ops, nz):
+    import ascend910a_extras.moe as moe
+    import decode_workloads as wl
+
+    g = torch.Generator().manual_seed(4)
+    t, hq, hkv, d, pages, p = 37, 8, 2, 128, 9, 16
+    qkv = torch.randn(t, (hq + 2 * hkv) * d, generator=g).half().to(DEV)
+    r = wl.rope_inputs(t, hq, hkv, d, 0, 200, seed=3)
+    pos, cos, sin = (r[n].to(DEV) for n in ("position_ids", "cos_cache", "sin_cache"))
+    pos[2] = 5000  # outside the table: zeros, as in ops.rope
+    slots = torch.randperm(pages * p, generator=g)[:t].int().to(DEV)
+    slots[5] = -1
+    shape = (pages, hkv * d // 16, p, 16) if nz else (pages, p, hkv, d)
+    base = torch.randn(shape, generator=g).half()
+    kc1, vc1, kc2, vc2 = (base.to(DEV).clone() for _ in range(4))
+    q1 = moe.fused_qkv_rope_cache(qkv, pos, cos, sin, slots, kc1, vc1, hq, hkv)
+    q = qkv[:, : hq * d].contiguous().view(t, hq, d)
+    k = qkv[:, hq * d:(hq + hkv) * d].contiguous().view(t, hkv, d)
+    v = qkv[:, (hq + hkv) * d:].contiguous().view(t, hkv, d)
+    q2, k2 = ops.rope(q, k, pos, cos, sin)
+    ops.reshape_and_cache(k2, v, kc2, vc2, slots)
+    torch.cuda.synchronize()
+    assert torch.equal(q1, q2) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert not torch.equal(kc1.cpu(), base)
+
+
+def test_captured_step_equals_eager_step(ops):
+    cfg, w, b, kc, vc = small_case(batch=9, seed=21)
+    layer = mdl.MoEDecodeLayer(cfg, w, DEV, ops)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    args = [b[n].to(DEV) for n in mdl.CapturedDecodeStep.NAMES]
+    y_eager, r_eager = layer.forward(*args, kd, vd)
+    step = mdl.CapturedDecodeStep(layer, b, kd, vd)
+    step.load({n: b[n].pin_memory() for n in step.NAMES})
+    y, r = step.run()
+    torch.cuda.synchronize()
+    assert torch.equal(y, y_eager) and torch.equal(r, r_eager)
+    # new inputs through the same graph
+    b2 = dict(b)
+    b2["x"] = (b["x"].float() * 0.5).half()
+    step.load(b2)
+    y2, _ = step.run()
+    y2_eager, _ = layer.forward(b2["x"].to(DEV), *args[1:], kd, vd)
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y2_eager) and not torch.equal(y2, y_eager)

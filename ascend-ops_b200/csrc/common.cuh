@@ -83,6 +83,26 @@ __device__ __forceinline__ void st_stream(void* p, const uint4& v) {
                : "memory");
 }
 
+// 256-bit global accesses (sm_100): one instruction per 32-byte sector.
+struct Vec256 {
+  uint32_t r[8];
+};
+
+__device__ __forceinline__ Vec256 ld_stream256(const void* p) {
+  Vec256 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v8.u32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+               : "=r"(v.r[0]), "=r"(v.r[1]), "=r"(v.r[2]), "=r"(v.r[3]), "=r"(v.r[4]), "=r"(v.r[5]),
+                 "=r"(v.r[6]), "=r"(v.r[7])
+               : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ void st256(void* p, const Vec256& v) {
+  asm volatile("st.global.v8.u32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(p), "r"(v.r[0]), "r"(v.r[1]),
+               "r"(v.r[2]), "r"(v.r[3]), "r"(v.r[4]), "r"(v.r[5]), "r"(v.r[6]), "r"(v.r[7])
+               : "memory");
+}
+
 __device__ __forceinline__ float2 h2_to_f2(uint32_t u) {
   return __half22float2(*reinterpret_cast<const __half2*>(&u));
 }

@@ -61,7 +61,7 @@ extern "C" int b200ops_print_info(int device_id, char* buf, size_t buf_len) {
 
 namespace b200ops {
 namespace gmm { int status_take(); }
-namespace pa { int fast_path_status_take(); }
+namespace pa { int fast_path_status_take(); int stream_status_take(); }
 }  // namespace b200ops
 
 // Codes 1-9 come from grouped_matmul's pipeline, 11-19 from paged_attention's TMA path.
@@ -71,7 +71,8 @@ extern "C" int b200ops_pipeline_status(int* status) {
   B200OPS_CUDA(cudaDeviceSynchronize());
   const int g = gmm::status_take();
   const int p = pa::fast_path_status_take();
-  if (g < 0 || p < 0) return fail(B200OPS_ECUDA, "pipeline_status: could not read the status words");
-  *status = g != 0 ? g : p;
+  const int s = pa::stream_status_take();
+  if (g < 0 || p < 0 || s < 0) return fail(B200OPS_ECUDA, "pipeline_status: could not read the status words");
+  *status = g != 0 ? g : (p != 0 ? p : s);
   return B200OPS_OK;
 }

@@ -183,9 +183,16 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attention_general_kernel(Ar
   }
 }
 
-// Combine: grid = (num_heads, bs).  Merges the chunk partials of sequences that were split.
-__global__ void __launch_bounds__(128) paged_attention_combine_kernel(Args a) {
-  const int h = blockIdx.x, b = blockIdx.y;
+// Combine: one warp per (sequence, query head) merges the chunk partials of sequences that
+// were split.  Lanes first take one chunk each for the maximum and the normaliser, then every
+// lane sums its channels (lane, lane + 32, ...) over the chunks.
+constexpr int kCombineWarps = 4;
+
+__global__ void __launch_bounds__(kCombineWarps * 32) paged_attention_combine_kernel(Args a) {
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
+  if (item >= a.bs * a.num_heads) return;
+  const int b = item / a.num_heads;
   int L = a.context_lens[b];
   const int cap = a.max_pages_per_seq * a.page_size;
   if (L > cap) L = cap;
@@ -194,22 +201,42 @@ __global__ void __launch_bounds__(128) paged_attention_combine_kernel(Args a) {
   if (n_chunks <= 1) return;
   const int D = a.head_dim;
   const size_t rec = partial_stride(D);
-  const float* base = a.partials + (static_cast<size_t>(b) * a.num_heads + h) * a.max_chunks * rec;
+  const float* base = a.partials + static_cast<size_t>(item) * a.max_chunks * rec;
   float mm = -INFINITY;
-  for (int c = 0; c < n_chunks; ++c) mm = fmaxf(mm, base[c * rec + D]);
+  for (int c = lane; c < n_chunks; c += 32) mm = fmaxf(mm, base[c * rec + D]);
+  mm = warp_max(mm);
   float ll = 0.f;
-  for (int c = 0; c < n_chunks; ++c) {
+  for (int c = lane; c < n_chunks; c += 32) {
     const float mc = base[c * rec + D];
     if (mc != -INFINITY) ll += base[c * rec + D + 1] * exp2f(mc - mm);
   }
+  ll = warp_sum(ll);
   const float inv = ll > 0.f ? 1.0f / ll : 0.f;
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float o = 0.f;
-    for (int c = 0; c < n_chunks; ++c) {
-      const float mc = base[c * rec + D];
-      if (mc != -INFINITY) o += base[c * rec + d] * exp2f(mc - mm);
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // head_dim <= 256 -> up to 8 per lane
+  for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+    const int mine = c0 + lane;
+    float w = 0.f;
+    if (mine < n_chunks) {
+      const float mc = base[mine * rec + D];
+      w = (mc == -INFINITY) ? 0.f : exp2f(mc - mm);
     }
-    a.out[(static_cast<size_t>(b) * a.num_heads + h) * D + d] = __float2half(o * inv);
+    const int n = min(32, n_chunks - c0);
+    for (int j = 0; j < n; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, w, j);
+      if (wj == 0.f) continue;
+      const float* p = base + static_cast<size_t>(c0 + j) * rec;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int d = lane + i * 32;
+        if (d < D) acc[i] = fmaf(wj, p[d], acc[i]);
+      }
+    }
+  }
+  __half* out = a.out + static_cast<size_t>(item) * D;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = lane + i * 32;
+    if (d < D) out[d] = __float2half(acc[i] * inv);
   }
 }
 
@@ -262,8 +289,8 @@ int launch_general(const Args& a, cudaStream_t st) {
 
 int launch_combine(const Args& a, cudaStream_t st) {
   if (a.max_chunks <= 1) return B200OPS_OK;
-  const dim3 grid(a.num_heads, a.bs);
-  paged_attention_combine_kernel<<<grid, 128, 0, st>>>(a);
+  const int items = a.bs * a.num_heads;
+  paged_attention_combine_kernel<<<(items + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, 0, st>>>(a);
   B200OPS_LAUNCH_CHECK("paged_attention combine");
   return B200OPS_OK;
 }
@@ -279,10 +306,17 @@ extern "C" size_t b200ops_paged_attention_workspace_size(int64_t bs, int64_t num
   if (bs <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || page_size <= 0 ||
       max_pages_per_seq <= 0)
     return 0;
+  // The layout is not part of the query, so the answer covers whichever path the launch takes:
+  // chunk partials of the split-context kernels, or prefix sums + segment records of the
+  // tile-balanced kernel.
   const pa::Plan p = pa::make_plan(bs, num_kv_heads, page_size, max_pages_per_seq);
-  if (p.max_chunks <= 1) return 0;
-  return static_cast<size_t>(bs) * num_heads * p.max_chunks * pa::partial_stride((int)head_dim) *
-         sizeof(float);
+  const size_t chunked = p.max_chunks <= 1 ? 0
+                                           : static_cast<size_t>(bs) * num_heads * p.max_chunks *
+                                                 pa::partial_stride((int)head_dim) * sizeof(float);
+  const size_t stream = num_heads % num_kv_heads == 0
+                            ? pa::stream_workspace_bytes(bs, num_heads, num_kv_heads, head_dim)
+                            : 0;
+  return chunked > stream ? chunked : stream;
 }
 
 extern "C" int b200ops_paged_attention(const void* q, const void* key_cache,
@@ -347,6 +381,7 @@ extern "C" int b200ops_paged_attention(const void* q, const void* key_cache,
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int rc;
+  if (pa::stream_path_supported(a)) return pa::launch_stream(a, workspace, st);
   if (pa::fast_path_supported(a))
     rc = pa::launch_fast(a, st);
   else

@@ -16,7 +16,7 @@
 // replaced by -inf and their V rows are zeroed in shared memory before the PV product, so
 // uninitialised cache memory (NaN patterns) cannot leak into the output.
 #include "paged_attention.cuh"
-#include "sm100_ptx.cuh"
+#include "paged_attention_tile.cuh"
 #include "tma_host.cuh"
 
 #include <cstdlib>
@@ -25,13 +25,9 @@ namespace b200ops {
 namespace pa {
 namespace {
 
-constexpr int kD = 128;
-constexpr int kTile = 64;             // tokens per pipeline stage
-constexpr int kConsumerWarps = 4;     // each owns 16 tokens of a tile
+using namespace tile;
+
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kSubTileBytes = kTile * 128;        // 64 tokens x 64 halfs
-constexpr int kTensorTileBytes = 2 * kSubTileBytes;  // both halves of D
-constexpr int kStageBytes = 2 * kTensorTileBytes;    // K and V
 constexpr int kMaxPagesPerChunk = 64;
 constexpr int kErrProducerWait = 11;
 constexpr int kErrConsumerWait = 12;
@@ -45,32 +41,6 @@ struct Smem {
 };
 
 __device__ int g_pa_status = 0;
-
-__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-
-__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
-  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
-               : "r"(addr));
-}
-
-__device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4], uint32_t b0,
-                                          uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
-      "{%0,%1,%2,%3};"
-      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// Byte offset of 16-byte chunk `c` (0..7) of row `r` inside a 128B-swizzled sub-tile.
-__device__ __forceinline__ uint32_t swz(int r, int c) {
-  return static_cast<uint32_t>(r * 128 + ((c ^ (r & 7)) << 4));
-}
 
 // kUpper: the GQA group has more than 8 query heads, so MMA rows 8..15 carry data.
 template <int kStages, bool kUpper>
@@ -155,132 +125,21 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
   } else {
     // ---------------- consumer warps ----------------
     const int g = lane >> 2, t4 = lane & 3;
-    // Q fragments (A operand, 16 heads x 16 channels per k-step), loaded once.
     uint32_t qa[kD / 16][4];
-    {
-      const __half* qb = a.q + (static_cast<size_t>(b) * a.num_heads + h0) * kD;
-#pragma unroll
-      for (int ks = 0; ks < kD / 16; ++ks) {
-        const int c = ks * 16 + 2 * t4;
-        qa[ks][0] = (g < group) ? *reinterpret_cast<const uint32_t*>(qb + g * kD + c) : 0u;
-        qa[ks][2] = (g < group) ? *reinterpret_cast<const uint32_t*>(qb + g * kD + c + 8) : 0u;
-        if (kUpper) {
-          qa[ks][1] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * kD + c) : 0u;
-          qa[ks][3] = (g + 8 < group) ? *reinterpret_cast<const uint32_t*>(qb + (g + 8) * kD + c + 8) : 0u;
-        } else {
-          qa[ks][1] = 0u;
-          qa[ks][3] = 0u;
-        }
-      }
-    }
-    float o[kD / 8][4];
-#pragma unroll
-    for (int i = 0; i < kD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
-
+    load_q_fragments<kUpper>(qa, a.q + (static_cast<size_t>(b) * a.num_heads + h0) * kD, group, lane);
+    WarpState st;
+    st.reset();
     int stage = 0;
     uint32_t phase = 0;
     const int row0 = warp * 16;  // this warp's token rows inside a tile
-    // ldmatrix row/chunk selectors of this lane
-    const int k_row = row0 + ((lane >> 4) << 3) + (lane & 7);  // K: matrices 2,3 are tokens +8
-    const int k_csel = (lane >> 3) & 1;                        //    matrices 1,3 are chunk +1
-    const int v_row = row0 + (((lane >> 3) & 1) << 3) + (lane & 7);  // V: matrices 1,3 tokens +8
-    const int v_csel = lane >> 4;                                    //    matrices 2,3 chunk +1
-    bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
       if (!ptx::mbar_wait(&full[stage], phase, abort_flag)) {
         *abort_flag = 1;
         atomicCAS(&g_pa_status, 0, kErrConsumerWait);
-        ok = false;
         break;
       }
-      const uint32_t kbase = ptx::smem_u32(smem + stage * kStageBytes);
-      const uint32_t vbase = kbase + kTensorTileBytes;
-      const int tok0 = start + t * kTile + row0;  // first token of this warp's slice
-      const bool tail = tok0 + 16 > end;          // warp-uniform
-      if (tail) {
-        // Zero the V rows of tokens past the end so that 0 * garbage cannot become NaN.
-        uint8_t* vt = smem + stage * kStageBytes + kTensorTileBytes;
-        for (int i = lane; i < 16 * 16; i += 32) {
-          const int r = row0 + (i >> 4), c = i & 15;
-          if (start + t * kTile + r >= end)
-            *reinterpret_cast<uint4*>(vt + (c >> 3) * kSubTileBytes + r * 128 + ((c & 7) << 4)) =
-                make_uint4(0, 0, 0, 0);
-        }
-        __syncwarp();
-      }
-
-      // ---- S = Q . K^T for 16 tokens (two n-blocks of 8) ----
-      float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-#pragma unroll
-      for (int ks = 0; ks < kD / 16; ++ks) {
-        uint32_t kb[4];
-        const int chunk_in_sub = (ks & 3) * 2 + k_csel;
-        ldmatrix_x4(kb, kbase + (ks >> 2) * kSubTileBytes + swz(k_row, chunk_in_sub));
-        mma_16816(s[0], qa[ks], kb[0], kb[1]);
-        mma_16816(s[1], qa[ks], kb[2], kb[3]);
-      }
-      // ---- online softmax (rows g and g+8; columns 2*t4, 2*t4+1 of each n-block) ----
-#pragma unroll
-      for (int nb = 0; nb < 2; ++nb) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const int tok = tok0 + nb * 8 + 2 * t4 + (j & 1);
-          s[nb][j] = (!tail || tok < end) ? s[nb][j] * a.scale_log2 : -INFINITY;
-        }
-      }
-      uint32_t pa_frag[4];
-      {
-        float mx = fmaxf(fmaxf(s[0][0], s[0][1]), fmaxf(s[1][0], s[1][1]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_lo, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = exp2f(m_lo - m_use);
-        const float p0 = exp2f(s[0][0] - m_use), p1 = exp2f(s[0][1] - m_use);
-        const float p2 = exp2f(s[1][0] - m_use), p3 = exp2f(s[1][1] - m_use);
-        l_lo = l_lo * alpha + (p0 + p1 + p2 + p3);
-        m_lo = m_new;
-        pa_frag[0] = f2_to_h2(p0, p1);
-        pa_frag[2] = f2_to_h2(p2, p3);
-#pragma unroll
-        for (int i = 0; i < kD / 8; ++i) {
-          o[i][0] *= alpha;
-          o[i][1] *= alpha;
-        }
-      }
-      if (kUpper) {
-        float mx = fmaxf(fmaxf(s[0][2], s[0][3]), fmaxf(s[1][2], s[1][3]));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-        const float m_new = fmaxf(m_hi, mx);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = exp2f(m_hi - m_use);
-        const float p0 = exp2f(s[0][2] - m_use), p1 = exp2f(s[0][3] - m_use);
-        const float p2 = exp2f(s[1][2] - m_use), p3 = exp2f(s[1][3] - m_use);
-        l_hi = l_hi * alpha + (p0 + p1 + p2 + p3);
-        m_hi = m_new;
-        pa_frag[1] = f2_to_h2(p0, p1);
-        pa_frag[3] = f2_to_h2(p2, p3);
-#pragma unroll
-        for (int i = 0; i < kD / 8; ++i) {
-          o[i][2] *= alpha;
-          o[i][3] *= alpha;
-        }
-      } else {
-        pa_frag[1] = 0u;
-        pa_frag[3] = 0u;
-      }
-      // ---- O += P . V (16 tokens x 128 channels) ----
-#pragma unroll
-      for (int cc = 0; cc < kD / 8; cc += 2) {
-        uint32_t vb[4];
-        const int c = cc + v_csel;
-        ldmatrix_x4_trans(vb, vbase + (c >> 3) * kSubTileBytes + swz(v_row, c & 7));
-        mma_16816(o[cc], pa_frag, vb[0], vb[1]);
-        mma_16816(o[cc + 1], pa_frag, vb[2], vb[3]);
-      }
-      if (tail) ptx::fence_proxy_async();
+      consume_slice<kUpper>(st, qa, smem + stage * kStageBytes, row0, start + t * kTile + row0, end, lane,
+                            a.scale_log2);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[stage]);
       if (++stage == kStages) {
@@ -288,12 +147,9 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
         phase ^= 1u;
       }
     }
-    (void)ok;
-    // Row sums were kept per thread; finish them across the quad.
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
-    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
-    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    st.finish_sums();
+    float (&o)[kD / 8][4] = st.o;
+    const float m_lo = st.m_lo, m_hi = st.m_hi, l_lo = st.l_lo, l_hi = st.l_hi;
 
     // All tiles of this CTA have landed and been read: reuse the stage memory for the merge.
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32));
@@ -373,7 +229,9 @@ int launch_with_stages(const CUtensorMap& mk, const CUtensorMap& mv, const Args&
 }  // namespace
 
 bool fast_path_supported(const Args& a) {
-  if (env_int("B200OPS_PA_FORCE_GENERAL", 0)) return false;
+  // B200OPS_PA_MODE: 0/1 = this split-context TMA path (default), 2 = general kernel,
+  // 3 = persistent tile-balanced kernel (paged_attention_stream.cu).
+  if (env_int("B200OPS_PA_MODE", 0) == 2) return false;
   const int group = a.num_heads / a.num_kv_heads;
   return a.layout == B200OPS_KV_LAYOUT_NHD && a.head_dim == kD && a.page_size % kTile == 0 &&
          group <= 16 && a.chunk_tokens % a.page_size == 0 &&

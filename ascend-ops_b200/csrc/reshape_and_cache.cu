@@ -6,8 +6,9 @@
 //        csrc/opdev/op_kernel/reshape_and_cache_ex.cpp:47-69)
 //   NHD [pages, P, Hkv, D]: cache[s/P, s%P, h, d] = key[t, h, d]             (vLLM standard)
 // Slots outside [0, pages*P) are skipped, as the reference kernel does (:50).  Where the
-// reference lets every core copy all tokens element by element, here each thread moves one
-// 16-byte vector of K and the matching vector of V.  If two tokens name the same slot the
+// reference lets every core copy all tokens element by element, here a warp moves one token's
+// K and V rows in 32-byte pieces (rows of whole sectors), or each thread one 16-byte vector of
+// K and the matching vector of V (other rows that are multiples of 8), or single elements.  If two tokens name the same slot the
 // reference keeps the later token; here the winner is unspecified (callers never do this:
 // a slot is one cache position).
 #include "common.cuh"
@@ -70,6 +71,56 @@ __global__ void __launch_bounds__(kThreads) scatter_nz_vec_kernel(ScatterParams 
     reinterpret_cast<uint4*>(p.value_cache)[dst] = vv;
   }
   reinterpret_cast<uint4*>(p.key_cache)[dst] = kv;
+}
+
+// Row-per-warp kernels for rows that are whole 32-byte sectors (row_elems % 16 == 0): a warp
+// owns one token, every lane moves 32-byte pieces of the K row and of the V row.  All loads
+// (including the slot) are issued before anything depends on them, so one DRAM round trip
+// covers them; stores are one full sector each.  kMaxPieces bounds the pieces a lane holds.
+constexpr int kRowWarps = 4;
+constexpr int kMaxPieces = 4;  // 32 lanes x 4 pieces x 32 B = rows up to 4 KB
+
+template <bool kNz>
+__global__ void __launch_bounds__(kRowWarps * 32) scatter_rows_kernel(ScatterParams p) {
+  const uint32_t token = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+  if (token >= p.num_tokens) return;
+  const uint32_t lane = threadIdx.x & 31;
+  const uint32_t pieces = p.row_elems >> 4;  // 32-byte pieces (= NZ chunks) per row
+  const char* ks = reinterpret_cast<const char*>(p.key) + static_cast<size_t>(token) * p.row_elems * 2;
+  const char* vs = reinterpret_cast<const char*>(p.value) + static_cast<size_t>(token) * p.row_elems * 2;
+  const int64_t slot = p.slots[token];
+  Vec256 kb[kMaxPieces], vb[kMaxPieces];
+#pragma unroll
+  for (int i = 0; i < kMaxPieces; ++i) {
+    const uint32_t c = lane + i * 32;
+    if (c < pieces) {
+      kb[i] = ld_stream256(ks + c * 32);
+      if (p.value != nullptr) vb[i] = ld_stream256(vs + c * 32);
+    }
+  }
+  if (slot < 0 || slot >= p.num_slots) return;
+  size_t base, stride;  // byte offset of piece 0 and distance between pieces in the cache
+  uint32_t limit = pieces;
+  if (kNz) {
+    const uint64_t page = static_cast<uint64_t>(slot) / p.page_size;
+    const uint64_t off = static_cast<uint64_t>(slot) - page * p.page_size;
+    base = (page * p.chunks * p.page_size + off) * 32;
+    stride = static_cast<size_t>(p.page_size) * 32;
+    limit = min(pieces, p.chunks);
+  } else {
+    base = static_cast<size_t>(slot) * p.row_elems * 2;
+    stride = 32;
+  }
+  char* kc = reinterpret_cast<char*>(p.key_cache) + base;
+  char* vc = reinterpret_cast<char*>(p.value_cache) + base;
+#pragma unroll
+  for (int i = 0; i < kMaxPieces; ++i) {
+    const uint32_t c = lane + i * 32;
+    if (c < limit) {
+      st256(kc + c * stride, kb[i]);
+      if (p.value != nullptr) st256(vc + c * stride, vb[i]);
+    }
+  }
 }
 
 // Any shape / alignment: one 16-bit element per item.
@@ -153,6 +204,19 @@ extern "C" int b200ops_reshape_and_cache(const void* key, const void* value, voi
   p.chunks = static_cast<uint32_t>(chunks);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
+  const bool aligned32 = ((reinterpret_cast<uintptr_t>(key) | reinterpret_cast<uintptr_t>(key_cache) |
+                           (with_value ? reinterpret_cast<uintptr_t>(value) |
+                                             reinterpret_cast<uintptr_t>(value_cache)
+                                       : 0)) & 31u) == 0;
+  if (row_elems % 16 == 0 && row_elems <= 16 * 32 * kMaxPieces && aligned32) {
+    const unsigned grid = static_cast<unsigned>((num_tokens + kRowWarps - 1) / kRowWarps);
+    if (layout == B200OPS_KV_LAYOUT_NZ)
+      scatter_rows_kernel<true><<<grid, kRowWarps * 32, 0, st>>>(p);
+    else
+      scatter_rows_kernel<false><<<grid, kRowWarps * 32, 0, st>>>(p);
+    B200OPS_LAUNCH_CHECK("reshape_and_cache");
+    return B200OPS_OK;
+  }
   const bool vec_ok = row_elems % 8 == 0 && aligned16(key) && aligned16(key_cache) &&
                       (!with_value || (aligned16(value) && aligned16(value_cache)));
   const int64_t vec_items = num_tokens * (row_elems / 8);

@@ -155,11 +155,11 @@ class MoEDecodeLayer:
         return y, res2
 
     # number of this library's kernels one single-GPU forward launches (for the benchmark's
-    # accounting): 2 add_rms_norm, 2 dense GEMMs, fused rope+cache, attention + combine,
-    # route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Expert parallelism adds
-    # ep_plan and two more copy_rows.
-    KERNEL_LAUNCHES = 14
-    KERNEL_LAUNCHES_EP = 17
+    # accounting): 2 add_rms_norm, 2 dense GEMMs, fused rope+cache, attention (plan, main,
+    # combine), route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Expert
+    # parallelism adds ep_plan and two more copy_rows.
+    KERNEL_LAUNCHES = 15
+    KERNEL_LAUNCHES_EP = 18
 
 
 class CapturedDecodeStep:

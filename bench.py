@@ -104,28 +104,30 @@ class ClockSampler:
 
 
 # --------------------------------------------------------------------------- timing
-def time_launches(launch, n_sets, steps, warmup, device):
+def time_launches(launch, n_sets, steps, warmup, device, repeats=3):
     """Device time of one launch, in microseconds.
 
-    `launch(i)` enqueues the operator on buffer set i (0 <= i < n_sets).  The sets rotate so
-    that consecutive launches touch different memory (the caller sizes n_sets so that the
-    sets together exceed L2, or the operator's own footprint does).  Each timed step is
-    bracketed by CUDA events on the launching stream; the median over steps is returned
-    together with the raw list.
+    `launch(i)` enqueues the operator on buffer set i (0 <= i < n_sets); the caller sizes the
+    sets so that together (or each by itself) they exceed L2.  `steps` launches are enqueued
+    back to back between two CUDA events on the launching stream, so the GPU never waits for
+    the host's per-call work (argument checks, output allocation, descriptor encoding) and
+    the figure is kernel time including the gaps between an operator's own kernels.  The
+    median over `repeats` such batches is returned together with the raw list.
     """
     stream = torch.cuda.current_stream(device)
     for i in range(warmup):
         launch(i % n_sets)
     torch.cuda.synchronize(device)
     times = []
-    for i in range(steps):
+    for r in range(repeats):
         e0 = torch.cuda.Event(enable_timing=True)
         e1 = torch.cuda.Event(enable_timing=True)
         e0.record(stream)
-        launch((warmup + i) % n_sets)
+        for i in range(steps):
+            launch(i % n_sets)
         e1.record(stream)
         e1.synchronize()
-        times.append(e0.elapsed_time(e1) * 1e3)
+        times.append(e0.elapsed_time(e1) * 1e3 / steps)
     return statistics.median(times), times
 
 
@@ -225,7 +227,7 @@ def case_paged_attention(ops, dev, steps, warmup, peaks):
     bt, cl = a["block_tables"].to(dev), a["context_lens"].to(dev)
     us, _ = time_launches(lambda i: ops.paged_attention(q, kc, vc, bt, cl), 1, steps, warmup, dev)
     rec = op_record("paged_attention", "B=64 28q/4kv D=128 L~U[512,8192] page 128", nbytes, us, peaks,
-                    "hbm", launches=2)
+                    "hbm", launches=3)
     rec["sum_context"] = int(a["context_lens"].sum())
     return rec
 
@@ -361,6 +363,63 @@ def run_layer(ops, dev, rank, world, group, steps, warmup, peaks):
     }
 
 
+# --------------------------------------------------------------------------- expert-parallel MoE MLP
+def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
+    """The grouped-GEMM benchmark config as a whole MoE MLP: 4096 tokens, top-2 of 8 experts with
+    softmax(N(0,1)) routing skew (8192 routed rows), gate_up [4096 -> 2*14336], swiglu, down
+    [14336 -> 4096].  Tokens are sharded over ranks, experts are placed contiguously on ranks,
+    rows travel with the fixed-capacity all-to-all.  Reports whole-job TFLOP/s of the two GEMMs."""
+    import ascend910a_extras.moe as moe
+    import moe_decode_layer as mdl
+    import moe_parallel
+
+    cfg = mdl.LayerConfig()
+    tokens, top_k = 4096, 2
+    _, ids_flat = wl.moe_group_list(rows=tokens * top_k, experts=cfg.experts, seed=4)
+    ids = ids_flat.view(tokens, top_k).int()
+    per = tokens // world
+    my_ids = ids[rank * per:(rank + 1) * per].contiguous().to(dev)
+    g = torch.Generator(device=dev).manual_seed(40 + rank)
+    x = torch.randn(per, cfg.hidden, generator=g, device=dev, dtype=torch.float16)
+    wts = torch.full((per, top_k), 0.5, device=dev)
+    mine = moe_parallel.local_experts(cfg.experts, world, rank).tolist()
+    w = mdl.make_weights(cfg, seed=7, experts=mine, device=dev)
+    w_gu, w_dn = w["w_gate_up"].transpose(1, 2), w["w_down"].transpose(1, 2)
+
+    def local_mlp(rows, gl):
+        return ops.grouped_matmul(ops.swiglu(ops.grouped_matmul(rows, w_gu, gl)), w_dn, gl)
+
+    def step():
+        return moe_parallel.expert_parallel_mlp_device(moe, x, my_ids, wts, cfg.experts, local_mlp, group,
+                                                       per * top_k)
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        torch.distributed.barrier(group)
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    for _ in range(steps):
+        step()
+    t1.record()
+    torch.cuda.synchronize(dev)
+    t = torch.tensor([t0.elapsed_time(t1)], device=dev)
+    if world > 1:
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=group)
+    us = float(t) * 1e3 / steps
+    flops = 2 * tokens * top_k * cfg.hidden * 3 * cfg.intermediate
+    counts = torch.bincount(ids_flat, minlength=cfg.experts)
+    per_rank = [int(counts[moe_parallel.local_experts(cfg.experts, world, r)].sum()) for r in range(world)]
+    tf = flops / us / 1e6
+    return {"op": "moe_mlp_expert_parallel", "shape": "4096 tokens top-2 of 8 experts, 4096->2x14336->4096 f16",
+            "flops": flops, "us": round(us, 1), "achieved": round(tf, 1), "unit": "TFLOP/s",
+            "peak": peaks["bf16_tflops"] * world, "frac": round(tf / (peaks["bf16_tflops"] * world), 4),
+            "bound": "tensor", "launches": 8 if world == 1 else 11, "rows_per_rank": per_rank,
+            "balance_ceiling": round(sum(per_rank) / (world * max(per_rank)), 3),
+            "includes": "route-independent glue, swiglu and (for >1 GPU) dispatch/combine all-to-all"}
+
+
 # --------------------------------------------------------------------------- CPU baseline
 def cpu_layer_sample(seqs=32, repeats=1):
     """The CPU oracle's layer on a bounded sample: the first `seqs` of the 256 sequences with
@@ -393,11 +452,17 @@ def cpu_layer_sample(seqs=32, repeats=1):
 def profile_case(name, ops, dev):
     """A small, self-ending run of one operator for `ncu` captures: inputs larger than L2 but
     at most a few hundred MB, one warm-up launch and three profiled-size launches."""
-    if name == "paged_attention":
-        a = wl.paged_attention_inputs(bs=16, blocks=16 * 64, seed=3)
+    if name in ("paged_attention", "paged_attention_full", "paged_attention_layer_shard"):
+        if name == "paged_attention_full":
+            a = wl.paged_attention_inputs()
+        elif name == "paged_attention_layer_shard":  # one rank's share of the layer batch at 8 GPUs
+            a = wl.paged_attention_inputs(bs=32, heads=32, kv_heads=8, min_len=1025, max_len=16385,
+                                          blocks=32 * 129, seed=8)
+        else:
+            a = wl.paged_attention_inputs(bs=16, blocks=16 * 64, seed=3)
         args = [a[n].to(dev) for n in ("q", "key_cache", "value_cache", "block_tables", "context_lens")]
         fn = lambda: ops.paged_attention(*args)
-        info = {"bytes": wl.paged_attention_bytes(a["context_lens"], 4, 128, 28, 128)}
+        info = {"bytes": wl.paged_attention_bytes(a["context_lens"], a["kv_heads"], 128, a["q"].shape[1], 128)}
     elif name == "grouped_matmul":
         w = wl.grouped_matmul_inputs(rows=2048, k=4096, n=4096, seed=4)
         x, ws, gl = w["x"].to(dev), w["w_storage"].to(dev).transpose(1, 2), w["group_list"].to(dev)
@@ -500,6 +565,7 @@ def main():
     if rank == 0:
         sampler.start()
     layer = None if ns.no_layer else run_layer(ops, dev, rank, world, group, ns.steps, ns.warmup, peaks)
+    mlp = None if ns.no_layer else run_moe_mlp(ops, dev, rank, world, group, max(3, ns.steps // 2), ns.warmup, peaks)
     clocks = sampler.stop() if rank == 0 else None
     torch.cuda.empty_cache()
 
@@ -516,7 +582,7 @@ def main():
         want = list(cases)
     else:
         want = [c for c in ns.ops.split(",") if c and c != "none"]
-    per_op = []
+    per_op = [mlp] if mlp is not None else []
     if rank == 0:
         for name in want:
             per_op.append(cases[name](ops, dev, max(5, ns.steps // 2), ns.warmup, peaks))

@@ -333,27 +333,52 @@ def test_grouped_matmul_moe_shape_sampled_rows(cabi):
     close(run_grouped_matmul(cabi, w["x"], w["w_storage"], w["group_list"]), want)
 
 
-def test_paged_attention_benchmark_size_fast_path_vs_general_and_oracle(cabi, monkeypatch):
-    """Full benchmark batch (64 sequences, lengths U[512, 8192], 8192 pages): the TMA/tensor-core
-    path, the general path and the CPU oracle must agree."""
+def test_paged_attention_benchmark_size_all_paths_agree(cabi, monkeypatch):
+    """Full benchmark batch (64 sequences, lengths U[512, 8192], 8192 pages): the tile-balanced
+    persistent kernel, the split-context TMA kernel, the general kernel and the CPU oracle."""
     w = wl.paged_attention_inputs()
-    fast = run_paged_attention(cabi, w)
-    monkeypatch.setenv("B200OPS_PA_FORCE_GENERAL", "1")
+    monkeypatch.setenv("B200OPS_PA_MODE", "3")
+    stream = run_paged_attention(cabi, w)
+    monkeypatch.setenv("B200OPS_PA_MODE", "1")
+    chunked = run_paged_attention(cabi, w)
+    monkeypatch.setenv("B200OPS_PA_MODE", "2")
     general = run_paged_attention(cabi, w)
-    monkeypatch.delenv("B200OPS_PA_FORCE_GENERAL")
-    close(fast, general)
+    monkeypatch.delenv("B200OPS_PA_MODE")
+    close(stream, general)
+    close(chunked, general)
     want = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
                                   w["context_lens"])
-    close(fast, want)
+    close(stream, want)
+    close(chunked, want)
 
 
 @pytest.mark.parametrize("stages", ["2", "4", "6"])
 @pytest.mark.parametrize("chunk", ["128", "2048"])
-def test_paged_attention_fast_path_pipeline_depths(cabi, monkeypatch, stages, chunk):
+def test_paged_attention_split_context_path_pipeline_depths(cabi, monkeypatch, stages, chunk):
+    monkeypatch.setenv("B200OPS_PA_MODE", "1")
     monkeypatch.setenv("B200OPS_PA_STAGES", stages)
     monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", chunk)
     lens = [1, 63, 64, 65, 127, 128, 129, 1000, 4097, 0, 2048]
     w = wl.paged_attention_inputs(heads=32, kv_heads=4, context_lens=lens, blocks=80, seed=int(stages))
+    w = poison_unused(w)
+    want = oracle.paged_attention(w["q"], w["key_cache_clean"], w["value_cache_clean"],
+                                  w["block_tables"], w["context_lens"])
+    close(run_paged_attention(cabi, w), want)
+
+
+@pytest.mark.parametrize("heads,kv_heads,page,lens", [
+    (28, 4, 128, [1, 63, 64, 65, 127, 128, 129, 1000, 4097, 0, 2048]),
+    (32, 8, 64, [0, 0, 5, 0, 700, 64, 0]),                 # empty sequences in every position
+    (16, 1, 256, [33000]),                                 # one long sequence spread over all CTAs
+    (64, 4, 128, [3000] * 3 + [17] * 40),                  # group of 16 (upper MMA rows in use)
+    (8, 8, 128, list(range(1, 400, 7))),                   # many short sequences, group 1
+    (8, 2, 64, [(i * 37) % 300 for i in range(700)]),      # batch beyond the in-kernel plan limit
+])
+def test_paged_attention_tile_balanced_path(cabi, monkeypatch, heads, kv_heads, page, lens):
+    monkeypatch.setenv("B200OPS_PA_MODE", "3")
+    blocks = sum((l + page - 1) // page for l in lens) + 2
+    w = wl.paged_attention_inputs(heads=heads, kv_heads=kv_heads, block_size=page, context_lens=lens,
+                                  blocks=blocks, seed=heads + page)
     w = poison_unused(w)
     want = oracle.paged_attention(w["q"], w["key_cache_clean"], w["value_cache_clean"],
                                   w["block_tables"], w["context_lens"])

@@ -150,11 +150,17 @@ def paged_attention_static(q, key_cache, value_cache, block_tables, context_lens
                                                 block_tables.shape[1], layout, _stream(stream)))
 
 
-def grouped_matmul(x, w_storage, group_list, y, stream=None):
-    """`w_storage` is the [E, N, K] storage tensor (the torch-level view is its transpose)."""
+def grouped_matmul_workspace_size(num_tokens, k, num_experts, n) -> int:
+    return load().b200ops_grouped_matmul_workspace_size(num_tokens, k, num_experts, n)
+
+
+def grouped_matmul(x, w_storage, group_list, y, workspace=None, stream=None):
+    """`w_storage` is the [E, N, K] storage tensor (the torch-level view is its transpose).
+    `workspace` (uint8 tensor of grouped_matmul_workspace_size bytes) enables split-K."""
     e, n, k = w_storage.shape
+    ws_size = 0 if workspace is None else workspace.numel() * workspace.element_size()
     check(load().b200ops_grouped_matmul(_ptr(x), _ptr(w_storage), _ptr(group_list), _ptr(y),
-                                        x.shape[0], k, e, n, None, 0, _stream(stream)))
+                                        x.shape[0], k, e, n, _ptr(workspace), ws_size, _stream(stream)))
 
 
 def pipeline_status() -> int:

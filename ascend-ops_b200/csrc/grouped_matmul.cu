@@ -17,6 +17,14 @@
 //               predicated on the group's row end (an M-tail tile never writes into the next
 //               group's rows; reading them is harmless)
 //
+// Split-K.  When the problem has fewer output tiles than SMs (decode batches: one m-tile per
+// expert; a down projection with N = 4096 has 16 n-tiles) each CTA can only stream its own
+// operands at about 100 GB/s and most SMs idle.  If the caller passes a workspace, every CTA
+// derives the same split factor s = floor(CTAs / tiles) from the tile count it computed on
+// the device, a work item becomes (tile, k-slice), and the s CTAs of a tile write fp32
+// partial tiles to the workspace.  A counter per tile identifies the last CTA to finish; it
+// alone sums the partials and writes the fp16 rows.  Nobody waits on another CTA.
+//
 // Tiles are enumerated group by group, m-tile fastest, so that CTAs running at the same
 // time share the same w tile (read from HBM once, then from L2) while the group's x rows
 // stay L2-resident.  Work is 2*M*K*N flops; at the sizes of interest the kernel is bound by
@@ -46,6 +54,26 @@ constexpr int kErrProducerWait = 1;
 constexpr int kErrMmaWaitFull = 2;
 constexpr int kErrMmaWaitTmem = 3;
 constexpr int kErrEpilogueWait = 4;
+constexpr int kMinKBlocksPerSplit = 4;  // keep every k-slice long enough to fill the ring
+
+// Workspace layout (only used when split-K engages): [kMaxGrid] tile counters, then
+// [kMaxGrid] fp32 partial tiles of BM x BN.  With s > 1 there is at most one work item per CTA.
+constexpr int kMaxGrid = 256;
+constexpr size_t kPartialTileBytes = static_cast<size_t>(BM) * BN * sizeof(float);
+constexpr size_t kCounterBytes = kMaxGrid * sizeof(int);
+
+// Host-side gate, shared by the size query and the launch: split-K can only pay off when even
+// the densest packing of the rows leaves at least half of the SMs without a tile, and K is long
+// enough to cut.
+inline bool split_k_possible(int64_t num_tokens, int64_t k, int64_t n, int sms) {
+  const int64_t n_tiles = (n + BN - 1) / BN;
+  const int64_t min_tiles = ((num_tokens + BM - 1) / BM) * n_tiles;
+  return min_tiles * 2 <= sms && k / BK >= 2 * kMinKBlocksPerSplit;
+}
+
+inline int launch_sms() { return sm_count() < kMaxGrid ? sm_count() : kMaxGrid; }
+
+inline size_t workspace_bytes() { return kCounterBytes + launch_sms() * kPartialTileBytes; }
 
 struct Control {
   uint64_t full[kStages];
@@ -54,6 +82,7 @@ struct Control {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
+  int split_rank;  // arrival order of this CTA among the k-slices of its tile
   int tile_prefix[kMaxExperts + 1];  // first tile id of each group; [E] = total tiles
   int row_start[kMaxExperts];
   int row_end[kMaxExperts];
@@ -67,6 +96,20 @@ __device__ int g_pipeline_status = 0;
 struct TileCoord {
   int group, row0, row_end, n0;
 };
+
+// Work item -> (tile, k-slice).  Items of one tile are adjacent so its CTAs run together.
+struct WorkItem {
+  int tile, kb0, kb1, split;
+};
+
+__device__ __forceinline__ WorkItem locate_item(int item, int splits, int k_blocks) {
+  WorkItem w;
+  w.tile = item / splits;
+  w.split = item - w.tile * splits;
+  w.kb0 = static_cast<int>(static_cast<long long>(w.split) * k_blocks / splits);
+  w.kb1 = static_cast<int>(static_cast<long long>(w.split + 1) * k_blocks / splits);
+  return w;
+}
 
 // Tiles of one group are numbered m-fastest.  `g` is carried between calls: tile ids only
 // grow within a CTA, so the search is amortised O(1).
@@ -89,7 +132,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
                       const __grid_constant__ CUtensorMap map_w,
                       const int64_t* __restrict__ group_list, __half* __restrict__ y, int M, int N,
-                      int K, int E) {
+                      int K, int E, int* __restrict__ tile_counters, float* __restrict__ partials) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -146,6 +189,14 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
   const int total_tiles = ctl->tile_prefix[E];
   const uint32_t tmem_base = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
+  // Split factor: identical in every CTA because it depends only on the tile count.
+  int splits = 1;
+  if (partials != nullptr && total_tiles > 0) {
+    splits = static_cast<int>(gridDim.x) / total_tiles;
+    splits = min(splits, k_blocks / kMinKBlocksPerSplit);
+    splits = max(splits, 1);
+  }
+  const int total_items = total_tiles * splits;
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -153,9 +204,10 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       int stage = 0, g = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const TileCoord tc = locate_tile(ctl, tile, g);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
+        const WorkItem wi = locate_item(item, splits, k_blocks);
+        const TileCoord tc = locate_tile(ctl, wi.tile, g);
+        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
             *abort_flag = 1;
             atomicCAS(&g_pipeline_status, 0, kErrProducerWait);
@@ -181,7 +233,8 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       uint32_t phase = 0;
       bool ok = true;
       int iter = 0;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x, ++iter) {
+      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++iter) {
+        const WorkItem wi = locate_item(item, splits, k_blocks);
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
         if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
@@ -191,7 +244,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
         }
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!ptx::mbar_wait(&ctl->full[stage], phase, abort_flag)) {
             *abort_flag = 1;
             atomicCAS(&g_pipeline_status, 0, kErrMmaWaitFull);
@@ -206,7 +259,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
             // Inside a 128-byte swizzle row the k-th 16-element slice starts 32 bytes on.
             const uint64_t a_desc = ptx::make_sw128_kmajor_desc(a_addr + k * UMMA_K * 2);
             const uint64_t b_desc = ptx::make_sw128_kmajor_desc(b_addr + k * UMMA_K * 2);
-            ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb != wi.kb0 || k != 0) ? 1u : 0u);
           }
           ptx::umma_commit(&ctl->empty[stage]);  // frees the stage once these MMAs retire
           if (++stage == kStages) {
@@ -221,8 +274,9 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
     int g = 0, iter = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++iter) {
-      const TileCoord tc = locate_tile(ctl, tile, g);
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++iter) {
+      const WorkItem wi = locate_item(item, splits, k_blocks);
+      const TileCoord tc = locate_tile(ctl, wi.tile, g);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
       if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) {
@@ -231,9 +285,11 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
         break;
       }
       ptx::tcgen05_fence_after();
-      const int row = tc.row0 + quarter * 32 + lane;
+      const int tile_row = quarter * 32 + lane;
+      const int row = tc.row0 + tile_row;
       const bool row_ok = row < tc.row_end;
       __half* yrow = y + static_cast<size_t>(row) * N + tc.n0;
+      float* prow = splits > 1 ? partials + static_cast<size_t>(item) * (BM * BN) + tile_row * BN : nullptr;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -241,7 +297,8 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
         uint32_t r[32];
         ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
         ptx::tmem_ld_wait();
-        if (row_ok) {
+        if (!row_ok) continue;
+        if (splits == 1) {
           uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
 #pragma unroll
           for (int v = 0; v < 4; ++v) {
@@ -252,11 +309,49 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
             o.w = f2_to_h2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
             dst[v] = o;
           }
+        } else {
+          uint4* dst = reinterpret_cast<uint4*>(prow + c * 32);
+#pragma unroll
+          for (int v = 0; v < 8; ++v) dst[v] = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
         }
       }
       ptx::tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
+      if (splits > 1) {
+        // Publish this k-slice; the CTA that finds the other s-1 slices already published
+        // reduces all of them.  Counters were zeroed by the host before the launch.
+        __threadfence();
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (threadIdx.x == 64) ctl->split_rank = atomicAdd(&tile_counters[wi.tile], 1);
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ctl->split_rank == splits - 1) {
+          __threadfence();
+          const float* first = partials + static_cast<size_t>(wi.tile) * splits * (BM * BN);
+          const int rows_here = min(BM, tc.row_end - tc.row0);
+          const int cols_here = min(BN, N - tc.n0);
+          // warp `quarter` reduces rows quarter, quarter+4, ...: a row is read and written by
+          // one warp, 8 columns per lane, coalesced.
+          for (int rr = quarter; rr < rows_here; rr += 4) {
+            const int col = lane * 8;
+            if (col >= cols_here) continue;
+            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int sidx = 0; sidx < splits; ++sidx) {
+              const float4* p = reinterpret_cast<const float4*>(first + static_cast<size_t>(sidx) * (BM * BN) +
+                                                                rr * BN + col);
+              const float4 a = __ldcg(p), b = __ldcg(p + 1);
+              acc8[0] += a.x; acc8[1] += a.y; acc8[2] += a.z; acc8[3] += a.w;
+              acc8[4] += b.x; acc8[5] += b.y; acc8[6] += b.z; acc8[7] += b.w;
+            }
+            uint4 o;
+            o.x = f2_to_h2(acc8[0], acc8[1]);
+            o.y = f2_to_h2(acc8[2], acc8[3]);
+            o.z = f2_to_h2(acc8[4], acc8[5]);
+            o.w = f2_to_h2(acc8[6], acc8[7]);
+            *reinterpret_cast<uint4*>(y + static_cast<size_t>(tc.row0 + rr) * N + tc.n0 + col) = o;
+          }
+        }
+      }
     }
   }
 
@@ -271,14 +366,18 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
 }  // namespace gmm
 }  // namespace b200ops
 
-extern "C" size_t b200ops_grouped_matmul_workspace_size(int64_t, int64_t, int64_t, int64_t) {
-  return 0;
+// The workspace enables split-K for problems with few output tiles (0 = split-K cannot help
+// this shape).  Without a workspace (NULL) the kernel always runs without split-K.
+extern "C" size_t b200ops_grouped_matmul_workspace_size(int64_t num_tokens, int64_t k, int64_t num_experts,
+                                                        int64_t n) {
+  using namespace b200ops;
+  if (num_tokens <= 0 || k <= 0 || num_experts <= 0 || n <= 0) return 0;
+  return gmm::split_k_possible(num_tokens, k, n, gmm::launch_sms()) ? gmm::workspace_bytes() : 0;
 }
 
 extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_t* group_list,
                                       void* y, int64_t num_tokens, int64_t k, int64_t num_experts,
-                                      int64_t n, void* /*workspace*/, size_t /*workspace_size*/,
-                                      void* stream) {
+                                      int64_t n, void* workspace, size_t workspace_size, void* stream) {
   using namespace b200ops;
   B200OPS_REQUIRE(num_tokens >= 0 && k > 0 && n > 0 && num_experts > 0,
                   "grouped_matmul: bad shape tokens=%lld k=%lld experts=%lld n=%lld",
@@ -323,11 +422,26 @@ extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_
   }
   const int64_t n_tiles = (n + gmm::BN - 1) / gmm::BN;
   const int64_t max_tiles = ((num_tokens + gmm::BM - 1) / gmm::BM + num_experts) * n_tiles;
-  const int grid = static_cast<int>(max_tiles < sm_count() ? max_tiles : sm_count());
-  gmm::grouped_matmul_kernel<<<grid, gmm::kThreads, gmm::kSmemBytes,
-                               static_cast<cudaStream_t>(stream)>>>(
+  const int sms = gmm::launch_sms();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int* counters = nullptr;
+  float* partials = nullptr;
+  int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
+  if (workspace != nullptr && gmm::split_k_possible(num_tokens, k, n, sms)) {
+    if (workspace_size < gmm::workspace_bytes())
+      return fail(B200OPS_EWORKSPACE, "grouped_matmul: workspace of %zu bytes needed, got %zu",
+                  gmm::workspace_bytes(), workspace_size);
+    B200OPS_REQUIRE(aligned16(workspace), "grouped_matmul: workspace must be 16-byte aligned");
+    {
+      counters = static_cast<int*>(workspace);
+      partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + gmm::kCounterBytes);
+      B200OPS_CUDA(cudaMemsetAsync(counters, 0, gmm::kCounterBytes, st));
+      grid = sms;  // idle CTAs exit; the split factor needs the full grid
+    }
+  }
+  gmm::grouped_matmul_kernel<<<grid, gmm::kThreads, gmm::kSmemBytes, st>>>(
       map_x, map_w, group_list, static_cast<__half*>(y), static_cast<int>(num_tokens),
-      static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts));
+      static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts), counters, partials);
   B200OPS_LAUNCH_CHECK("grouped_matmul");
   return B200OPS_OK;
 }

@@ -28,46 +28,55 @@ namespace b200ops {
 namespace moe {
 namespace {
 
-constexpr int kRouteWarps = 4;
 constexpr int kMaxExperts = 256;
 constexpr int kMaxTopK = 8;
 
-// One warp per token.  The token's row is staged in shared memory once and reused for
-// every expert; lanes stride the hidden dimension with 128-bit loads.
-__global__ void __launch_bounds__(kRouteWarps * 32)
+// One CTA per token, one warp per expert (warps loop when there are more experts than warps):
+// every warp forms its expert's dot product with 128-bit loads and four independent
+// accumulators, so even a handful of tokens keeps hundreds of loads in flight.  Warp 0 then
+// does the softmax and the top-k selection.
+__global__ void __launch_bounds__(1024)
 route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, int32_t* __restrict__ ids,
-                  float* __restrict__ weights, int num_tokens, int hidden, int num_experts, int top_k) {
-  extern __shared__ uint4 smem_rows[];
-  __shared__ float logits_s[kRouteWarps][kMaxExperts];
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int token = blockIdx.x * kRouteWarps + warp;
-  if (token >= num_tokens) return;
+                  float* __restrict__ weights, int hidden, int num_experts, int top_k) {
+  __shared__ float logits[kMaxExperts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
+  const int token = blockIdx.x;
   const int vecs = hidden >> 3;
-  uint4* row = smem_rows + static_cast<size_t>(warp) * vecs;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(token) * hidden);
-  for (int v = lane; v < vecs; v += 32) row[v] = xr[v];
-  __syncwarp();
-  float* logits = logits_s[warp];
-  for (int e = 0; e < num_experts; ++e) {
+  for (int e = warp; e < num_experts; e += warps) {
     const uint4* w = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * hidden);
-    float acc = 0.f;
-    for (int v = lane; v < vecs; v += 32) {
-      const uint4 a = row[v];
-      const uint4 b = __ldg(w + v);
-      const uint32_t* as = reinterpret_cast<const uint32_t*>(&a);
-      const uint32_t* bs = reinterpret_cast<const uint32_t*>(&b);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int v0 = lane; v0 < vecs; v0 += 128) {
+      uint4 a[4], b[4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 fa = h2_to_f2(as[j]);
-        const float2 fb = h2_to_f2(bs[j]);
-        acc = fmaf(fa.x, fb.x, acc);
-        acc = fmaf(fa.y, fb.y, acc);
+      for (int u = 0; u < 4; ++u) {
+        const int v = v0 + u * 32;
+        if (v < vecs) {
+          a[u] = __ldg(xr + v);
+          b[u] = __ldg(w + v);
+        } else {
+          a[u] = make_uint4(0, 0, 0, 0);
+          b[u] = make_uint4(0, 0, 0, 0);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const uint32_t* as = reinterpret_cast<const uint32_t*>(&a[u]);
+        const uint32_t* bs = reinterpret_cast<const uint32_t*>(&b[u]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 fa = h2_to_f2(as[j]);
+          const float2 fb = h2_to_f2(bs[j]);
+          acc[u] = fmaf(fa.x, fb.x, acc[u]);
+          acc[u] = fmaf(fa.y, fb.y, acc[u]);
+        }
       }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) logits[e] = __half2float(__float2half_rn(acc));
+    const float dot = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+    if (lane == 0) logits[e] = __half2float(__float2half_rn(dot));
   }
-  __syncwarp();
+  __syncthreads();
+  if (warp != 0) return;
   // softmax over experts in fp32
   float mx = -INFINITY;
   for (int e = lane; e < num_experts; e += 32) mx = fmaxf(mx, logits[e]);
@@ -271,27 +280,14 @@ extern "C" int b200ops_moe_route_topk(const void* x, const void* router_weight, 
                   moe::kMaxExperts, (long long)num_experts);
   B200OPS_REQUIRE(top_k >= 1 && top_k <= moe::kMaxTopK && top_k <= num_experts,
                   "moe_route_topk: top_k must be in 1..min(%d, experts), got %lld", moe::kMaxTopK, (long long)top_k);
-  B200OPS_REQUIRE(hidden * 2 * moe::kRouteWarps <= 200 * 1024, "moe_route_topk: hidden size %lld too large",
-                  (long long)hidden);
   if (num_tokens == 0) return B200OPS_OK;
+  B200OPS_REQUIRE(num_tokens < (1LL << 31), "moe_route_topk: too many tokens");
   B200OPS_REQUIRE(x && router_weight && expert_ids && expert_weights, "moe_route_topk: null pointer");
   B200OPS_REQUIRE(aligned16(x) && aligned16(router_weight), "moe_route_topk: pointers must be 16-byte aligned");
-  const size_t smem = static_cast<size_t>(moe::kRouteWarps) * hidden * 2;
-  if (smem > 48 * 1024) {
-    static bool set[64] = {false};
-    int dev = 0;
-    B200OPS_CUDA(cudaGetDevice(&dev));
-    if (dev >= 0 && dev < 64 && !set[dev]) {
-      B200OPS_CUDA(cudaFuncSetAttribute(moe::route_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        200 * 1024));
-      set[dev] = true;
-    }
-  }
-  const unsigned grid = static_cast<unsigned>((num_tokens + moe::kRouteWarps - 1) / moe::kRouteWarps);
-  moe::route_topk_kernel<<<grid, moe::kRouteWarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
+  const int warps = static_cast<int>(num_experts < 32 ? num_experts : 32);
+  moe::route_topk_kernel<<<static_cast<unsigned>(num_tokens), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half*>(x), static_cast<const __half*>(router_weight), expert_ids, expert_weights,
-      static_cast<int>(num_tokens), static_cast<int>(hidden), static_cast<int>(num_experts),
-      static_cast<int>(top_k));
+      static_cast<int>(hidden), static_cast<int>(num_experts), static_cast<int>(top_k));
   B200OPS_LAUNCH_CHECK("moe_route_topk");
   return B200OPS_OK;
 }

@@ -161,8 +161,11 @@ int b200ops_paged_attention_static(const void* q, const void* key_cache, const v
  *   view is [E, k, n] with strides (n*k, 1, k), csrc/ffi/ops.cpp:171-172);
  *   group_list : int64 [num_experts], inclusive cumulative row ends;  y : f16 [num_tokens, n]
  * Requires k % 64 == 0 and n % 64 == 0 (csrc/ffi/ops.cpp:173).  Rows past gl[E-1] are not
- * written.  Empty groups are skipped (grouped_mat_mul_ex.cpp:40).  No workspace is needed
- * today; the query exists so that callers can keep the two-phase shape.
+ * written.  Empty groups are skipped (grouped_mat_mul_ex.cpp:40).
+ * Workspace: optional.  Shapes with fewer output tiles than SMs (decode batches) run split-K
+ * when a workspace of b200ops_grouped_matmul_workspace_size() bytes is passed (the query
+ * returns 0 for shapes that cannot benefit); the call zeroes the counters it needs itself.
+ * With workspace == NULL the same result is computed without split-K.
  */
 size_t b200ops_grouped_matmul_workspace_size(int64_t num_tokens, int64_t k, int64_t num_experts,
                                              int64_t n);

@@ -278,9 +278,13 @@ def test_paged_attention_workspace_too_small(cabi):
 
 
 # ------------------------------------------------------------------ grouped_matmul
-def run_grouped_matmul(cabi, x, w_storage, gl, fill=float("nan")):
+def run_grouped_matmul(cabi, x, w_storage, gl, fill=float("nan"), split_k=True):
+    """With split_k the call gets the workspace the size query asks for (if any)."""
     y = torch.full((x.shape[0], w_storage.shape[1]), fill, dtype=torch.float16, device=DEV)
-    cabi.grouped_matmul(x.to(DEV), w_storage.to(DEV), gl.to(DEV), y)
+    e, n, k = w_storage.shape
+    nbytes = cabi.grouped_matmul_workspace_size(x.shape[0], k, e, n) if split_k else 0
+    ws = torch.full((nbytes,), 0xAB, dtype=torch.uint8, device=DEV) if nbytes else None
+    cabi.grouped_matmul(x.to(DEV), w_storage.to(DEV), gl.to(DEV), y, ws)
     torch.cuda.synchronize()
     assert cabi.pipeline_status() == 0
     return y.cpu()
@@ -383,3 +387,26 @@ def test_paged_attention_tile_balanced_path(cabi, monkeypatch, heads, kv_heads, 
     want = oracle.paged_attention(w["q"], w["key_cache_clean"], w["value_cache_clean"],
                                   w["block_tables"], w["context_lens"])
     close(run_paged_attention(cabi, w), want)
+
+
+@pytest.mark.parametrize("counts,k,n", [
+    ([256], 4096, 6144),               # decode-size dense projection: 48 tiles -> 3 k-slices each
+    ([40, 0, 3, 90, 7, 64, 1, 128], 14336, 4096),  # expert down projection at decode size
+    ([70], 14336, 4096),               # one expert per GPU: 16 tiles -> 9 k-slices each
+    ([100], 1024, 320),                # N tail with split-K
+    ([130], 512, 256),                 # two m-tiles, second one a tail, 2 k-slices of 4 blocks
+])
+def test_grouped_matmul_split_k(cabi, counts, k, n):
+    g = torch.Generator().manual_seed(sum(counts) + k)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half()
+    w_storage = (torch.randn(len(counts), n, k, generator=g) * 0.03).half()
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64)
+    assert cabi.grouped_matmul_workspace_size(m, k, len(counts), n) > 0
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    split = run_grouped_matmul(cabi, x, w_storage, gl, split_k=True)
+    plain = run_grouped_matmul(cabi, x, w_storage, gl, split_k=False)
+    close(split, want)
+    close(plain, want)
+    # twice in a row on the same workspace contents: the call resets its own counters
+    close(run_grouped_matmul(cabi, x, w_storage, gl, split_k=True), want)

@@ -62,13 +62,19 @@ constexpr int kMaxGrid = 256;
 constexpr size_t kPartialTileBytes = static_cast<size_t>(BM) * BN * sizeof(float);
 constexpr size_t kCounterBytes = kMaxGrid * sizeof(int);
 
-// Host-side gate, shared by the size query and the launch: split-K can only pay off when even
-// the densest packing of the rows leaves at least half of the SMs without a tile, and K is long
-// enough to cut.
+// Host-side gate, shared by the size query and the launch.  Split-K adds a serial tail of
+// about 12 us (publish the partial tile, count, reduce), so it only pays when a tile's k-loop is
+// long: measured on B200, K = 14336 with 16-32 tiles drops from 92-98 us to 47-70 us, while
+// K = 4096 with 32-48 tiles gets slower (29-32 us -> 35-37 us).  Hence K >= 8192, and at least
+// half of the SMs left without a tile even by the densest packing of the rows.  (Narrower
+// output tiles were also tried for these shapes and lost: with BN = 64 two thirds of every
+// stage is the re-read activation tile, and an 8-expert down projection went from 152 to 262 us.)
+constexpr int64_t kMinSplitK = 8192;
+
 inline bool split_k_possible(int64_t num_tokens, int64_t k, int64_t n, int sms) {
   const int64_t n_tiles = (n + BN - 1) / BN;
   const int64_t min_tiles = ((num_tokens + BM - 1) / BM) * n_tiles;
-  return min_tiles * 2 <= sms && k / BK >= 2 * kMinKBlocksPerSplit;
+  return min_tiles * 2 <= sms && k >= kMinSplitK;
 }
 
 inline int launch_sms() { return sm_count() < kMaxGrid ? sm_count() : kMaxGrid; }
@@ -330,25 +336,60 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
           const float* first = partials + static_cast<size_t>(wi.tile) * splits * (BM * BN);
           const int rows_here = min(BM, tc.row_end - tc.row0);
           const int cols_here = min(BN, N - tc.n0);
-          // warp `quarter` reduces rows quarter, quarter+4, ...: a row is read and written by
-          // one warp, 8 columns per lane, coalesced.
-          for (int rr = quarter; rr < rows_here; rr += 4) {
-            const int col = lane * 8;
-            if (col >= cols_here) continue;
-            float acc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int sidx = 0; sidx < splits; ++sidx) {
-              const float4* p = reinterpret_cast<const float4*>(first + static_cast<size_t>(sidx) * (BM * BN) +
-                                                                rr * BN + col);
-              const float4 a = __ldcg(p), b = __ldcg(p + 1);
-              acc8[0] += a.x; acc8[1] += a.y; acc8[2] += a.z; acc8[3] += a.w;
-              acc8[4] += b.x; acc8[5] += b.y; acc8[6] += b.z; acc8[7] += b.w;
+          // Warp `quarter` reduces rows quarter, quarter+4, ...; a row is read and written by one
+          // warp, 8 columns per lane, coalesced.  Four rows and two k-slices are loaded before
+          // anything is added, so each lane keeps sixteen 16-byte loads in flight: the step is a
+          // chain of L2 round trips otherwise.
+          const int col = lane * 8;
+          if (col < cols_here) {
+            for (int r0 = quarter; r0 < rows_here; r0 += 16) {
+              float acc8[4][8];
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc8[j][i] = 0.f;
+              for (int s0 = 0; s0 < splits; s0 += 2) {
+                float4 v[2][4][2];
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    const int rr = r0 + 4 * j;
+                    if (s0 + u < splits && rr < rows_here) {
+                      const float4* p = reinterpret_cast<const float4*>(
+                          first + static_cast<size_t>(s0 + u) * (BM * BN) + rr * BN + col);
+                      v[u][j][0] = __ldcg(p);
+                      v[u][j][1] = __ldcg(p + 1);
+                    } else {
+                      v[u][j][0] = make_float4(0.f, 0.f, 0.f, 0.f);
+                      v[u][j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    }
+                  }
+                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u) {
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    acc8[j][0] += v[u][j][0].x; acc8[j][1] += v[u][j][0].y;
+                    acc8[j][2] += v[u][j][0].z; acc8[j][3] += v[u][j][0].w;
+                    acc8[j][4] += v[u][j][1].x; acc8[j][5] += v[u][j][1].y;
+                    acc8[j][6] += v[u][j][1].z; acc8[j][7] += v[u][j][1].w;
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int rr = r0 + 4 * j;
+                if (rr < rows_here) {
+                  uint4 o;
+                  o.x = f2_to_h2(acc8[j][0], acc8[j][1]);
+                  o.y = f2_to_h2(acc8[j][2], acc8[j][3]);
+                  o.z = f2_to_h2(acc8[j][4], acc8[j][5]);
+                  o.w = f2_to_h2(acc8[j][6], acc8[j][7]);
+                  *reinterpret_cast<uint4*>(y + static_cast<size_t>(tc.row0 + rr) * N + tc.n0 + col) = o;
+                }
+              }
             }
-            uint4 o;
-            o.x = f2_to_h2(acc8[0], acc8[1]);
-            o.y = f2_to_h2(acc8[2], acc8[3]);
-            o.z = f2_to_h2(acc8[4], acc8[5]);
-            o.w = f2_to_h2(acc8[6], acc8[7]);
-            *reinterpret_cast<uint4*>(y + static_cast<size_t>(tc.row0 + rr) * N + tc.n0 + col) = o;
           }
         }
       }

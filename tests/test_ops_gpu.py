@@ -390,11 +390,11 @@ def test_paged_attention_tile_balanced_path(cabi, monkeypatch, heads, kv_heads, 
 
 
 @pytest.mark.parametrize("counts,k,n", [
-    ([256], 4096, 6144),               # decode-size dense projection: 48 tiles -> 3 k-slices each
     ([40, 0, 3, 90, 7, 64, 1, 128], 14336, 4096),  # expert down projection at decode size
     ([70], 14336, 4096),               # one expert per GPU: 16 tiles -> 9 k-slices each
-    ([100], 1024, 320),                # N tail with split-K
-    ([130], 512, 256),                 # two m-tiles, second one a tail, 2 k-slices of 4 blocks
+    ([100], 8192, 320),                # N tail with split-K
+    ([130], 8192, 256),                # two m-tiles, the second one a tail
+    ([256], 16384, 1024),              # dense projection with a long K
 ])
 def test_grouped_matmul_split_k(cabi, counts, k, n):
     g = torch.Generator().manual_seed(sum(counts) + k)

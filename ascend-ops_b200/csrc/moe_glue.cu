@@ -125,10 +125,11 @@ constexpr int kPermuteWarps = kPermuteThreads / 32;
 
 __global__ void __launch_bounds__(kPermuteThreads)
 permute_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ pos, int32_t* __restrict__ counts,
-               int64_t* __restrict__ group_list, int num_slots, int num_experts, int experts_per_rank,
-               int segment_rows) {
-  extern __shared__ int hist[];  // [kPermuteWarps][num_experts], then base[num_experts]
+               int64_t* __restrict__ group_list, int32_t* __restrict__ overflow, int num_slots,
+               int num_experts, int experts_per_rank, int segment_rows) {
+  extern __shared__ int hist[];  // [kPermuteWarps][num_experts], then base[num_experts], limit[num_experts]
   int* base = hist + kPermuteWarps * num_experts;
+  int* limit = base + num_experts;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   for (int i = threadIdx.x; i < kPermuteWarps * num_experts; i += kPermuteThreads) hist[i] = 0;
   __syncthreads();
@@ -149,20 +150,28 @@ permute_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ pos, int32
       run += c;
     }
     base[e] = run;  // total of expert e for now
-    counts[e] = run;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
+    // A destination rank's segment holds at most segment_rows rows (segment_rows == 0: one
+    // unbounded segment).  Rows that do not fit are dropped: their slot maps to -1, the count
+    // sent to the peers is clamped, and the overflow flag is raised for the caller to act on.
     long long cum = 0;
-    int in_segment = 0;
+    int in_segment = 0, dropped = 0;
     for (int e = 0; e < num_experts; ++e) {
       const int c = base[e];
       if (e % experts_per_rank == 0) in_segment = 0;
+      int keep = c;
+      if (segment_rows > 0) keep = min(c, max(0, segment_rows - in_segment));
+      dropped += c - keep;
       base[e] = (e / experts_per_rank) * segment_rows + in_segment;
-      in_segment += c;
-      cum += c;
+      limit[e] = base[e] + keep;
+      counts[e] = keep;
+      in_segment += keep;
+      cum += keep;
       group_list[e] = cum;
     }
+    if (overflow != nullptr) *overflow = dropped;
   }
   __syncthreads();
   for (int s0 = lo; s0 < hi; s0 += 32) {
@@ -173,7 +182,8 @@ permute_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ pos, int32
     const unsigned peers = __match_any_sync(0xffffffffu, e);
     const int before = __popc(peers & ((1u << lane) - 1u));
     if (e >= 0) {
-      pos[s] = base[e] + my[e] + before;
+      const int p = base[e] + my[e] + before;
+      pos[s] = p < limit[e] ? p : -1;
     } else if (ok) {
       pos[s] = -1;
     }
@@ -293,21 +303,22 @@ extern "C" int b200ops_moe_route_topk(const void* x, const void* router_weight, 
 }
 
 extern "C" int b200ops_moe_permute(const int32_t* expert_ids, int32_t* slot_to_row, int32_t* counts,
-                                   int64_t* group_list, int64_t num_slots, int64_t num_experts,
-                                   int64_t world, int64_t segment_rows, void* stream) {
+                                   int64_t* group_list, int32_t* overflow, int64_t num_slots,
+                                   int64_t num_experts, int64_t world, int64_t segment_rows,
+                                   void* stream) {
   B200OPS_REQUIRE(num_slots >= 0 && num_slots < (1LL << 30), "moe_permute: bad slot count %lld", (long long)num_slots);
   B200OPS_REQUIRE(num_experts >= 1 && num_experts <= moe::kMaxExperts, "moe_permute: 1..%d experts, got %lld",
                   moe::kMaxExperts, (long long)num_experts);
   B200OPS_REQUIRE(world >= 1 && num_experts % world == 0,
                   "moe_permute: experts (%lld) must divide evenly over ranks (%lld)", (long long)num_experts,
                   (long long)world);
-  B200OPS_REQUIRE(segment_rows >= num_slots || world == 1,
-                  "moe_permute: a rank's segment (%lld rows) must hold all %lld slots", (long long)segment_rows,
-                  (long long)num_slots);
+  B200OPS_REQUIRE(world == 1 || (segment_rows > 0 && segment_rows * world < (1LL << 31)),
+                  "moe_permute: bad segment capacity %lld", (long long)segment_rows);
   B200OPS_REQUIRE(slot_to_row && counts && group_list && (expert_ids || num_slots == 0), "moe_permute: null pointer");
-  const size_t smem = (static_cast<size_t>(moe::kPermuteWarps) + 1) * num_experts * sizeof(int);
+  const size_t smem = (static_cast<size_t>(moe::kPermuteWarps) + 2) * num_experts * sizeof(int);
   moe::permute_kernel<<<1, moe::kPermuteThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      expert_ids, slot_to_row, counts, group_list, static_cast<int>(num_slots), static_cast<int>(num_experts),
+      expert_ids, slot_to_row, counts, group_list, overflow, static_cast<int>(num_slots),
+      static_cast<int>(num_experts),
       static_cast<int>(num_experts / world), static_cast<int>(world == 1 ? 0 : segment_rows));
   B200OPS_LAUNCH_CHECK("moe_permute");
   return B200OPS_OK;

@@ -317,19 +317,23 @@ std::tuple<at::Tensor, at::Tensor> moe_route_topk(at::Tensor x, at::Tensor route
   return {ids, wts};
 }
 
-std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_permute(at::Tensor expert_ids, int64_t num_experts,
-                                                           int64_t world, int64_t segment_rows) {
+// Returns (slot_to_row, counts, group_list, overflow[1]).
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> moe_permute(at::Tensor expert_ids,
+                                                                       int64_t num_experts, int64_t world,
+                                                                       int64_t segment_rows) {
   check_i32_cuda(expert_ids, "moe_permute", "expert_ids");
   const c10::cuda::CUDAGuard guard(expert_ids.device());
   const int64_t slots = expert_ids.numel();
   at::Tensor pos = at::empty({slots}, expert_ids.options());
   at::Tensor counts = at::empty({num_experts}, expert_ids.options());
   at::Tensor gl = at::empty({num_experts}, expert_ids.options().dtype(at::kLong));
+  at::Tensor overflow = at::empty({1}, expert_ids.options());
   check_status(b200ops_moe_permute(expert_ids.data_ptr<int32_t>(), pos.data_ptr<int32_t>(),
-                                   counts.data_ptr<int32_t>(), gl.data_ptr<int64_t>(), slots, num_experts,
-                                   world, segment_rows, current_stream()),
+                                   counts.data_ptr<int32_t>(), gl.data_ptr<int64_t>(),
+                                   overflow.data_ptr<int32_t>(), slots, num_experts, world, segment_rows,
+                                   current_stream()),
                "moe_permute");
-  return {pos, counts, gl};
+  return {pos, counts, gl, overflow};
 }
 
 std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_ep_plan(at::Tensor all_counts, int64_t rank,

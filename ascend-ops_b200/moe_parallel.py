@@ -132,7 +132,7 @@ def expert_parallel_mlp(x, expert_ids, expert_weights, num_experts, local_mlp, g
 
 
 def expert_parallel_mlp_device(moe, x, expert_ids, expert_weights, num_experts, local_mlp, group=None,
-                               segment_rows=None):
+                               segment_rows=None, overflow_out=None):
     """Same contract as expert_parallel_mlp, built from the library's own glue kernels
     (`ascend910a_extras.moe`) with every piece of metadata on the device: no host
     synchronisation anywhere in the step.
@@ -143,19 +143,23 @@ def expert_parallel_mlp_device(moe, x, expert_ids, expert_weights, num_experts, 
     can be owed), of which only the leading rows are meaningful; the per-expert counts
     travel in a small all-gather and stay on the device, where `moe.ep_plan` turns them into
     the grouped order and the group ends grouped_matmul reads.  All ranks must pass the same
-    `segment_rows`.
+    `segment_rows`.  A capacity below T*top_k can overflow: rows that do not fit are left out of
+    the result and counted in a device int32 that is appended to `overflow_out` (a list) for the
+    caller to inspect later -- reading it here would be the host sync this path exists to avoid.
     """
     t, top_k = expert_ids.shape
     slots, hidden = t * top_k, x.shape[1]
     distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
     if not distributed:
-        pos, _, group_list = moe.permute(expert_ids, num_experts, 1, 0)
+        pos, _, group_list, _ = moe.permute(expert_ids, num_experts, 1, 0)
         rows = x.new_empty(slots, hidden)
         moe.copy_rows(rows, x, dst_index=pos, src_div=top_k, n_max=slots)
         return moe.finalize(local_mlp(rows, group_list), pos, expert_weights)
     rank, world = dist.get_rank(group), dist.get_world_size(group)
     cap = slots if segment_rows is None else int(segment_rows)
-    pos, counts, _ = moe.permute(expert_ids, num_experts, world, cap)
+    pos, counts, _, overflow = moe.permute(expert_ids, num_experts, world, cap)
+    if overflow_out is not None:
+        overflow_out.append(overflow)
     send = x.new_empty(world * cap, hidden)
     moe.copy_rows(send, x, dst_index=pos, src_div=top_k, n_max=slots)
     all_counts = counts.new_empty(world * num_experts)
@@ -171,3 +175,77 @@ def expert_parallel_mlp_device(moe, x, expert_ids, expert_weights, num_experts, 
     returned = torch.empty_like(back)
     dist.all_to_all_single(returned, back, group=group)
     return moe.finalize(returned, pos, expert_weights)
+
+
+# --------------------------------------------------------------------------- balanced placement
+@dataclass
+class Placement:
+    """Which expert each slot holds.  Slots are placed contiguously on ranks
+    (`slots_per_rank` each), so a slot id is used as the expert id of the exchange; an expert
+    with several slots is replicated and its rows are spread over the replicas."""
+    slot_expert: torch.Tensor    # [num_slots] expert held by each slot
+    expert_slots: torch.Tensor   # [E, max_replicas] slots of each expert, padded by repeating
+    num_replicas: torch.Tensor   # [E]
+    slots_per_rank: int
+
+    @property
+    def num_slots(self):
+        return int(self.slot_expert.numel())
+
+    def local_slot_experts(self, rank):
+        s = self.slots_per_rank
+        return self.slot_expert[rank * s:(rank + 1) * s].tolist()
+
+
+def balanced_placement(load, world: int, slots_per_rank: int) -> Placement:
+    """Replicate heavily loaded experts and pack the replicas onto ranks so that every rank
+    gets about the same number of rows.
+
+    `load[e]` = expected rows of expert e (a routing histogram).  With one slot per expert a
+    skewed router leaves most GPUs idle: the busiest expert bounds the step.  Here the
+    world*slots_per_rank slots go first one to each expert, then one at a time to the expert
+    with the largest load per replica; the replicas (each worth load/replicas rows) are then
+    assigned largest-first to the rank with the least load that still has a free slot.
+    """
+    load = [float(v) for v in load]
+    num_experts = len(load)
+    num_slots = world * slots_per_rank
+    assert num_slots >= num_experts, "need at least one slot per expert"
+    replicas = [1] * num_experts
+    for _ in range(num_slots - num_experts):
+        e = max(range(num_experts), key=lambda i: (load[i] / replicas[i], -i))
+        replicas[e] += 1
+    items = sorted(((load[e] / replicas[e], e) for e in range(num_experts) for _ in range(replicas[e])),
+                   key=lambda t: (-t[0], t[1]))
+    rank_load = [0.0] * world
+    rank_slots = [[] for _ in range(world)]
+    for share, e in items:
+        r = min((r for r in range(world) if len(rank_slots[r]) < slots_per_rank),
+                key=lambda r: (rank_load[r], r))
+        rank_slots[r].append(e)
+        rank_load[r] += share
+    slot_expert = torch.tensor([e for r in range(world) for e in sorted(rank_slots[r])], dtype=torch.long)
+    max_rep = max(replicas)
+    table = torch.zeros(num_experts, max_rep, dtype=torch.long)
+    for e in range(num_experts):
+        mine = torch.nonzero(slot_expert == e).flatten()
+        table[e] = mine[torch.arange(max_rep) % mine.numel()]
+    return Placement(slot_expert, table, torch.tensor(replicas, dtype=torch.long), slots_per_rank)
+
+
+def to_slot_ids(expert_ids: torch.Tensor, placement: Placement, token_offset: int = 0) -> torch.Tensor:
+    """Replace expert ids [T, top_k] by slot ids: replica (token index mod replicas) of the
+    expert, which spreads an expert's rows evenly over its replicas without any counting."""
+    dev = expert_ids.device
+    ids = expert_ids.long()
+    t = torch.arange(token_offset, token_offset + ids.shape[0], device=dev)[:, None]
+    which = t % placement.num_replicas.to(dev)[ids]
+    return placement.expert_slots.to(dev)[ids, which].to(expert_ids.dtype)
+
+
+def placement_balance(load, placement: Placement, world: int) -> float:
+    """mean / max rows per rank under the placement (1.0 = perfectly even)."""
+    per_rank = [0.0] * world
+    for s, e in enumerate(placement.slot_expert.tolist()):
+        per_rank[s // placement.slots_per_rank] += float(load[e]) / int(placement.num_replicas[e])
+    return sum(per_rank) / (world * max(per_rank)) if max(per_rank) > 0 else 1.0

@@ -201,11 +201,11 @@ def case_rope(ops, dev, steps, warmup, peaks):
     return op_record("rope", f"q[{t},{hq},{d}] k[{t},{hkv},{d}] f16", nbytes, us, peaks, "hbm", launches=1)
 
 
-def case_reshape_and_cache(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_NHD):
-    c = wl.reshape_and_cache_inputs(layout=layout)
+def case_reshape_and_cache(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_NHD, tokens=2048):
+    c = wl.reshape_and_cache_inputs(tokens=tokens, layout=layout)
     t, hkv, d = c["key"].shape
     nbytes = 2 * (t * hkv * d * 2) * 2 + 4 * t
-    n = 16
+    n = 16 if tokens <= 4096 else 3
     g = torch.Generator().manual_seed(77)
     keys = [c["key"].to(dev).clone() for _ in range(n)]
     vals = [c["value"].to(dev).clone() for _ in range(n)]
@@ -215,7 +215,8 @@ def case_reshape_and_cache(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_N
     vc = torch.zeros(c["cache_shape"], dtype=torch.float16, device=dev)
     us, _ = time_graph(lambda i: ops.reshape_and_cache(keys[i], vals[i], kc, vc, slots[i]), n, 2 * n,
                        steps, warmup, dev)
-    name = "reshape_and_cache" + ("" if layout == wl.KV_LAYOUT_NHD else "_nz")
+    name = "reshape_and_cache" + ("" if layout == wl.KV_LAYOUT_NHD else "_nz") + (
+        "" if tokens == 2048 else f"_{tokens}tok")
     return op_record(name, f"{t} tokens -> cache {list(c['cache_shape'])} f16", nbytes, us, peaks, "hbm",
                      launches=1)
 
@@ -367,8 +368,13 @@ def run_layer(ops, dev, rank, world, group, steps, warmup, peaks):
 def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
     """The grouped-GEMM benchmark config as a whole MoE MLP: 4096 tokens, top-2 of 8 experts with
     softmax(N(0,1)) routing skew (8192 routed rows), gate_up [4096 -> 2*14336], swiglu, down
-    [14336 -> 4096].  Tokens are sharded over ranks, experts are placed contiguously on ranks,
-    rows travel with the fixed-capacity all-to-all.  Reports whole-job TFLOP/s of the two GEMMs."""
+    [14336 -> 4096].  Tokens are sharded over ranks.  Experts are placed by load: every rank has
+    ceil(E/G) + 2 slots, hot experts are replicated into the spare slots and their rows spread
+    over the replicas (moe_parallel.balanced_placement), because with one expert per GPU the
+    busiest expert (47 % of the rows here) would bound the step.  Rows travel with the
+    fixed-capacity all-to-all at twice the balanced share per peer; an overflow is detected on
+    the device and the measurement repeated at full capacity.  Reports whole-job TFLOP/s of the
+    two GEMMs (everything else in the step is overhead counted against them)."""
     import ascend910a_extras.moe as moe
     import moe_decode_layer as mdl
     import moe_parallel
@@ -377,47 +383,65 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
     tokens, top_k = 4096, 2
     _, ids_flat = wl.moe_group_list(rows=tokens * top_k, experts=cfg.experts, seed=4)
     ids = ids_flat.view(tokens, top_k).int()
+    load = torch.bincount(ids_flat, minlength=cfg.experts).tolist()
     per = tokens // world
+    spr = -(-cfg.experts // world) + (2 if world > 1 else 0)
+    placement = moe_parallel.balanced_placement(load, world, spr)
+    placement.expert_slots = placement.expert_slots.to(dev)
+    placement.num_replicas = placement.num_replicas.to(dev)
     my_ids = ids[rank * per:(rank + 1) * per].contiguous().to(dev)
     g = torch.Generator(device=dev).manual_seed(40 + rank)
     x = torch.randn(per, cfg.hidden, generator=g, device=dev, dtype=torch.float16)
     wts = torch.full((per, top_k), 0.5, device=dev)
-    mine = moe_parallel.local_experts(cfg.experts, world, rank).tolist()
-    w = mdl.make_weights(cfg, seed=7, experts=mine, device=dev)
+    w = mdl.make_weights(cfg, seed=7, experts=placement.local_slot_experts(rank), device=dev)
     w_gu, w_dn = w["w_gate_up"].transpose(1, 2), w["w_down"].transpose(1, 2)
+    full_cap = per * top_k
+    # twice the share a peer is owed under perfect balance, rounded up to 64 rows
+    cap = min(full_cap, (-(-2 * full_cap // world) + 63) // 64 * 64) if world > 1 else full_cap
 
     def local_mlp(rows, gl):
         return ops.grouped_matmul(ops.swiglu(ops.grouped_matmul(rows, w_gu, gl)), w_dn, gl)
 
-    def step():
-        return moe_parallel.expert_parallel_mlp_device(moe, x, my_ids, wts, cfg.experts, local_mlp, group,
-                                                       per * top_k)
+    def measure(capacity):
+        flags = []
 
-    for _ in range(warmup):
-        step()
-    torch.cuda.synchronize(dev)
-    if world > 1:
-        torch.distributed.barrier(group)
-    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    t0.record()
-    for _ in range(steps):
-        step()
-    t1.record()
-    torch.cuda.synchronize(dev)
-    t = torch.tensor([t0.elapsed_time(t1)], device=dev)
-    if world > 1:
-        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=group)
-    us = float(t) * 1e3 / steps
+        def step():
+            slot_ids = moe_parallel.to_slot_ids(my_ids, placement, rank * per)
+            return moe_parallel.expert_parallel_mlp_device(moe, x, slot_ids, wts, placement.num_slots, local_mlp,
+                                                           group, capacity, overflow_out=flags)
+
+        for _ in range(warmup):
+            step()
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            torch.distributed.barrier(group)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
+        for _ in range(steps):
+            step()
+        t1.record()
+        torch.cuda.synchronize(dev)
+        t = torch.tensor([t0.elapsed_time(t1), float(flags[-1].item()) if flags else 0.0], device=dev)
+        if world > 1:
+            torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=group)
+        return float(t[0]) * 1e3 / steps, int(t[1])
+
+    us, dropped = measure(cap)
+    used_cap = cap
+    if dropped > 0:
+        us, dropped = measure(full_cap)
+        used_cap = full_cap
     flops = 2 * tokens * top_k * cfg.hidden * 3 * cfg.intermediate
-    counts = torch.bincount(ids_flat, minlength=cfg.experts)
-    per_rank = [int(counts[moe_parallel.local_experts(cfg.experts, world, r)].sum()) for r in range(world)]
     tf = flops / us / 1e6
     return {"op": "moe_mlp_expert_parallel", "shape": "4096 tokens top-2 of 8 experts, 4096->2x14336->4096 f16",
             "flops": flops, "us": round(us, 1), "achieved": round(tf, 1), "unit": "TFLOP/s",
             "peak": peaks["bf16_tflops"] * world, "frac": round(tf / (peaks["bf16_tflops"] * world), 4),
-            "bound": "tensor", "launches": 8 if world == 1 else 11, "rows_per_rank": per_rank,
-            "balance_ceiling": round(sum(per_rank) / (world * max(per_rank)), 3),
-            "includes": "route-independent glue, swiglu and (for >1 GPU) dispatch/combine all-to-all"}
+            "bound": "tensor", "launches": 8 if world == 1 else 11, "rows_per_expert": load,
+            "slots_per_rank": spr, "replicas_per_expert": placement.num_replicas.tolist(),
+            "balance": round(moe_parallel.placement_balance(load, placement, world), 3),
+            "one_expert_per_slot_balance": round(sum(load) / (cfg.experts * max(load)), 3),
+            "segment_rows": used_cap, "dropped_rows": dropped,
+            "includes": "slot remap, permutation, swiglu and (for >1 GPU) dispatch/combine all-to-all"}
 
 
 # --------------------------------------------------------------------------- CPU baseline
@@ -572,6 +596,9 @@ def main():
     cases = {
         "add_rms_norm": case_add_rms_norm, "reshape_and_cache": case_reshape_and_cache,
         "reshape_and_cache_nz": lambda *a: case_reshape_and_cache(*a, layout=wl.KV_LAYOUT_NZ),
+        # same kernel on a prefill-size batch: shows its streaming rate once the launch is not
+        # a single DRAM round trip
+        "reshape_and_cache_32768tok": lambda *a: case_reshape_and_cache(*a, tokens=32768),
         "rope": case_rope, "swiglu": case_swiglu, "paged_attention": case_paged_attention,
         "grouped_matmul_gate_up": lambda *a: case_grouped_matmul(*a, which="gate_up"),
         "grouped_matmul_down": lambda *a: case_grouped_matmul(*a, which="down"),

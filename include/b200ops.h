@@ -206,6 +206,11 @@ int b200ops_fused_qkv_rope_cache(const void* qkv, const int32_t* position_ids, c
  *   world == 1: rows are packed expert-major from row 0.  world > 1 (experts placed
  *   contiguously, num_experts/world per rank): rows for rank r start at r*segment_rows and are
  *   packed by expert inside that segment -- the layout an equal-split all-to-all sends.
+ *   A segment holds at most segment_rows rows; with segment_rows >= num_slots nothing can be
+ *   lost.  A smaller capacity trades exchange volume for the risk of overflow: rows that do
+ *   not fit get slot_to_row = -1 (finalize then leaves their contribution out), counts are
+ *   clamped, and *overflow (int32, may be NULL) receives the number of dropped rows so the
+ *   caller can repeat the step with a larger capacity.
  * ep_plan: on the receiving rank.  all_counts int32 [world, num_experts] (every rank's
  *   `counts`, all-gathered).  grouped_to_received[d] = row of the received buffer
  *   ([world segments of segment_rows]) that supplies grouped (expert-major) row d;
@@ -219,8 +224,8 @@ int b200ops_moe_route_topk(const void* x, const void* router_weight, int32_t* ex
                            float* expert_weights, int64_t num_tokens, int64_t hidden,
                            int64_t num_experts, int64_t top_k, void* stream);
 int b200ops_moe_permute(const int32_t* expert_ids, int32_t* slot_to_row, int32_t* counts,
-                        int64_t* group_list, int64_t num_slots, int64_t num_experts, int64_t world,
-                        int64_t segment_rows, void* stream);
+                        int64_t* group_list, int32_t* overflow, int64_t num_slots, int64_t num_experts,
+                        int64_t world, int64_t segment_rows, void* stream);
 int b200ops_moe_ep_plan(const int32_t* all_counts, int32_t* grouped_to_received, int64_t* group_list,
                         int32_t* total_rows, int64_t world, int64_t num_experts, int64_t rank,
                         int64_t segment_rows, void* stream);

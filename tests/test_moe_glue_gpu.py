@@ -54,8 +54,8 @@ def test_permute_is_the_stable_sort(cabi, tokens, top_k, experts, world):
     pos = torch.full((slots,), -5, dtype=torch.int32, device=DEV)
     counts = torch.zeros(experts, dtype=torch.int32, device=DEV)
     gl = torch.zeros(experts, dtype=torch.int64, device=DEV)
-    cabi.check(cabi.load().b200ops_moe_permute(p(idd), p(pos), p(counts), p(gl), slots, experts, world, cap,
-                                               stream()))
+    cabi.check(cabi.load().b200ops_moe_permute(p(idd), p(pos), p(counts), p(gl), None, slots, experts, world,
+                                               cap, stream()))
     torch.cuda.synchronize()
     flat = ids.reshape(-1).long()
     want_counts = torch.bincount(flat, minlength=experts)
@@ -112,7 +112,7 @@ def test_copy_rows_and_finalize(cabi):
     pos = torch.empty(t * k, dtype=torch.int32, device=DEV)
     counts = torch.empty(4, dtype=torch.int32, device=DEV)
     gl = torch.empty(4, dtype=torch.int64, device=DEV)
-    cabi.check(lib.b200ops_moe_permute(p(ids), p(pos), p(counts), p(gl), t * k, 4, 1, 0, stream()))
+    cabi.check(lib.b200ops_moe_permute(p(ids), p(pos), p(counts), p(gl), None, t * k, 4, 1, 0, stream()))
     rows = torch.zeros(t * k, h, dtype=torch.float16, device=DEV)
     cabi.check(lib.b200ops_moe_copy_rows(p(rows), p(x), p(pos), None, k, None, t * k, h, stream()))
     torch.cuda.synchronize()
@@ -133,3 +133,24 @@ def test_copy_rows_and_finalize(cabi):
     torch.cuda.synchronize()
     want = (rows[pos.long()].float().view(t, k, h) * wts[:, :, None]).sum(1)
     torch.testing.assert_close(y.float(), want, rtol=1e-2, atol=1e-3)
+
+
+def test_permute_bounded_capacity_drops_and_reports(cabi):
+    """Two ranks, two experts each, capacity 5 rows per destination: 9 rows want rank 0."""
+    ids = torch.tensor([0, 1, 0, 0, 3, 1, 1, 0, 2, 0, 1, 3], dtype=torch.int32, device=DEV)  # e0 x5, e1 x4, e2 x1, e3 x2
+    pos = torch.empty(12, dtype=torch.int32, device=DEV)
+    counts = torch.empty(4, dtype=torch.int32, device=DEV)
+    gl = torch.empty(4, dtype=torch.int64, device=DEV)
+    ov = torch.full((1,), -1, dtype=torch.int32, device=DEV)
+    cabi.check(cabi.load().b200ops_moe_permute(p(ids), p(pos), p(counts), p(gl), p(ov), 12, 4, 2, 5, stream()))
+    torch.cuda.synchronize()
+    assert counts.cpu().tolist() == [5, 0, 1, 2]  # expert 1's four rows do not fit behind expert 0's five
+    assert int(ov) == 4
+    got = pos.cpu().tolist()
+    assert [got[i] for i in (0, 2, 3, 7, 9)] == [0, 1, 2, 3, 4]  # expert 0, stable order, segment 0
+    assert [got[i] for i in (1, 5, 6, 10)] == [-1] * 4             # dropped
+    assert got[8] == 5 and [got[4], got[11]] == [6, 7]             # segment 1 starts at row 5
+    # ample capacity: nothing dropped
+    cabi.check(cabi.load().b200ops_moe_permute(p(ids), p(pos), p(counts), p(gl), p(ov), 12, 4, 2, 12, stream()))
+    torch.cuda.synchronize()
+    assert int(ov) == 0 and counts.cpu().tolist() == [5, 4, 1, 2] and (pos >= 0).all()

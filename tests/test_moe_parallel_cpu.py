@@ -110,3 +110,33 @@ def test_two_gloo_ranks_dispatch_and_combine():
         p.join(120)
         assert p.exitcode == 0
     assert dict(results) == {0: True, 1: True}
+
+
+def test_balanced_placement_replicates_hot_experts():
+    load = [99, 512, 3881, 990, 1329, 287, 98, 996]  # the benchmark's routing skew
+    plain = moe_parallel.balanced_placement(load, 8, 1)
+    assert sorted(plain.slot_expert.tolist()) == list(range(8))
+    assert moe_parallel.placement_balance(load, plain, 8) < 0.3  # one expert per GPU: the hot one dominates
+    p = moe_parallel.balanced_placement(load, 8, 3)
+    assert p.num_slots == 24 and int(p.num_replicas.sum()) == 24 and int(p.num_replicas.min()) >= 1
+    assert int(p.num_replicas[2]) == int(p.num_replicas.max())
+    assert moe_parallel.placement_balance(load, p, 8) > 0.85
+    for e in range(8):  # the slot table lists exactly the slots that hold the expert
+        assert set(p.expert_slots[e].tolist()) == set(torch.nonzero(p.slot_expert == e).flatten().tolist())
+    # fewer ranks than experts
+    p2 = moe_parallel.balanced_placement(load, 2, 6)
+    assert moe_parallel.placement_balance(load, p2, 2) > 0.9
+
+
+def test_slot_ids_keep_the_expert_and_spread_over_replicas():
+    load = [10, 1000, 10, 10]
+    p = moe_parallel.balanced_placement(load, 4, 2)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.stack([torch.randperm(4, generator=g)[:2] for _ in range(4000)]).int()
+    slots = moe_parallel.to_slot_ids(ids, p)
+    assert torch.equal(p.slot_expert[slots.long()], ids.long())  # a slot always holds the routed expert
+    hot = slots[ids == 1].long()
+    used = torch.bincount(hot, minlength=p.num_slots)
+    reps = int(p.num_replicas[1])
+    assert reps > 1 and int((used > 0).sum()) == reps and int(used.max()) < 1.25 * int(used[used > 0].min())
+    assert (slots[:, 0] != slots[:, 1]).all()  # top-k experts differ, so their slots differ

@@ -14,3 +14,5 @@ ep_plan = _C.moe.ep_plan
 copy_rows = _C.moe.copy_rows
 finalize = _C.moe.finalize
 fused_qkv_rope_cache = _C.moe.fused_qkv_rope_cache
+push_rows = _C.moe.push_rows
+peer_barrier = _C.moe.peer_barrier

@@ -370,3 +370,148 @@ extern "C" int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row
   B200OPS_LAUNCH_CHECK("moe_finalize");
   return B200OPS_OK;
 }
+
+// ---------------------------------------------------------------------------------------
+// Expert-parallel exchange over peer memory (NVLink / NVSwitch), in place of NCCL.
+//
+// Every rank owns a receive buffer of `world` segments of `cap` rows in memory that its peers
+// have mapped (symmetric memory).  A sender does not stage rows in a send buffer and hand them
+// to a collective: the kernel that gathers the routed rows stores each row directly into the
+// destination rank's segment (plain 16-byte stores through the peer mapping), and writes its
+// per-expert counts into every peer's count table in the same launch.  A second, one-CTA
+// kernel is the barrier: a system-scope release of "I have pushed step n" into every peer's
+// flag array, then a bounded wait until every peer has said the same.  The wait gives up after
+// two seconds, records an error code and returns, so a missing peer cannot hang the GPU.
+// Flags carry a step number kept on the device, never reset, so the same launches can be
+// replayed from a CUDA graph.
+namespace b200ops {
+namespace moe {
+namespace {
+
+constexpr int kMaxPeers = 64;
+
+struct PeerTable {
+  void* base[kMaxPeers];
+};
+
+// Logical row i (i < *n_valid, or n_max) of `src` (row i / src_div) goes to peer idx / cap,
+// row my_rank * cap + idx % cap of that peer's buffer, where idx = index[i] (negative: skip).
+// CTA 0 additionally copies `counts` into row my_rank of every peer's count table.
+__global__ void __launch_bounds__(128)
+push_rows_kernel(const __half* __restrict__ src, const int32_t* __restrict__ index, int src_div,
+                 const int32_t* __restrict__ n_valid, PeerTable rows, int cap, int my_rank, int row_vecs,
+                 const int32_t* __restrict__ counts, int num_counts, PeerTable count_tables, int world) {
+  const int i = blockIdx.x;
+  if (i == 0 && counts != nullptr) {
+    for (int t = threadIdx.x; t < num_counts * world; t += blockDim.x) {
+      const int peer = t / num_counts, e = t - peer * num_counts;
+      static_cast<int32_t*>(count_tables.base[peer])[my_rank * num_counts + e] = counts[e];
+    }
+  }
+  if (n_valid != nullptr && i >= *n_valid) return;
+  const int idx = index[i];
+  if (idx < 0) return;
+  const int peer = idx / cap, off = idx - peer * cap;
+  const uint4* s = reinterpret_cast<const uint4*>(src) + static_cast<size_t>(i / src_div) * row_vecs;
+  uint4* d = static_cast<uint4*>(rows.base[peer]) + (static_cast<size_t>(my_rank) * cap + off) * row_vecs;
+  for (int v = threadIdx.x; v < row_vecs; v += blockDim.x) d[v] = s[v];
+}
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// One CTA, thread t talks to peer t.  `state[0]` = this rank's step counter, `state[1]` = error
+// word (0 ok, otherwise 100 + the peer that never arrived).  flags[r] on a rank = last step
+// rank r announced.  The preceding kernel on the stream has completed, so its peer stores are
+// ordered before the release below.
+__global__ void __launch_bounds__(kMaxPeers)
+peer_barrier_kernel(PeerTable flag_arrays, uint32_t* __restrict__ my_flags, uint32_t* __restrict__ state,
+                    int world, int my_rank) {
+  __shared__ uint32_t step_s;
+  if (threadIdx.x == 0) step_s = state[0] + 1;
+  __syncthreads();
+  const uint32_t step = step_s;
+  const int t = threadIdx.x;
+  if (t < world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(flag_arrays.base[t]) + my_rank, step);
+    const uint64_t t0 = [] {
+      uint64_t x;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(x));
+      return x;
+    }();
+    uint32_t spins = 0;
+    // step numbers only grow; compare with wrap-around in mind
+    while (static_cast<int32_t>(ld_acquire_sys(my_flags + t) - step) < 0) {
+      if ((++spins & 0xffu) == 0) {
+        uint64_t now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (now - t0 > 2000000000ull) {
+          atomicCAS(reinterpret_cast<unsigned int*>(state + 1), 0u, 100u + static_cast<unsigned>(t));
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) state[0] = step;
+}
+
+}  // namespace
+}  // namespace moe
+}  // namespace b200ops
+
+extern "C" int b200ops_moe_push_rows(const void* src, const int32_t* index, int64_t src_div,
+                                     const int32_t* n_valid, int64_t n_max, void* const* peer_rows,
+                                     int64_t world, int64_t cap, int64_t my_rank, int64_t row_elems,
+                                     const int32_t* counts, int64_t num_counts, void* const* peer_counts,
+                                     void* stream) {
+  B200OPS_REQUIRE(world >= 1 && world <= moe::kMaxPeers && my_rank >= 0 && my_rank < world && cap > 0 &&
+                      cap * world < (1LL << 31),
+                  "moe_push_rows: bad geometry world=%lld rank=%lld cap=%lld", (long long)world,
+                  (long long)my_rank, (long long)cap);
+  B200OPS_REQUIRE(n_max >= 0 && n_max < (1LL << 31) && row_elems > 0 && row_elems % 8 == 0 && src_div >= 1,
+                  "moe_push_rows: bad shape n=%lld row=%lld div=%lld", (long long)n_max, (long long)row_elems,
+                  (long long)src_div);
+  B200OPS_REQUIRE(peer_rows != nullptr && (counts == nullptr || (peer_counts != nullptr && num_counts > 0)),
+                  "moe_push_rows: null peer table");
+  B200OPS_REQUIRE(n_max == 0 || (src && index && aligned16(src)), "moe_push_rows: null or misaligned pointer");
+  moe::PeerTable rows, cnt;
+  for (int r = 0; r < moe::kMaxPeers; ++r) {
+    rows.base[r] = r < world ? peer_rows[r] : nullptr;
+    cnt.base[r] = (counts != nullptr && r < world) ? peer_counts[r] : nullptr;
+    B200OPS_REQUIRE(r >= world || (rows.base[r] != nullptr && aligned16(rows.base[r])),
+                    "moe_push_rows: peer %d has no buffer", r);
+  }
+  const unsigned grid = static_cast<unsigned>(n_max > 0 ? n_max : 1);
+  moe::push_rows_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(src), index, static_cast<int>(src_div), n_max > 0 ? n_valid : nullptr, rows,
+      static_cast<int>(cap), static_cast<int>(my_rank), static_cast<int>(row_elems / 8), counts,
+      static_cast<int>(num_counts), cnt, static_cast<int>(world));
+  B200OPS_LAUNCH_CHECK("moe_push_rows");
+  return B200OPS_OK;
+}
+
+extern "C" int b200ops_peer_barrier(void* const* peer_flags, void* my_flags, void* state, int64_t world,
+                                    int64_t my_rank, void* stream) {
+  B200OPS_REQUIRE(world >= 1 && world <= moe::kMaxPeers && my_rank >= 0 && my_rank < world,
+                  "peer_barrier: bad geometry world=%lld rank=%lld", (long long)world, (long long)my_rank);
+  B200OPS_REQUIRE(peer_flags && my_flags && state, "peer_barrier: null pointer");
+  moe::PeerTable flags;
+  for (int r = 0; r < moe::kMaxPeers; ++r) {
+    flags.base[r] = r < world ? peer_flags[r] : nullptr;
+    B200OPS_REQUIRE(r >= world || flags.base[r] != nullptr, "peer_barrier: peer %d has no flag array", r);
+  }
+  moe::peer_barrier_kernel<<<1, moe::kMaxPeers, 0, static_cast<cudaStream_t>(stream)>>>(
+      flags, static_cast<uint32_t*>(my_flags), static_cast<uint32_t*>(state), static_cast<int>(world),
+      static_cast<int>(my_rank));
+  B200OPS_LAUNCH_CHECK("peer_barrier");
+  return B200OPS_OK;
+}

@@ -429,7 +429,52 @@ at::Tensor fused_qkv_rope_cache(at::Tensor qkv, at::Tensor position_ids, at::Ten
   return q_out;
 }
 
+// Peer-memory exchange (see b200ops_moe_push_rows / b200ops_peer_barrier).  Peer addresses are
+// passed as Python ints (what torch's symmetric-memory handle reports as buffer_ptrs).
+void moe_push_rows(at::Tensor src, at::Tensor index, int64_t src_div, c10::optional<at::Tensor> n_valid,
+                   int64_t n_max, std::vector<int64_t> peer_rows, int64_t cap, int64_t my_rank,
+                   c10::optional<at::Tensor> counts, std::vector<int64_t> peer_counts) {
+  TORCH_CHECK(src.dim() == 2 && src.is_contiguous(), "moe_push_rows: src must be contiguous [rows, H]");
+  check_f16_cuda(src, "moe_push_rows", "src");
+  check_i32_cuda(index, "moe_push_rows", "index");
+  TORCH_CHECK(index.numel() >= n_max, "moe_push_rows: index shorter than n_max");
+  TORCH_CHECK(n_max <= src.size(0) * src_div, "moe_push_rows: n_max exceeds the source rows");
+  if (n_valid) check_i32_cuda(*n_valid, "moe_push_rows", "n_valid");
+  if (counts) {
+    check_i32_cuda(*counts, "moe_push_rows", "counts");
+    TORCH_CHECK(peer_counts.size() == peer_rows.size(), "moe_push_rows: one count table per peer");
+  }
+  std::vector<void*> rows(peer_rows.size()), cnts(peer_counts.size());
+  for (size_t i = 0; i < peer_rows.size(); ++i) rows[i] = reinterpret_cast<void*>(peer_rows[i]);
+  for (size_t i = 0; i < peer_counts.size(); ++i) cnts[i] = reinterpret_cast<void*>(peer_counts[i]);
+  const c10::cuda::CUDAGuard guard(src.device());
+  check_status(b200ops_moe_push_rows(src.data_ptr(), index.data_ptr<int32_t>(), src_div,
+                                     n_valid ? n_valid->data_ptr<int32_t>() : nullptr, n_max, rows.data(),
+                                     static_cast<int64_t>(rows.size()), cap, my_rank, src.size(1),
+                                     counts ? counts->data_ptr<int32_t>() : nullptr,
+                                     counts ? counts->numel() : 0, counts ? cnts.data() : nullptr,
+                                     current_stream()),
+               "moe_push_rows");
+}
+
+void peer_barrier(std::vector<int64_t> peer_flags, at::Tensor my_flags, at::Tensor state, int64_t my_rank) {
+  TORCH_CHECK(my_flags.is_cuda() && state.is_cuda() && state.numel() >= 2 &&
+                  my_flags.numel() >= static_cast<int64_t>(peer_flags.size()) &&
+                  my_flags.element_size() == 4 && state.element_size() == 4,
+              "peer_barrier: flags [world] and state [2] must be 32-bit CUDA tensors");
+  std::vector<void*> flags(peer_flags.size());
+  for (size_t i = 0; i < peer_flags.size(); ++i) flags[i] = reinterpret_cast<void*>(peer_flags[i]);
+  const c10::cuda::CUDAGuard guard(state.device());
+  check_status(b200ops_peer_barrier(flags.data(), my_flags.data_ptr(), state.data_ptr(),
+                                    static_cast<int64_t>(flags.size()), my_rank, current_stream()),
+               "peer_barrier");
+}
+
 void init_ffi_moe(py::module_&& m) {
+  m.def("push_rows", &moe_push_rows, py::arg("src"), py::arg("index"), py::arg("src_div"),
+        py::arg("n_valid"), py::arg("n_max"), py::arg("peer_rows"), py::arg("cap"), py::arg("my_rank"),
+        py::arg("counts") = py::none(), py::arg("peer_counts") = std::vector<int64_t>());
+  m.def("peer_barrier", &peer_barrier);
   m.def("fused_qkv_rope_cache", &fused_qkv_rope_cache);
   m.def("route_topk", &moe_route_topk);
   m.def("permute", &moe_permute);

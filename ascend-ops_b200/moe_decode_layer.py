@@ -84,11 +84,13 @@ def route(logits: torch.Tensor, top_k: int):
 class MoEDecodeLayer:
     """Device-resident weights + the decode-step forward.  `ops` is ascend910a_extras.ops."""
 
-    def __init__(self, cfg: LayerConfig, weights: dict, device, ops, group=None, segment_rows=None):
+    def __init__(self, cfg: LayerConfig, weights: dict, device, ops, group=None, segment_rows=None,
+                 exchange=None):
         import ascend910a_extras.moe as moe
 
         self.cfg, self.ops, self.device, self.group, self.moe = cfg, ops, device, group, moe
         self.segment_rows = segment_rows  # rows each rank sends each peer under expert parallelism
+        self.exchange = exchange  # a moe_parallel.PeerExchange: NVLink peer-memory dispatch/combine
         self.fuse_rope_cache = True  # False: split + ops.rope + ops.reshape_and_cache separately
         d = lambda t: t.to(device)
         self.ln1, self.ln2 = d(weights["ln1"]), d(weights["ln2"])
@@ -148,8 +150,11 @@ class MoEDecodeLayer:
         o = self._dense(attn.view(t, nq), self.wo)
         h2, res2 = ops.add_rms_norm(o, res1, self.ln2, cfg.eps)
         ids, wts = self.moe.route_topk(h2, self.wrouter, cfg.top_k)
-        y = moe_parallel.expert_parallel_mlp_device(self.moe, h2, ids, wts, cfg.experts, self._local_mlp,
-                                                    self.group, self.segment_rows)
+        if self.exchange is not None:
+            y = self.exchange.mlp(h2, ids, wts, self._local_mlp)
+        else:
+            y = moe_parallel.expert_parallel_mlp_device(self.moe, h2, ids, wts, cfg.experts, self._local_mlp,
+                                                        self.group, self.segment_rows)
         if return_routing:
             return y, res2, ids, wts
         return y, res2

@@ -260,6 +260,19 @@ LAYER_WORKLOAD = ("MoE decoder layer, decode step: batch 256, hidden 4096, 32q/8
                   "positions U[1024,16384], block 128, 8 experts top-2, intermediate 14336")
 
 
+EXCHANGE = "peer"  # "peer": NVLink peer-memory pushes (moe_parallel.PeerExchange); "nccl": collectives
+
+
+def make_exchange(group, dev, segment_rows, hidden, hidden_out, num_experts):
+    """The expert-parallel exchange object for this run (None = NCCL collectives or 1 GPU)."""
+    if group is None or EXCHANGE != "peer":
+        return None
+    import ascend910a_extras.moe as moe
+    import moe_parallel
+
+    return moe_parallel.PeerExchange(moe, group, dev, segment_rows, hidden, hidden_out, num_experts)
+
+
 def build_layer(ops, dev, rank, world, group):
     """This rank's share of the layer: all dense weights, its experts, its sequences and
     their KV pages (filled with N(0,1) on the device)."""
@@ -270,7 +283,8 @@ def build_layer(ops, dev, rank, world, group):
     mine = moe_parallel.local_experts(cfg.experts, world, rank).tolist()
     weights = mdl.make_weights(cfg, seed=7, experts=mine, device=dev)
     per = 256 // world
-    layer = mdl.MoEDecodeLayer(cfg, weights, dev, ops, group, segment_rows=per * cfg.top_k)
+    exchange = make_exchange(group, dev, per * cfg.top_k, cfg.hidden, cfg.hidden, cfg.experts)
+    layer = mdl.MoEDecodeLayer(cfg, weights, dev, ops, group, segment_rows=per * cfg.top_k, exchange=exchange)
     pos = mdl.draw_positions(256)
     batch = mdl.make_decode_batch(cfg, positions=pos[rank * per:(rank + 1) * per], seed=80 + rank)
     g = torch.Generator(device=dev).manual_seed(90 + rank)
@@ -404,9 +418,12 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
 
     def measure(capacity):
         flags = []
+        exchange = make_exchange(group, dev, capacity, cfg.hidden, cfg.hidden, placement.num_slots)
 
         def step():
             slot_ids = moe_parallel.to_slot_ids(my_ids, placement, rank * per)
+            if exchange is not None:
+                return exchange.mlp(x, slot_ids, wts, local_mlp, overflow_out=flags)
             return moe_parallel.expert_parallel_mlp_device(moe, x, slot_ids, wts, placement.num_slots, local_mlp,
                                                            group, capacity, overflow_out=flags)
 
@@ -548,9 +565,13 @@ def main():
                     help="per-op cases: comma list, 'all', 'none', or 'auto' (all at 1 GPU, none otherwise)")
     ap.add_argument("--no-layer", action="store_true", help="skip the layer step (per-op cases only)")
     ap.add_argument("--cpu-seqs", type=int, default=128, help="sequences in the CPU-baseline sample")
+    ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
+                    help="expert-parallel exchange: NVLink peer-memory pushes, or NCCL collectives")
     ap.add_argument("--profile-case", default=None,
                     help="run a small case of one operator (for ncu) and exit")
     ns = ap.parse_args()
+    global EXCHANGE
+    EXCHANGE = ns.exchange
     ns.warmup = max(ns.warmup, 3)
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -561,6 +582,9 @@ def main():
         "metric": "moe_decode_layer_latency", "unit": "us", "n_gpus": ns.gpus, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": LAYER_WORKLOAD, "parallelism": f"ep{ns.gpus}+batch-sharded attention",
+                   "exchange": ("none (1 GPU)" if ns.gpus == 1 else
+                                "NVLink peer-memory pushes + flag barrier" if ns.exchange == "peer" else
+                                "NCCL all-gather + all-to-all"),
                    "execution": "step replayed from a CUDA graph; eager_us is the same step launched op by op",
                    "l2": "inputs larger than L2 (the step streams GBs of KV cache and expert weights)"},
     }

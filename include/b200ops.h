@@ -236,6 +236,32 @@ int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row, const flo
                          void* y, int64_t num_tokens, int64_t top_k, int64_t row_elems, void* stream);
 
 /*
+ * Expert-parallel exchange over peer memory (NVLink), an alternative to an all-to-all
+ * collective; no counterpart in the reference, which has no multi-device code.
+ *
+ * push_rows: for logical row i < *n_valid (n_max if n_valid is NULL) with idx = index[i] >= 0:
+ *   row i / src_div of `src` (f16, row_elems wide) is stored into the buffer of peer idx / cap
+ *   at row my_rank * cap + idx % cap.  peer_rows[r] is the address, valid on THIS device, of
+ *   rank r's receive buffer ([world * cap, row_elems] f16; peer_rows[my_rank] is the local
+ *   one).  If `counts` is given, its num_counts int32 values are also stored into row my_rank
+ *   of every peer's count table peer_counts[r] ([world, num_counts] int32).  The arrays of peer
+ *   addresses are HOST arrays of `world` entries.
+ * peer_barrier: announces "this rank has finished pushing" to every peer and waits (at most two
+ *   seconds) for the same announcement from every peer.  peer_flags[r] = address of rank r's
+ *   flag array ([world] uint32, zero-initialised once); my_flags = the local one; state =
+ *   [2] uint32 in local memory, zero-initialised once: state[0] counts barriers, state[1]
+ *   becomes 100 + r if peer r never arrived (the kernel then returns instead of hanging).
+ *   Launch it on the same stream right after the pushes; kernels after it may read what the
+ *   peers pushed.  All ranks must call it the same number of times.
+ */
+int b200ops_moe_push_rows(const void* src, const int32_t* index, int64_t src_div, const int32_t* n_valid,
+                          int64_t n_max, void* const* peer_rows, int64_t world, int64_t cap,
+                          int64_t my_rank, int64_t row_elems, const int32_t* counts, int64_t num_counts,
+                          void* const* peer_counts, void* stream);
+int b200ops_peer_barrier(void* const* peer_flags, void* my_flags, void* state, int64_t world,
+                         int64_t my_rank, void* stream);
+
+/*
  * Health word of the pipelined kernels (grouped_matmul, paged_attention's TMA path).  Their
  * producer/consumer waits are bounded; a wait that runs out ends the kernel and leaves a
  * non-zero code here.  This call synchronises the device, returns the code in *status

@@ -37,6 +37,18 @@ def main():
     ep = mdl.MoEDecodeLayer(cfg, part, dev, ops, group=dist.group.WORLD, segment_rows=per * cfg.top_k)
     y_ep, res_ep = ep.forward(*args, kc.to(dev), vc.to(dev))
     torch.cuda.synchronize()
+    # the same layer with the NVLink peer-memory exchange instead of NCCL: identical rows move,
+    # so the output must be bit-identical; run it three times to cross the buffer-reuse path
+    import ascend910a_extras.moe as moe
+    ex = moe_parallel.PeerExchange(moe, dist.group.WORLD, dev, per * cfg.top_k, cfg.hidden, cfg.hidden,
+                                   cfg.experts)
+    peer = mdl.MoEDecodeLayer(cfg, part, dev, ops, group=dist.group.WORLD, segment_rows=per * cfg.top_k,
+                              exchange=ex)
+    for _ in range(3):
+        y_peer, res_peer = peer.forward(*args, kc.to(dev), vc.to(dev))
+    torch.cuda.synchronize()
+    assert ex.barrier_error() == 0, f"peer barrier gave up waiting: {ex.barrier_error()}"
+    assert torch.equal(y_peer, y_ep) and torch.equal(res_peer, res_ep)
     dist.barrier()
     dist.destroy_process_group()  # from here on expert_parallel_mlp sees no group: local path
     y_solo, res_solo = solo.forward(*args, kc.to(dev), vc.to(dev))

@@ -50,6 +50,9 @@ SIGNATURES = {
     "b200ops_moe_ep_plan": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p]),
     "b200ops_moe_copy_rows": (c_int, [c_void_p] * 4 + [c_int64, c_void_p, c_int64, c_int64, c_void_p]),
     "b200ops_moe_finalize": (c_int, [c_void_p] * 4 + [c_int64] * 3 + [c_void_p]),
+    "b200ops_grouped_matmul_scatter": (c_int, [c_void_p] * 3 + [c_int64] * 4 + [c_void_p, c_size_t, c_void_p,
+                                                                                 c_void_p, c_int64, c_int64,
+                                                                                 c_int64, c_void_p]),
     "b200ops_moe_push_rows": (c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_int64,
                                       c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200ops_peer_barrier": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),

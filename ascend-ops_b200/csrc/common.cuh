@@ -48,6 +48,13 @@ inline int fail(int code, const char* fmt, ...) {
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Addresses, valid on this device, of one buffer per rank (peer-mapped memory); passed to
+// kernels by value.
+constexpr int kMaxPeers = 64;
+struct PeerTable {
+  void* base[kMaxPeers];
+};
+
 // Number of SMs of the current device (cached per device).
 int sm_count();
 

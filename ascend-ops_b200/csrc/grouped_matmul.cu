@@ -103,6 +103,27 @@ struct TileCoord {
   int group, row0, row_end, n0;
 };
 
+// Optional output redirection: row r of the result is not written to y[r] but into the buffer
+// of rank index[r] / cap, at row my_rank * cap + index[r] % cap -- the return leg of the
+// expert-parallel exchange fused into the GEMM's epilogue (plain stores through the NVLink
+// peer mapping).  index == nullptr: ordinary output.
+struct RowScatter {
+  const int32_t* index;
+  PeerTable peers;
+  int cap, my_rank;
+};
+
+__device__ __forceinline__ __half* output_row(const RowScatter& sc, __half* y, int row, int N, bool& ok) {
+  if (sc.index == nullptr) return y + static_cast<size_t>(row) * N;
+  const int idx = ok ? sc.index[row] : -1;
+  if (idx < 0) {
+    ok = false;
+    return y;
+  }
+  const int peer = idx / sc.cap, off = idx - peer * sc.cap;
+  return static_cast<__half*>(sc.peers.base[peer]) + (static_cast<size_t>(sc.my_rank) * sc.cap + off) * N;
+}
+
 // Work item -> (tile, k-slice).  Items of one tile are adjacent so its CTAs run together.
 struct WorkItem {
   int tile, kb0, kb1, split;
@@ -138,7 +159,8 @@ __global__ void __launch_bounds__(kThreads, 1)
 grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
                       const __grid_constant__ CUtensorMap map_w,
                       const int64_t* __restrict__ group_list, __half* __restrict__ y, int M, int N,
-                      int K, int E, int* __restrict__ tile_counters, float* __restrict__ partials) {
+                      int K, int E, int* __restrict__ tile_counters, float* __restrict__ partials,
+                      const RowScatter scatter) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -293,8 +315,8 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       ptx::tcgen05_fence_after();
       const int tile_row = quarter * 32 + lane;
       const int row = tc.row0 + tile_row;
-      const bool row_ok = row < tc.row_end;
-      __half* yrow = y + static_cast<size_t>(row) * N + tc.n0;
+      bool row_ok = row < tc.row_end;
+      __half* yrow = output_row(scatter, y, row, N, row_ok) + tc.n0;
       float* prow = splits > 1 ? partials + static_cast<size_t>(item) * (BM * BN) + tile_row * BN : nullptr;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll 1
@@ -380,13 +402,15 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int rr = r0 + 4 * j;
-                if (rr < rows_here) {
+                bool out_ok = rr < rows_here;
+                __half* out_row = output_row(scatter, y, tc.row0 + rr, N, out_ok);
+                if (out_ok) {
                   uint4 o;
                   o.x = f2_to_h2(acc8[j][0], acc8[j][1]);
                   o.y = f2_to_h2(acc8[j][2], acc8[j][3]);
                   o.z = f2_to_h2(acc8[j][4], acc8[j][5]);
                   o.w = f2_to_h2(acc8[j][6], acc8[j][7]);
-                  *reinterpret_cast<uint4*>(y + static_cast<size_t>(tc.row0 + rr) * N + tc.n0 + col) = o;
+                  *reinterpret_cast<uint4*>(out_row + tc.n0 + col) = o;
                 }
               }
             }
@@ -416,9 +440,54 @@ extern "C" size_t b200ops_grouped_matmul_workspace_size(int64_t num_tokens, int6
   return gmm::split_k_possible(num_tokens, k, n, gmm::launch_sms()) ? gmm::workspace_bytes() : 0;
 }
 
+namespace b200ops {
+namespace gmm {
+int launch(const void* x, const void* w, const int64_t* group_list, void* y, int64_t num_tokens, int64_t k,
+           int64_t num_experts, int64_t n, void* workspace, size_t workspace_size, const RowScatter& scatter,
+           void* stream);
+}
+}  // namespace b200ops
+
 extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_t* group_list,
                                       void* y, int64_t num_tokens, int64_t k, int64_t num_experts,
                                       int64_t n, void* workspace, size_t workspace_size, void* stream) {
+  b200ops::gmm::RowScatter none;
+  none.index = nullptr;
+  none.cap = 1;
+  none.my_rank = 0;
+  for (int r = 0; r < b200ops::kMaxPeers; ++r) none.peers.base[r] = nullptr;
+  B200OPS_REQUIRE(num_tokens <= 0 || y != nullptr, "grouped_matmul: null pointer");
+  return b200ops::gmm::launch(x, w, group_list, y, num_tokens, k, num_experts, n, workspace, workspace_size,
+                              none, stream);
+}
+
+extern "C" int b200ops_grouped_matmul_scatter(const void* x, const void* w, const int64_t* group_list,
+                                              int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n,
+                                              void* workspace, size_t workspace_size,
+                                              const int32_t* row_index, void* const* peer_out, int64_t world,
+                                              int64_t cap, int64_t my_rank, void* stream) {
+  using namespace b200ops;
+  B200OPS_REQUIRE(world >= 1 && world <= kMaxPeers && my_rank >= 0 && my_rank < world && cap > 0 &&
+                      cap * world < (1LL << 31),
+                  "grouped_matmul_scatter: bad geometry world=%lld rank=%lld cap=%lld", (long long)world,
+                  (long long)my_rank, (long long)cap);
+  B200OPS_REQUIRE(row_index != nullptr && peer_out != nullptr, "grouped_matmul_scatter: null pointer");
+  gmm::RowScatter sc;
+  sc.index = row_index;
+  sc.cap = static_cast<int>(cap);
+  sc.my_rank = static_cast<int>(my_rank);
+  for (int r = 0; r < kMaxPeers; ++r) {
+    sc.peers.base[r] = r < world ? peer_out[r] : nullptr;
+    B200OPS_REQUIRE(r >= world || (sc.peers.base[r] != nullptr && aligned16(sc.peers.base[r])),
+                    "grouped_matmul_scatter: peer %d has no buffer", r);
+  }
+  return gmm::launch(x, w, group_list, sc.peers.base[my_rank], num_tokens, k, num_experts, n, workspace,
+                     workspace_size, sc, stream);
+}
+
+int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list, void* y, int64_t num_tokens,
+                         int64_t k, int64_t num_experts, int64_t n, void* workspace, size_t workspace_size,
+                         const RowScatter& scatter, void* stream) {
   using namespace b200ops;
   B200OPS_REQUIRE(num_tokens >= 0 && k > 0 && n > 0 && num_experts > 0,
                   "grouped_matmul: bad shape tokens=%lld k=%lld experts=%lld n=%lld",
@@ -482,7 +551,7 @@ extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_
   }
   gmm::grouped_matmul_kernel<<<grid, gmm::kThreads, gmm::kSmemBytes, st>>>(
       map_x, map_w, group_list, static_cast<__half*>(y), static_cast<int>(num_tokens),
-      static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts), counters, partials);
+      static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts), counters, partials, scatter);
   B200OPS_LAUNCH_CHECK("grouped_matmul");
   return B200OPS_OK;
 }

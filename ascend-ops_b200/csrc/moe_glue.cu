@@ -32,7 +32,7 @@ constexpr int kMaxExperts = 256;
 constexpr int kMaxTopK = 8;
 
 // One CTA per token, one warp per expert (warps loop when there are more experts than warps):
-// every warp forms its expert's dot product with 128-bit loads and four independent
+// every warp forms its expert's dot product with 128-bit loads and eight independent
 // accumulators, so even a handful of tokens keeps hundreds of loads in flight.  Warp 0 then
 // does the softmax and the top-k selection.
 __global__ void __launch_bounds__(1024)
@@ -45,11 +45,12 @@ route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, i
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(token) * hidden);
   for (int e = warp; e < num_experts; e += warps) {
     const uint4* w = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * hidden);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int v0 = lane; v0 < vecs; v0 += 128) {
-      uint4 a[4], b[4];
+    constexpr int kBatch = 8;  // 16-byte loads of x and of w in flight per lane
+    float acc[kBatch] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int v0 = lane; v0 < vecs; v0 += 32 * kBatch) {
+      uint4 a[kBatch], b[kBatch];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < kBatch; ++u) {
         const int v = v0 + u * 32;
         if (v < vecs) {
           a[u] = __ldg(xr + v);
@@ -60,7 +61,7 @@ route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, i
         }
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < kBatch; ++u) {
         const uint32_t* as = reinterpret_cast<const uint32_t*>(&a[u]);
         const uint32_t* bs = reinterpret_cast<const uint32_t*>(&b[u]);
 #pragma unroll
@@ -72,7 +73,7 @@ route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, i
         }
       }
     }
-    const float dot = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+    const float dot = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7])));
     if (lane == 0) logits[e] = __half2float(__float2half_rn(dot));
   }
   __syncthreads();
@@ -388,12 +389,6 @@ namespace b200ops {
 namespace moe {
 namespace {
 
-constexpr int kMaxPeers = 64;
-
-struct PeerTable {
-  void* base[kMaxPeers];
-};
-
 // Logical row i (i < *n_valid, or n_max) of `src` (row i / src_div) goes to peer idx / cap,
 // row my_rank * cap + idx % cap of that peer's buffer, where idx = index[i] (negative: skip).
 // CTA 0 additionally copies `counts` into row my_rank of every peer's count table.
@@ -473,7 +468,7 @@ extern "C" int b200ops_moe_push_rows(const void* src, const int32_t* index, int6
                                      int64_t world, int64_t cap, int64_t my_rank, int64_t row_elems,
                                      const int32_t* counts, int64_t num_counts, void* const* peer_counts,
                                      void* stream) {
-  B200OPS_REQUIRE(world >= 1 && world <= moe::kMaxPeers && my_rank >= 0 && my_rank < world && cap > 0 &&
+  B200OPS_REQUIRE(world >= 1 && world <= kMaxPeers && my_rank >= 0 && my_rank < world && cap > 0 &&
                       cap * world < (1LL << 31),
                   "moe_push_rows: bad geometry world=%lld rank=%lld cap=%lld", (long long)world,
                   (long long)my_rank, (long long)cap);
@@ -483,8 +478,8 @@ extern "C" int b200ops_moe_push_rows(const void* src, const int32_t* index, int6
   B200OPS_REQUIRE(peer_rows != nullptr && (counts == nullptr || (peer_counts != nullptr && num_counts > 0)),
                   "moe_push_rows: null peer table");
   B200OPS_REQUIRE(n_max == 0 || (src && index && aligned16(src)), "moe_push_rows: null or misaligned pointer");
-  moe::PeerTable rows, cnt;
-  for (int r = 0; r < moe::kMaxPeers; ++r) {
+  PeerTable rows, cnt;
+  for (int r = 0; r < kMaxPeers; ++r) {
     rows.base[r] = r < world ? peer_rows[r] : nullptr;
     cnt.base[r] = (counts != nullptr && r < world) ? peer_counts[r] : nullptr;
     B200OPS_REQUIRE(r >= world || (rows.base[r] != nullptr && aligned16(rows.base[r])),
@@ -501,15 +496,15 @@ extern "C" int b200ops_moe_push_rows(const void* src, const int32_t* index, int6
 
 extern "C" int b200ops_peer_barrier(void* const* peer_flags, void* my_flags, void* state, int64_t world,
                                     int64_t my_rank, void* stream) {
-  B200OPS_REQUIRE(world >= 1 && world <= moe::kMaxPeers && my_rank >= 0 && my_rank < world,
+  B200OPS_REQUIRE(world >= 1 && world <= kMaxPeers && my_rank >= 0 && my_rank < world,
                   "peer_barrier: bad geometry world=%lld rank=%lld", (long long)world, (long long)my_rank);
   B200OPS_REQUIRE(peer_flags && my_flags && state, "peer_barrier: null pointer");
-  moe::PeerTable flags;
-  for (int r = 0; r < moe::kMaxPeers; ++r) {
+  PeerTable flags;
+  for (int r = 0; r < kMaxPeers; ++r) {
     flags.base[r] = r < world ? peer_flags[r] : nullptr;
     B200OPS_REQUIRE(r >= world || flags.base[r] != nullptr, "peer_barrier: peer %d has no flag array", r);
   }
-  moe::peer_barrier_kernel<<<1, moe::kMaxPeers, 0, static_cast<cudaStream_t>(stream)>>>(
+  moe::peer_barrier_kernel<<<1, kMaxPeers, 0, static_cast<cudaStream_t>(stream)>>>(
       flags, static_cast<uint32_t*>(my_flags), static_cast<uint32_t*>(state), static_cast<int>(world),
       static_cast<int>(my_rank));
   B200OPS_LAUNCH_CHECK("peer_barrier");

@@ -457,6 +457,33 @@ void moe_push_rows(at::Tensor src, at::Tensor index, int64_t src_div, c10::optio
                "moe_push_rows");
 }
 
+// grouped_matmul with the result rows stored straight into the peers' return buffers.
+void grouped_matmul_scatter(at::Tensor x, at::Tensor w, at::Tensor group_list, at::Tensor row_index,
+                            std::vector<int64_t> peer_out, int64_t cap, int64_t my_rank) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && group_list.dim() == 1 && x.size(1) == w.size(1),
+              "grouped_matmul_scatter: x [M, K], w [E, K, N], group_list [E]");
+  TORCH_CHECK(x.is_contiguous() && group_list.is_contiguous() && w.stride(1) == 1 && w.stride(2) == x.size(1),
+              "grouped_matmul_scatter: x must be contiguous and w K-major");
+  TORCH_CHECK(w.size(1) % 64 == 0 && w.size(2) % 64 == 0 && group_list.size(0) == w.size(0),
+              "grouped_matmul_scatter: K and N must be multiples of 64, one group end per expert");
+  check_f16_cuda(x, "grouped_matmul_scatter", "x");
+  check_f16_cuda(w, "grouped_matmul_scatter", "w");
+  check_i32_cuda(row_index, "grouped_matmul_scatter", "row_index");
+  TORCH_CHECK(group_list.is_cuda() && group_list.scalar_type() == at::kLong && row_index.numel() >= x.size(0),
+              "grouped_matmul_scatter: group_list must be CUDA int64, row_index must cover every row");
+  std::vector<void*> peers(peer_out.size());
+  for (size_t i = 0; i < peer_out.size(); ++i) peers[i] = reinterpret_cast<void*>(peer_out[i]);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const size_t ws = b200ops_grouped_matmul_workspace_size(x.size(0), x.size(1), w.size(0), w.size(2));
+  at::Tensor workspace = at::empty({static_cast<int64_t>(ws)}, x.options().dtype(at::kByte));
+  check_status(b200ops_grouped_matmul_scatter(x.data_ptr(), w.data_ptr(), group_list.data_ptr<int64_t>(),
+                                              x.size(0), x.size(1), w.size(0), w.size(2),
+                                              ws ? workspace.data_ptr() : nullptr, ws,
+                                              row_index.data_ptr<int32_t>(), peers.data(),
+                                              static_cast<int64_t>(peers.size()), cap, my_rank, current_stream()),
+               "grouped_matmul_scatter");
+}
+
 void peer_barrier(std::vector<int64_t> peer_flags, at::Tensor my_flags, at::Tensor state, int64_t my_rank) {
   TORCH_CHECK(my_flags.is_cuda() && state.is_cuda() && state.numel() >= 2 &&
                   my_flags.numel() >= static_cast<int64_t>(peer_flags.size()) &&
@@ -475,6 +502,7 @@ void init_ffi_moe(py::module_&& m) {
         py::arg("n_valid"), py::arg("n_max"), py::arg("peer_rows"), py::arg("cap"), py::arg("my_rank"),
         py::arg("counts") = py::none(), py::arg("peer_counts") = std::vector<int64_t>());
   m.def("peer_barrier", &peer_barrier);
+  m.def("grouped_matmul_scatter", &grouped_matmul_scatter);
   m.def("fused_qkv_rope_cache", &fused_qkv_rope_cache);
   m.def("route_topk", &moe_route_topk);
   m.def("permute", &moe_permute);

@@ -91,6 +91,7 @@ class MoEDecodeLayer:
         self.cfg, self.ops, self.device, self.group, self.moe = cfg, ops, device, group, moe
         self.segment_rows = segment_rows  # rows each rank sends each peer under expert parallelism
         self.exchange = exchange  # a moe_parallel.PeerExchange: NVLink peer-memory dispatch/combine
+        self.fuse_return = True  # down projection stores into the peers' buffers in its epilogue
         self.fuse_rope_cache = True  # False: split + ops.rope + ops.reshape_and_cache separately
         d = lambda t: t.to(device)
         self.ln1, self.ln2 = d(weights["ln1"]), d(weights["ln2"])
@@ -122,6 +123,12 @@ class MoEDecodeLayer:
         act = self.ops.swiglu(gu)
         return self.ops.grouped_matmul(act, self.w_down, group_list)
 
+    def _local_mlp_scatter(self, rows, group_list, scatter):
+        """Expert MLP whose down projection stores its rows into the peers' return buffers."""
+        gu = self.ops.grouped_matmul(rows, self.w_gate_up, group_list)
+        act = self.ops.swiglu(gu)
+        self.moe.grouped_matmul_scatter(act, self.w_down, group_list, *scatter)
+
     def forward(self, x, residual, positions, slots, block_tables, context_lens, k_cache, v_cache,
                 return_routing=False, attention_events=None):
         """`attention_events`, if given, is a pair of CUDA events recorded right before and
@@ -151,7 +158,8 @@ class MoEDecodeLayer:
         h2, res2 = ops.add_rms_norm(o, res1, self.ln2, cfg.eps)
         ids, wts = self.moe.route_topk(h2, self.wrouter, cfg.top_k)
         if self.exchange is not None:
-            y = self.exchange.mlp(h2, ids, wts, self._local_mlp)
+            y = self.exchange.mlp(h2, ids, wts, self._local_mlp,
+                                  local_mlp_scatter=self._local_mlp_scatter if self.fuse_return else None)
         else:
             y = moe_parallel.expert_parallel_mlp_device(self.moe, h2, ids, wts, cfg.experts, self._local_mlp,
                                                         self.group, self.segment_rows)
@@ -161,10 +169,12 @@ class MoEDecodeLayer:
 
     # number of this library's kernels one single-GPU forward launches (for the benchmark's
     # accounting): 2 add_rms_norm, 2 dense GEMMs, fused rope+cache, attention (plan, main,
-    # combine), route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Expert
-    # parallelism adds ep_plan and two more copy_rows.
+    # combine), route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Under expert
+    # parallelism with the peer-memory exchange the MoE part is route, permute, push_rows,
+    # barrier, ep_plan, copy_rows, gate_up GEMM, swiglu, down GEMM with scatter epilogue,
+    # barrier, finalize.
     KERNEL_LAUNCHES = 15
-    KERNEL_LAUNCHES_EP = 18
+    KERNEL_LAUNCHES_EP = 19
 
 
 class CapturedDecodeStep:

@@ -304,8 +304,12 @@ class PeerExchange:
         """0, or 100 + the rank that did not arrive within the barrier's time limit (synchronises)."""
         return int(self.state[1].item())
 
-    def mlp(self, x, expert_ids, expert_weights, local_mlp, overflow_out=None):
-        """Same contract as expert_parallel_mlp_device for world > 1."""
+    def mlp(self, x, expert_ids, expert_weights, local_mlp, overflow_out=None, local_mlp_scatter=None):
+        """Same contract as expert_parallel_mlp_device for world > 1.
+
+        `local_mlp_scatter(rows, group_list, scatter)`, if given, replaces `local_mlp` plus the
+        return push: it must end in `moe.grouped_matmul_scatter(..., *scatter)`, whose epilogue
+        stores the result rows into the peers' return buffers itself."""
         moe, world, rank, cap = self.moe, self.world, self.rank, self.cap
         t, top_k = expert_ids.shape
         pos, counts, _, overflow = moe.permute(expert_ids, self.num_experts, world, cap)
@@ -316,7 +320,10 @@ class PeerExchange:
         grouped_to_received, group_list, total = moe.ep_plan(self.counts_all, rank, cap)
         grouped = x.new_empty(world * cap, x.shape[1])
         moe.copy_rows(grouped, self.recv, src_index=grouped_to_received, n_valid=total, n_max=world * cap)
-        res = local_mlp(grouped, group_list)
-        moe.push_rows(res, grouped_to_received, 1, total, world * cap, self.peer_ret, cap, rank)
+        if local_mlp_scatter is not None:
+            local_mlp_scatter(grouped, group_list, (grouped_to_received, self.peer_ret, cap, rank))
+        else:
+            res = local_mlp(grouped, group_list)
+            moe.push_rows(res, grouped_to_received, 1, total, world * cap, self.peer_ret, cap, rank)
         moe.peer_barrier(self.peer_flags, self.flags, self.state, rank)
         return moe.finalize(self.ret, pos, expert_weights)

@@ -236,6 +236,21 @@ int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row, const flo
                          void* y, int64_t num_tokens, int64_t top_k, int64_t row_elems, void* stream);
 
 /*
+ * grouped_matmul whose epilogue performs the return leg of the expert-parallel exchange
+ * (GEMM + peer store in one kernel; no counterpart in the reference).  Same computation as
+ * b200ops_grouped_matmul, but result row r is stored into the buffer of rank
+ * row_index[r] / cap at row my_rank * cap + row_index[r] % cap (rows with a negative index
+ * are not stored).  peer_out is a HOST array of `world` addresses, valid on this device, of
+ * every rank's [world * cap, n] f16 return buffer; row_index is device int32 [num_tokens]
+ * (the grouped_to_received map of b200ops_moe_ep_plan).  Follow it with b200ops_peer_barrier.
+ */
+int b200ops_grouped_matmul_scatter(const void* x, const void* w, const int64_t* group_list,
+                                   int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n,
+                                   void* workspace, size_t workspace_size, const int32_t* row_index,
+                                   void* const* peer_out, int64_t world, int64_t cap, int64_t my_rank,
+                                   void* stream);
+
+/*
  * Expert-parallel exchange over peer memory (NVLink), an alternative to an all-to-all
  * collective; no counterpart in the reference, which has no multi-device code.
  *

@@ -49,6 +49,10 @@ def main():
     torch.cuda.synchronize()
     assert ex.barrier_error() == 0, f"peer barrier gave up waiting: {ex.barrier_error()}"
     assert torch.equal(y_peer, y_ep) and torch.equal(res_peer, res_ep)
+    peer.fuse_return = False  # separate push_rows launch instead of the fused GEMM epilogue
+    y_unfused, _ = peer.forward(*args, kc.to(dev), vc.to(dev))
+    torch.cuda.synchronize()
+    assert torch.equal(y_unfused, y_ep)
     dist.barrier()
     dist.destroy_process_group()  # from here on expert_parallel_mlp sees no group: local path
     y_solo, res_solo = solo.forward(*args, kc.to(dev), vc.to(dev))

@@ -154,3 +154,100 @@ def test_permute_bounded_capacity_drops_and_reports(cabi):
     cabi.check(cabi.load().b200ops_moe_permute(p(ids), p(pos), p(counts), p(gl), p(ov), 12, 4, 2, 12, stream()))
     torch.cuda.synchronize()
     assert int(ov) == 0 and counts.cpu().tolist() == [5, 4, 1, 2] and (pos >= 0).all()
+
+
+def _ptr_array(addresses):
+    arr = (ctypes.c_void_p * len(addresses))(*addresses)
+    return arr
+
+
+def test_push_rows_two_emulated_ranks_on_one_gpu(cabi):
+    """Both 'ranks' live on this GPU (their buffers are ordinary tensors), pushed one after the
+    other: checks the addressing of rows and count tables without any cross-GPU wait."""
+    lib = cabi.load()
+    world, cap, h, experts, top_k, t = 2, 16, 64, 4, 2, 6
+    g = torch.Generator().manual_seed(5)
+    recv = [torch.zeros(world * cap, h, dtype=torch.float16, device=DEV) for _ in range(world)]
+    tables = [torch.full((world, experts), -1, dtype=torch.int32, device=DEV) for _ in range(world)]
+    rows_ptrs = _ptr_array([b.data_ptr() for b in recv])
+    table_ptrs = _ptr_array([b.data_ptr() for b in tables])
+    xs, poss, cnts = [], [], []
+    for rank in range(world):
+        x = torch.randn(t, h, generator=g).half().to(DEV)
+        ids = torch.randint(0, experts, (t, top_k), generator=g, dtype=torch.int32).to(DEV)
+        pos = torch.empty(t * top_k, dtype=torch.int32, device=DEV)
+        counts = torch.empty(experts, dtype=torch.int32, device=DEV)
+        gl = torch.empty(experts, dtype=torch.int64, device=DEV)
+        cabi.check(lib.b200ops_moe_permute(p(ids), p(pos), p(counts), p(gl), None, t * top_k, experts, world, cap,
+                                           stream()))
+        cabi.check(lib.b200ops_moe_push_rows(p(x), p(pos), top_k, None, t * top_k, rows_ptrs, world, cap, rank, h,
+                                             p(counts), experts, table_ptrs, stream()))
+        xs.append(x), poss.append(pos), cnts.append(counts)
+    torch.cuda.synchronize()
+    for rank in range(world):
+        for dest in range(world):
+            assert tables[dest][rank].cpu().tolist() == cnts[rank].cpu().tolist()
+        for s, idx in enumerate(poss[rank].cpu().tolist()):
+            dest, off = divmod(idx, cap)
+            assert torch.equal(recv[dest][rank * cap + off], xs[rank][s // top_k])
+    total = sum(int(c.sum()) for c in cnts)
+    assert sum(int((b.abs().sum(1) > 0).sum()) for b in recv) == total
+
+
+def test_peer_barrier_passes_when_peers_arrived_and_gives_up_when_not(cabi):
+    """The barrier's wait is bounded.  Flags of a second, emulated rank are set by hand: with the
+    flag in place the barrier returns at once and counts the step; without it the kernel gives
+    up after its time limit, records which peer was missing, and the context stays usable."""
+    import time
+
+    lib = cabi.load()
+    flags = torch.zeros(2, dtype=torch.int32, device=DEV)       # this rank's flag array
+    other = torch.zeros(2, dtype=torch.int32, device=DEV)       # the emulated peer's flag array
+    state = torch.zeros(2, dtype=torch.int32, device=DEV)
+    ptrs = _ptr_array([flags.data_ptr(), other.data_ptr()])
+    flags[1] = 1  # "rank 1 has reached step 1"
+    cabi.check(lib.b200ops_peer_barrier(ptrs, p(flags), p(state), 2, 0, stream()))
+    torch.cuda.synchronize()
+    assert state.cpu().tolist() == [1, 0]
+    assert flags.cpu().tolist() == [1, 1] and other.cpu().tolist() == [1, 0]  # own arrival announced to both
+    t0 = time.perf_counter()
+    cabi.check(lib.b200ops_peer_barrier(ptrs, p(flags), p(state), 2, 0, stream()))  # nobody sets step 2
+    torch.cuda.synchronize()
+    waited = time.perf_counter() - t0
+    assert state.cpu().tolist() == [2, 101]  # peer 1 never arrived
+    assert 1.0 < waited < 10.0
+    assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0  # the device still answers
+
+
+@pytest.mark.parametrize("counts,k,n", [([40, 3, 0, 21], 256, 192), ([70], 8192, 256)])  # second: split-K path
+def test_grouped_matmul_scatter_equals_matmul_then_push(cabi, counts, k, n):
+    """The GEMM whose epilogue stores into the (emulated) peers' return buffers must leave
+    exactly what grouped_matmul followed by push_rows leaves."""
+    lib = cabi.load()
+    world, rank, cap = 2, 1, 64
+    g = torch.Generator().manual_seed(sum(counts) + k)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half().to(DEV)
+    w = (torch.randn(len(counts), n, k, generator=g) * 0.05).half().to(DEV)
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64).to(DEV)
+    # every grouped row returns to a distinct (peer, offset); a few rows are dropped (-1)
+    idx = torch.randperm(world * cap, generator=g)[:m].int()
+    idx[::9] = -1
+    idx = idx.to(DEV)
+    nbytes = cabi.grouped_matmul_workspace_size(m, k, len(counts), n)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=DEV)
+    fused = [torch.zeros(world * cap, n, dtype=torch.float16, device=DEV) for _ in range(world)]
+    cabi.check(lib.b200ops_grouped_matmul_scatter(p(x), p(w), p(gl), m, k, len(counts), n,
+                                                  p(ws) if nbytes else None, nbytes, p(idx),
+                                                  _ptr_array([b.data_ptr() for b in fused]), world, cap, rank,
+                                                  stream()))
+    y = torch.empty(m, n, dtype=torch.float16, device=DEV)
+    cabi.grouped_matmul(x, w, gl, y, ws if nbytes else None)
+    plain = [torch.zeros(world * cap, n, dtype=torch.float16, device=DEV) for _ in range(world)]
+    cabi.check(lib.b200ops_moe_push_rows(p(y), p(idx), 1, None, m, _ptr_array([b.data_ptr() for b in plain]),
+                                         world, cap, rank, n, None, 0, None, stream()))
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    for a, b in zip(fused, plain):
+        assert torch.equal(a, b)
+    assert sum(int((b.abs().sum(1) > 0).sum()) for b in fused) == int((idx >= 0).sum())

@@ -33,8 +33,10 @@ inline int fail(int code, const char* fmt, ...) {
 #define B200OPS_CUDA(expr)                                                          \
   do {                                                                              \
     cudaError_t err__ = (expr);                                                     \
-    if (err__ != cudaSuccess)                                                       \
+    if (err__ != cudaSuccess) {                                                     \
+      (void)cudaGetLastError(); /* do not leave the error for an unrelated later launch check */ \
       return ::b200ops::fail(B200OPS_ECUDA, "%s failed: %s", #expr, cudaGetErrorString(err__)); \
+    }                                                                               \
   } while (0)
 
 // Launch check: reports configuration errors of the launch just made without

@@ -199,48 +199,23 @@ __global__ void __launch_bounds__(kCombineWarps * 32) paged_attention_combine_ke
   if (L <= 0) return;
   const int n_chunks = (L + a.chunk_tokens - 1) / a.chunk_tokens;
   if (n_chunks <= 1) return;
-  const int D = a.head_dim;
-  const size_t rec = partial_stride(D);
-  const float* base = a.partials + static_cast<size_t>(item) * a.max_chunks * rec;
-  float mm = -INFINITY;
-  for (int c = lane; c < n_chunks; c += 32) mm = fmaxf(mm, base[c * rec + D]);
-  mm = warp_max(mm);
-  float ll = 0.f;
-  for (int c = lane; c < n_chunks; c += 32) {
-    const float mc = base[c * rec + D];
-    if (mc != -INFINITY) ll += base[c * rec + D + 1] * exp2f(mc - mm);
-  }
-  ll = warp_sum(ll);
-  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // head_dim <= 256 -> up to 8 per lane
-  for (int c0 = 0; c0 < n_chunks; c0 += 32) {
-    const int mine = c0 + lane;
-    float w = 0.f;
-    if (mine < n_chunks) {
-      const float mc = base[mine * rec + D];
-      w = (mc == -INFINITY) ? 0.f : exp2f(mc - mm);
-    }
-    const int n = min(32, n_chunks - c0);
-    for (int j = 0; j < n; ++j) {
-      const float wj = __shfl_sync(0xffffffffu, w, j);
-      if (wj == 0.f) continue;
-      const float* p = base + static_cast<size_t>(c0 + j) * rec;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int d = lane + i * 32;
-        if (d < D) acc[i] = fmaf(wj, p[d], acc[i]);
-      }
-    }
-  }
-  __half* out = a.out + static_cast<size_t>(item) * D;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int d = lane + i * 32;
-    if (d < D) out[d] = __float2half(acc[i] * inv);
-  }
+  combine_head(a, b, item - b * a.num_heads, n_chunks, lane);
 }
 
 }  // namespace
+
+// Chunk partials, then one int per (sequence, kv head) for the fused merge.
+size_t chunk_partial_bytes(int64_t bs, int64_t num_heads, int64_t head_dim, int max_chunks) {
+  if (max_chunks <= 1) return 0;
+  const size_t n = static_cast<size_t>(bs) * num_heads * max_chunks * partial_stride((int)head_dim) * sizeof(float);
+  return (n + 255) & ~static_cast<size_t>(255);
+}
+
+size_t chunk_workspace_bytes(int64_t bs, int64_t num_heads, int64_t num_kv_heads, int64_t head_dim,
+                             int max_chunks) {
+  const size_t partials = chunk_partial_bytes(bs, num_heads, head_dim, max_chunks);
+  return partials == 0 ? 0 : partials + static_cast<size_t>(bs) * num_kv_heads * sizeof(int);
+}
 
 Plan make_plan(int64_t bs, int64_t num_kv_heads, int64_t page_size, int64_t max_pages_per_seq) {
   // Chunk length.  Each CTA pays a fixed start-up (barrier set-up, first TMA round trip) and
@@ -310,9 +285,7 @@ extern "C" size_t b200ops_paged_attention_workspace_size(int64_t bs, int64_t num
   // chunk partials of the split-context kernels, or prefix sums + segment records of the
   // tile-balanced kernel.
   const pa::Plan p = pa::make_plan(bs, num_kv_heads, page_size, max_pages_per_seq);
-  const size_t chunked = p.max_chunks <= 1 ? 0
-                                           : static_cast<size_t>(bs) * num_heads * p.max_chunks *
-                                                 pa::partial_stride((int)head_dim) * sizeof(float);
+  const size_t chunked = pa::chunk_workspace_bytes(bs, num_heads, num_kv_heads, head_dim, p.max_chunks);
   const size_t stream = num_heads % num_kv_heads == 0
                             ? pa::stream_workspace_bytes(bs, num_heads, num_kv_heads, head_dim)
                             : 0;
@@ -380,12 +353,20 @@ extern "C" int b200ops_paged_attention(const void* q, const void* key_cache,
   a.scale_log2 = (1.0f / std::sqrt(static_cast<float>(head_dim))) * 1.44269504088896340736f;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int rc;
+  a.pair_counters = nullptr;
   if (pa::stream_path_supported(a)) return pa::launch_stream(a, workspace, st);
-  if (pa::fast_path_supported(a))
-    rc = pa::launch_fast(a, st);
-  else
-    rc = pa::launch_general(a, st);
+  if (pa::fast_path_supported(a)) {
+    // The split-context TMA kernel merges a pair's chunks itself: the CTA that finishes the
+    // pair's last outstanding chunk (a counter per pair, zeroed here) does the merge, so no
+    // second launch follows.
+    if (a.max_chunks > 1) {
+      a.pair_counters = reinterpret_cast<int*>(
+          static_cast<char*>(workspace) + pa::chunk_partial_bytes(bs, num_heads, head_dim, a.max_chunks));
+      B200OPS_CUDA(cudaMemsetAsync(a.pair_counters, 0, static_cast<size_t>(bs) * num_kv_heads * sizeof(int), st));
+    }
+    return pa::launch_fast(a, st);
+  }
+  const int rc = pa::launch_general(a, st);
   if (rc != B200OPS_OK) return rc;
   return pa::launch_combine(a, st);
 }

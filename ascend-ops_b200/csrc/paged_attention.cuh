@@ -32,6 +32,7 @@ struct Args {
   const int32_t* context_lens;
   __half* out;
   float* partials;
+  int* pair_counters;  // [bs * num_kv_heads] finished chunks per pair; non-null = the last chunk merges
   int bs, num_heads, num_kv_heads, head_dim;
   int num_pages, page_size, max_pages_per_seq;
   int layout;
@@ -39,7 +40,59 @@ struct Args {
   float scale_log2;  // 1/sqrt(head_dim) * log2(e)
 };
 
+#ifdef __CUDACC__
+// Merge the n_chunks partial records of (sequence b, query head h) and write the fp16 row.
+// One warp; lanes first take one chunk each for the maximum and the normaliser, then every
+// lane sums its channels (lane, lane + 32, ...) over the chunks.  Records are read with
+// ld.global.cg because in the fused form they were written by other SMs of the same launch.
+__device__ __forceinline__ void combine_head(const Args& a, int b, int h, int n_chunks, int lane) {
+  const int D = a.head_dim;
+  const size_t rec = partial_stride(D);
+  const size_t item = static_cast<size_t>(b) * a.num_heads + h;
+  const float* base = a.partials + item * a.max_chunks * rec;
+  float mm = -INFINITY;
+  for (int c = lane; c < n_chunks; c += 32) mm = fmaxf(mm, __ldcg(base + c * rec + D));
+  mm = warp_max(mm);
+  float ll = 0.f;
+  for (int c = lane; c < n_chunks; c += 32) {
+    const float mc = __ldcg(base + c * rec + D);
+    if (mc != -INFINITY) ll += __ldcg(base + c * rec + D + 1) * exp2f(mc - mm);
+  }
+  ll = warp_sum(ll);
+  const float inv = ll > 0.f ? 1.0f / ll : 0.f;
+  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // head_dim <= 256 -> up to 8 per lane
+  for (int c0 = 0; c0 < n_chunks; c0 += 32) {
+    const int mine = c0 + lane;
+    float w = 0.f;
+    if (mine < n_chunks) {
+      const float mc = __ldcg(base + mine * rec + D);
+      w = (mc == -INFINITY) ? 0.f : exp2f(mc - mm);
+    }
+    const int n = min(32, n_chunks - c0);
+    for (int j = 0; j < n; ++j) {
+      const float wj = __shfl_sync(0xffffffffu, w, j);
+      if (wj == 0.f) continue;
+      const float* p = base + static_cast<size_t>(c0 + j) * rec;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int d = lane + i * 32;
+        if (d < D) acc[i] = fmaf(wj, __ldcg(p + d), acc[i]);
+      }
+    }
+  }
+  __half* out = a.out + item * D;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int d = lane + i * 32;
+    if (d < D) out[d] = __float2half(acc[i] * inv);
+  }
+}
+#endif
+
 Plan make_plan(int64_t bs, int64_t num_kv_heads, int64_t page_size, int64_t max_pages_per_seq);
+size_t chunk_partial_bytes(int64_t bs, int64_t num_heads, int64_t head_dim, int max_chunks);
+size_t chunk_workspace_bytes(int64_t bs, int64_t num_heads, int64_t num_kv_heads, int64_t head_dim,
+                             int max_chunks);
 
 // Launchers implemented in the .cu files.  Each returns a B200OPS_* code.
 int launch_general(const Args& a, cudaStream_t st);

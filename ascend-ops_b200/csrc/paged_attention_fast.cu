@@ -10,7 +10,9 @@
 // softmax is fp32 with exp2 and scale*log2(e) folded in.  Every K/V byte crosses HBM -> smem
 // once and is shared by all query heads of the group; the kernel is HBM-bound (about 28
 // flop per KV byte at group 7).  Warps merge their (max, sum, O) through shared memory and
-// the CTA writes either the final fp16 rows (single-chunk sequence) or a partial record.
+// the CTA writes either the final fp16 rows (single-chunk sequence) or a partial record; the
+// CTA that completes a pair's last outstanding chunk (an atomic counter, nobody waits) then
+// merges the pair's records into the output, so the operator is a single kernel.
 //
 // Cache bytes past a sequence's length are never trusted: scores of such tokens are
 // replaced by -inf and their V rows are zeroed in shared memory before the PV product, so
@@ -197,6 +199,19 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
           pr[kD] = mm;
           pr[kD + 1] = ll;
         }
+      }
+    }
+    if (n_chunks > 1 && a.pair_counters != nullptr) {
+      // Publish this chunk, then see whether it was the pair's last one; if so merge all of
+      // the pair's chunks here (one warp per query head).  No CTA waits for another.
+      int* arrival = abort_flag + 1;
+      __threadfence();
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32));
+      if (threadIdx.x == 0) *arrival = atomicAdd(&a.pair_counters[b * a.num_kv_heads + kvh], 1);
+      asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32));
+      if (*arrival == n_chunks - 1) {
+        __threadfence();
+        for (int r = warp; r < group; r += kConsumerWarps) combine_head(a, b, h0 + r, n_chunks, lane);
       }
     }
   }

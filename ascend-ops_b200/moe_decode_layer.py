@@ -168,13 +168,13 @@ class MoEDecodeLayer:
         return y, res2
 
     # number of this library's kernels one single-GPU forward launches (for the benchmark's
-    # accounting): 2 add_rms_norm, 2 dense GEMMs, fused rope+cache, attention (plan, main,
-    # combine), route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Under expert
+    # accounting): 2 add_rms_norm, 2 dense GEMMs, fused rope+cache, attention (one kernel: the
+    # chunk merge is fused), route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Under expert
     # parallelism with the peer-memory exchange the MoE part is route, permute, push_rows,
     # barrier, ep_plan, copy_rows, gate_up GEMM, swiglu, down GEMM with scatter epilogue,
     # barrier, finalize.
-    KERNEL_LAUNCHES = 15
-    KERNEL_LAUNCHES_EP = 19
+    KERNEL_LAUNCHES = 13
+    KERNEL_LAUNCHES_EP = 17
 
 
 class CapturedDecodeStep:

@@ -228,7 +228,7 @@ def case_paged_attention(ops, dev, steps, warmup, peaks):
     bt, cl = a["block_tables"].to(dev), a["context_lens"].to(dev)
     us, _ = time_launches(lambda i: ops.paged_attention(q, kc, vc, bt, cl), 1, steps, warmup, dev)
     rec = op_record("paged_attention", "B=64 28q/4kv D=128 L~U[512,8192] page 128", nbytes, us, peaks,
-                    "hbm", launches=3)
+                    "hbm", launches=1)
     rec["sum_context"] = int(a["context_lens"].sum())
     return rec
 
@@ -684,7 +684,7 @@ def main():
             "eager_us": round(layer["eager_us"], 1),
             "e2e": {"value": round(layer["e2e_us"], 1), "unit": "us",
                     "h2d_bytes_per_step": layer["h2d"], "d2h_bytes_per_step": layer["d2h"]},
-            "roofline": {"bound": "hbm", "kernel": "paged_attention (fast kernel + combine) inside the step",
+            "roofline": {"bound": "hbm", "kernel": "paged_attention_fast_kernel (chunk merge fused) inside the step",
                          "achieved": round(att["gbs"], 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(att["gbs"] / peaks["hbm_gbs"], 4),
                          "traffic": int(att["bytes"] * ATTENTION_TRAFFIC_RATIO),

@@ -37,17 +37,15 @@ namespace b200ops {
 namespace gmm {
 
 constexpr int BM = 128;
-constexpr int BN = 256;
+constexpr int kWideBN = 256;    // output tile width of the throughput configuration
+constexpr int kNarrowBN = 64;   // single m-tile problems: four times as many CTAs stream the weights
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int kStages = 4;
+constexpr int kMaxStages = 8;
 constexpr int kThreads = 192;
 constexpr int kMaxExperts = 1024;
-constexpr int kTmemCols = 512;  // two fp32 accumulators of BN columns
 
 constexpr int kABytes = BM * BK * 2;
-constexpr int kBBytes = BN * BK * 2;
-constexpr int kStageBytes = kABytes + kBBytes;
 
 // Error codes left in the device status word.
 constexpr int kErrProducerWait = 1;
@@ -59,7 +57,7 @@ constexpr int kMinKBlocksPerSplit = 4;  // keep every k-slice long enough to fil
 // Workspace layout (only used when split-K engages): [kMaxGrid] tile counters, then
 // [kMaxGrid] fp32 partial tiles of BM x BN.  With s > 1 there is at most one work item per CTA.
 constexpr int kMaxGrid = 256;
-constexpr size_t kPartialTileBytes = static_cast<size_t>(BM) * BN * sizeof(float);
+constexpr size_t kPartialTileBytes = static_cast<size_t>(BM) * kWideBN * sizeof(float);
 constexpr size_t kCounterBytes = kMaxGrid * sizeof(int);
 
 // Host-side gate, shared by the size query and the launch.  Split-K adds a serial tail of
@@ -72,9 +70,16 @@ constexpr size_t kCounterBytes = kMaxGrid * sizeof(int);
 constexpr int64_t kMinSplitK = 8192;
 
 inline bool split_k_possible(int64_t num_tokens, int64_t k, int64_t n, int sms) {
-  const int64_t n_tiles = (n + BN - 1) / BN;
+  const int64_t n_tiles = (n + kWideBN - 1) / kWideBN;
   const int64_t min_tiles = ((num_tokens + BM - 1) / BM) * n_tiles;
   return min_tiles * 2 <= sms && k >= kMinSplitK;
+}
+
+// Narrow tiles: one m-tile of rows at most, wide tiles would occupy under a quarter of the SMs,
+// and K too short for split-K (which wins where both apply: 51 us against 71 us for a
+// 70-row, K = 14336, N = 4096 projection).
+inline bool use_narrow_tiles(int64_t num_tokens, int64_t k, int64_t n, int sms) {
+  return num_tokens <= BM && ((n + kWideBN - 1) / kWideBN) * 4 <= sms && k < kMinSplitK;
 }
 
 inline int launch_sms() { return sm_count() < kMaxGrid ? sm_count() : kMaxGrid; }
@@ -82,8 +87,8 @@ inline int launch_sms() { return sm_count() < kMaxGrid ? sm_count() : kMaxGrid; 
 inline size_t workspace_bytes() { return kCounterBytes + launch_sms() * kPartialTileBytes; }
 
 struct Control {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
@@ -94,7 +99,24 @@ struct Control {
   int row_end[kMaxExperts];
 };
 
-constexpr size_t kSmemBytes = 1024 /* alignment slack */ + kStages * kStageBytes + sizeof(Control);
+// Tile configuration: BM x BN_ output tile, STAGES_-deep ring of (A 16 KB + B BN_*128 B) stages,
+// two fp32 accumulators of BN_ TMEM columns.  <256, 4> is the throughput shape (48 KB stages).
+// <64, 8> (24 KB stages, the same 192 KB in flight) is for problems whose rows fit ONE m-tile and
+// whose wide tiles would occupy under a quarter of the SMs (decode-size dense projections): a
+// CTA can only pull about 100 GB/s through its ring, so four times as many CTAs stream the
+// weights four times as fast.  With more than one m-tile the narrow shape loses (two thirds of
+// every stage is the re-read activation tile), so it is not used there.
+template <int BN_, int STAGES_>
+struct Cfg {
+  static constexpr int BN = BN_;
+  static constexpr int kStages = STAGES_;
+  static constexpr int kBBytes = BN_ * BK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kTmemCols = 2 * BN_ < 32 ? 32 : 2 * BN_;  // a power of two >= 32
+  static constexpr size_t kSmemBytes = 1024 /* alignment slack */ + STAGES_ * kStageBytes + sizeof(Control);
+};
+using WideCfg = Cfg<kWideBN, 4>;
+using NarrowCfg = Cfg<kNarrowBN, 8>;
 
 // Sticky per-device status of the pipeline kernels (0 = no failure).
 __device__ int g_pipeline_status = 0;
@@ -140,7 +162,7 @@ __device__ __forceinline__ WorkItem locate_item(int item, int splits, int k_bloc
 
 // Tiles of one group are numbered m-fastest.  `g` is carried between calls: tile ids only
 // grow within a CTA, so the search is amortised O(1).
-__device__ __forceinline__ TileCoord locate_tile(const Control* c, int tile, int& g) {
+__device__ __forceinline__ TileCoord locate_tile(const Control* c, int tile, int& g, int bn) {
   while (tile >= c->tile_prefix[g + 1]) ++g;
   const int local = tile - c->tile_prefix[g];
   const int rows = c->row_end[g] - c->row_start[g];
@@ -151,16 +173,22 @@ __device__ __forceinline__ TileCoord locate_tile(const Control* c, int tile, int
   t.group = g;
   t.row0 = c->row_start[g] + m_tile * BM;
   t.row_end = c->row_end[g];
-  t.n0 = n_tile * BN;
+  t.n0 = n_tile * bn;
   return t;
 }
 
+template <class C>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
                       const __grid_constant__ CUtensorMap map_w,
                       const int64_t* __restrict__ group_list, __half* __restrict__ y, int M, int N,
                       int K, int E, int* __restrict__ tile_counters, float* __restrict__ partials,
                       const RowScatter scatter) {
+  constexpr int BN = C::BN;
+  constexpr int kStages = C::kStages;
+  constexpr int kBBytes = C::kBBytes;
+  constexpr int kStageBytes = C::kStageBytes;
+  constexpr int kTmemCols = C::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -234,7 +262,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const WorkItem wi = locate_item(item, splits, k_blocks);
-        const TileCoord tc = locate_tile(ctl, wi.tile, g);
+        const TileCoord tc = locate_tile(ctl, wi.tile, g, BN);
         for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
             *abort_flag = 1;
@@ -304,7 +332,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
     int g = 0, iter = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++iter) {
       const WorkItem wi = locate_item(item, splits, k_blocks);
-      const TileCoord tc = locate_tile(ctl, wi.tile, g);
+      const TileCoord tc = locate_tile(ctl, wi.tile, g, BN);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
       if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) {
@@ -512,27 +540,30 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
     const int rc = encode_f16_map(&map_x, x, 2, dims, strides, box, "grouped_matmul(x)");
     if (rc != B200OPS_OK) return rc;
   }
+  const int sms = gmm::launch_sms();
+  const bool narrow = gmm::use_narrow_tiles(num_tokens, k, n, sms);
+  const int bn = narrow ? gmm::kNarrowBN : gmm::kWideBN;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
                               static_cast<uint64_t>(num_experts)};
     const uint64_t strides[2] = {static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(k) * n * 2};
-    const uint32_t box[3] = {gmm::BK, gmm::BN, 1};
+    const uint32_t box[3] = {gmm::BK, static_cast<uint32_t>(bn), 1};
     const int rc = encode_f16_map(&map_w, w, 3, dims, strides, box, "grouped_matmul(w)");
     if (rc != B200OPS_OK) return rc;
   }
 
-  static bool attr_set[64] = {false};
+  auto kern = narrow ? gmm::grouped_matmul_kernel<gmm::NarrowCfg> : gmm::grouped_matmul_kernel<gmm::WideCfg>;
+  const size_t smem = narrow ? gmm::NarrowCfg::kSmemBytes : gmm::WideCfg::kSmemBytes;
+  static bool attr_set[2][64] = {{false}};
   int dev = 0;
   B200OPS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    B200OPS_CUDA(cudaFuncSetAttribute(gmm::grouped_matmul_kernel,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      static_cast<int>(gmm::kSmemBytes)));
-    attr_set[dev] = true;
+  if (dev >= 0 && dev < 64 && !attr_set[narrow][dev]) {
+    B200OPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(smem)));
+    attr_set[narrow][dev] = true;
   }
-  const int64_t n_tiles = (n + gmm::BN - 1) / gmm::BN;
+  const int64_t n_tiles = (n + bn - 1) / bn;
   const int64_t max_tiles = ((num_tokens + gmm::BM - 1) / gmm::BM + num_experts) * n_tiles;
-  const int sms = gmm::launch_sms();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   int* counters = nullptr;
   float* partials = nullptr;
@@ -542,16 +573,15 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
       return fail(B200OPS_EWORKSPACE, "grouped_matmul: workspace of %zu bytes needed, got %zu",
                   gmm::workspace_bytes(), workspace_size);
     B200OPS_REQUIRE(aligned16(workspace), "grouped_matmul: workspace must be 16-byte aligned");
-    {
-      counters = static_cast<int*>(workspace);
-      partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + gmm::kCounterBytes);
-      B200OPS_CUDA(cudaMemsetAsync(counters, 0, gmm::kCounterBytes, st));
-      grid = sms;  // idle CTAs exit; the split factor needs the full grid
-    }
+    counters = static_cast<int*>(workspace);
+    partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + gmm::kCounterBytes);
+    B200OPS_CUDA(cudaMemsetAsync(counters, 0, gmm::kCounterBytes, st));
+    grid = sms;  // idle CTAs exit; the split factor needs the full grid
   }
-  gmm::grouped_matmul_kernel<<<grid, gmm::kThreads, gmm::kSmemBytes, st>>>(
-      map_x, map_w, group_list, static_cast<__half*>(y), static_cast<int>(num_tokens),
-      static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts), counters, partials, scatter);
+  kern<<<grid, gmm::kThreads, smem, st>>>(map_x, map_w, group_list, static_cast<__half*>(y),
+                                          static_cast<int>(num_tokens), static_cast<int>(n),
+                                          static_cast<int>(k), static_cast<int>(num_experts), counters,
+                                          partials, scatter);
   B200OPS_LAUNCH_CHECK("grouped_matmul");
   return B200OPS_OK;
 }

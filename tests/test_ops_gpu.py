@@ -410,3 +410,21 @@ def test_grouped_matmul_split_k(cabi, counts, k, n):
     close(plain, want)
     # twice in a row on the same workspace contents: the call resets its own counters
     close(run_grouped_matmul(cabi, x, w_storage, gl, split_k=True), want)
+
+
+@pytest.mark.parametrize("counts,k,n", [
+    ([100], 4096, 6144),          # decode-size QKV projection: 96 narrow tiles, one per CTA
+    ([32], 4096, 4096),           # output projection at 32 tokens
+    ([128], 64, 64),              # smallest narrow problem
+    ([10] * 8, 512, 4096),        # several groups: 512 narrow tiles, several per CTA
+    ([3, 0, 60, 1, 64], 1024, 2304),  # ragged groups, empty group, N not a multiple of 256
+])
+def test_grouped_matmul_narrow_tiles(cabi, counts, k, n):
+    """At most 128 rows in total and few output columns: the 128 x 64 tile configuration."""
+    g = torch.Generator().manual_seed(sum(counts) + k + n)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half()
+    w_storage = (torch.randn(len(counts), n, k, generator=g) * 0.05).half()
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64)
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    close(run_grouped_matmul(cabi, x, w_storage, gl), want)

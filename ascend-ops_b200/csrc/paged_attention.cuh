@@ -42,47 +42,71 @@ struct Args {
 
 #ifdef __CUDACC__
 // Merge the n_chunks partial records of (sequence b, query head h) and write the fp16 row.
-// One warp; lanes first take one chunk each for the maximum and the normaliser, then every
-// lane sums its channels (lane, lane + 32, ...) over the chunks.  Records are read with
-// ld.global.cg because in the fused form they were written by other SMs of the same launch.
+// One warp.  Lane c keeps the maximum and normaliser of chunk c (further chunks of a very
+// long context are folded in by loops); then every lane sums its channels (lane, lane + 32,
+// ...) over the chunks, eight chunks per batch so that their loads are all in flight before
+// the first one is used: the merge is a chain of L2 round trips, not of bandwidth.  Records
+// are read with ld.global.cg because in the fused form other SMs of the same launch wrote them.
+// kStaticD is the head dimension when the caller knows it at compile time (0 = read it from
+// the arguments, up to 256): a known 128 halves the registers per chunk and doubles the batch.
+template <int kStaticD = 0>
 __device__ __forceinline__ void combine_head(const Args& a, int b, int h, int n_chunks, int lane) {
-  const int D = a.head_dim;
+  constexpr int kPerLane = kStaticD > 0 ? kStaticD / 32 : 8;
+  constexpr int kBatch = 64 / kPerLane;
+  const int D = kStaticD > 0 ? kStaticD : a.head_dim;
   const size_t rec = partial_stride(D);
   const size_t item = static_cast<size_t>(b) * a.num_heads + h;
   const float* base = a.partials + item * a.max_chunks * rec;
-  float mm = -INFINITY;
-  for (int c = lane; c < n_chunks; c += 32) mm = fmaxf(mm, __ldcg(base + c * rec + D));
+  float m0 = -INFINITY, l0 = 0.f;
+  if (lane < n_chunks) {
+    m0 = __ldcg(base + lane * rec + D);
+    l0 = __ldcg(base + lane * rec + D + 1);
+  }
+  float mm = m0;
+  for (int c = lane + 32; c < n_chunks; c += 32) mm = fmaxf(mm, __ldcg(base + c * rec + D));
   mm = warp_max(mm);
-  float ll = 0.f;
-  for (int c = lane; c < n_chunks; c += 32) {
+  float ll = (m0 == -INFINITY) ? 0.f : l0 * exp2f(m0 - mm);
+  for (int c = lane + 32; c < n_chunks; c += 32) {
     const float mc = __ldcg(base + c * rec + D);
     if (mc != -INFINITY) ll += __ldcg(base + c * rec + D + 1) * exp2f(mc - mm);
   }
   ll = warp_sum(ll);
   const float inv = ll > 0.f ? 1.0f / ll : 0.f;
-  float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};  // head_dim <= 256 -> up to 8 per lane
+  float acc[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) acc[i] = 0.f;
   for (int c0 = 0; c0 < n_chunks; c0 += 32) {
     const int mine = c0 + lane;
     float w = 0.f;
     if (mine < n_chunks) {
-      const float mc = __ldcg(base + mine * rec + D);
+      const float mc = c0 == 0 ? m0 : __ldcg(base + mine * rec + D);
       w = (mc == -INFINITY) ? 0.f : exp2f(mc - mm);
     }
     const int n = min(32, n_chunks - c0);
-    for (int j = 0; j < n; ++j) {
-      const float wj = __shfl_sync(0xffffffffu, w, j);
-      if (wj == 0.f) continue;
-      const float* p = base + static_cast<size_t>(c0 + j) * rec;
+    for (int j0 = 0; j0 < n; j0 += kBatch) {
+      float v[kBatch][kPerLane];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int d = lane + i * 32;
-        if (d < D) acc[i] = fmaf(wj, __ldcg(p + d), acc[i]);
+      for (int u = 0; u < kBatch; ++u) {
+        const float* p = base + static_cast<size_t>(c0 + min(j0 + u, n - 1)) * rec;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+          const int d = lane + i * 32;
+          v[u][i] = d < D ? __ldcg(p + d) : 0.f;
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        float wu = __shfl_sync(0xffffffffu, w, (j0 + u) & 31);
+        if (j0 + u >= n) wu = 0.f;
+        // A chunk of weight zero may hold anything (an empty chunk's sums): select, not multiply.
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) acc[i] = fmaf(wu, wu != 0.f ? v[u][i] : 0.f, acc[i]);
       }
     }
   }
   __half* out = a.out + item * D;
 #pragma unroll
-  for (int i = 0; i < 8; ++i) {
+  for (int i = 0; i < kPerLane; ++i) {
     const int d = lane + i * 32;
     if (d < D) out[d] = __float2half(acc[i] * inv);
   }

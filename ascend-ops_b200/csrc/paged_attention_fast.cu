@@ -211,7 +211,7 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
       asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32));
       if (*arrival == n_chunks - 1) {
         __threadfence();
-        for (int r = warp; r < group; r += kConsumerWarps) combine_head(a, b, h0 + r, n_chunks, lane);
+        for (int r = warp; r < group; r += kConsumerWarps) combine_head<kD>(a, b, h0 + r, n_chunks, lane);
       }
     }
   }

@@ -25,10 +25,16 @@
 // partial tiles to the workspace.  A counter per tile identifies the last CTA to finish; it
 // alone sums the partials and writes the fp16 rows.  Nobody waits on another CTA.
 //
+// CTA pairs.  Problems of a wave of tiles or more run grouped_matmul_pair_kernel instead
+// (grouped_matmul_pair.cuh): clusters of two CTAs issue one 256 x 256 x 16 MMA (cta_group::2), each
+// CTA loading its own rows of x and half of the w tile.
+//
 // Tiles are enumerated group by group, m-tile fastest, so that CTAs running at the same
 // time share the same w tile (read from HBM once, then from L2) while the group's x rows
 // stay L2-resident.  Work is 2*M*K*N flops; at the sizes of interest the kernel is bound by
 // the tensor pipe, at decode sizes (few rows per expert) by streaming w from HBM.
+#include <cstdlib>
+
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 #include "tma_host.cuh"
@@ -80,6 +86,26 @@ inline bool split_k_possible(int64_t num_tokens, int64_t k, int64_t n, int sms) 
 // 70-row, K = 14336, N = 4096 projection).
 inline bool use_narrow_tiles(int64_t num_tokens, int64_t k, int64_t n, int sms) {
   return num_tokens <= BM && ((n + kWideBN - 1) / kWideBN) * 4 <= sms && k < kMinSplitK;
+}
+
+// CTA pairs (grouped_matmul_pair.cuh): for problems bound by the tensor pipe and not by streaming
+// the weights once -- at least one wave of 128 x 256 output tiles, and two m-tiles per expert on
+// average (with one m-tile per expert the second CTA of every pair would multiply nothing useful).
+// Measured on B200 against the single-CTA kernel: 4096^3 dense 103 us against 112 us; the
+// power-capped benchmark shapes (8192 rows, 8 experts) 1595 against 1600 us and 820 against 833 us.
+// B200OPS_GMM_PAIR: 0 = never, 2 = always (tests), otherwise this rule.
+inline int pair_mode() {
+  const char* s = std::getenv("B200OPS_GMM_PAIR");
+  return (s && *s) ? std::atoi(s) : 1;
+}
+
+inline bool use_cta_pairs(int64_t num_tokens, int64_t num_experts, int64_t n, int sms) {
+  const int mode = pair_mode();
+  if (mode == 0) return false;
+  if (mode == 2) return true;
+  const int64_t n_tiles = (n + kWideBN - 1) / kWideBN;
+  const int64_t min_tiles = ((num_tokens + BM - 1) / BM) * n_tiles;
+  return min_tiles >= sms && num_tokens >= 2 * BM * num_experts;
 }
 
 inline int launch_sms() { return sm_count() < kMaxGrid ? sm_count() : kMaxGrid; }
@@ -176,6 +202,8 @@ __device__ __forceinline__ TileCoord locate_tile(const Control* c, int tile, int
   t.n0 = n_tile * bn;
   return t;
 }
+
+#include "grouped_matmul_pair.cuh"
 
 template <class C>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -513,6 +541,78 @@ extern "C" int b200ops_grouped_matmul_scatter(const void* x, const void* w, cons
                      workspace_size, sc, stream);
 }
 
+namespace b200ops {
+namespace gmm {
+// Clusters of two CTAs that the device can keep resident at once (cached per device).
+static int resident_pairs(int dev, int sms) {
+  static int cached[64] = {0};
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(sms / 2 * 2));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, grouped_matmul_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    n = sms / 2;
+  }
+  if (n > sms / 2) n = sms / 2;
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  return n;
+}
+
+static int launch_pairs(const CUtensorMap& map_x, const void* w, const int64_t* group_list, void* y,
+                        int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n,
+                        const RowScatter& scatter, cudaStream_t st) {
+  CUtensorMap map_w;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                              static_cast<uint64_t>(num_experts)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(k) * n * 2};
+    const uint32_t box[3] = {BK, kPairBN / 2, 1};
+    const int rc = encode_f16_map(&map_w, w, 3, dims, strides, box, "grouped_matmul(w)");
+    if (rc != B200OPS_OK) return rc;
+  }
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  B200OPS_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    B200OPS_CUDA(cudaFuncSetAttribute(grouped_matmul_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(kPairSmemBytes)));
+    attr_set[dev] = true;
+  }
+  const int64_t n_tiles = (n + kPairBN - 1) / kPairBN;
+  const int64_t max_items = (((num_tokens + BM - 1) / BM + 1) / 2 + num_experts) * n_tiles;
+  const int64_t resident = resident_pairs(dev, launch_sms());
+  const int pairs = static_cast<int>(max_items < resident ? max_items : resident);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kPairSmemBytes;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B200OPS_CUDA(cudaLaunchKernelEx(&cfg, grouped_matmul_pair_kernel, map_x, map_w, group_list,
+                                  static_cast<__half*>(y), static_cast<int>(num_tokens), static_cast<int>(n),
+                                  static_cast<int>(k), static_cast<int>(num_experts), scatter));
+  B200OPS_LAUNCH_CHECK("grouped_matmul");
+  return B200OPS_OK;
+}
+}  // namespace gmm
+}  // namespace b200ops
+
 int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list, void* y, int64_t num_tokens,
                          int64_t k, int64_t num_experts, int64_t n, void* workspace, size_t workspace_size,
                          const RowScatter& scatter, void* stream) {
@@ -541,6 +641,9 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
     if (rc != B200OPS_OK) return rc;
   }
   const int sms = gmm::launch_sms();
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (gmm::use_cta_pairs(num_tokens, num_experts, n, sms))
+    return gmm::launch_pairs(map_x, w, group_list, y, num_tokens, k, num_experts, n, scatter, st);
   const bool narrow = gmm::use_narrow_tiles(num_tokens, k, n, sms);
   const int bn = narrow ? gmm::kNarrowBN : gmm::kWideBN;
   {
@@ -564,7 +667,6 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   }
   const int64_t n_tiles = (n + bn - 1) / bn;
   const int64_t max_tiles = ((num_tokens + gmm::BM - 1) / gmm::BM + num_experts) * n_tiles;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
   int* counters = nullptr;
   float* partials = nullptr;
   int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);

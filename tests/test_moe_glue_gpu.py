@@ -219,12 +219,15 @@ def test_peer_barrier_passes_when_peers_arrived_and_gives_up_when_not(cabi):
     assert float((torch.ones(4, device=DEV) * 2).sum()) == 8.0  # the device still answers
 
 
-@pytest.mark.parametrize("counts,k,n", [([40, 3, 0, 21], 256, 192), ([70], 8192, 256)])  # second: split-K path
-def test_grouped_matmul_scatter_equals_matmul_then_push(cabi, counts, k, n):
+@pytest.mark.parametrize("pair_mode", ["0", "2"])  # single-CTA kernel / CTA-pair kernel
+@pytest.mark.parametrize("counts,k,n", [([40, 3, 0, 21], 256, 192), ([70], 8192, 256),  # second: split-K path
+                                        ([300, 129, 0, 60], 512, 320)])
+def test_grouped_matmul_scatter_equals_matmul_then_push(cabi, monkeypatch, counts, k, n, pair_mode):
     """The GEMM whose epilogue stores into the (emulated) peers' return buffers must leave
     exactly what grouped_matmul followed by push_rows leaves."""
+    monkeypatch.setenv("B200OPS_GMM_PAIR", pair_mode)
     lib = cabi.load()
-    world, rank, cap = 2, 1, 64
+    world, rank, cap = 2, 1, 256
     g = torch.Generator().manual_seed(sum(counts) + k)
     m = sum(counts)
     x = torch.randn(m, k, generator=g).half().to(DEV)

@@ -428,3 +428,46 @@ def test_grouped_matmul_narrow_tiles(cabi, counts, k, n):
     gl = torch.tensor(counts).cumsum(0).to(torch.int64)
     want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
     close(run_grouped_matmul(cabi, x, w_storage, gl), want)
+
+
+@pytest.mark.parametrize("counts,k,n", [
+    ([128], 64, 64),                        # smallest: CTA 1 of the pair has no rows at all
+    ([256], 128, 256),                      # exactly one full pair
+    ([300, 0, 1, 129, 70], 256, 320),       # odd m-tile counts, an empty group, N tail (256 + 64)
+    ([5, 250, 3, 0, 0, 77, 128, 256], 512, 1024),
+    ([1000], 1024, 768),                    # one group: 4 pairs x 3 n-tiles
+    ([17] * 128, 128, 192),                 # many experts, every pair half empty
+    ([0, 0, 40], 64, 128),                  # leading empty groups; second half of w past N
+    ([700, 900, 3000], 2048, 1536),         # several items per cluster, long k loop (ring wraps)
+])
+def test_grouped_matmul_cta_pairs(cabi, monkeypatch, counts, k, n):
+    """The CTA-pair kernel (two CTAs per 256-row MMA), forced for shapes of every kind; the
+    single-CTA kernel on the same inputs must give the same bits (same fp32 sums, same order)."""
+    g = torch.Generator().manual_seed(sum(counts) + k + n)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half()
+    w_storage = (torch.randn(len(counts), n, k, generator=g) * 0.05).half()
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64)
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    monkeypatch.setenv("B200OPS_GMM_PAIR", "2")
+    pairs = run_grouped_matmul(cabi, x, w_storage, gl, fill=3.0, split_k=False)
+    monkeypatch.setenv("B200OPS_GMM_PAIR", "0")
+    single = run_grouped_matmul(cabi, x, w_storage, gl, fill=3.0, split_k=False)
+    close(pairs, want)
+    assert torch.equal(pairs, single)
+
+
+def test_grouped_matmul_cta_pairs_engage_at_benchmark_scale(cabi, monkeypatch):
+    """A problem of several tile waves takes the pair kernel by default; sampled rows of every
+    group are checked against the oracle, all rows against the single-CTA kernel."""
+    w = wl.grouped_matmul_inputs(rows=8192, k=1024, n=4096, experts=8, seed=12)
+    monkeypatch.delenv("B200OPS_GMM_PAIR", raising=False)
+    auto = run_grouped_matmul(cabi, w["x"], w["w_storage"], w["group_list"])
+    monkeypatch.setenv("B200OPS_GMM_PAIR", "0")
+    single = run_grouped_matmul(cabi, w["x"], w["w_storage"], w["group_list"])
+    assert torch.equal(auto, single)
+    rows = torch.arange(0, 8192, 61)
+    ends = w["group_list"]
+    expert = torch.searchsorted(ends, rows, right=True)
+    want = torch.stack([(w["x"][r].float() @ w["w_storage"][e].float().T) for r, e in zip(rows, expert)])
+    close(auto[rows], want.half())

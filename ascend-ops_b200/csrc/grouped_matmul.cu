@@ -93,7 +93,11 @@ inline bool use_narrow_tiles(int64_t num_tokens, int64_t k, int64_t n, int sms) 
 // average (with one m-tile per expert the second CTA of every pair would multiply nothing useful).
 // Measured on B200 against the single-CTA kernel: 4096^3 dense 103 us against 112 us; the
 // power-capped benchmark shapes (8192 rows, 8 experts) 1595 against 1600 us and 820 against 833 us.
+// The row count the host sees is only a bound (an expert-parallel receive buffer of 1536 rows
+// holds about 128 at decode time, and the pair kernel then takes 54 us where the single-CTA kernel
+// takes 45 us), hence also an absolute floor on it.
 // B200OPS_GMM_PAIR: 0 = never, 2 = always (tests), otherwise this rule.
+constexpr int64_t kMinRowsForPairs = 2048;
 inline int pair_mode() {
   const char* s = std::getenv("B200OPS_GMM_PAIR");
   return (s && *s) ? std::atoi(s) : 1;
@@ -105,7 +109,7 @@ inline bool use_cta_pairs(int64_t num_tokens, int64_t num_experts, int64_t n, in
   if (mode == 2) return true;
   const int64_t n_tiles = (n + kWideBN - 1) / kWideBN;
   const int64_t min_tiles = ((num_tokens + BM - 1) / BM) * n_tiles;
-  return min_tiles >= sms && num_tokens >= 2 * BM * num_experts;
+  return min_tiles >= sms && num_tokens >= 2 * BM * num_experts && num_tokens >= kMinRowsForPairs;
 }
 
 inline int launch_sms() { return sm_count() < kMaxGrid ? sm_count() : kMaxGrid; }

@@ -112,6 +112,24 @@ inline bool use_cta_pairs(int64_t num_tokens, int64_t num_experts, int64_t n, in
   return min_tiles >= sms && num_tokens >= 2 * BM * num_experts && num_tokens >= kMinRowsForPairs;
 }
 
+// Cluster split-K (grouped_matmul_ksplit.cuh): one group, at most 256 rows (a dense projection of
+// a decode batch, whose row count the host knows), and so few output tiles that at least two
+// CTAs can share each.  Returns the cluster size, 0 = not this path.
+// B200OPS_GMM_KSPLIT=0 disables it.
+constexpr int kMaxClusterSplitRows = 256;
+constexpr int kMaxClusterSplitHost = 8;
+
+inline int cluster_split_factor(int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n, int sms) {
+  const char* env = std::getenv("B200OPS_GMM_KSPLIT");
+  if (env && *env && std::atoi(env) == 0) return 0;
+  if (num_experts != 1 || num_tokens > kMaxClusterSplitRows) return 0;
+  const int64_t tiles = ((num_tokens + BM - 1) / BM) * ((n + kWideBN - 1) / kWideBN);
+  int64_t s = sms / tiles;
+  if (s > kMaxClusterSplitHost) s = kMaxClusterSplitHost;
+  if (s > (k / BK) / kMinKBlocksPerSplit) s = (k / BK) / kMinKBlocksPerSplit;
+  return s >= 2 ? static_cast<int>(s) : 0;
+}
+
 inline int launch_sms() { return sm_count() < kMaxGrid ? sm_count() : kMaxGrid; }
 
 inline size_t workspace_bytes() { return kCounterBytes + launch_sms() * kPartialTileBytes; }
@@ -208,6 +226,7 @@ __device__ __forceinline__ TileCoord locate_tile(const Control* c, int tile, int
 }
 
 #include "grouped_matmul_pair.cuh"
+#include "grouped_matmul_ksplit.cuh"
 
 template <class C>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -572,6 +591,89 @@ static int resident_pairs(int dev, int sms) {
   return n;
 }
 
+// Clusters of `splits` CTAs of the split-K kernel that the device keeps resident at once.
+static int resident_split_clusters(int dev, int splits) {
+  static int cached[64][kMaxClusterSplitHost + 1] = {{0}};
+  if (dev >= 0 && dev < 64 && cached[dev][splits] != 0) return cached[dev][splits];
+  // The query counts against the function's shared-memory limit, so raise that first.
+  if (cudaFuncSetAttribute(grouped_matmul_ksplit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           static_cast<int>(kSplitSmemBytes)) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(launch_sms() / splits * splits));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSplitSmemBytes;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = 0;
+  if (cudaOccupancyMaxActiveClusters(&n, grouped_matmul_ksplit_kernel, &cfg) != cudaSuccess) {
+    cudaGetLastError();
+    n = 0;
+  }
+  if (n <= 0) n = -1;  // cached as "none fit"
+  if (dev >= 0 && dev < 64) cached[dev][splits] = n;
+  return n;
+}
+
+// All clusters must be resident at once: a cluster that has to wait for a free slot starts
+// when the others end and doubles the time.  Clusters are placed within a GPC, so fewer fit
+// than SMs / s: the largest s <= `splits` whose clusters all fit, 0 if none of two or more does.
+static int fit_split_to_device(int splits, int64_t num_tokens, int64_t n) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+  const int64_t tiles = ((num_tokens + BM - 1) / BM) * ((n + kSplitBN - 1) / kSplitBN);
+  while (splits > 1 && resident_split_clusters(dev, splits) < tiles) --splits;
+  return splits >= 2 ? splits : 0;
+}
+
+static int launch_ksplit(const CUtensorMap& map_x, const void* w, const int64_t* group_list, void* y,
+                         int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n, int splits,
+                         const RowScatter& scatter, cudaStream_t st) {
+  CUtensorMap map_w;
+  {
+    const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
+                              static_cast<uint64_t>(num_experts)};
+    const uint64_t strides[2] = {static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(k) * n * 2};
+    const uint32_t box[3] = {BK, kSplitBN, 1};
+    const int rc = encode_f16_map(&map_w, w, 3, dims, strides, box, "grouped_matmul(w)");
+    if (rc != B200OPS_OK) return rc;
+  }
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  B200OPS_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    B200OPS_CUDA(cudaFuncSetAttribute(grouped_matmul_ksplit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      static_cast<int>(kSplitSmemBytes)));
+    attr_set[dev] = true;
+  }
+  static_assert(kMaxClusterSplitHost == kMaxClusterSplit, "host and device agree on the cluster limit");
+  const int64_t tiles = ((num_tokens + BM - 1) / BM) * ((n + kSplitBN - 1) / kSplitBN);
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.gridDim = dim3(static_cast<unsigned>(tiles * splits));
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSplitSmemBytes;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  B200OPS_CUDA(cudaLaunchKernelEx(&cfg, grouped_matmul_ksplit_kernel, map_x, map_w, group_list,
+                                  static_cast<__half*>(y), static_cast<int>(num_tokens), static_cast<int>(n),
+                                  static_cast<int>(k), static_cast<int>(num_experts), scatter));
+  B200OPS_LAUNCH_CHECK("grouped_matmul");
+  return B200OPS_OK;
+}
+
 static int launch_pairs(const CUtensorMap& map_x, const void* w, const int64_t* group_list, void* y,
                         int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n,
                         const RowScatter& scatter, cudaStream_t st) {
@@ -646,6 +748,10 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   }
   const int sms = gmm::launch_sms();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
+  int s = gmm::cluster_split_factor(num_tokens, k, num_experts, n, sms);
+  if (s) s = gmm::fit_split_to_device(s, num_tokens, n);
+  if (s)
+    return gmm::launch_ksplit(map_x, w, group_list, y, num_tokens, k, num_experts, n, s, scatter, st);
   if (gmm::use_cta_pairs(num_tokens, num_experts, n, sms))
     return gmm::launch_pairs(map_x, w, group_list, y, num_tokens, k, num_experts, n, scatter, st);
   const bool narrow = gmm::use_narrow_tiles(num_tokens, k, n, sms);

@@ -396,7 +396,8 @@ def test_paged_attention_tile_balanced_path(cabi, monkeypatch, heads, kv_heads, 
     ([130], 8192, 256),                # two m-tiles, the second one a tail
     ([256], 16384, 1024),              # dense projection with a long K
 ])
-def test_grouped_matmul_split_k(cabi, counts, k, n):
+def test_grouped_matmul_split_k(cabi, monkeypatch, counts, k, n):
+    monkeypatch.setenv("B200OPS_GMM_KSPLIT", "0")  # single-group shapes would take the cluster path
     g = torch.Generator().manual_seed(sum(counts) + k)
     m = sum(counts)
     x = torch.randn(m, k, generator=g).half()
@@ -419,8 +420,10 @@ def test_grouped_matmul_split_k(cabi, counts, k, n):
     ([10] * 8, 512, 4096),        # several groups: 512 narrow tiles, several per CTA
     ([3, 0, 60, 1, 64], 1024, 2304),  # ragged groups, empty group, N not a multiple of 256
 ])
-def test_grouped_matmul_narrow_tiles(cabi, counts, k, n):
-    """At most 128 rows in total and few output columns: the 128 x 64 tile configuration."""
+def test_grouped_matmul_narrow_tiles(cabi, monkeypatch, counts, k, n):
+    """At most 128 rows in total and few output columns: the 128 x 64 tile configuration
+    (reached by single-group shapes only when the cluster split-K path is switched off)."""
+    monkeypatch.setenv("B200OPS_GMM_KSPLIT", "0")
     g = torch.Generator().manual_seed(sum(counts) + k + n)
     m = sum(counts)
     x = torch.randn(m, k, generator=g).half()
@@ -471,3 +474,44 @@ def test_grouped_matmul_cta_pairs_engage_at_benchmark_scale(cabi, monkeypatch):
     expert = torch.searchsorted(ends, rows, right=True)
     want = torch.stack([(w["x"][r].float() @ w["w_storage"][e].float().T) for r, e in zip(rows, expert)])
     close(auto[rows], want.half())
+
+
+@pytest.mark.parametrize("counts,k,n", [
+    ([256], 4096, 6144),     # QKV projection of a 256-row decode batch: 48 tiles x 3 CTAs
+    ([256], 4096, 4096),     # output projection: 32 tiles x 4
+    ([32], 4096, 6144),      # 32 rows: 24 tiles x 6
+    ([32], 4096, 4096),      # 16 tiles x 8 (the largest cluster)
+    ([200], 1024, 320),      # second m-tile a tail, N tail (256 + 64), 4 k-blocks per CTA
+    ([1], 512, 64),          # one row, one tile, two CTAs
+    ([70], 14336, 4096),     # long K
+    ([129], 960, 2048),      # 15 k-blocks over 3 CTAs: uneven slices
+])
+def test_grouped_matmul_cluster_split_k(cabi, monkeypatch, counts, k, n):
+    """Dense decode-size projections: the CTAs of a cluster share one output tile and reduce
+    their k-slices through distributed shared memory."""
+    g = torch.Generator().manual_seed(sum(counts) + k + n)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half()
+    w_storage = (torch.randn(1, n, k, generator=g) * 0.05).half()
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64)
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    monkeypatch.delenv("B200OPS_GMM_KSPLIT", raising=False)
+    got = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False)
+    close(got, want)
+    again = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False)
+    assert torch.equal(got, again)  # fixed summation order: bitwise repeatable
+    monkeypatch.setenv("B200OPS_GMM_KSPLIT", "0")
+    close(run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False), want)
+
+
+def test_grouped_matmul_cluster_split_k_fewer_rows_than_the_bound(cabi):
+    """group_list may end before num_tokens: clusters whose tile does not exist do nothing, rows
+    past the group's end stay untouched."""
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(256, 2048, generator=g).half()
+    w_storage = (torch.randn(1, 1024, 2048, generator=g) * 0.05).half()
+    gl = torch.tensor([100], dtype=torch.int64)
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    got = run_grouped_matmul(cabi, x, w_storage, gl, fill=9.0, split_k=False)
+    close(got[:100], want[:100])
+    assert (got[100:] == 9.0).all()

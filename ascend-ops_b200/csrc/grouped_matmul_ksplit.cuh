@@ -10,6 +10,7 @@
 // r, r + s, ... by reading all s copies through distributed shared memory, in rank order, so
 // the result does not depend on timing.  The hardware co-schedules a cluster, so the barrier
 // is a hardware one and there is no workspace, no counter and no spin.
+// Single group only: the tile grid follows from the host's row bound.
 #pragma once
 
 constexpr int kSplitBN = kWideBN;
@@ -112,6 +113,19 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   const int kb0 = static_cast<int>(static_cast<long long>(rank) * k_blocks / splits);
   const int kb1 = static_cast<int>(static_cast<long long>(rank + 1) * k_blocks / splits);
 
+  // One group only (the host checks): tile -> (m-tile, n-tile) needs no table, and the row count
+  // matters only to the stores.  Every cluster of the grid multiplies its tile; rows past the
+  // group's end are computed from whatever x holds there and never stored.
+  const int m_tiles = (M + BM - 1) / BM;
+  TileCoord tc;
+  tc.group = 0;
+  tc.n0 = (tile / m_tiles) * kSplitBN;
+  tc.row0 = (tile - (tile / m_tiles) * m_tiles) * BM;
+  tc.row_end = 0;  // read after the first loads are on their way
+  // splits <= k_blocks gives every rank at least one k-block; the host never asks otherwise.
+  const bool active = splits <= k_blocks && tile < m_tiles * n_tiles;
+  const int prefill = active ? min(kSplitStages, kb1 - kb0) : 0;
+
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSplitStages; ++s) {
       ptx::mbar_init(&ctl->full[s], 1);
@@ -120,30 +134,17 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
     ptx::mbar_init(&ctl->tmem_full[0], 1);
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
-    ptx::prefetch_tensormap(&map_x);
-    ptx::prefetch_tensormap(&map_w);
+    // The first ring-full of loads needs nobody else: issue it before the CTA-wide set-up so
+    // that its latency (about 2 us from HBM) overlaps the TMEM allocation and the barrier.
+    for (int i = 0; i < prefill; ++i) {
+      ptx::mbar_arrive_expect_tx(&ctl->full[i], kSplitStageBytes);
+      ptx::tma_load_2d(a_tiles + i * kABytes, &map_x, &ctl->full[i], (kb0 + i) * BK, tc.row0);
+      ptx::tma_load_3d(b_tiles + i * kSplitBBytes, &map_w, &ctl->full[i], (kb0 + i) * BK, tc.n0, 0);
+    }
   }
   if (warp == 1) {
     ptx::tmem_alloc(&ctl->tmem_base, kSplitTmemCols);
     ptx::tmem_relinquish_alloc_permit();
-  }
-  for (int e = threadIdx.x; e < E; e += kThreads) {
-    long long s = e ? group_list[e - 1] : 0;
-    long long t = group_list[e];
-    s = s < 0 ? 0 : (s > M ? M : s);
-    t = t < s ? s : (t > M ? M : t);
-    ctl->row_start[e] = static_cast<int>(s);
-    ctl->row_end[e] = static_cast<int>(t);
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int acc = 0;
-    ctl->tile_prefix[0] = 0;
-    for (int e = 0; e < E; ++e) {
-      const int rows = ctl->row_end[e] - ctl->row_start[e];
-      acc += ((rows + BM - 1) / BM) * n_tiles;
-      ctl->tile_prefix[e + 1] = acc;
-    }
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
@@ -151,21 +152,18 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
 
   const uint32_t tmem_base = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
-  // Every CTA of the cluster sees the same table, so they agree on whether the tile exists.
-  // (splits <= k_blocks gives every rank at least one k-block; the host never asks otherwise.)
-  const bool active = tile < ctl->tile_prefix[E] && splits <= k_blocks;
-  TileCoord tc = {0, 0, 0, 0};
-  if (active) {
-    int g = 0;
-    tc = locate_tile(ctl, tile, g, kSplitBN);
+  {
+    long long rows = group_list[0];
+    rows = rows < 0 ? 0 : (rows > M ? M : rows);
+    tc.row_end = static_cast<int>(rows);
   }
 
   if (active && warp == 0) {
-    // ---------------- TMA producer ----------------
+    // ---------------- TMA producer (the rest of the k-slice) ----------------
     if (lane == 0) {
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int kb = kb0; kb < kb1; ++kb) {
+      int stage = prefill == kSplitStages ? 0 : prefill;
+      uint32_t phase = prefill == kSplitStages ? 1u : 0u;
+      for (int kb = kb0 + prefill; kb < kb1; ++kb) {
         if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
           *abort_flag = 1;
           atomicCAS(&g_pipeline_status, 0, kErrProducerWait);
@@ -173,8 +171,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
         }
         ptx::mbar_arrive_expect_tx(&ctl->full[stage], kSplitStageBytes);
         ptx::tma_load_2d(a_tiles + stage * kABytes, &map_x, &ctl->full[stage], kb * BK, tc.row0);
-        ptx::tma_load_3d(b_tiles + stage * kSplitBBytes, &map_w, &ctl->full[stage], kb * BK, tc.n0,
-                         tc.group);
+        ptx::tma_load_3d(b_tiles + stage * kSplitBBytes, &map_w, &ctl->full[stage], kb * BK, tc.n0, 0);
         if (++stage == kSplitStages) {
           stage = 0;
           phase ^= 1u;

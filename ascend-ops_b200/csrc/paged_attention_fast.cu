@@ -62,6 +62,32 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
   const int group = a.num_heads / a.num_kv_heads;
   const int h0 = kvh * group;
 
+  // The producer warp starts the chunk's block-table reads before the sequence length is
+  // known (entries past the sequence's end are clamped to valid pages and never used), and its
+  // first lane sets up the barriers: three dependent global round trips (length, table, data)
+  // become two, and the first tiles are on their way before the CTA-wide barrier.
+  const int start = chunk * a.chunk_tokens;
+  if (warp == kConsumerWarps) {
+    const int pages_per_chunk = a.chunk_tokens / a.page_size;
+    const int first_page = chunk * pages_per_chunk;
+    const int32_t* table = a.block_tables + static_cast<size_t>(b) * a.max_pages_per_seq;
+    for (int i = lane; i < pages_per_chunk && first_page + i < a.max_pages_per_seq; i += 32) {
+      int pg = table[first_page + i];
+      pg = pg < 0 ? 0 : (pg >= a.num_pages ? a.num_pages - 1 : pg);
+      page_ids[i] = pg;
+    }
+    if (lane == 0) {
+      for (int s = 0; s < kStages; ++s) {
+        ptx::mbar_init(&full[s], 1);
+        ptx::mbar_init(&empty[s], kConsumerWarps);
+      }
+      *abort_flag = 0;
+      ptx::fence_barrier_init();
+      ptx::prefetch_tensormap(&map_k);
+      ptx::prefetch_tensormap(&map_v);
+    }
+  }
+
   int L = a.context_lens[b];
   const int cap = a.max_pages_per_seq * a.page_size;
   if (L > cap) L = cap;
@@ -71,53 +97,43 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
         a.out[(static_cast<size_t>(b) * a.num_heads + h0) * kD + i] = __float2half(0.f);
     return;
   }
-  const int start = chunk * a.chunk_tokens;
   if (start >= L) return;
   const int end = min(L, start + a.chunk_tokens);
   const int n_tiles = (end - start + kTile - 1) / kTile;
   const int n_chunks = (L + a.chunk_tokens - 1) / a.chunk_tokens;
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(&full[s], 1);
-      ptx::mbar_init(&empty[s], kConsumerWarps);
-    }
-    *abort_flag = 0;
-    ptx::fence_barrier_init();
+  // One tile = K and V of 64 tokens of this kv head: four boxes of 64 channels.
+  auto issue_tile = [&](int t, int stage) {
+    const int tok = t * kTile;  // relative to the chunk start (a page boundary)
+    const int pg = page_ids[tok / a.page_size];
+    const int off = tok % a.page_size;
+    uint8_t* st = smem + stage * kStageBytes;
+    ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
+    ptx::tma_load_4d(st, &map_k, &full[stage], 0, kvh, off, pg);
+    ptx::tma_load_4d(st + kSubTileBytes, &map_k, &full[stage], 64, kvh, off, pg);
+    ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, kvh, off, pg);
+    ptx::tma_load_4d(st + kTensorTileBytes + kSubTileBytes, &map_v, &full[stage], 64, kvh, off, pg);
+  };
+  const int prefill = min(kStages, n_tiles);
+  if (warp == kConsumerWarps) {
+    __syncwarp();  // page_ids of all lanes are in shared memory
+    if (lane == 0)
+      for (int t = 0; t < prefill; ++t) issue_tile(t, t);  // a fresh ring: nothing to wait for
   }
   __syncthreads();
 
   if (warp == kConsumerWarps) {
-    // ---------------- producer warp ----------------
-    const int first_page = start / a.page_size;
-    const int n_pages = (end - start + a.page_size - 1) / a.page_size;
-    const int32_t* table = a.block_tables + static_cast<size_t>(b) * a.max_pages_per_seq;
-    for (int i = lane; i < n_pages; i += 32) {
-      int pg = table[first_page + i];
-      pg = pg < 0 ? 0 : (pg >= a.num_pages ? a.num_pages - 1 : pg);
-      page_ids[i] = pg;
-    }
-    __syncwarp();
+    // ---------------- producer warp: the rest of the chunk ----------------
     if (lane == 0) {
-      ptx::prefetch_tensormap(&map_k);
-      ptx::prefetch_tensormap(&map_v);
-      int stage = 0;
-      uint32_t phase = 0;
-      for (int t = 0; t < n_tiles; ++t) {
+      int stage = prefill == kStages ? 0 : prefill;
+      uint32_t phase = prefill == kStages ? 1u : 0u;
+      for (int t = prefill; t < n_tiles; ++t) {
         if (!ptx::mbar_wait(&empty[stage], phase ^ 1u, abort_flag)) {
           *abort_flag = 1;
           atomicCAS(&g_pa_status, 0, kErrProducerWait);
           break;
         }
-        const int tok = t * kTile;  // relative to the chunk start (a page boundary)
-        const int pg = page_ids[tok / a.page_size];
-        const int off = tok % a.page_size;
-        uint8_t* st = smem + stage * kStageBytes;
-        ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
-        ptx::tma_load_4d(st, &map_k, &full[stage], 0, kvh, off, pg);
-        ptx::tma_load_4d(st + kSubTileBytes, &map_k, &full[stage], 64, kvh, off, pg);
-        ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, kvh, off, pg);
-        ptx::tma_load_4d(st + kTensorTileBytes + kSubTileBytes, &map_v, &full[stage], 64, kvh, off, pg);
+        issue_tile(t, stage);
         if (++stage == kStages) {
           stage = 0;
           phase ^= 1u;

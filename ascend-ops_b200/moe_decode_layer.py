@@ -130,10 +130,12 @@ class MoEDecodeLayer:
         self.moe.grouped_matmul_scatter(act, self.w_down, group_list, *scatter)
 
     def forward(self, x, residual, positions, slots, block_tables, context_lens, k_cache, v_cache,
-                return_routing=False, attention_events=None):
+                return_routing=False, attention_events=None, on_residual=None):
         """`attention_events`, if given, is a pair of CUDA events recorded right before and
         after the attention operator on the current stream (used by the benchmark to time the
-        dominant kernel inside the step)."""
+        dominant kernel inside the step).  `on_residual(residual_out)` is called as soon as the
+        launch that produces the step's second output has been enqueued, well before the expert
+        MLP: a caller that ships results to the host can start that copy early."""
         cfg, ops = self.cfg, self.ops
         t = x.shape[0]
         h1, res1 = ops.add_rms_norm(x, residual, self.ln1, cfg.eps)
@@ -156,6 +158,8 @@ class MoEDecodeLayer:
             attention_events[1].record()
         o = self._dense(attn.view(t, nq), self.wo)
         h2, res2 = ops.add_rms_norm(o, res1, self.ln2, cfg.eps)
+        if on_residual is not None:
+            on_residual(res2)
         ids, wts = self.moe.route_topk(h2, self.wrouter, cfg.top_k)
         if self.exchange is not None:
             y = self.exchange.mlp(h2, ids, wts, self._local_mlp,
@@ -190,7 +194,7 @@ class CapturedDecodeStep:
 
     NAMES = ("x", "residual", "positions", "slots", "block_tables", "context_lens")
 
-    def __init__(self, layer: MoEDecodeLayer, example: dict, k_cache, v_cache, warmup=3):
+    def __init__(self, layer: MoEDecodeLayer, example: dict, k_cache, v_cache, warmup=3, host_io=False):
         self.layer, self.k_cache, self.v_cache = layer, k_cache, v_cache
         dev = layer.device
         self.inputs = {n: example[n].to(dev).clone() for n in self.NAMES}
@@ -204,11 +208,64 @@ class CapturedDecodeStep:
         with torch.cuda.graph(self.graph, stream=self.stream):
             self.y, self.res = self._forward()
         torch.cuda.current_stream(dev).wait_stream(self.stream)
+        self.graph_host = None
+        if host_io:
+            self._capture_host_io(example)
 
-    def _forward(self):
+    def _forward(self, on_residual=None):
         i = self.inputs
         return self.layer.forward(i["x"], i["residual"], i["positions"], i["slots"], i["block_tables"],
-                                  i["context_lens"], self.k_cache, self.v_cache)
+                                  i["context_lens"], self.k_cache, self.v_cache, on_residual=on_residual)
+
+    def _capture_host_io(self, example):
+        """A second graph for callers whose inputs and results live in host memory: the step's
+        copies are part of the recording.  The two activation tensors go up on the main stream
+        while the small integer tensors go up on a side stream; `residual_out` starts down on
+        the side stream as soon as the launch producing it is enqueued (it is final before the
+        expert MLP, which is a quarter of the step), `y` follows at the end."""
+        dev = self.layer.device
+        self.host_in = {n: example[n].clone().pin_memory() for n in self.NAMES}
+        self.host_y = torch.empty(self.y.shape, dtype=self.y.dtype).pin_memory()
+        self.host_res = torch.empty(self.res.shape, dtype=self.res.dtype).pin_memory()
+        self.side = torch.cuda.Stream(dev)
+        big = ("x", "residual")
+
+        def record():
+            self.side.wait_stream(self.stream)
+            with torch.cuda.stream(self.side):
+                for n in self.NAMES:
+                    if n not in big:
+                        self.inputs[n].copy_(self.host_in[n], non_blocking=True)
+            for n in big:
+                self.inputs[n].copy_(self.host_in[n], non_blocking=True)
+            self.stream.wait_stream(self.side)
+
+            def ship_residual(res):
+                self.side.wait_stream(self.stream)
+                with torch.cuda.stream(self.side):
+                    self.host_res.copy_(res, non_blocking=True)
+
+            y, _ = self._forward(on_residual=ship_residual)
+            self.host_y.copy_(y, non_blocking=True)
+            self.stream.wait_stream(self.side)
+
+        self.stream.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(self.stream):
+            record()  # once outside capture, so that errors surface eagerly
+        self.stream.synchronize()
+        self.side.synchronize()
+        self.graph_host = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph_host, stream=self.stream):
+            record()
+        torch.cuda.current_stream(dev).wait_stream(self.stream)
+
+    def run_host(self):
+        """Replay the host-to-host step: reads `host_in` (pinned; fill it before the call), leaves
+        the results in `host_y` / `host_res` (valid once the current stream has been synchronised)."""
+        if self.graph_host is None:
+            raise RuntimeError("CapturedDecodeStep was built without host_io=True")
+        self.graph_host.replay()
+        return self.host_y, self.host_res
 
     def load(self, batch: dict, non_blocking=True):
         """Copy a step's inputs (host or device tensors) into the graph's input buffers."""

@@ -3,8 +3,7 @@
     python bench.py --gpus N --steps K --warmup W          this implementation (GPU)
     python bench.py --impl reference ...                    the CPU golden path, for the ratio
 
-Prints ONE JSON line on rank 0.  See DESIGN.md for what each field means; in short
-`value` is device-timed with inputs resident in HBM, `e2e` goes through the public
+Prints ONE JSON line on rank 0: `value` is device-timed with inputs resident in HBM, `e2e` goes through the public
 `ascend910a_extras.ops` API from pinned host buffers with the copies inside the timed
 region, `roofline` is the dominant kernel against the measured peak, `per_op` lists every
 operator of the path, and `cpu_baseline` times the CPU oracle on a bounded sample.
@@ -363,25 +362,26 @@ def run_layer(ops, dev, rank, world, group, steps, warmup, peaks):
     layer_us = max_over_ranks(t0.elapsed_time(t1)) * 1e3 / steps
 
     # ---- end to end: host buffers in, result out, copies inside the timed region ----
-    out_host = torch.empty(batch["x"].shape, dtype=torch.float16).pin_memory()
-    res_host = torch.empty(batch["x"].shape, dtype=torch.float16).pin_memory()
-    d2h = 2 * out_host.numel() * 2
-
-    def e2e_step():
-        captured.load(host)
-        y, res = captured.run()
-        out_host.copy_(y, non_blocking=True)
-        res_host.copy_(res, non_blocking=True)
+    # The library's host-to-host step: inputs sit in pinned host memory, every step copies
+    # them up, runs the layer and copies both results down (residual_out as soon as it is final).
+    hosted = mdl.CapturedDecodeStep(layer, batch, k_cache, v_cache, warmup=warmup, host_io=True)
+    for n in names:
+        hosted.host_in[n].copy_(host[n])
+    d2h = hosted.host_y.numel() * 2 + hosted.host_res.numel() * 2
 
     for _ in range(warmup):
-        e2e_step()
+        hosted.run_host()
     sync_all()
     t0.record()
     for _ in range(steps):
-        e2e_step()
+        hosted.run_host()
     t1.record()
     sync_all()
     e2e_us = max_over_ranks(t0.elapsed_time(t1)) * 1e3 / steps
+    y_dev, res_dev = captured.run()
+    torch.cuda.synchronize(dev)
+    if not (torch.equal(hosted.host_y, y_dev.cpu()) and torch.equal(hosted.host_res, res_dev.cpu())):
+        raise RuntimeError("host-to-host step and device-resident step disagree")
 
     local_ctx = int(batch["context_lens"].long().sum())
     attn_bytes = wl.paged_attention_bytes(batch["context_lens"], cfg.kv_heads, cfg.head_dim, cfg.heads,

@@ -125,3 +125,28 @@ def test_captured_step_equals_eager_step(ops):
     y2_eager, _ = layer.forward(b2["x"].to(DEV), *args[1:], kd, vd)
     torch.cuda.synchronize()
     assert torch.equal(y2, y2_eager) and not torch.equal(y2, y_eager)
+
+
+def test_host_to_host_step_equals_eager_step(ops):
+    """The recording that includes the copies (inputs up from pinned host memory, residual_out
+    down early on a side stream, y down at the end) must return what the eager step returns,
+    also for new contents of the host buffers."""
+    cfg, w, b, kc, vc = small_case(batch=9, seed=22)
+    layer = mdl.MoEDecodeLayer(cfg, w, DEV, ops)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    args = [b[n].to(DEV) for n in mdl.CapturedDecodeStep.NAMES]
+    y_eager, r_eager = layer.forward(*args, kd, vd)
+    step = mdl.CapturedDecodeStep(layer, b, kd, vd, host_io=True)
+    y, r = step.run_host()
+    torch.cuda.synchronize()
+    assert torch.equal(y, y_eager.cpu()) and torch.equal(r, r_eager.cpu())
+    step.host_in["x"].copy_((b["x"].float() * 0.25).half())
+    step.host_in["residual"].copy_((b["residual"].float() - 1.0).half())
+    y2, r2 = step.run_host()
+    torch.cuda.synchronize()
+    y2_eager, r2_eager = layer.forward(step.host_in["x"].to(DEV), step.host_in["residual"].to(DEV), *args[2:], kd, vd)
+    torch.cuda.synchronize()
+    assert torch.equal(y2, y2_eager.cpu()) and torch.equal(r2, r2_eager.cpu())
+    assert not torch.equal(y2, y_eager.cpu())
+    with pytest.raises(RuntimeError):
+        mdl.CapturedDecodeStep(layer, b, kd, vd).run_host()

@@ -43,6 +43,7 @@ SIGNATURES = {
     "b200ops_grouped_matmul_workspace_size": (c_size_t, [c_int64] * 4),
     "b200ops_grouped_matmul": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p, c_size_t,
                                                                         c_void_p]),
+    "b200ops_grouped_matmul_swiglu": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p]),
     "b200ops_fused_qkv_rope_cache": (c_int, [c_void_p] * 8 + [c_int64] * 5 + [ctypes.POINTER(c_int64), c_int,
                                                                               c_void_p]),
     "b200ops_moe_route_topk": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p]),
@@ -167,6 +168,13 @@ def grouped_matmul(x, w_storage, group_list, y, workspace=None, stream=None):
     ws_size = 0 if workspace is None else workspace.numel() * workspace.element_size()
     check(load().b200ops_grouped_matmul(_ptr(x), _ptr(w_storage), _ptr(group_list), _ptr(y),
                                         x.shape[0], k, e, n, _ptr(workspace), ws_size, _stream(stream)))
+
+
+def grouped_matmul_swiglu(x, w_storage, group_list, y, stream=None):
+    """`w_storage` [E, 2*d, K]: gate rows then up rows; y [M, d] = swiglu(x @ w)."""
+    e, n, k = w_storage.shape
+    check(load().b200ops_grouped_matmul_swiglu(_ptr(x), _ptr(w_storage), _ptr(group_list), _ptr(y),
+                                               x.shape[0], k, e, n, _stream(stream)))
 
 
 def pipeline_status() -> int:

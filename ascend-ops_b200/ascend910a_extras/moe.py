@@ -17,3 +17,4 @@ fused_qkv_rope_cache = _C.moe.fused_qkv_rope_cache
 push_rows = _C.moe.push_rows
 peer_barrier = _C.moe.peer_barrier
 grouped_matmul_scatter = _C.moe.grouped_matmul_scatter
+grouped_matmul_swiglu = _C.moe.grouped_matmul_swiglu

@@ -121,6 +121,13 @@ __device__ __forceinline__ uint32_t f2_to_h2(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
+// SwiGLU element: (g * sigmoid(g)) * u in fp32, the operand order of the reference's golden
+// (benchmark/test_swiglu.py:6-12) and kernel (csrc/opdev/op_kernel/swi_glu_ex.cpp:52-57).
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
+  return (g * sig) * u;
+}
+
 #endif  // __CUDACC__
 
 }  // namespace b200ops

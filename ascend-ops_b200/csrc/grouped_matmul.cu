@@ -154,10 +154,16 @@ struct Control {
 // CTA can only pull about 100 GB/s through its ring, so four times as many CTAs stream the
 // weights four times as fast.  With more than one m-tile the narrow shape loses (two thirds of
 // every stage is the re-read activation tile), so it is not used there.
-template <int BN_, int STAGES_>
+template <int BN_, int STAGES_, bool GLU_ = false>
 struct Cfg {
   static constexpr int BN = BN_;
   static constexpr int kStages = STAGES_;
+  // GLU_: the gate/up projection with SwiGLU in the epilogue.  The 256 accumulator columns of a
+  // tile are 128 gate columns and the 128 up columns of the SAME outputs (two 128-row boxes of
+  // w, at n0 and at d + n0); the epilogue rounds both to fp16, as the unfused GEMM would have
+  // stored them, applies (g * sigmoid(g)) * u and writes 128 columns.
+  static constexpr bool kGlu = GLU_;
+  static constexpr int kOutBN = GLU_ ? BN_ / 2 : BN_;
   static constexpr int kBBytes = BN_ * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN_ < 32 ? 32 : 2 * BN_;  // a power of two >= 32
@@ -165,6 +171,7 @@ struct Cfg {
 };
 using WideCfg = Cfg<kWideBN, 4>;
 using NarrowCfg = Cfg<kNarrowBN, 8>;
+using GluCfg = Cfg<kWideBN, 4, true>;
 
 // Sticky per-device status of the pipeline kernels (0 = no failure).
 __device__ int g_pipeline_status = 0;
@@ -225,6 +232,36 @@ __device__ __forceinline__ TileCoord locate_tile(const Control* c, int tile, int
   return t;
 }
 
+// Epilogue of the fused gate/up projection: this thread's accumulator row holds kOut gate columns
+// followed by the kOut up columns of the same outputs.  Both are rounded to fp16 first -- the
+// values the unfused GEMM would have stored and SwiGLU would have read -- so the result is
+// bit-identical to grouped_matmul followed by swiglu.
+template <int kOut>
+__device__ __forceinline__ void glu_epilogue(uint32_t taddr, __half* yrow, bool row_ok, int n0, int n_out) {
+#pragma unroll 1
+  for (int c = 0; c < kOut / 32; ++c) {
+    if (n0 + c * 32 >= n_out) break;  // n_out is a multiple of 32: chunks are all-or-nothing
+    uint32_t g[32], u[32];
+    ptx::tmem_ld_32x32b_x32(taddr + c * 32, g);
+    ptx::tmem_ld_32x32b_x32(taddr + kOut + c * 32, u);
+    ptx::tmem_ld_wait();
+    if (!row_ok) continue;
+    uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+#pragma unroll
+    for (int v = 0; v < 4; ++v) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int i = v * 8 + j * 2;
+        const float2 gf = h2_to_f2(f2_to_h2(__uint_as_float(g[i]), __uint_as_float(g[i + 1])));
+        const float2 uf = h2_to_f2(f2_to_h2(__uint_as_float(u[i]), __uint_as_float(u[i + 1])));
+        o[j] = f2_to_h2(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
+      }
+      dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 #include "grouped_matmul_pair.cuh"
 #include "grouped_matmul_ksplit.cuh"
 
@@ -247,9 +284,12 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
   uint8_t* b_tiles = smem + kStages * kABytes;
   Control* ctl = reinterpret_cast<Control*>(smem + kStages * kStageBytes);
 
+  constexpr bool kGlu = C::kGlu;
+  constexpr int kOutBN = C::kOutBN;  // output columns per tile
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int n_tiles = (N + BN - 1) / BN;
+  const int n_out = kGlu ? N / 2 : N;  // columns of y (N counts the rows of w)
+  const int n_tiles = (n_out + kOutBN - 1) / kOutBN;
   const int k_blocks = K / BK;
 
   if (threadIdx.x == 0) {
@@ -313,7 +353,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       bool ok = true;
       for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
         const WorkItem wi = locate_item(item, splits, k_blocks);
-        const TileCoord tc = locate_tile(ctl, wi.tile, g, BN);
+        const TileCoord tc = locate_tile(ctl, wi.tile, g, kOutBN);
         for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
           if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
             *abort_flag = 1;
@@ -323,6 +363,11 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
           }
           ptx::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
           ptx::tma_load_2d(a_tiles + stage * kABytes, &map_x, &ctl->full[stage], kb * BK, tc.row0);
+          if (kGlu) {  // gate rows, then the up rows of the same outputs (boxes of BN / 2 rows)
+            ptx::tma_load_3d(b_tiles + stage * kBBytes, &map_w, &ctl->full[stage], kb * BK, tc.n0, tc.group);
+            ptx::tma_load_3d(b_tiles + stage * kBBytes + kBBytes / 2, &map_w, &ctl->full[stage], kb * BK,
+                             n_out + tc.n0, tc.group);
+          } else
           ptx::tma_load_3d(b_tiles + stage * kBBytes, &map_w, &ctl->full[stage], kb * BK, tc.n0,
                            tc.group);
           if (++stage == kStages) {
@@ -383,7 +428,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
     int g = 0, iter = 0;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++iter) {
       const WorkItem wi = locate_item(item, splits, k_blocks);
-      const TileCoord tc = locate_tile(ctl, wi.tile, g, BN);
+      const TileCoord tc = locate_tile(ctl, wi.tile, g, kOutBN);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
       if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) {
@@ -395,9 +440,12 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       const int tile_row = quarter * 32 + lane;
       const int row = tc.row0 + tile_row;
       bool row_ok = row < tc.row_end;
-      __half* yrow = output_row(scatter, y, row, N, row_ok) + tc.n0;
+      __half* yrow = output_row(scatter, y, row, n_out, row_ok) + tc.n0;
       float* prow = splits > 1 ? partials + static_cast<size_t>(item) * (BM * BN) + tile_row * BN : nullptr;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if constexpr (kGlu) {
+        glu_epilogue<kOutBN>(taddr, yrow, row_ok, tc.n0, n_out);
+      } else {
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         if (tc.n0 + c * 32 >= N) break;  // N is a multiple of 64, so chunks are all-or-nothing
@@ -421,6 +469,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
 #pragma unroll
           for (int v = 0; v < 8; ++v) dst[v] = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
         }
+      }
       }
       ptx::tcgen05_fence_before();
       __syncwarp();
@@ -523,7 +572,7 @@ namespace b200ops {
 namespace gmm {
 int launch(const void* x, const void* w, const int64_t* group_list, void* y, int64_t num_tokens, int64_t k,
            int64_t num_experts, int64_t n, void* workspace, size_t workspace_size, const RowScatter& scatter,
-           void* stream);
+           bool glu, void* stream);
 }
 }  // namespace b200ops
 
@@ -537,7 +586,20 @@ extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_
   for (int r = 0; r < b200ops::kMaxPeers; ++r) none.peers.base[r] = nullptr;
   B200OPS_REQUIRE(num_tokens <= 0 || y != nullptr, "grouped_matmul: null pointer");
   return b200ops::gmm::launch(x, w, group_list, y, num_tokens, k, num_experts, n, workspace, workspace_size,
-                              none, stream);
+                              none, false, stream);
+}
+
+extern "C" int b200ops_grouped_matmul_swiglu(const void* x, const void* w, const int64_t* group_list, void* y,
+                                             int64_t num_tokens, int64_t k, int64_t num_experts, int64_t two_d,
+                                             void* stream) {
+  b200ops::gmm::RowScatter none;
+  none.index = nullptr;
+  none.cap = 1;
+  none.my_rank = 0;
+  for (int r = 0; r < b200ops::kMaxPeers; ++r) none.peers.base[r] = nullptr;
+  B200OPS_REQUIRE(num_tokens <= 0 || y != nullptr, "grouped_matmul_swiglu: null pointer");
+  return b200ops::gmm::launch(x, w, group_list, y, num_tokens, k, num_experts, two_d, nullptr, 0, none, true,
+                              stream);
 }
 
 extern "C" int b200ops_grouped_matmul_scatter(const void* x, const void* w, const int64_t* group_list,
@@ -561,7 +623,7 @@ extern "C" int b200ops_grouped_matmul_scatter(const void* x, const void* w, cons
                     "grouped_matmul_scatter: peer %d has no buffer", r);
   }
   return gmm::launch(x, w, group_list, sc.peers.base[my_rank], num_tokens, k, num_experts, n, workspace,
-                     workspace_size, sc, stream);
+                     workspace_size, sc, false, stream);
 }
 
 namespace b200ops {
@@ -582,7 +644,7 @@ static int resident_pairs(int dev, int sms) {
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   int n = 0;
-  if (cudaOccupancyMaxActiveClusters(&n, grouped_matmul_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+  if (cudaOccupancyMaxActiveClusters(&n, grouped_matmul_pair_kernel<false>, &cfg) != cudaSuccess || n <= 0) {
     cudaGetLastError();
     n = sms / 2;
   }
@@ -675,7 +737,7 @@ static int launch_ksplit(const CUtensorMap& map_x, const void* w, const int64_t*
 }
 
 static int launch_pairs(const CUtensorMap& map_x, const void* w, const int64_t* group_list, void* y,
-                        int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n,
+                        int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n, bool glu,
                         const RowScatter& scatter, cudaStream_t st) {
   CUtensorMap map_w;
   {
@@ -686,15 +748,16 @@ static int launch_pairs(const CUtensorMap& map_x, const void* w, const int64_t* 
     const int rc = encode_f16_map(&map_w, w, 3, dims, strides, box, "grouped_matmul(w)");
     if (rc != B200OPS_OK) return rc;
   }
-  static bool attr_set[64] = {false};
+  auto kern = glu ? grouped_matmul_pair_kernel<true> : grouped_matmul_pair_kernel<false>;
+  static bool attr_set[2][64] = {{false}};
   int dev = 0;
   B200OPS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    B200OPS_CUDA(cudaFuncSetAttribute(grouped_matmul_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+  if (dev >= 0 && dev < 64 && !attr_set[glu][dev]) {
+    B200OPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(kPairSmemBytes)));
-    attr_set[dev] = true;
+    attr_set[glu][dev] = true;
   }
-  const int64_t n_tiles = (n + kPairBN - 1) / kPairBN;
+  const int64_t n_tiles = (n + kPairBN - 1) / kPairBN;  // the same count with and without SwiGLU
   const int64_t max_items = (((num_tokens + BM - 1) / BM + 1) / 2 + num_experts) * n_tiles;
   const int64_t resident = resident_pairs(dev, launch_sms());
   const int pairs = static_cast<int>(max_items < resident ? max_items : resident);
@@ -710,7 +773,7 @@ static int launch_pairs(const CUtensorMap& map_x, const void* w, const int64_t* 
   cfg.stream = st;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  B200OPS_CUDA(cudaLaunchKernelEx(&cfg, grouped_matmul_pair_kernel, map_x, map_w, group_list,
+  B200OPS_CUDA(cudaLaunchKernelEx(&cfg, kern, map_x, map_w, group_list,
                                   static_cast<__half*>(y), static_cast<int>(num_tokens), static_cast<int>(n),
                                   static_cast<int>(k), static_cast<int>(num_experts), scatter));
   B200OPS_LAUNCH_CHECK("grouped_matmul");
@@ -721,7 +784,7 @@ static int launch_pairs(const CUtensorMap& map_x, const void* w, const int64_t* 
 
 int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list, void* y, int64_t num_tokens,
                          int64_t k, int64_t num_experts, int64_t n, void* workspace, size_t workspace_size,
-                         const RowScatter& scatter, void* stream) {
+                         const RowScatter& scatter, bool glu, void* stream) {
   using namespace b200ops;
   B200OPS_REQUIRE(num_tokens >= 0 && k > 0 && n > 0 && num_experts > 0,
                   "grouped_matmul: bad shape tokens=%lld k=%lld experts=%lld n=%lld",
@@ -733,6 +796,8 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
                   gmm::kMaxExperts, (long long)num_experts);
   B200OPS_REQUIRE(num_tokens < (1LL << 30) && k < (1LL << 30) && n < (1LL << 30),
                   "grouped_matmul: dimension too large");
+  B200OPS_REQUIRE(!glu || n % 128 == 0,
+                  "grouped_matmul_swiglu: w must have 2*d rows with d a multiple of 64, got %lld", (long long)n);
   if (num_tokens == 0) return B200OPS_OK;
   B200OPS_REQUIRE(x && w && group_list && y, "grouped_matmul: null pointer");
   B200OPS_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y),
@@ -748,39 +813,44 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   }
   const int sms = gmm::launch_sms();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  int s = gmm::cluster_split_factor(num_tokens, k, num_experts, n, sms);
+  // The fused gate/up form exists in the two throughput kernels only (its shapes have thousands
+  // of output columns and a short K: neither split-K nor narrow tiles apply).
+  int s = glu ? 0 : gmm::cluster_split_factor(num_tokens, k, num_experts, n, sms);
   if (s) s = gmm::fit_split_to_device(s, num_tokens, n);
   if (s)
     return gmm::launch_ksplit(map_x, w, group_list, y, num_tokens, k, num_experts, n, s, scatter, st);
   if (gmm::use_cta_pairs(num_tokens, num_experts, n, sms))
-    return gmm::launch_pairs(map_x, w, group_list, y, num_tokens, k, num_experts, n, scatter, st);
-  const bool narrow = gmm::use_narrow_tiles(num_tokens, k, n, sms);
+    return gmm::launch_pairs(map_x, w, group_list, y, num_tokens, k, num_experts, n, glu, scatter, st);
+  const bool narrow = !glu && gmm::use_narrow_tiles(num_tokens, k, n, sms);
   const int bn = narrow ? gmm::kNarrowBN : gmm::kWideBN;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
                               static_cast<uint64_t>(num_experts)};
     const uint64_t strides[2] = {static_cast<uint64_t>(k) * 2, static_cast<uint64_t>(k) * n * 2};
-    const uint32_t box[3] = {gmm::BK, static_cast<uint32_t>(bn), 1};
+    const uint32_t box[3] = {gmm::BK, static_cast<uint32_t>(glu ? bn / 2 : bn), 1};  // glu: gate and up boxes
     const int rc = encode_f16_map(&map_w, w, 3, dims, strides, box, "grouped_matmul(w)");
     if (rc != B200OPS_OK) return rc;
   }
 
-  auto kern = narrow ? gmm::grouped_matmul_kernel<gmm::NarrowCfg> : gmm::grouped_matmul_kernel<gmm::WideCfg>;
+  auto kern = glu      ? gmm::grouped_matmul_kernel<gmm::GluCfg>
+              : narrow ? gmm::grouped_matmul_kernel<gmm::NarrowCfg>
+                       : gmm::grouped_matmul_kernel<gmm::WideCfg>;
   const size_t smem = narrow ? gmm::NarrowCfg::kSmemBytes : gmm::WideCfg::kSmemBytes;
-  static bool attr_set[2][64] = {{false}};
+  const int variant = glu ? 2 : (narrow ? 1 : 0);
+  static bool attr_set[3][64] = {{false}};
   int dev = 0;
   B200OPS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[narrow][dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[variant][dev]) {
     B200OPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
-    attr_set[narrow][dev] = true;
+    attr_set[variant][dev] = true;
   }
-  const int64_t n_tiles = (n + bn - 1) / bn;
+  const int64_t n_tiles = (n + bn - 1) / bn;  // glu: n / 2 columns in tiles of bn / 2, the same count
   const int64_t max_tiles = ((num_tokens + gmm::BM - 1) / gmm::BM + num_experts) * n_tiles;
   int* counters = nullptr;
   float* partials = nullptr;
   int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
-  if (workspace != nullptr && gmm::split_k_possible(num_tokens, k, n, sms)) {
+  if (!glu && workspace != nullptr && gmm::split_k_possible(num_tokens, k, n, sms)) {
     if (workspace_size < gmm::workspace_bytes())
       return fail(B200OPS_EWORKSPACE, "grouped_matmul: workspace of %zu bytes needed, got %zu",
                   gmm::workspace_bytes(), workspace_size);

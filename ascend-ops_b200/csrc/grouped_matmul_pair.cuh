@@ -26,7 +26,7 @@ constexpr int kPairTmemCols = 2 * kPairBN;
 constexpr size_t kPairSmemBytes = 1024 + kPairStages * kPairStageBytes + sizeof(Control);
 
 // Items of one group are numbered m-pair fastest, like the tiles of the single-CTA kernel.
-__device__ __forceinline__ TileCoord locate_pair_item(const Control* c, int item, int& g, int rank) {
+__device__ __forceinline__ TileCoord locate_pair_item(const Control* c, int item, int& g, int rank, int out_bn) {
   while (item >= c->tile_prefix[g + 1]) ++g;
   const int local = item - c->tile_prefix[g];
   const int rows = c->row_end[g] - c->row_start[g];
@@ -37,10 +37,14 @@ __device__ __forceinline__ TileCoord locate_pair_item(const Control* c, int item
   t.group = g;
   t.row0 = c->row_start[g] + (2 * m_pair + rank) * BM;
   t.row_end = c->row_end[g];
-  t.n0 = n_tile * kPairBN;
+  t.n0 = n_tile * out_bn;
   return t;
 }
 
+// kGlu: the fused gate/up projection (see Cfg::kGlu): the even CTA's half of the w tile is the
+// 128 gate rows, the odd CTA's half the 128 up rows of the same outputs, and each CTA's
+// epilogue applies SwiGLU to its own 128 rows.
+template <bool kGlu>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
                            const __grid_constant__ CUtensorMap map_w,
@@ -58,7 +62,9 @@ grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
   const int rank = static_cast<int>(ptx::cluster_ctarank());
   const int cluster = static_cast<int>(ptx::cluster_id_x());
   const int n_clusters = static_cast<int>(ptx::num_clusters_x());
-  const int n_tiles = (N + kPairBN - 1) / kPairBN;
+  constexpr int kOutBN = kGlu ? kPairBN / 2 : kPairBN;
+  const int n_out = kGlu ? N / 2 : N;
+  const int n_tiles = (n_out + kOutBN - 1) / kOutBN;
   const int k_blocks = K / BK;
 
   if (threadIdx.x == 0) {
@@ -113,7 +119,7 @@ grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       uint32_t phase = 0;
       bool ok = true;
       for (int item = cluster; ok && item < total_items; item += n_clusters) {
-        const TileCoord tc = locate_pair_item(ctl, item, g, rank);
+        const TileCoord tc = locate_pair_item(ctl, item, g, rank, kOutBN);
         for (int kb = 0; kb < k_blocks; ++kb) {
           if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
             *abort_flag = 1;
@@ -125,7 +131,7 @@ grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
           if (rank == 0) ptx::mbar_arrive_expect_tx(&ctl->full[stage], 2 * kPairStageBytes);
           ptx::tma_load_2d_pair(a_tiles + stage * kABytes, &map_x, lead_full, kb * BK, tc.row0);
           ptx::tma_load_3d_pair(b_tiles + stage * kPairBHalfBytes, &map_w, lead_full, kb * BK,
-                                tc.n0 + rank * (kPairBN / 2), tc.group);
+                                kGlu ? rank * n_out + tc.n0 : tc.n0 + rank * (kPairBN / 2), tc.group);
           if (++stage == kPairStages) {
             stage = 0;
             phase ^= 1u;
@@ -182,7 +188,7 @@ grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
     const int quarter = warp & 3;
     int g = 0, iter = 0;
     for (int item = cluster; item < total_items; item += n_clusters, ++iter) {
-      const TileCoord tc = locate_pair_item(ctl, item, g, rank);
+      const TileCoord tc = locate_pair_item(ctl, item, g, rank, kOutBN);
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
       if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) {
@@ -193,10 +199,11 @@ grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
       ptx::tcgen05_fence_after();
       const int row = tc.row0 + quarter * 32 + lane;
       bool row_ok = row < tc.row_end;
-      __half* yrow = output_row(scatter, y, row, N, row_ok) + tc.n0;
+      __half* yrow = output_row(scatter, y, row, n_out, row_ok) + tc.n0;
       const uint32_t taddr = tmem_base + acc * kPairBN + (static_cast<uint32_t>(quarter * 32) << 16);
+      if constexpr (kGlu) glu_epilogue<kOutBN>(taddr, yrow, row_ok, tc.n0, n_out);
 #pragma unroll 1
-      for (int c = 0; c < kPairBN / 32; ++c) {
+      for (int c = 0; !kGlu && c < kPairBN / 32; ++c) {
         if (tc.n0 + c * 32 >= N) break;
         uint32_t r[32];
         ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);

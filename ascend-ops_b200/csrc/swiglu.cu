@@ -11,11 +11,6 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;  // 128-bit vector pairs in flight per thread
 
-__device__ __forceinline__ float silu_mul(float g, float u) {
-  const float sig = __fdividef(1.0f, 1.0f + __expf(-g));
-  return (g * sig) * u;
-}
-
 template <typename index_t>
 __global__ void __launch_bounds__(kThreads)
 swiglu_kernel(const __half* __restrict__ x, __half* __restrict__ y, index_t total_vecs,

@@ -484,6 +484,33 @@ void grouped_matmul_scatter(at::Tensor x, at::Tensor w, at::Tensor group_list, a
                "grouped_matmul_scatter");
 }
 
+// Gate/up projection with SwiGLU in the GEMM's epilogue: w [E, K, 2*d] (the first d output
+// columns are the gate, the rest the up projection) -> [M, d], bit-identical to
+// ops.swiglu(ops.grouped_matmul(x, w, group_list)).
+at::Tensor grouped_matmul_swiglu(at::Tensor x, at::Tensor w, at::Tensor group_list) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 3 && group_list.dim() == 1 && x.size(1) == w.size(1),
+              "grouped_matmul_swiglu: x [M, K], w [E, K, 2*d], group_list [E]");
+  TORCH_CHECK(x.is_contiguous() && group_list.is_contiguous() && w.stride(1) == 1 && w.stride(2) == x.size(1),
+              "grouped_matmul_swiglu: x must be contiguous and w K-major");
+  TORCH_CHECK(w.size(0) <= 1 || w.stride(0) == w.size(1) * w.size(2),
+              "grouped_matmul_swiglu: experts of w must be densely packed");
+  TORCH_CHECK(w.size(1) % 64 == 0 && w.size(2) % 128 == 0 && group_list.size(0) == w.size(0),
+              "grouped_matmul_swiglu: K must be a multiple of 64 and 2*d of 128, one group end per expert");
+  check_f16_cuda(x, "grouped_matmul_swiglu", "x");
+  check_f16_cuda(w, "grouped_matmul_swiglu", "w");
+  TORCH_CHECK(group_list.is_cuda() && group_list.scalar_type() == at::kLong,
+              "grouped_matmul_swiglu: group_list must be a CUDA int64 tensor");
+  check_same_device(x, w, "grouped_matmul_swiglu");
+  check_same_device(x, group_list, "grouped_matmul_swiglu");
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty({x.size(0), w.size(2) / 2}, x.options());
+  check_status(b200ops_grouped_matmul_swiglu(x.data_ptr(), w.data_ptr(), group_list.data_ptr<int64_t>(),
+                                             y.data_ptr(), x.size(0), x.size(1), w.size(0), w.size(2),
+                                             current_stream()),
+               "grouped_matmul_swiglu");
+  return y;
+}
+
 void peer_barrier(std::vector<int64_t> peer_flags, at::Tensor my_flags, at::Tensor state, int64_t my_rank) {
   TORCH_CHECK(my_flags.is_cuda() && state.is_cuda() && state.numel() >= 2 &&
                   my_flags.numel() >= static_cast<int64_t>(peer_flags.size()) &&
@@ -503,6 +530,7 @@ void init_ffi_moe(py::module_&& m) {
         py::arg("counts") = py::none(), py::arg("peer_counts") = std::vector<int64_t>());
   m.def("peer_barrier", &peer_barrier);
   m.def("grouped_matmul_scatter", &grouped_matmul_scatter);
+  m.def("grouped_matmul_swiglu", &grouped_matmul_swiglu);
   m.def("fused_qkv_rope_cache", &fused_qkv_rope_cache);
   m.def("route_topk", &moe_route_topk);
   m.def("permute", &moe_permute);

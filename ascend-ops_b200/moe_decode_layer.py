@@ -93,6 +93,7 @@ class MoEDecodeLayer:
         self.exchange = exchange  # a moe_parallel.PeerExchange: NVLink peer-memory dispatch/combine
         self.fuse_return = True  # down projection stores into the peers' buffers in its epilogue
         self.fuse_rope_cache = True  # False: split + ops.rope + ops.reshape_and_cache separately
+        self.fuse_swiglu = True  # False: ops.grouped_matmul then ops.swiglu
         d = lambda t: t.to(device)
         self.ln1, self.ln2 = d(weights["ln1"]), d(weights["ln2"])
         # NT-GEMM weights as single-group stacks [1, N, K]; the op takes the [1, K, N] view.
@@ -116,18 +117,20 @@ class MoEDecodeLayer:
             self._one_group[t] = gl
         return self.ops.grouped_matmul(x, w, gl)
 
+    def _gate_up(self, rows, group_list):
+        """silu(gate) * up of the routed rows: one kernel, or the reference's two operators."""
+        if self.fuse_swiglu:
+            return self.moe.grouped_matmul_swiglu(rows, self.w_gate_up, group_list)
+        return self.ops.swiglu(self.ops.grouped_matmul(rows, self.w_gate_up, group_list))
+
     def _local_mlp(self, rows, group_list):
         if rows.shape[0] == 0:
             return rows.new_zeros(0, self.cfg.hidden)
-        gu = self.ops.grouped_matmul(rows, self.w_gate_up, group_list)
-        act = self.ops.swiglu(gu)
-        return self.ops.grouped_matmul(act, self.w_down, group_list)
+        return self.ops.grouped_matmul(self._gate_up(rows, group_list), self.w_down, group_list)
 
     def _local_mlp_scatter(self, rows, group_list, scatter):
         """Expert MLP whose down projection stores its rows into the peers' return buffers."""
-        gu = self.ops.grouped_matmul(rows, self.w_gate_up, group_list)
-        act = self.ops.swiglu(gu)
-        self.moe.grouped_matmul_scatter(act, self.w_down, group_list, *scatter)
+        self.moe.grouped_matmul_scatter(self._gate_up(rows, group_list), self.w_down, group_list, *scatter)
 
     def forward(self, x, residual, positions, slots, block_tables, context_lens, k_cache, v_cache,
                 return_routing=False, attention_events=None, on_residual=None):
@@ -173,12 +176,12 @@ class MoEDecodeLayer:
 
     # number of this library's kernels one single-GPU forward launches (for the benchmark's
     # accounting): 2 add_rms_norm, 2 dense GEMMs, fused rope+cache, attention (one kernel: the
-    # chunk merge is fused), route, permute, copy_rows, 2 grouped GEMMs, swiglu, finalize.  Under expert
-    # parallelism with the peer-memory exchange the MoE part is route, permute, push_rows,
-    # barrier, ep_plan, copy_rows, gate_up GEMM, swiglu, down GEMM with scatter epilogue,
-    # barrier, finalize.
-    KERNEL_LAUNCHES = 13
-    KERNEL_LAUNCHES_EP = 17
+    # chunk merge is fused), route, permute, copy_rows, gate/up GEMM with SwiGLU epilogue, down GEMM,
+    # finalize.  Under expert parallelism with the peer-memory exchange the MoE part is route,
+    # permute, push_rows, barrier, ep_plan, copy_rows, gate/up GEMM with SwiGLU epilogue, down GEMM
+    # with scatter epilogue, barrier, finalize.
+    KERNEL_LAUNCHES = 12
+    KERNEL_LAUNCHES_EP = 16
 
 
 class CapturedDecodeStep:

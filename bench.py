@@ -430,7 +430,7 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
     cap = min(full_cap, (-(-2 * full_cap // world) + 63) // 64 * 64) if world > 1 else full_cap
 
     def local_mlp(rows, gl):
-        return ops.grouped_matmul(ops.swiglu(ops.grouped_matmul(rows, w_gu, gl)), w_dn, gl)
+        return ops.grouped_matmul(moe.grouped_matmul_swiglu(rows, w_gu, gl), w_dn, gl)
 
     def measure(capacity):
         flags = []
@@ -482,12 +482,12 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
     return {"op": "moe_mlp_expert_parallel", "shape": "4096 tokens top-2 of 8 experts, 4096->2x14336->4096 f16",
             "flops": flops, "us": round(us, 1), "achieved": round(tf, 1), "unit": "TFLOP/s",
             "peak": peaks["bf16_tflops"] * world, "frac": round(tf / (peaks["bf16_tflops"] * world), 4),
-            "bound": "tensor", "launches": 8 if world == 1 else 11, "rows_per_expert": load,
+            "bound": "tensor", "launches": 7 if world == 1 else 10, "rows_per_expert": load,
             "slots_per_rank": spr, "replicas_per_expert": placement.num_replicas.tolist(),
             "balance": round(moe_parallel.placement_balance(load, placement, world), 3),
             "one_expert_per_slot_balance": round(sum(load) / (cfg.experts * max(load)), 3),
             "segment_rows": used_cap, "dropped_rows": dropped,
-            "includes": "slot remap, permutation, swiglu and (for >1 GPU) dispatch/combine all-to-all"}
+            "includes": "slot remap, permutation, SwiGLU (in the gate/up GEMM's epilogue) and (for >1 GPU) dispatch/combine"}
 
 
 # --------------------------------------------------------------------------- CPU baseline
@@ -665,6 +665,8 @@ def main():
     per_op = [mlp] if mlp is not None else []
     if rank == 0:
         for name in want:
+            if name not in cases:
+                raise SystemExit(f"--ops: unknown case {name!r}; choose from {', '.join(cases)}")
             per_op.append(cases[name](ops, dev, max(5, ns.steps // 2), ns.warmup, peaks))
             torch.cuda.empty_cache()
     if world > 1:

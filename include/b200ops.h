@@ -236,6 +236,18 @@ int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row, const flo
                          void* y, int64_t num_tokens, int64_t top_k, int64_t row_elems, void* stream);
 
 /*
+ * The gate/up projection of a gated MLP with SwiGLU in the GEMM's epilogue: replaces
+ * b200ops_grouped_matmul (csrc/ffi/ops.cpp:157-233) followed by b200ops_swiglu
+ * (csrc/ffi/ops.cpp:126-154) on its result, without the [num_tokens, two_d] intermediate.
+ * w [num_experts, two_d, k] f16, k contiguous: rows [0, d) are the gate projection, rows
+ * [d, 2d) the up projection, d = two_d / 2 a multiple of 64.  y [num_tokens, d] f16.  The
+ * accumulators are rounded to f16 before SwiGLU, so the result equals the two-call form bit for bit.
+ */
+int b200ops_grouped_matmul_swiglu(const void* x, const void* w, const int64_t* group_list, void* y,
+                                  int64_t num_tokens, int64_t k, int64_t num_experts, int64_t two_d,
+                                  void* stream);
+
+/*
  * grouped_matmul whose epilogue performs the return leg of the expert-parallel exchange
  * (GEMM + peer store in one kernel; no counterpart in the reference).  Same computation as
  * b200ops_grouped_matmul, but result row r is stored into the buffer of rank

@@ -515,3 +515,41 @@ def test_grouped_matmul_cluster_split_k_fewer_rows_than_the_bound(cabi):
     got = run_grouped_matmul(cabi, x, w_storage, gl, fill=9.0, split_k=False)
     close(got[:100], want[:100])
     assert (got[100:] == 9.0).all()
+
+
+@pytest.mark.parametrize("pair_mode", ["0", "2"])  # single-CTA kernel / CTA-pair kernel
+@pytest.mark.parametrize("counts,k,d", [
+    ([128], 64, 64),                         # one tile, half of it columns
+    ([300, 0, 1, 129, 70], 256, 192),        # M tails, an empty group, d = 128 + 64 (a column tail)
+    ([40, 3, 90, 7], 512, 1024),             # decode-size groups
+    ([700, 900, 300], 1024, 1408),           # several tiles per CTA; d = 11 * 128
+])
+def test_grouped_matmul_swiglu_equals_the_two_operators(cabi, monkeypatch, counts, k, d, pair_mode):
+    """SwiGLU in the GEMM's epilogue: the same bits as grouped_matmul followed by swiglu (the
+    accumulators are rounded to fp16 in between, as the intermediate tensor would be)."""
+    monkeypatch.setenv("B200OPS_GMM_PAIR", pair_mode)
+    g = torch.Generator().manual_seed(sum(counts) + k + d)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half().to(DEV)
+    w_storage = (torch.randn(len(counts), 2 * d, k, generator=g) * 0.05).half().to(DEV)
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64).to(DEV)
+    gu = torch.zeros(m, 2 * d, dtype=torch.float16, device=DEV)
+    cabi.grouped_matmul(x, w_storage, gl, gu, None)
+    two_step = torch.empty(m, d, dtype=torch.float16, device=DEV)
+    cabi.swiglu(gu, two_step)
+    fused = torch.full((m, d), 3.0, dtype=torch.float16, device=DEV)
+    cabi.grouped_matmul_swiglu(x, w_storage, gl, fused)
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    assert torch.equal(fused, two_step)
+    want = oracle.swiglu(oracle.grouped_matmul(x.cpu(), w_storage.cpu().transpose(1, 2), gl.cpu()))
+    close(fused.cpu(), want)
+
+
+def test_grouped_matmul_swiglu_rejects_odd_widths(cabi):
+    x = torch.zeros(4, 64, dtype=torch.float16, device=DEV)
+    w = torch.zeros(1, 192, 64, dtype=torch.float16, device=DEV)  # d = 96: not a multiple of 64
+    gl = torch.tensor([4], dtype=torch.int64, device=DEV)
+    with pytest.raises(cabi.B200OpsError) as e:
+        cabi.grouped_matmul_swiglu(x, w, gl, torch.zeros(4, 96, dtype=torch.float16, device=DEV))
+    assert e.value.code == cabi.EINVAL

@@ -112,21 +112,35 @@ inline bool use_cta_pairs(int64_t num_tokens, int64_t num_experts, int64_t n, in
   return min_tiles >= sms && num_tokens >= 2 * BM * num_experts && num_tokens >= kMinRowsForPairs;
 }
 
-// Cluster split-K (grouped_matmul_ksplit.cuh): one group, at most 256 rows (a dense projection of
-// a decode batch, whose row count the host knows), and so few output tiles that at least two
-// CTAs can share each.  Returns the cluster size, 0 = not this path.
-// B200OPS_GMM_KSPLIT=0 disables it.
+// Cluster split-K (grouped_matmul_ksplit.cuh), single group only.  Two cases:
+//  * at most 256 rows (a dense projection of a decode batch, whose row count the host knows)
+//    and so few output tiles that at least two CTAs can share each;
+//  * a row BOUND of up to 1024 with K >= 8192 (the down projection of a rank that hosts one
+//    expert: the bound is the receive buffer, the rows present are about a tile's worth): the
+//    cluster size is chosen for the tiles of the first m-tile, further m-tiles run as extra waves.
+// Returns the wanted cluster size (0 = not this path) and the tile count that must be resident.
+// B200OPS_GMM_KSPLIT=0 disables the path.
 constexpr int kMaxClusterSplitRows = 256;
+constexpr int kMaxClusterSplitRowBound = 1024;
 constexpr int kMaxClusterSplitHost = 8;
 
-inline int cluster_split_factor(int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n, int sms) {
+inline int cluster_split_factor(int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n, int sms,
+                                int64_t* resident_tiles) {
   const char* env = std::getenv("B200OPS_GMM_KSPLIT");
   if (env && *env && std::atoi(env) == 0) return 0;
-  if (num_experts != 1 || num_tokens > kMaxClusterSplitRows) return 0;
-  const int64_t tiles = ((num_tokens + BM - 1) / BM) * ((n + kWideBN - 1) / kWideBN);
+  if (num_experts != 1) return 0;
+  const int64_t n_tiles = (n + kWideBN - 1) / kWideBN;
+  int64_t tiles;
+  if (num_tokens <= kMaxClusterSplitRows)
+    tiles = ((num_tokens + BM - 1) / BM) * n_tiles;
+  else if (num_tokens <= kMaxClusterSplitRowBound && k >= kMinSplitK)
+    tiles = n_tiles;
+  else
+    return 0;
   int64_t s = sms / tiles;
   if (s > kMaxClusterSplitHost) s = kMaxClusterSplitHost;
   if (s > (k / BK) / kMinKBlocksPerSplit) s = (k / BK) / kMinKBlocksPerSplit;
+  *resident_tiles = tiles;
   return s >= 2 ? static_cast<int>(s) : 0;
 }
 
@@ -687,10 +701,9 @@ static int resident_split_clusters(int dev, int splits) {
 // All clusters must be resident at once: a cluster that has to wait for a free slot starts
 // when the others end and doubles the time.  Clusters are placed within a GPC, so fewer fit
 // than SMs / s: the largest s <= `splits` whose clusters all fit, 0 if none of two or more does.
-static int fit_split_to_device(int splits, int64_t num_tokens, int64_t n) {
+static int fit_split_to_device(int splits, int64_t tiles) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return 0;
-  const int64_t tiles = ((num_tokens + BM - 1) / BM) * ((n + kSplitBN - 1) / kSplitBN);
   while (splits > 1 && resident_split_clusters(dev, splits) < tiles) --splits;
   return splits >= 2 ? splits : 0;
 }
@@ -815,8 +828,9 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The fused gate/up form exists in the two throughput kernels only (its shapes have thousands
   // of output columns and a short K: neither split-K nor narrow tiles apply).
-  int s = glu ? 0 : gmm::cluster_split_factor(num_tokens, k, num_experts, n, sms);
-  if (s) s = gmm::fit_split_to_device(s, num_tokens, n);
+  int64_t resident_tiles = 0;
+  int s = glu ? 0 : gmm::cluster_split_factor(num_tokens, k, num_experts, n, sms, &resident_tiles);
+  if (s) s = gmm::fit_split_to_device(s, resident_tiles);
   if (s)
     return gmm::launch_ksplit(map_x, w, group_list, y, num_tokens, k, num_experts, n, s, scatter, st);
   if (gmm::use_cta_pairs(num_tokens, num_experts, n, sms))

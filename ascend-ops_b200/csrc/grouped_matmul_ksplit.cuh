@@ -10,7 +10,8 @@
 // r, r + s, ... by reading all s copies through distributed shared memory, in rank order, so
 // the result does not depend on timing.  The hardware co-schedules a cluster, so the barrier
 // is a hardware one and there is no workspace, no counter and no spin.
-// Single group only: the tile grid follows from the host's row bound.
+// Single group only: the tile grid follows from the host's row bound; clusters whose rows do
+// not exist leave at once.
 #pragma once
 
 constexpr int kSplitBN = kWideBN;
@@ -113,17 +114,25 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   const int kb0 = static_cast<int>(static_cast<long long>(rank) * k_blocks / splits);
   const int kb1 = static_cast<int>(static_cast<long long>(rank + 1) * k_blocks / splits);
 
-  // One group only (the host checks): tile -> (m-tile, n-tile) needs no table, and the row count
-  // matters only to the stores.  Every cluster of the grid multiplies its tile; rows past the
-  // group's end are computed from whatever x holds there and never stored.
+  // One group only (the host checks): tile -> (m-tile, n-tile) needs no table.  Tiles are
+  // numbered m-tile by m-tile, so the clusters of the first m-tile are scheduled first.  They
+  // always run, even before the row count is known (rows past the group's end are computed from
+  // whatever x holds there and never stored).  Clusters of further m-tiles first read the row
+  // count and leave if their rows do not exist: the host's row bound can be far above the rows
+  // present (an expert-parallel receive buffer), and idle clusters must cost next to nothing.
   const int m_tiles = (M + BM - 1) / BM;
+  const int m_tile = tile / n_tiles;
   TileCoord tc;
   tc.group = 0;
-  tc.n0 = (tile / m_tiles) * kSplitBN;
-  tc.row0 = (tile - (tile / m_tiles) * m_tiles) * BM;
-  tc.row_end = 0;  // read after the first loads are on their way
+  tc.n0 = (tile - m_tile * n_tiles) * kSplitBN;
+  tc.row0 = m_tile * BM;
+  tc.row_end = 0;  // first m-tile: read after the first loads are on their way
   // splits <= k_blocks gives every rank at least one k-block; the host never asks otherwise.
-  const bool active = splits <= k_blocks && tile < m_tiles * n_tiles;
+  bool active = splits <= k_blocks && tile < m_tiles * n_tiles;
+  if (m_tile > 0) {
+    long long rows = group_list[0];
+    active = active && tc.row0 < (rows > M ? M : rows);
+  }
   const int prefill = active ? min(kSplitStages, kb1 - kb0) : 0;
 
   if (threadIdx.x == 0) {
@@ -142,7 +151,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
       ptx::tma_load_3d(b_tiles + i * kSplitBBytes, &map_w, &ctl->full[i], (kb0 + i) * BK, tc.n0, 0);
     }
   }
-  if (warp == 1) {
+  if (active && warp == 1) {
     ptx::tmem_alloc(&ctl->tmem_base, kSplitTmemCols);
     ptx::tmem_relinquish_alloc_permit();
   }
@@ -150,7 +159,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   __syncthreads();
   ptx::tcgen05_fence_after();
 
-  const uint32_t tmem_base = ctl->tmem_base;
+  const uint32_t tmem_base = active ? ctl->tmem_base : 0u;
   volatile int* abort_flag = &ctl->abort_flag;
   {
     long long rows = group_list[0];
@@ -250,7 +259,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   // Nobody leaves (and frees its shared memory) while a peer may still be reading it.
   __syncthreads();
   ptx::cluster_sync();
-  if (warp == 1) {
+  if (active && warp == 1) {
     ptx::tcgen05_fence_after();
     ptx::tmem_dealloc(tmem_base, kSplitTmemCols);
   }

@@ -553,3 +553,17 @@ def test_grouped_matmul_swiglu_rejects_odd_widths(cabi):
     with pytest.raises(cabi.B200OpsError) as e:
         cabi.grouped_matmul_swiglu(x, w, gl, torch.zeros(4, 96, dtype=torch.float16, device=DEV))
     assert e.value.code == cabi.EINVAL
+
+
+@pytest.mark.parametrize("rows", [0, 100, 128, 300, 512])
+def test_grouped_matmul_cluster_split_k_loose_row_bound(cabi, rows):
+    """One expert, a 512-row buffer, K = 8192: the cluster size is chosen for one m-tile of rows;
+    clusters of m-tiles without rows leave at once, those with rows run as further waves."""
+    g = torch.Generator().manual_seed(rows + 5)
+    x = torch.randn(512, 8192, generator=g).half()
+    w_storage = (torch.randn(1, 512, 8192, generator=g) * 0.03).half()
+    gl = torch.tensor([rows], dtype=torch.int64)
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    got = run_grouped_matmul(cabi, x, w_storage, gl, fill=9.0, split_k=True)
+    close(got[:rows], want[:rows])
+    assert (got[rows:] == 9.0).all()

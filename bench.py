@@ -243,8 +243,24 @@ def case_grouped_matmul(ops, dev, steps, warmup, peaks, which="gate_up"):
     peak = peaks["bf16_tflops"]
     return {"op": f"grouped_matmul_{which}", "shape": f"8 experts, 8192 rows, {k}->{n} f16",
             "flops": flops, "us": round(us, 2), "achieved": round(tf, 1), "unit": "TFLOP/s",
-            "peak": peak, "frac": round(tf / peak, 4), "bound": "tensor", "launches": 1,
+            "peak": peak, "frac": round(tf / peak, 4),
+            "frac_of_sustained": round(tf / peaks.get("bf16_tflops_sustained", peak), 4),
+            "bound": "tensor", "launches": 1,
             "group_rows": torch.diff(w["group_list"], prepend=torch.zeros(1, dtype=torch.int64)).tolist()}
+
+
+def case_dense_projection(ops, dev, steps, warmup, peaks, rows=256, k=4096, n=6144):
+    """The QKV projection of the layer's decode batch as the layer calls it (a one-group
+    grouped_matmul): weights stream from HBM once, so the bound is HBM."""
+    nbytes = 2 * (n * k + rows * k + rows * n)
+    sets = sets_for(nbytes)
+    g = torch.Generator(device=dev).manual_seed(3)
+    x = torch.randn(rows, k, generator=g, device=dev, dtype=torch.float16)
+    ws = [(0.02 * torch.randn(1, n, k, generator=g, device=dev, dtype=torch.float16)).transpose(1, 2)
+          for _ in range(sets)]
+    gl = torch.tensor([rows], dtype=torch.int64, device=dev)
+    us, _ = time_graph(lambda i: ops.grouped_matmul(x, ws[i], gl), sets, 2 * sets, steps, warmup, dev)
+    return op_record("dense_projection_qkv", f"[{rows},{k}] x [{k},{n}] f16", nbytes, us, peaks, "hbm", launches=1)
 
 
 def op_record(name, shape, nbytes, us, peaks, bound, launches):
@@ -538,6 +554,25 @@ def profile_case(name, ops, dev):
         x, ws, gl = w["x"].to(dev), w["w_storage"].to(dev).transpose(1, 2), w["group_list"].to(dev)
         fn = lambda: ops.grouped_matmul(x, ws, gl)
         info = {"flops": 2 * 2048 * 4096 * 4096}
+    elif name == "grouped_matmul_pairs":  # 4096 rows: the CTA-pair kernel
+        w = wl.grouped_matmul_inputs(rows=4096, k=4096, n=4096, seed=4)
+        x, ws, gl = w["x"].to(dev), w["w_storage"].to(dev).transpose(1, 2), w["group_list"].to(dev)
+        fn = lambda: ops.grouped_matmul(x, ws, gl)
+        info = {"flops": 2 * 4096 * 4096 * 4096}
+    elif name == "grouped_matmul_swiglu":  # gate/up projection with SwiGLU epilogue, CTA pairs
+        import ascend910a_extras.moe as moe
+
+        w = wl.grouped_matmul_inputs(rows=4096, k=4096, n=4096, seed=4)
+        x, ws, gl = w["x"].to(dev), w["w_storage"].to(dev).transpose(1, 2), w["group_list"].to(dev)
+        fn = lambda: moe.grouped_matmul_swiglu(x, ws, gl)
+        info = {"flops": 2 * 4096 * 4096 * 4096}
+    elif name == "dense_projection":  # QKV projection of a 256-row decode batch: cluster split-K
+        g = torch.Generator().manual_seed(4)
+        x = torch.randn(256, 4096, generator=g).half().to(dev)
+        ws = (torch.randn(1, 6144, 4096, generator=g) * 0.02).half().to(dev).transpose(1, 2)
+        gl = torch.tensor([256], dtype=torch.int64, device=dev)
+        fn = lambda: ops.grouped_matmul(x, ws, gl)
+        info = {"bytes": 2 * (6144 * 4096 + 256 * 4096 + 256 * 6144)}
     elif name == "add_rms_norm":
         d = wl.add_rms_norm_inputs()
         x, r, wt = d["x"].to(dev), d["residual"].to(dev), d["weight"].to(dev)
@@ -655,6 +690,7 @@ def main():
         "rope": case_rope, "swiglu": case_swiglu, "paged_attention": case_paged_attention,
         "grouped_matmul_gate_up": lambda *a: case_grouped_matmul(*a, which="gate_up"),
         "grouped_matmul_down": lambda *a: case_grouped_matmul(*a, which="down"),
+        "dense_projection_qkv": case_dense_projection,
     }
     if ns.ops == "auto":
         want = list(cases) if world == 1 else []

@@ -81,6 +81,35 @@ def test_attention_and_gemm_stay_inside_their_outputs(cabi):
         assert buf.intact()
 
 
+@pytest.mark.parametrize("ksplit", ["1", "0"])  # cluster split-K / split-K through the workspace
+def test_split_k_paths_stay_inside_their_outputs(cabi, monkeypatch, ksplit):
+    monkeypatch.setenv("B200OPS_GMM_KSPLIT", ksplit)
+    g2 = wl.grouped_matmul_inputs(rows=70, k=8192, n=320, experts=1, seed=7)
+    nb = cabi.grouped_matmul_workspace_size(70, 8192, 1, 320)
+    assert nb > 0
+    ws2, y2 = Guarded((nb // 2,)), Guarded((70, 320))
+    cabi.grouped_matmul(g2["x"].to(DEV), g2["w_storage"].to(DEV), g2["group_list"].to(DEV), y2.t,
+                        ws2.t.view(torch.uint8))
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    assert ws2.intact() and y2.intact()
+    assert not bool((y2.t.view(torch.int16) == CANARY).all())
+
+
+@pytest.mark.parametrize("pairs", ["0", "2"])  # single-CTA kernel / CTA-pair kernel
+def test_pair_and_swiglu_epilogues_stay_inside_their_outputs(cabi, monkeypatch, pairs):
+    monkeypatch.setenv("B200OPS_GMM_PAIR", pairs)
+    g = wl.grouped_matmul_inputs(rows=301, k=256, n=384, experts=5, seed=6)
+    x, w, gl = g["x"].to(DEV), g["w_storage"].to(DEV), g["group_list"].to(DEV)
+    y, act = Guarded((301, 384)), Guarded((301, 192))
+    cabi.grouped_matmul(x, w, gl, y.t)
+    cabi.grouped_matmul_swiglu(x, w, gl, act.t)
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    assert y.intact() and act.intact()
+    assert not bool((act.t.view(torch.int16) == CANARY).all())
+
+
 def test_print_info_reports_the_device(cabi):
     buf = ctypes.create_string_buffer(2048)
     cabi.check(cabi.load().b200ops_print_info(0, buf, 2048))

@@ -46,6 +46,8 @@ SIGNATURES = {
     "b200ops_grouped_matmul_swiglu": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p]),
     "b200ops_fused_qkv_rope_cache": (c_int, [c_void_p] * 8 + [c_int64] * 5 + [ctypes.POINTER(c_int64), c_int,
                                                                               c_void_p]),
+    "b200ops_fused_qkv_norm_rope_cache": (c_int, [c_void_p] * 3 + [c_float] + [c_void_p] * 7 + [c_int64] * 5 +
+                                          [ctypes.POINTER(c_int64), c_int, c_void_p]),
     "b200ops_moe_route_topk": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p]),
     "b200ops_moe_permute": (c_int, [c_void_p] * 5 + [c_int64] * 4 + [c_void_p]),
     "b200ops_moe_ep_plan": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p]),

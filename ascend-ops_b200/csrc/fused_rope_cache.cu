@@ -10,6 +10,12 @@
 //     token's slot (either cache layout).
 // Arithmetic and rounding are those of rope.cu followed by reshape_and_cache.cu, so the
 // result is bit-identical to calling the two operators in sequence.
+//
+// Optionally the per-head RMSNorm that Qwen3-style layers apply to q and k between the split
+// and the rotary embedding (csrc/ffi/graph.cpp:252-255: add_rmsnorm on q [T, Hq, D] and
+// k [T, Hkv, D] with a [D] weight, then add_rope) is applied on the way: the D/16 threads that
+// hold one head reduce its sum of squares with shuffles, and the normalised values are rounded
+// to fp16 before the rotation, as the stand-alone operator would have stored them.
 #include "common.cuh"
 
 namespace b200ops {
@@ -23,6 +29,9 @@ struct FusedParams {
   const __half* cos_cache;
   const __half* sin_cache;
   const int32_t* slots;
+  const __half* q_norm_w;  // [D] or nullptr: RMSNorm weights of the query / key heads
+  const __half* k_norm_w;
+  float eps, inv_dim;
   __half* q_out;
   __half* k_cache;
   __half* v_cache;
@@ -45,8 +54,11 @@ __device__ __forceinline__ size_t cache_vec(const FusedParams& p, int64_t slot, 
 }
 
 __global__ void __launch_bounds__(kThreads) fused_qkv_rope_cache_kernel(FusedParams p) {
-  const uint32_t item = blockIdx.x * kThreads + threadIdx.x;
-  if (item >= p.total_items) return;
+  // No early return: with the norm switched on, the lanes of a head reduce with shuffles, so
+  // every lane of the warp stays (threads past the end work on the last item and store nothing).
+  const uint32_t raw_item = blockIdx.x * kThreads + threadIdx.x;
+  const bool valid = raw_item < p.total_items;
+  const uint32_t item = valid ? raw_item : p.total_items - 1;
   const uint32_t token = item / p.items_per_token;
   const uint32_t rem = item - token * p.items_per_token;
   const uint32_t head = rem / p.vecs_per_half;  // index over Hq + 2*Hkv heads of the qkv row
@@ -59,6 +71,36 @@ __global__ void __launch_bounds__(kThreads) fused_qkv_rope_cache_kernel(FusedPar
   uint4 yv = ld_stream(in + j + p.vecs_per_half);
   const bool is_q = head < p.num_heads;
   const bool is_k = !is_q && head < p.num_heads + p.num_kv_heads;
+  if (p.q_norm_w != nullptr || p.k_norm_w != nullptr) {
+    // vecs_per_half is a power of two <= 32 here (host check) and heads start at multiples of
+    // it, so the lanes of one head are an aligned group of the warp.
+    uint32_t* xs = reinterpret_cast<uint32_t*>(&xv);
+    uint32_t* ys = reinterpret_cast<uint32_t*>(&yv);
+    float sumsq = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 xf = h2_to_f2(xs[i]);
+      const float2 yf = h2_to_f2(ys[i]);
+      sumsq += xf.x * xf.x + xf.y * xf.y + yf.x * yf.x + yf.y * yf.y;
+    }
+    for (uint32_t m = p.vecs_per_half >> 1; m > 0; m >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, m);
+    const __half* w = is_q ? p.q_norm_w : (is_k ? p.k_norm_w : nullptr);
+    if (w != nullptr) {
+      const float inv_rms = 1.0f / sqrtf(sumsq * p.inv_dim + p.eps);
+      const uint4 wx = __ldg(reinterpret_cast<const uint4*>(w) + j);
+      const uint4 wy = __ldg(reinterpret_cast<const uint4*>(w) + j + p.vecs_per_half);
+      const uint32_t* wxs = reinterpret_cast<const uint32_t*>(&wx);
+      const uint32_t* wys = reinterpret_cast<const uint32_t*>(&wy);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 xf = h2_to_f2(xs[i]), yf = h2_to_f2(ys[i]);
+        const float2 wxf = h2_to_f2(wxs[i]), wyf = h2_to_f2(wys[i]);
+        xs[i] = f2_to_h2(xf.x * inv_rms * wxf.x, xf.y * inv_rms * wxf.y);
+        ys[i] = f2_to_h2(yf.x * inv_rms * wyf.x, yf.y * inv_rms * wyf.y);
+      }
+    }
+  }
+  if (!valid) return;
   if (is_q || is_k) {
     const int pos = p.positions[token];
     if (pos < 0 || pos >= p.max_pos) {
@@ -110,12 +152,33 @@ extern "C" int b200ops_fused_qkv_rope_cache(const void* qkv, const int32_t* posi
                                             void* value_cache, int64_t num_tokens, int64_t num_heads,
                                             int64_t num_kv_heads, int64_t head_dim, int64_t max_pos,
                                             const int64_t cache_dims[4], int layout, void* stream) {
+  return b200ops_fused_qkv_norm_rope_cache(qkv, nullptr, nullptr, 0.f, position_ids, cos_cache, sin_cache,
+                                           slot_indices, q_out, key_cache, value_cache, num_tokens, num_heads,
+                                           num_kv_heads, head_dim, max_pos, cache_dims, layout, stream);
+}
+
+extern "C" int b200ops_fused_qkv_norm_rope_cache(const void* qkv, const void* q_norm_weight,
+                                                 const void* k_norm_weight, float eps,
+                                                 const int32_t* position_ids, const void* cos_cache,
+                                                 const void* sin_cache, const int32_t* slot_indices,
+                                                 void* q_out, void* key_cache, void* value_cache,
+                                                 int64_t num_tokens, int64_t num_heads, int64_t num_kv_heads,
+                                                 int64_t head_dim, int64_t max_pos, const int64_t cache_dims[4],
+                                                 int layout, void* stream) {
   using namespace b200ops;
   B200OPS_REQUIRE(num_tokens >= 0 && num_heads > 0 && num_kv_heads > 0 && head_dim > 0 && max_pos >= 0,
                   "fused_qkv_rope_cache: bad shape tokens=%lld heads=%lld kv_heads=%lld head_dim=%lld",
                   (long long)num_tokens, (long long)num_heads, (long long)num_kv_heads, (long long)head_dim);
   B200OPS_REQUIRE(head_dim % 16 == 0, "fused_qkv_rope_cache: head_dim must be a multiple of 16, got %lld",
                   (long long)head_dim);
+  if (q_norm_weight != nullptr || k_norm_weight != nullptr) {
+    const int64_t v = head_dim / 16;
+    B200OPS_REQUIRE(v <= 32 && (v & (v - 1)) == 0,
+                    "fused_qkv_rope_cache: the q/k norm needs head_dim in {16, 32, 64, 128, 256, 512}, got %lld",
+                    (long long)head_dim);
+    B200OPS_REQUIRE((!q_norm_weight || aligned16(q_norm_weight)) && (!k_norm_weight || aligned16(k_norm_weight)),
+                    "fused_qkv_rope_cache: norm weights must be 16-byte aligned");
+  }
   B200OPS_REQUIRE(cache_dims != nullptr, "fused_qkv_rope_cache: cache_dims is null");
   B200OPS_REQUIRE(layout == B200OPS_KV_LAYOUT_NZ || layout == B200OPS_KV_LAYOUT_NHD,
                   "fused_qkv_rope_cache: unknown cache layout %d", layout);
@@ -144,6 +207,10 @@ extern "C" int b200ops_fused_qkv_rope_cache(const void* qkv, const int32_t* posi
   p.cos_cache = static_cast<const __half*>(cos_cache);
   p.sin_cache = static_cast<const __half*>(sin_cache);
   p.slots = slot_indices;
+  p.q_norm_w = static_cast<const __half*>(q_norm_weight);
+  p.k_norm_w = static_cast<const __half*>(k_norm_weight);
+  p.eps = eps;
+  p.inv_dim = 1.0f / static_cast<float>(head_dim);
   p.q_out = static_cast<__half*>(q_out);
   p.k_cache = static_cast<__half*>(key_cache);
   p.v_cache = static_cast<__half*>(value_cache);

@@ -394,9 +394,12 @@ at::Tensor moe_finalize(at::Tensor rows, at::Tensor slot_to_row, at::Tensor expe
 }
 
 // q_out = rope(q part of qkv); rope(k) and v go into the caches.  See b200ops_fused_qkv_rope_cache.
+// q_norm_weight / k_norm_weight ([head_dim] f16, optional): per-head RMSNorm before the rotation.
 at::Tensor fused_qkv_rope_cache(at::Tensor qkv, at::Tensor position_ids, at::Tensor cos_cache,
                                 at::Tensor sin_cache, at::Tensor slot_indices, at::Tensor key_cache,
-                                at::Tensor value_cache, int64_t num_heads, int64_t num_kv_heads) {
+                                at::Tensor value_cache, int64_t num_heads, int64_t num_kv_heads,
+                                c10::optional<at::Tensor> q_norm_weight, c10::optional<at::Tensor> k_norm_weight,
+                                double epsilon) {
   TORCH_CHECK(qkv.dim() == 2 && qkv.is_contiguous() && qkv.size(1) % (num_heads + 2 * num_kv_heads) == 0,
               "fused_qkv_rope_cache: qkv must be contiguous [T, (Hq + 2*Hkv) * D], got ", qkv.sizes());
   const int64_t head_dim = qkv.size(1) / (num_heads + 2 * num_kv_heads);
@@ -415,11 +418,21 @@ at::Tensor fused_qkv_rope_cache(at::Tensor qkv, at::Tensor position_ids, at::Ten
   check_f16_cuda(sin_cache, "fused_qkv_rope_cache", "sin_cache");
   check_i32_cuda(position_ids, "fused_qkv_rope_cache", "position_ids");
   check_i32_cuda(slot_indices, "fused_qkv_rope_cache", "slot_indices");
+  for (const auto* w : {&q_norm_weight, &k_norm_weight}) {
+    if (!w->has_value()) continue;
+    TORCH_CHECK((*w)->dim() == 1 && (*w)->size(0) == head_dim && (*w)->is_contiguous(),
+                "fused_qkv_rope_cache: a norm weight must be a contiguous [head_dim] tensor");
+    check_f16_cuda(**w, "fused_qkv_rope_cache", "norm weight");
+    check_same_device(qkv, **w, "fused_qkv_rope_cache");
+  }
   const int layout = cache_layout_for_key(key_cache, num_kv_heads, head_dim, "fused_qkv_rope_cache");
   const int64_t dims[4] = {key_cache.size(0), key_cache.size(1), key_cache.size(2), key_cache.size(3)};
   const c10::cuda::CUDAGuard guard(qkv.device());
   at::Tensor q_out = at::empty({qkv.size(0), num_heads, head_dim}, qkv.options());
-  check_status(b200ops_fused_qkv_rope_cache(qkv.data_ptr(), position_ids.data_ptr<int32_t>(),
+  check_status(b200ops_fused_qkv_norm_rope_cache(qkv.data_ptr(),
+                                            q_norm_weight ? q_norm_weight->data_ptr() : nullptr,
+                                            k_norm_weight ? k_norm_weight->data_ptr() : nullptr,
+                                            static_cast<float>(epsilon), position_ids.data_ptr<int32_t>(),
                                             cos_cache.data_ptr(), sin_cache.data_ptr(),
                                             slot_indices.data_ptr<int32_t>(), q_out.data_ptr(),
                                             key_cache.data_ptr(), value_cache.data_ptr(), qkv.size(0),
@@ -531,7 +544,11 @@ void init_ffi_moe(py::module_&& m) {
   m.def("peer_barrier", &peer_barrier);
   m.def("grouped_matmul_scatter", &grouped_matmul_scatter);
   m.def("grouped_matmul_swiglu", &grouped_matmul_swiglu);
-  m.def("fused_qkv_rope_cache", &fused_qkv_rope_cache);
+  m.def("fused_qkv_rope_cache", &fused_qkv_rope_cache, py::arg("qkv"), py::arg("position_ids"),
+        py::arg("cos_cache"), py::arg("sin_cache"), py::arg("slot_indices"), py::arg("key_cache"),
+        py::arg("value_cache"), py::arg("num_heads"), py::arg("num_kv_heads"),
+        py::arg("q_norm_weight") = py::none(), py::arg("k_norm_weight") = py::none(),
+        py::arg("epsilon") = 1e-6);
   m.def("route_topk", &moe_route_topk);
   m.def("permute", &moe_permute);
   m.def("ep_plan", &moe_ep_plan);

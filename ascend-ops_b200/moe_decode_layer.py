@@ -39,6 +39,7 @@ class LayerConfig:
     rope_theta: float = 1e6
     eps: float = 1e-6
     block_size: int = 128
+    qk_norm: bool = False  # per-head RMSNorm of q and k before rope (Qwen3; csrc/ffi/graph.cpp:252-255)
 
 
 def make_weights(cfg: LayerConfig, seed=7, experts=None, std=0.02, device="cpu"):
@@ -63,6 +64,10 @@ def make_weights(cfg: LayerConfig, seed=7, experts=None, std=0.02, device="cpu")
         "wo": mat(cfg.hidden, cfg.heads * cfg.head_dim, g),
         "wrouter": mat(cfg.experts, cfg.hidden, g),
     }
+    if cfg.qk_norm:
+        gn = gen(seed + 500)
+        w["q_norm"] = (1 + 0.1 * torch.randn(cfg.head_dim, generator=gn, device=device)).half()
+        w["k_norm"] = (1 + 0.1 * torch.randn(cfg.head_dim, generator=gn, device=device)).half()
     keep = list(range(cfg.experts)) if experts is None else [int(e) for e in experts]
     gu = torch.empty(len(keep), 2 * cfg.intermediate, cfg.hidden, dtype=torch.float16, device=device)
     dn = torch.empty(len(keep), cfg.hidden, cfg.intermediate, dtype=torch.float16, device=device)
@@ -96,6 +101,8 @@ class MoEDecodeLayer:
         self.fuse_swiglu = True  # False: ops.grouped_matmul then ops.swiglu
         d = lambda t: t.to(device)
         self.ln1, self.ln2 = d(weights["ln1"]), d(weights["ln2"])
+        self.q_norm = d(weights["q_norm"]) if cfg.qk_norm else None
+        self.k_norm = d(weights["k_norm"]) if cfg.qk_norm else None
         # NT-GEMM weights as single-group stacks [1, N, K]; the op takes the [1, K, N] view.
         self.wqkv = d(weights["wqkv"])[None].transpose(1, 2)
         self.wo = d(weights["wo"])[None].transpose(1, 2)
@@ -146,12 +153,18 @@ class MoEDecodeLayer:
         nq = cfg.heads * cfg.head_dim
         if self.fuse_rope_cache:
             q = self.moe.fused_qkv_rope_cache(qkv, positions, self.cos, self.sin, slots, k_cache, v_cache,
-                                              cfg.heads, cfg.kv_heads)
+                                              cfg.heads, cfg.kv_heads, self.q_norm, self.k_norm, cfg.eps)
         else:
             nkv = cfg.kv_heads * cfg.head_dim
             q = qkv[:, :nq].contiguous().view(t, cfg.heads, cfg.head_dim)
             k = qkv[:, nq:nq + nkv].contiguous().view(t, cfg.kv_heads, cfg.head_dim)
             v = qkv[:, nq + nkv:].contiguous().view(t, cfg.kv_heads, cfg.head_dim)
+            if cfg.qk_norm:  # the stand-alone operator, one head per row and a zero residual
+                zq, zk = torch.zeros_like(q), torch.zeros_like(k)
+                q = ops.add_rms_norm(q.view(-1, cfg.head_dim), zq.view(-1, cfg.head_dim), self.q_norm,
+                                     cfg.eps)[0].view_as(q)
+                k = ops.add_rms_norm(k.view(-1, cfg.head_dim), zk.view(-1, cfg.head_dim), self.k_norm,
+                                     cfg.eps)[0].view_as(k)
             q, k = ops.rope(q, k, positions, self.cos, self.sin)
             ops.reshape_and_cache(k, v, k_cache, v_cache, slots)
         if attention_events is not None:

@@ -190,6 +190,21 @@ int b200ops_fused_qkv_rope_cache(const void* qkv, const int32_t* position_ids, c
                                  int64_t max_pos, const int64_t cache_dims[4], int layout, void* stream);
 
 /*
+ * The same launch with the per-head RMSNorm of Qwen3-style layers between the split and the
+ * rotary embedding (the reference's graph builder inserts two RmsNorm nodes there,
+ * csrc/ffi/graph.cpp:252-255): q heads are normalised over head_dim with q_norm_weight [head_dim]
+ * f16, k heads with k_norm_weight, y = x / sqrt(mean(x^2) + eps) * w rounded to f16, then rotated.
+ * Either weight may be NULL (that tensor is not normalised); head_dim must then be a power of
+ * two times 16, at most 512.
+ */
+int b200ops_fused_qkv_norm_rope_cache(const void* qkv, const void* q_norm_weight, const void* k_norm_weight,
+                                      float eps, const int32_t* position_ids, const void* cos_cache,
+                                      const void* sin_cache, const int32_t* slot_indices, void* q_out,
+                                      void* key_cache, void* value_cache, int64_t num_tokens,
+                                      int64_t num_heads, int64_t num_kv_heads, int64_t head_dim,
+                                      int64_t max_pos, const int64_t cache_dims[4], int layout, void* stream);
+
+/*
  * MoE routing glue: the steps around grouped_matmul that the reference leaves to its caller
  * (its grouped_matmul expects rows pre-sorted by expert and cumulative group ends,
  * csrc/opdev/op_kernel/grouped_mat_mul_ex.cpp:29-38; the sorting lives in the companion

@@ -45,6 +45,14 @@ def add_rms_norm(x, residual, weight, epsilon):
     return out.to(x.dtype), y.to(x.dtype)
 
 
+def head_rms_norm(x, weight, epsilon):
+    """RMSNorm over the last dimension without a residual: the per-head q / k normalisation the
+    reference's graph builder inserts before rope (csrc/ffi/graph.cpp:252-255), with the
+    arithmetic of `add_rms_norm` above (fp32 mean of squares, one rounding)."""
+    rms = torch.sqrt((x.float() ** 2).mean(-1, keepdim=True) + epsilon)
+    return (x / rms * weight).to(x.dtype)
+
+
 def swiglu(x):
     """benchmark/test_swiglu.py:6-12 (`swiglu_cpu`): silu(first half) * second half in fp32."""
     x1, x2 = x.chunk(2, -1)
@@ -190,6 +198,9 @@ def moe_decode_layer(w, batch, k_cache, v_cache, *, heads, kv_heads, head_dim, e
     q = qkv[:, :nq].reshape(t, heads, head_dim)
     k = qkv[:, nq:nq + nkv].reshape(t, kv_heads, head_dim)
     v = qkv[:, nq + nkv:].reshape(t, kv_heads, head_dim)
+    if "q_norm" in w:  # Qwen3-style per-head normalisation of q and k
+        q = head_rms_norm(q, w["q_norm"], eps)
+        k = head_rms_norm(k, w["k_norm"], eps)
     q, k = rope(q, k, batch["positions"], cos_cache, sin_cache)
     reshape_and_cache(k, k_cache, batch["slots"], v, v_cache)
     attn = paged_attention(q, k_cache, v_cache, batch["block_tables"], batch["context_lens"])

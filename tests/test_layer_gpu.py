@@ -150,3 +150,66 @@ def test_host_to_host_step_equals_eager_step(ops):
     assert not torch.equal(y2, y_eager.cpu())
     with pytest.raises(RuntimeError):
         mdl.CapturedDecodeStep(layer, b, kd, vd).run_host()
+
+
+def test_layer_with_per_head_qk_norm_matches_oracle_and_unfused_operators(ops):
+    """Qwen3-style layer: RMSNorm over head_dim on q and k between the split and rope.  The
+    fused kernel (norm + rope + cache scatter in one launch) against the oracle, and against the
+    stand-alone operators (add_rms_norm with a zero residual, rope, reshape_and_cache)."""
+    cfg = mdl.LayerConfig(hidden=512, heads=8, kv_heads=2, head_dim=128, intermediate=256, experts=4, qk_norm=True)
+    w = mdl.make_weights(cfg, seed=31, std=0.05)
+    b = mdl.make_decode_batch(cfg, batch=11, min_pos=3, max_pos=900, seed=32)
+    g = torch.Generator().manual_seed(33)
+    kc = torch.randn(b["cache_shape"], generator=g).half()
+    vc = torch.randn(b["cache_shape"], generator=g).half()
+    names = ("x", "residual", "positions", "slots", "block_tables", "context_lens")
+    layer = mdl.MoEDecodeLayer(cfg, w, DEV, ops)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    y, res, ids, wts = layer.forward(*(b[n].to(DEV) for n in names), kd, vd, return_routing=True)
+    layer.fuse_rope_cache = False
+    kd2, vd2 = kc.to(DEV), vc.to(DEV)
+    y2, res2 = layer.forward(*(b[n].to(DEV) for n in names), kd2, vd2)
+    torch.cuda.synchronize()
+    torch.testing.assert_close(kd.float(), kd2.float(), rtol=1e-2, atol=2e-3)
+    assert torch.equal(vd, vd2)
+    torch.testing.assert_close(y.float(), y2.float(), rtol=2e-2, atol=3e-3)
+    cos, sin = oracle.cos_sin_cache(16385, cfg.head_dim, cfg.rope_theta)
+    kc_o, vc_o = kc.clone(), vc.clone()
+    ey, eres, _, _, st = oracle.moe_decode_layer(
+        w, b, kc_o, vc_o, expert_ids=ids.cpu(), expert_weights=wts.cpu(), heads=cfg.heads, kv_heads=cfg.kv_heads,
+        head_dim=cfg.head_dim, experts=cfg.experts, top_k=cfg.top_k, eps=cfg.eps, cos_cache=cos, sin_cache=sin)
+    slots = b["slots"].long()
+    flat_k = kd.cpu().view(-1, cfg.kv_heads, cfg.head_dim)
+    torch.testing.assert_close(flat_k[slots].float(), st["k_rot"].float(), rtol=1e-2, atol=2e-3)
+    assert float(st["k_rot"].float().pow(2).mean().sqrt()) > 0.5  # normalised keys: unit scale, not 0.05-ish
+    torch.testing.assert_close(res.cpu().float(), eres.float(), rtol=1e-2, atol=2e-3)
+    torch.testing.assert_close(y.cpu().float(), ey.float(), rtol=2e-2, atol=3e-3)
+
+
+@pytest.mark.parametrize("head_dim,heads,kv_heads", [(64, 5, 1), (128, 4, 4), (256, 3, 1), (32, 7, 2)])
+def test_fused_qk_norm_head_sizes(head_dim, heads, kv_heads):
+    """The in-kernel head reduction for every supported head size, including head counts that
+    leave a warp's last lanes past the end of the work."""
+    import ascend910a_extras.moe as moe
+
+    g = torch.Generator().manual_seed(head_dim + heads)
+    t = 9
+    qkv = torch.randn(t, (heads + 2 * kv_heads) * head_dim, generator=g).half()
+    qw = (1 + 0.1 * torch.randn(head_dim, generator=g)).half()
+    kw = (1 + 0.1 * torch.randn(head_dim, generator=g)).half()
+    pos = torch.randint(0, 50, (t,), generator=g, dtype=torch.int32)
+    cos, sin = oracle.cos_sin_cache(64, head_dim, 1e4)
+    slots = torch.randperm(32, generator=g)[:t].int()
+    kc = torch.zeros(2, 16, kv_heads, head_dim, dtype=torch.float16, device=DEV)
+    vc = torch.zeros_like(kc)
+    q = moe.fused_qkv_rope_cache(qkv.to(DEV), pos.to(DEV), cos.to(DEV), sin.to(DEV), slots.to(DEV), kc, vc,
+                                 heads, kv_heads, qw.to(DEV), kw.to(DEV), 1e-6).cpu()
+    nq, nkv = heads * head_dim, kv_heads * head_dim
+    q_ref = oracle.head_rms_norm(qkv[:, :nq].reshape(t, heads, head_dim), qw, 1e-6)
+    k_ref = oracle.head_rms_norm(qkv[:, nq:nq + nkv].reshape(t, kv_heads, head_dim), kw, 1e-6)
+    q_ref, k_ref = oracle.rope(q_ref, k_ref, pos, cos, sin)
+    torch.testing.assert_close(q.float(), q_ref.float(), rtol=1e-2, atol=2e-3)
+    flat_k = kc.cpu().view(-1, kv_heads, head_dim)
+    torch.testing.assert_close(flat_k[slots.long()].float(), k_ref.float(), rtol=1e-2, atol=2e-3)
+    flat_v = vc.cpu().view(-1, kv_heads, head_dim)
+    assert torch.equal(flat_v[slots.long()], qkv[:, nq + nkv:].reshape(t, kv_heads, head_dim))

@@ -148,3 +148,14 @@ def test_c_oracle_agrees_with_python_oracle():
                                      ctypes.c_int64(128), ctypes.c_int64(8), ctypes.c_int64(C),
                                      ctypes.c_int64(P), ctypes.c_int(nhd))
         assert np.array_equal(bits(kc), bits(ek)) and np.array_equal(bits(vc), bits(ev))
+
+
+def test_head_rms_norm_is_add_rms_norm_without_residual():
+    """The per-head q/k normalisation is pinned through the add_rms_norm golden: with a zero
+    residual both must give the same bits, row by row (one head per row)."""
+    g = torch.Generator().manual_seed(9)
+    x = torch.randn(7, 5, 128, generator=g).half()
+    w = (1 + 0.1 * torch.randn(128, generator=g)).half()
+    got = oracle.head_rms_norm(x, w, 1e-6)
+    want, _ = oracle.add_rms_norm(x.view(-1, 128), torch.zeros(35, 128, dtype=torch.float16), w, 1e-6)
+    assert torch.equal(got.view(-1, 128), want)

@@ -89,14 +89,18 @@ inline bool use_narrow_tiles(int64_t num_tokens, int64_t k, int64_t n, int sms) 
 }
 
 // CTA pairs (grouped_matmul_pair.cuh): for problems bound by the tensor pipe and not by streaming
-// the weights once -- at least two waves of 128 x 256 output tiles, and two m-tiles per expert on
-// average (groups of a single m-tile have no pair to form).  The pair kernel takes the whole
-// pairs of m-tiles, a second launch of the single-CTA kernel the last tile of odd groups.
-// Measured on B200 against the single-CTA kernel alone: 4096^3 dense 104 us against 114 us; the
-// power-capped benchmark shapes (8192 rows, 8 experts) 1540 against 1559 us and 793 against
-// 814 us; 2048 rows x 4096 x 4096 (1.7 waves) 100 against 97 us, hence the two-wave floor.
+// the weights once -- at least one wave of 128 x 256 output tiles, and two m-tiles per expert on
+// average (with one m-tile per expert the second CTA of every pair would multiply nothing useful).
+// Measured on B200 against the single-CTA kernel, interleaved on one GPU: 4096^3 dense 102 us
+// against 112 us; 2048 rows x 4096 x 4096 (1.7 waves) 94 against 97 us; the 8192-row, 8-expert
+// benchmark shapes 1525 against 1555 us and 806 against 824 us on a cool GPU, and 1686 against
+// 1854 us and 830 against 903 us once the 1 kW power cap has pulled the clocks down -- a pair
+// moves a third less operand data per flop, and under the cap that is clock speed.
+// (Running the odd last m-tile of a group in a launch of its own instead of pairing it with a
+// tile past the group's end was tried and is no faster: 1677 / 929 us.)
 // The row count the host sees is only a bound (an expert-parallel receive buffer of 1536 rows
-// holds about 128 at decode time), hence also an absolute floor on it.
+// holds about 128 at decode time, and the pair kernel then takes 54 us where the single-CTA kernel
+// takes 45 us), hence also an absolute floor on it.
 // B200OPS_GMM_PAIR: 0 = never, 2 = always (tests), otherwise this rule.
 constexpr int64_t kMinRowsForPairs = 2048;
 inline int pair_mode() {
@@ -110,8 +114,7 @@ inline bool use_cta_pairs(int64_t num_tokens, int64_t num_experts, int64_t n, in
   if (mode == 2) return true;
   const int64_t n_tiles = (n + kWideBN - 1) / kWideBN;
   const int64_t min_tiles = ((num_tokens + BM - 1) / BM) * n_tiles;
-  return min_tiles >= 2 * static_cast<int64_t>(sms) && num_tokens >= 2 * BM * num_experts &&
-         num_tokens >= kMinRowsForPairs;
+  return min_tiles >= sms && num_tokens >= 2 * BM * num_experts && num_tokens >= kMinRowsForPairs;
 }
 
 // Cluster split-K (grouped_matmul_ksplit.cuh), single group only.  Two cases:
@@ -158,7 +161,6 @@ struct Control {
   uint32_t tmem_base;
   int abort_flag;
   int split_rank;  // arrival order of this CTA among the k-slices of its tile
-  int odd_only;    // 1: only the last m-tile of groups with an odd m-tile count (after the pair kernel)
   int tile_prefix[kMaxExperts + 1];  // first tile id of each group; [E] = total tiles
   int row_start[kMaxExperts];
   int row_end[kMaxExperts];
@@ -234,21 +236,13 @@ __device__ __forceinline__ WorkItem locate_item(int item, int splits, int k_bloc
 
 // Tiles of one group are numbered m-fastest.  `g` is carried between calls: tile ids only
 // grow within a CTA, so the search is amortised O(1).
-// m-tiles of a group that this launch covers.  Normally all of them; after the CTA-pair kernel
-// has taken the whole pairs, only the last tile of a group with an odd count.
-__device__ __forceinline__ int covered_m_tiles(int rows, int odd_only) {
-  const int all = (rows + BM - 1) / BM;
-  return odd_only ? (all & 1) : all;
-}
-
 __device__ __forceinline__ TileCoord locate_tile(const Control* c, int tile, int& g, int bn) {
   while (tile >= c->tile_prefix[g + 1]) ++g;
   const int local = tile - c->tile_prefix[g];
   const int rows = c->row_end[g] - c->row_start[g];
-  const int m_tiles = covered_m_tiles(rows, c->odd_only);
-  const int m_first = c->odd_only ? (rows + BM - 1) / BM - 1 : 0;
+  const int m_tiles = (rows + BM - 1) / BM;
   const int n_tile = local / m_tiles;
-  const int m_tile = m_first + local - n_tile * m_tiles;
+  const int m_tile = local - n_tile * m_tiles;
   TileCoord t;
   t.group = g;
   t.row0 = c->row_start[g] + m_tile * BM;
@@ -296,7 +290,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
                       const __grid_constant__ CUtensorMap map_w,
                       const int64_t* __restrict__ group_list, __half* __restrict__ y, int M, int N,
                       int K, int E, int* __restrict__ tile_counters, float* __restrict__ partials,
-                      const RowScatter scatter, int odd_only) {
+                      const RowScatter scatter) {
   constexpr int BN = C::BN;
   constexpr int kStages = C::kStages;
   constexpr int kBBytes = C::kBBytes;
@@ -327,7 +321,6 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       ptx::mbar_init(&ctl->tmem_empty[i], 4);  // one arrival per epilogue warp
     }
     ctl->abort_flag = 0;
-    ctl->odd_only = odd_only;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_x);
     ptx::prefetch_tensormap(&map_w);
@@ -351,7 +344,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
     ctl->tile_prefix[0] = 0;
     for (int e = 0; e < E; ++e) {
       const int rows = ctl->row_end[e] - ctl->row_start[e];
-      acc += covered_m_tiles(rows, odd_only) * n_tiles;
+      acc += ((rows + BM - 1) / BM) * n_tiles;
       ctl->tile_prefix[e + 1] = acc;
     }
   }
@@ -845,14 +838,9 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   if (s) s = gmm::fit_split_to_device(s, resident_tiles);
   if (s)
     return gmm::launch_ksplit(map_x, w, group_list, y, num_tokens, k, num_experts, n, s, scatter, st);
-  // CTA pairs take every whole pair of m-tiles; the single-CTA kernel below then covers the last
-  // m-tile of each group with an odd count (instead of a pair whose second CTA multiplies nothing).
-  const bool pairs = gmm::use_cta_pairs(num_tokens, num_experts, n, sms);
-  if (pairs) {
-    const int rc = gmm::launch_pairs(map_x, w, group_list, y, num_tokens, k, num_experts, n, glu, scatter, st);
-    if (rc != B200OPS_OK) return rc;
-  }
-  const bool narrow = !glu && !pairs && gmm::use_narrow_tiles(num_tokens, k, n, sms);
+  if (gmm::use_cta_pairs(num_tokens, num_experts, n, sms))
+    return gmm::launch_pairs(map_x, w, group_list, y, num_tokens, k, num_experts, n, glu, scatter, st);
+  const bool narrow = !glu && gmm::use_narrow_tiles(num_tokens, k, n, sms);
   const int bn = narrow ? gmm::kNarrowBN : gmm::kWideBN;
   {
     const uint64_t dims[3] = {static_cast<uint64_t>(k), static_cast<uint64_t>(n),
@@ -877,12 +865,11 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
     attr_set[variant][dev] = true;
   }
   const int64_t n_tiles = (n + bn - 1) / bn;  // glu: n / 2 columns in tiles of bn / 2, the same count
-  const int64_t max_tiles = pairs ? num_experts * n_tiles  // at most one left-over m-tile per group
-                                  : ((num_tokens + gmm::BM - 1) / gmm::BM + num_experts) * n_tiles;
+  const int64_t max_tiles = ((num_tokens + gmm::BM - 1) / gmm::BM + num_experts) * n_tiles;
   int* counters = nullptr;
   float* partials = nullptr;
   int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
-  if (!glu && !pairs && workspace != nullptr && gmm::split_k_possible(num_tokens, k, n, sms)) {
+  if (!glu && workspace != nullptr && gmm::split_k_possible(num_tokens, k, n, sms)) {
     if (workspace_size < gmm::workspace_bytes())
       return fail(B200OPS_EWORKSPACE, "grouped_matmul: workspace of %zu bytes needed, got %zu",
                   gmm::workspace_bytes(), workspace_size);
@@ -895,7 +882,7 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   kern<<<grid, gmm::kThreads, smem, st>>>(map_x, map_w, group_list, static_cast<__half*>(y),
                                           static_cast<int>(num_tokens), static_cast<int>(n),
                                           static_cast<int>(k), static_cast<int>(num_experts), counters,
-                                          partials, scatter, pairs ? 1 : 0);
+                                          partials, scatter);
   B200OPS_LAUNCH_CHECK("grouped_matmul");
   return B200OPS_OK;
 }

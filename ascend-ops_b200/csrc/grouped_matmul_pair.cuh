@@ -8,9 +8,8 @@
 // tensor cores of both SMs read.
 //
 //   item        (group, n-tile of 256 columns, pair of m-tiles): CTA r of the cluster owns m-tile
-//               2p + r.  Only whole pairs: the last m-tile of a group with an odd count is left
-//               to a launch of the single-CTA kernel that covers just those tiles (a pair whose
-//               second CTA multiplies nothing would cost a full tile of tensor time).
+//               2p + r.  A group with an odd number of m-tiles leaves CTA 1 of its last pair a
+//               tile past the group's end: it multiplies whatever rows lie there and stores nothing.
 //   warp 0      TMA producer in BOTH CTAs (own x rows, own half of w); completion is counted on
 //               the even CTA's `full` barrier, which expects the bytes of both
 //   warp 1      even CTA: MMA issuer for the pair; commits signal `empty` / `tmem_full` in both
@@ -31,7 +30,7 @@ __device__ __forceinline__ TileCoord locate_pair_item(const Control* c, int item
   while (item >= c->tile_prefix[g + 1]) ++g;
   const int local = item - c->tile_prefix[g];
   const int rows = c->row_end[g] - c->row_start[g];
-  const int m_pairs = ((rows + BM - 1) / BM) / 2;  // whole pairs only
+  const int m_pairs = ((rows + BM - 1) / BM + 1) / 2;
   const int n_tile = local / m_pairs;
   const int m_pair = local - n_tile * m_pairs;
   TileCoord t;
@@ -100,7 +99,7 @@ grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
     ctl->tile_prefix[0] = 0;
     for (int e = 0; e < E; ++e) {
       const int rows = ctl->row_end[e] - ctl->row_start[e];
-      acc += (((rows + BM - 1) / BM) / 2) * n_tiles;
+      acc += (((rows + BM - 1) / BM + 1) / 2) * n_tiles;
       ctl->tile_prefix[e + 1] = acc;
     }
   }

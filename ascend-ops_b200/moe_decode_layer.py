@@ -214,6 +214,9 @@ class CapturedDecodeStep:
         self.layer, self.k_cache, self.v_cache = layer, k_cache, v_cache
         dev = layer.device
         self.inputs = {n: example[n].to(dev).clone() for n in self.NAMES}
+        # x and residual share one allocation so that a host caller can send both with one copy
+        self._act = torch.stack([self.inputs["x"], self.inputs["residual"]])
+        self.inputs["x"], self.inputs["residual"] = self._act[0], self._act[1]
         self.stream = torch.cuda.Stream(dev)
         self.stream.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(self.stream):
@@ -235,12 +238,14 @@ class CapturedDecodeStep:
 
     def _capture_host_io(self, example):
         """A second graph for callers whose inputs and results live in host memory: the step's
-        copies are part of the recording.  The two activation tensors go up on the main stream
-        while the small integer tensors go up on a side stream; `residual_out` starts down on
+        copies are part of the recording.  The two activation tensors go up in one transfer on the
+        main stream while the small integer tensors go up on a side stream; `residual_out` starts down on
         the side stream as soon as the launch producing it is enqueued (it is final before the
         expert MLP, which is a quarter of the step), `y` follows at the end."""
         dev = self.layer.device
-        self.host_in = {n: example[n].clone().pin_memory() for n in self.NAMES}
+        self.host_in = {n: example[n].clone().pin_memory() for n in self.NAMES if n not in ("x", "residual")}
+        self._act_host = torch.stack([example["x"], example["residual"]]).pin_memory()
+        self.host_in["x"], self.host_in["residual"] = self._act_host[0], self._act_host[1]
         self.host_y = torch.empty(self.y.shape, dtype=self.y.dtype).pin_memory()
         self.host_res = torch.empty(self.res.shape, dtype=self.res.dtype).pin_memory()
         self.side = torch.cuda.Stream(dev)
@@ -252,8 +257,7 @@ class CapturedDecodeStep:
                 for n in self.NAMES:
                     if n not in big:
                         self.inputs[n].copy_(self.host_in[n], non_blocking=True)
-            for n in big:
-                self.inputs[n].copy_(self.host_in[n], non_blocking=True)
+            self._act.copy_(self._act_host, non_blocking=True)  # x and residual in one transfer
             self.stream.wait_stream(self.side)
 
             def ship_residual(res):

@@ -29,6 +29,13 @@
 // (grouped_matmul_pair.cuh): clusters of two CTAs issue one 256 x 256 x 16 MMA (cta_group::2), each
 // CTA loading its own rows of x and half of the w tile.
 //
+// Cluster split-K.  A single group of at most 256 rows (the dense projections of a decode batch)
+// runs grouped_matmul_ksplit_kernel (grouped_matmul_ksplit.cuh): the CTAs of a cluster share one
+// output tile and reduce their k-slices through distributed shared memory, without a workspace.
+//
+// SwiGLU epilogue.  Cfg<.., true> and grouped_matmul_pair_kernel<true> compute the gate/up
+// projection of a gated MLP and apply SwiGLU before storing (b200ops_grouped_matmul_swiglu).
+//
 // Tiles are enumerated group by group, m-tile fastest, so that CTAs running at the same
 // time share the same w tile (read from HBM once, then from L2) while the group's x rows
 // stay L2-resident.  Work is 2*M*K*N flops; at the sizes of interest the kernel is bound by

@@ -1,10 +1,12 @@
-// Paged-attention decode, fast path for sm_100a: [pages, P, Hkv, 128] caches, P % 64 == 0,
-// GQA group <= 16.
+// Paged-attention decode, fast path for sm_100a: head_dim 128, page size a multiple of 64,
+// GQA group <= 16; caches [pages, P, Hkv, 128] (NHD) or [pages, Hkv*8, P, 16] (NZ, the
+// reference's layout).
 //
 // One CTA = one (sequence, kv head, context chunk).  A producer warp walks the chunk's pages
 // through the block table and streams 64-token K and V tiles into a ring of 128B-swizzled
-// shared-memory stages with TMA (cp.async.bulk.tensor.4d over the cache viewed as
-// [pages][P][Hkv][D]; two 64-wide boxes per tile and tensor).  Four consumer warps each own
+// shared-memory stages with TMA (cp.async.bulk.tensor.4d; NHD: the cache viewed as
+// [pages][P][Hkv][D], two 64-channel boxes per tile and tensor; NZ: the cache viewed as
+// [pages][Hkv*8][P][16], one box of 8 chunks x 64 tokens per tile and tensor).  Four consumer warps each own
 // 16 tokens of every tile: S = Q.K^T and O += P.V run on warp-level tensor-core MMAs
 // (m16n8k16, query heads padded to the 16-row operand, fp32 accumulation), the online
 // softmax is fp32 with exp2 and scale*log2(e) folded in.  Every K/V byte crosses HBM -> smem
@@ -45,7 +47,7 @@ struct Smem {
 __device__ int g_pa_status = 0;
 
 // kUpper: the GQA group has more than 8 query heads, so MMA rows 8..15 carry data.
-template <int kStages, bool kUpper>
+template <int kStages, bool kUpper, bool kNz>
 __global__ void __launch_bounds__(kThreads)
 paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, Args a) {
@@ -109,10 +111,15 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
     const int off = tok % a.page_size;
     uint8_t* st = smem + stage * kStageBytes;
     ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
-    ptx::tma_load_4d(st, &map_k, &full[stage], 0, kvh, off, pg);
-    ptx::tma_load_4d(st + kSubTileBytes, &map_k, &full[stage], 64, kvh, off, pg);
-    ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, kvh, off, pg);
-    ptx::tma_load_4d(st + kTensorTileBytes + kSubTileBytes, &map_v, &full[stage], 64, kvh, off, pg);
+    if (kNz) {  // {16 halfs, 64 tokens, the head's 8 chunks, 1 page}
+      ptx::tma_load_4d(st, &map_k, &full[stage], 0, off, kvh * (kD / 16), pg);
+      ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, off, kvh * (kD / 16), pg);
+    } else {    // {64 channels, 1 head, 64 tokens, 1 page}, twice
+      ptx::tma_load_4d(st, &map_k, &full[stage], 0, kvh, off, pg);
+      ptx::tma_load_4d(st + kSubTileBytes, &map_k, &full[stage], 64, kvh, off, pg);
+      ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, kvh, off, pg);
+      ptx::tma_load_4d(st + kTensorTileBytes + kSubTileBytes, &map_v, &full[stage], 64, kvh, off, pg);
+    }
   };
   const int prefill = min(kStages, n_tiles);
   if (warp == kConsumerWarps) {
@@ -156,7 +163,7 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
         atomicCAS(&g_pa_status, 0, kErrConsumerWait);
         break;
       }
-      consume_slice<kUpper>(st, qa, smem + stage * kStageBytes, row0, start + t * kTile + row0, end, lane,
+      consume_slice<kUpper, kNz>(st, qa, smem + stage * kStageBytes, row0, start + t * kTile + row0, end, lane,
                             a.scale_log2);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[stage]);
@@ -238,23 +245,31 @@ int env_int(const char* name, int fallback) {
   return (s && *s) ? std::atoi(s) : fallback;
 }
 
-template <int kStages>
-int launch_with_stages(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid,
-                       cudaStream_t st) {
-  const bool upper = a.num_heads / a.num_kv_heads > 8;
-  auto kern = upper ? paged_attention_fast_kernel<kStages, true>
-                    : paged_attention_fast_kernel<kStages, false>;
-  static bool attr_set[2][64] = {{false}};
+template <int kStages, bool kUpper, bool kNz>
+int launch_variant(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid, cudaStream_t st) {
+  auto kern = paged_attention_fast_kernel<kStages, kUpper, kNz>;
+  static bool attr_set[64] = {false};
   int dev = 0;
   B200OPS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[upper][dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     B200OPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(Smem<kStages>::kBytes)));
-    attr_set[upper][dev] = true;
+    attr_set[dev] = true;
   }
   kern<<<grid, kThreads, Smem<kStages>::kBytes, st>>>(mk, mv, a);
   B200OPS_LAUNCH_CHECK("paged_attention");
   return B200OPS_OK;
+}
+
+template <int kStages>
+int launch_with_stages(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid,
+                       cudaStream_t st) {
+  const bool upper = a.num_heads / a.num_kv_heads > 8;
+  const bool nz = a.layout == B200OPS_KV_LAYOUT_NZ;
+  if (nz) return upper ? launch_variant<kStages, true, true>(mk, mv, a, grid, st)
+                       : launch_variant<kStages, false, true>(mk, mv, a, grid, st);
+  return upper ? launch_variant<kStages, true, false>(mk, mv, a, grid, st)
+               : launch_variant<kStages, false, false>(mk, mv, a, grid, st);
 }
 
 }  // namespace
@@ -264,23 +279,39 @@ bool fast_path_supported(const Args& a) {
   // 3 = persistent tile-balanced kernel (paged_attention_stream.cu).
   if (env_int("B200OPS_PA_MODE", 0) == 2) return false;
   const int group = a.num_heads / a.num_kv_heads;
-  return a.layout == B200OPS_KV_LAYOUT_NHD && a.head_dim == kD && a.page_size % kTile == 0 &&
+  return a.head_dim == kD && a.page_size % kTile == 0 &&
          group <= 16 && a.chunk_tokens % a.page_size == 0 &&
          a.chunk_tokens / a.page_size <= kMaxPagesPerChunk && a.page_size <= 256 * kTile;
 }
 
 int launch_fast(const Args& a, cudaStream_t st) {
   CUtensorMap mk, mv;
-  const uint64_t dims[4] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(a.num_kv_heads),
-                            static_cast<uint64_t>(a.page_size), static_cast<uint64_t>(a.num_pages)};
-  const uint64_t strides[3] = {static_cast<uint64_t>(kD) * 2,
-                               static_cast<uint64_t>(a.num_kv_heads) * kD * 2,
-                               static_cast<uint64_t>(a.page_size) * a.num_kv_heads * kD * 2};
-  const uint32_t box[4] = {64, 1, kTile, 1};
-  int rc = encode_f16_map(&mk, a.k_cache, 4, dims, strides, box, "paged_attention(key_cache)");
-  if (rc != B200OPS_OK) return rc;
-  rc = encode_f16_map(&mv, a.v_cache, 4, dims, strides, box, "paged_attention(value_cache)");
-  if (rc != B200OPS_OK) return rc;
+  int rc;
+  if (a.layout == B200OPS_KV_LAYOUT_NZ) {
+    // [pages][Hkv*8 chunks][P tokens][16 halfs]: a tile is the head's 8 chunks x 64 tokens
+    const uint64_t chunks = static_cast<uint64_t>(a.num_kv_heads) * (kD / 16);
+    const uint64_t dims[4] = {16, static_cast<uint64_t>(a.page_size), chunks, static_cast<uint64_t>(a.num_pages)};
+    const uint64_t strides[3] = {32, static_cast<uint64_t>(a.page_size) * 32,
+                                 chunks * static_cast<uint64_t>(a.page_size) * 32};
+    const uint32_t box[4] = {16, kTile, kD / 16, 1};
+    rc = encode_f16_map(&mk, a.k_cache, 4, dims, strides, box, "paged_attention(key_cache)",
+                        CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc != B200OPS_OK) return rc;
+    rc = encode_f16_map(&mv, a.v_cache, 4, dims, strides, box, "paged_attention(value_cache)",
+                        CU_TENSOR_MAP_SWIZZLE_32B);
+    if (rc != B200OPS_OK) return rc;
+  } else {
+    const uint64_t dims[4] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(a.num_kv_heads),
+                              static_cast<uint64_t>(a.page_size), static_cast<uint64_t>(a.num_pages)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(kD) * 2,
+                                 static_cast<uint64_t>(a.num_kv_heads) * kD * 2,
+                                 static_cast<uint64_t>(a.page_size) * a.num_kv_heads * kD * 2};
+    const uint32_t box[4] = {64, 1, kTile, 1};
+    rc = encode_f16_map(&mk, a.k_cache, 4, dims, strides, box, "paged_attention(key_cache)");
+    if (rc != B200OPS_OK) return rc;
+    rc = encode_f16_map(&mv, a.v_cache, 4, dims, strides, box, "paged_attention(value_cache)");
+    if (rc != B200OPS_OK) return rc;
+  }
   const dim3 grid(a.max_chunks, a.num_kv_heads, a.bs);
   B200OPS_REQUIRE(grid.y <= 65535 && grid.z <= 65535,
                   "paged_attention: batch or head count too large for one launch");

@@ -1,5 +1,12 @@
 // Warp-level building blocks shared by the TMA-staged paged-attention kernels: one warp
-// consumes its 16-token slice of a 64-token K/V tile held in 128B-swizzled shared memory.
+// consumes its 16-token slice of a 64-token K/V tile held in swizzled shared memory.
+//
+// Two tile layouts, following the two cache layouts:
+//   NHD cache  a tensor's tile is two sub-tiles [64 tokens][64 channels] (128-byte rows,
+//              128-byte swizzle), one per half of head_dim;
+//   NZ cache   a tensor's tile is eight sub-tiles [64 tokens][16 channels] (32-byte rows,
+//              32-byte swizzle), one per 16-channel chunk of the head -- the cache's own
+//              [chunk][token][16] order, so one TMA box fetches the whole tile.
 #pragma once
 
 #include "paged_attention.cuh"
@@ -42,6 +49,17 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
   return static_cast<uint32_t>(r * 128 + ((c ^ (r & 7)) << 4));
 }
 
+constexpr int kNzSubTileBytes = kTile * 32;  // 64 tokens x 16 halfs
+
+// Byte offset inside a tensor's tile of the 8 channels starting at 8*c (c = 0..15) of token row
+// `r`.  NHD: sub-tile c/8, 128-byte swizzle.  NZ: sub-tile c/2 (a 16-channel chunk), and the
+// 32-byte swizzle flips the two 16-byte halves of a row in rows 4..7 of every eight.
+template <bool kNz>
+__device__ __forceinline__ uint32_t tile_offset(int r, int c) {
+  if (kNz) return static_cast<uint32_t>((c >> 1) * kNzSubTileBytes + r * 32 + (((c & 1) ^ ((r >> 2) & 1)) << 4));
+  return static_cast<uint32_t>((c >> 3) * kSubTileBytes) + swz(r, c & 7);
+}
+
 // Running softmax state of one warp: rows g (lo) and g+8 (hi) of the 16-row MMA operand.
 struct WarpState {
   float o[kD / 8][4];
@@ -66,7 +84,7 @@ struct WarpState {
 // sub-tiles); `tok0` the sequence position of the warp's first token; tokens >= `end` are
 // masked and their V rows zeroed first so that 0 * garbage cannot become NaN.
 // kUpper: the GQA group has more than 8 query heads, so MMA rows 8..15 carry data.
-template <bool kUpper>
+template <bool kUpper, bool kNz = false>
 __device__ __forceinline__ void consume_slice(WarpState& st, const uint32_t (&qa)[kD / 16][4],
                                               uint8_t* stage, int row0, int tok0, int end, int lane,
                                               float scale_log2) {
@@ -83,8 +101,9 @@ __device__ __forceinline__ void consume_slice(WarpState& st, const uint32_t (&qa
     uint8_t* vt = stage + kTensorTileBytes;
     for (int i = lane; i < 16 * 16; i += 32) {
       const int r = row0 + (i >> 4), c = i & 15;
-      if (tok0 + (i >> 4) >= end)
-        *reinterpret_cast<uint4*>(vt + (c >> 3) * kSubTileBytes + r * 128 + ((c & 7) << 4)) =
+      if (tok0 + (i >> 4) >= end)  // the whole row goes to zero, so the swizzle does not matter
+        *reinterpret_cast<uint4*>(vt + (kNz ? (c >> 1) * kNzSubTileBytes + r * 32 + ((c & 1) << 4)
+                                            : (c >> 3) * kSubTileBytes + r * 128 + ((c & 7) << 4))) =
             make_uint4(0, 0, 0, 0);
     }
     __syncwarp();
@@ -93,8 +112,7 @@ __device__ __forceinline__ void consume_slice(WarpState& st, const uint32_t (&qa
 #pragma unroll
   for (int ks = 0; ks < kD / 16; ++ks) {
     uint32_t kb[4];
-    const int chunk_in_sub = (ks & 3) * 2 + k_csel;
-    ldmatrix_x4(kb, kbase + (ks >> 2) * kSubTileBytes + swz(k_row, chunk_in_sub));
+    ldmatrix_x4(kb, kbase + tile_offset<kNz>(k_row, ks * 2 + k_csel));
     mma_16816(s[0], qa[ks], kb[0], kb[1]);
     mma_16816(s[1], qa[ks], kb[2], kb[3]);
   }
@@ -152,7 +170,7 @@ __device__ __forceinline__ void consume_slice(WarpState& st, const uint32_t (&qa
   for (int cc = 0; cc < kD / 8; cc += 2) {
     uint32_t vb[4];
     const int c = cc + v_csel;
-    ldmatrix_x4_trans(vb, vbase + (c >> 3) * kSubTileBytes + swz(v_row, c & 7));
+    ldmatrix_x4_trans(vb, vbase + tile_offset<kNz>(v_row, c));
     mma_16816(st.o[cc], pa_frag, vb[0], vb[1]);
     mma_16816(st.o[cc + 1], pa_frag, vb[2], vb[3]);
   }

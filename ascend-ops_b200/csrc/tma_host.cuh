@@ -28,10 +28,11 @@ inline EncodeTiledFn tensor_map_encoder() {
 }
 
 // Tiled map over an fp16 tensor of `rank` dimensions (innermost first).  `strides_bytes`
-// has rank-1 entries (the innermost dimension is dense).  128-byte swizzle, zero fill
-// outside the tensor.
+// has rank-1 entries (the innermost dimension is dense).  128-byte swizzle unless another mode
+// is given (the box's inner extent must then match it), zero fill outside the tensor.
 inline int encode_f16_map(CUtensorMap* map, const void* base, int rank, const uint64_t* dims,
-                          const uint64_t* strides_bytes, const uint32_t* box, const char* what) {
+                          const uint64_t* strides_bytes, const uint32_t* box, const char* what,
+                          CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   EncodeTiledFn enc = tensor_map_encoder();
   if (enc == nullptr) return fail(B200OPS_ECUDA, "%s: cuTensorMapEncodeTiled is unavailable", what);
   cuuint64_t gdim[5];
@@ -46,7 +47,7 @@ inline int encode_f16_map(CUtensorMap* map, const void* base, int rank, const ui
   }
   const CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, static_cast<cuuint32_t>(rank),
                          const_cast<void*>(base), gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                         swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return fail(B200OPS_ECUDA, "%s: cuTensorMapEncodeTiled failed with CUresult %d", what, (int)r);

@@ -220,14 +220,16 @@ def case_reshape_and_cache(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_N
                      launches=1)
 
 
-def case_paged_attention(ops, dev, steps, warmup, peaks):
-    a = wl.paged_attention_inputs()
+def case_paged_attention(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_NHD):
+    a = wl.paged_attention_inputs(layout=layout)
     nbytes = wl.paged_attention_bytes(a["context_lens"], 4, 128, 28, 128)
     q, kc, vc = a["q"].to(dev), a["key_cache"].to(dev), a["value_cache"].to(dev)
     bt, cl = a["block_tables"].to(dev), a["context_lens"].to(dev)
     us, _ = time_launches(lambda i: ops.paged_attention(q, kc, vc, bt, cl), 1, steps, warmup, dev)
-    rec = op_record("paged_attention", "B=64 28q/4kv D=128 L~U[512,8192] page 128", nbytes, us, peaks,
-                    "hbm", launches=1)
+    nz = layout == wl.KV_LAYOUT_NZ
+    rec = op_record("paged_attention_nz" if nz else "paged_attention",
+                    "B=64 28q/4kv D=128 L~U[512,8192] page 128" + (", cache [blocks, 32, 128, 16]" if nz else ""),
+                    nbytes, us, peaks, "hbm", launches=1)
     rec["sum_context"] = int(a["context_lens"].sum())
     return rec
 
@@ -696,6 +698,8 @@ def main():
         # a single DRAM round trip
         "reshape_and_cache_32768tok": lambda *a: case_reshape_and_cache(*a, tokens=32768),
         "rope": case_rope, "swiglu": case_swiglu, "paged_attention": case_paged_attention,
+        # the same batch on the reference's own cache layout
+        "paged_attention_nz": lambda *a: case_paged_attention(*a, layout=wl.KV_LAYOUT_NZ),
         "grouped_matmul_gate_up": lambda *a: case_grouped_matmul(*a, which="gate_up"),
         "grouped_matmul_down": lambda *a: case_grouped_matmul(*a, which="down"),
         "dense_projection_qkv": case_dense_projection,

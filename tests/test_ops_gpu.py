@@ -356,14 +356,18 @@ def test_paged_attention_benchmark_size_all_paths_agree(cabi, monkeypatch):
     close(chunked, want)
 
 
+@pytest.mark.parametrize("layout", [wl.KV_LAYOUT_NHD, wl.KV_LAYOUT_NZ])
 @pytest.mark.parametrize("stages", ["2", "4", "6"])
 @pytest.mark.parametrize("chunk", ["128", "2048"])
-def test_paged_attention_split_context_path_pipeline_depths(cabi, monkeypatch, stages, chunk):
+def test_paged_attention_split_context_path_pipeline_depths(cabi, monkeypatch, stages, chunk, layout):
+    """The TMA path on both cache layouts, every ring depth, short and long chunks, with NaN in
+    every cache token that no sequence owns."""
     monkeypatch.setenv("B200OPS_PA_MODE", "1")
     monkeypatch.setenv("B200OPS_PA_STAGES", stages)
     monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", chunk)
     lens = [1, 63, 64, 65, 127, 128, 129, 1000, 4097, 0, 2048]
-    w = wl.paged_attention_inputs(heads=32, kv_heads=4, context_lens=lens, blocks=80, seed=int(stages))
+    w = wl.paged_attention_inputs(heads=32, kv_heads=4, context_lens=lens, blocks=80, seed=int(stages),
+                                  layout=layout)
     w = poison_unused(w)
     want = oracle.paged_attention(w["q"], w["key_cache_clean"], w["value_cache_clean"],
                                   w["block_tables"], w["context_lens"])
@@ -567,3 +571,17 @@ def test_grouped_matmul_cluster_split_k_loose_row_bound(cabi, rows):
     got = run_grouped_matmul(cabi, x, w_storage, gl, fill=9.0, split_k=True)
     close(got[:rows], want[:rows])
     assert (got[rows:] == 9.0).all()
+
+
+def test_paged_attention_nz_layout_fast_and_general_paths_agree(cabi, monkeypatch):
+    """The reference's own cache layout [blocks, Hkv*D/16, P, 16] at a 16-sequence slice of the
+    benchmark batch with 16 query heads per kv head: TMA path, general path and the oracle."""
+    w = wl.paged_attention_inputs(bs=16, heads=32, kv_heads=2, blocks=16 * 64, layout=wl.KV_LAYOUT_NZ, seed=13)
+    monkeypatch.setenv("B200OPS_PA_MODE", "1")
+    fast = run_paged_attention(cabi, w)
+    monkeypatch.setenv("B200OPS_PA_MODE", "2")
+    general = run_paged_attention(cabi, w)
+    monkeypatch.delenv("B200OPS_PA_MODE")
+    close(fast, general)
+    close(fast, oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
+                                       w["context_lens"]))

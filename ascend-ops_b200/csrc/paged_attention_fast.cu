@@ -6,7 +6,7 @@
 // through the block table and streams 64-token K and V tiles into a ring of 128B-swizzled
 // shared-memory stages with TMA (cp.async.bulk.tensor.4d; NHD: the cache viewed as
 // [pages][P][Hkv][D], two 64-channel boxes per tile and tensor; NZ: the cache viewed as
-// [pages][Hkv*8][P][16], one box of 8 chunks x 64 tokens per tile and tensor).  Four consumer warps each own
+// [pages][Hkv*8][P/16][256], one box of 8 chunks x 64 tokens per tile and tensor).  Four consumer warps each own
 // 16 tokens of every tile: S = Q.K^T and O += P.V run on warp-level tensor-core MMAs
 // (m16n8k16, query heads padded to the 16-row operand, fp32 accumulation), the online
 // softmax is fp32 with exp2 and scale*log2(e) folded in.  Every K/V byte crosses HBM -> smem
@@ -111,9 +111,9 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
     const int off = tok % a.page_size;
     uint8_t* st = smem + stage * kStageBytes;
     ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
-    if (kNz) {  // {16 halfs, 64 tokens, the head's 8 chunks, 1 page}
-      ptx::tma_load_4d(st, &map_k, &full[stage], 0, off, kvh * (kD / 16), pg);
-      ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, off, kvh * (kD / 16), pg);
+    if (kNz) {  // {256 halfs = 16 tokens, 4 such rows, the head's 8 chunks, 1 page}
+      ptx::tma_load_4d(st, &map_k, &full[stage], 0, off / 16, kvh * (kD / 16), pg);
+      ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, off / 16, kvh * (kD / 16), pg);
     } else {    // {64 channels, 1 head, 64 tokens, 1 page}, twice
       ptx::tma_load_4d(st, &map_k, &full[stage], 0, kvh, off, pg);
       ptx::tma_load_4d(st + kSubTileBytes, &map_k, &full[stage], 64, kvh, off, pg);
@@ -288,17 +288,17 @@ int launch_fast(const Args& a, cudaStream_t st) {
   CUtensorMap mk, mv;
   int rc;
   if (a.layout == B200OPS_KV_LAYOUT_NZ) {
-    // [pages][Hkv*8 chunks][P tokens][16 halfs]: a tile is the head's 8 chunks x 64 tokens
+    // [pages][Hkv*8 chunks][P/16][16 tokens x 16 halfs]: a tile is the head's 8 chunks x 64 tokens
     const uint64_t chunks = static_cast<uint64_t>(a.num_kv_heads) * (kD / 16);
-    const uint64_t dims[4] = {16, static_cast<uint64_t>(a.page_size), chunks, static_cast<uint64_t>(a.num_pages)};
-    const uint64_t strides[3] = {32, static_cast<uint64_t>(a.page_size) * 32,
+    const uint64_t dims[4] = {256, static_cast<uint64_t>(a.page_size) / 16, chunks, static_cast<uint64_t>(a.num_pages)};
+    const uint64_t strides[3] = {512, static_cast<uint64_t>(a.page_size) * 32,
                                  chunks * static_cast<uint64_t>(a.page_size) * 32};
-    const uint32_t box[4] = {16, kTile, kD / 16, 1};
+    const uint32_t box[4] = {256, kTile / 16, kD / 16, 1};
     rc = encode_f16_map(&mk, a.k_cache, 4, dims, strides, box, "paged_attention(key_cache)",
-                        CU_TENSOR_MAP_SWIZZLE_32B);
+                        CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != B200OPS_OK) return rc;
     rc = encode_f16_map(&mv, a.v_cache, 4, dims, strides, box, "paged_attention(value_cache)",
-                        CU_TENSOR_MAP_SWIZZLE_32B);
+                        CU_TENSOR_MAP_SWIZZLE_NONE);
     if (rc != B200OPS_OK) return rc;
   } else {
     const uint64_t dims[4] = {static_cast<uint64_t>(kD), static_cast<uint64_t>(a.num_kv_heads),

@@ -4,9 +4,13 @@
 // Two tile layouts, following the two cache layouts:
 //   NHD cache  a tensor's tile is two sub-tiles [64 tokens][64 channels] (128-byte rows,
 //              128-byte swizzle), one per half of head_dim;
-//   NZ cache   a tensor's tile is eight sub-tiles [64 tokens][16 channels] (32-byte rows,
-//              32-byte swizzle), one per 16-channel chunk of the head -- the cache's own
-//              [chunk][token][16] order, so one TMA box fetches the whole tile.
+//   NZ cache   a tensor's tile is eight sub-tiles [64 tokens][16 channels] (32-byte rows, no
+//              swizzle), one per 16-channel chunk of the head -- the cache's own
+//              [chunk][token][16] order, so one TMA box fetches the whole tile.  The box is
+//              declared with 512-byte rows (16 tokens x 16 halfs are contiguous in the cache):
+//              with 32-byte rows the copy engine had 1024 row requests per tile to issue and
+//              the kernel ran 18 % slower.  Unswizzled 32-byte rows cost ldmatrix a two-way
+//              bank conflict, which this HBM-bound kernel does not notice.
 #pragma once
 
 #include "paged_attention.cuh"
@@ -52,11 +56,10 @@ __device__ __forceinline__ uint32_t swz(int r, int c) {
 constexpr int kNzSubTileBytes = kTile * 32;  // 64 tokens x 16 halfs
 
 // Byte offset inside a tensor's tile of the 8 channels starting at 8*c (c = 0..15) of token row
-// `r`.  NHD: sub-tile c/8, 128-byte swizzle.  NZ: sub-tile c/2 (a 16-channel chunk), and the
-// 32-byte swizzle flips the two 16-byte halves of a row in rows 4..7 of every eight.
+// `r`.  NHD: sub-tile c/8, 128-byte swizzle.  NZ: sub-tile c/2 (a 16-channel chunk), plain rows.
 template <bool kNz>
 __device__ __forceinline__ uint32_t tile_offset(int r, int c) {
-  if (kNz) return static_cast<uint32_t>((c >> 1) * kNzSubTileBytes + r * 32 + (((c & 1) ^ ((r >> 2) & 1)) << 4));
+  if (kNz) return static_cast<uint32_t>((c >> 1) * kNzSubTileBytes + r * 32 + ((c & 1) << 4));
   return static_cast<uint32_t>((c >> 3) * kSubTileBytes) + swz(r, c & 7);
 }
 

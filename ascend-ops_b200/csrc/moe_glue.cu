@@ -35,7 +35,11 @@ constexpr int kMaxTopK = 8;
 // every warp forms its expert's dot product with 128-bit loads and eight independent
 // accumulators, so even a handful of tokens keeps hundreds of loads in flight.  Warp 0 then
 // does the softmax and the top-k selection.
-__global__ void __launch_bounds__(1024)
+// kBatch 16-byte loads of x and of w are in flight per lane: with 16, a hidden size of 4096 is
+// one batch, i.e. one memory round trip per expert, but that needs 128 registers for the loads
+// alone, so it is the variant for up to 8 experts (a CTA of at most 256 threads).
+template <int kBatch, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
 route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, int32_t* __restrict__ ids,
                   float* __restrict__ weights, int hidden, int num_experts, int top_k) {
   __shared__ float logits[kMaxExperts];
@@ -45,8 +49,9 @@ route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, i
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(token) * hidden);
   for (int e = warp; e < num_experts; e += warps) {
     const uint4* w = reinterpret_cast<const uint4*>(wr + static_cast<size_t>(e) * hidden);
-    constexpr int kBatch = 8;  // 16-byte loads of x and of w in flight per lane
-    float acc[kBatch] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float acc[kBatch];
+#pragma unroll
+    for (int u = 0; u < kBatch; ++u) acc[u] = 0.f;
     for (int v0 = lane; v0 < vecs; v0 += 32 * kBatch) {
       uint4 a[kBatch], b[kBatch];
 #pragma unroll
@@ -73,7 +78,10 @@ route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, i
         }
       }
     }
-    const float dot = warp_sum(((acc[0] + acc[1]) + (acc[2] + acc[3])) + ((acc[4] + acc[5]) + (acc[6] + acc[7])));
+    float part = 0.f;
+#pragma unroll
+    for (int u = 0; u < kBatch; u += 4) part += (acc[u] + acc[u + 1]) + (acc[u + 2] + acc[u + 3]);
+    const float dot = warp_sum(part);
     if (lane == 0) logits[e] = __half2float(__float2half_rn(dot));
   }
   __syncthreads();
@@ -296,7 +304,8 @@ extern "C" int b200ops_moe_route_topk(const void* x, const void* router_weight, 
   B200OPS_REQUIRE(x && router_weight && expert_ids && expert_weights, "moe_route_topk: null pointer");
   B200OPS_REQUIRE(aligned16(x) && aligned16(router_weight), "moe_route_topk: pointers must be 16-byte aligned");
   const int warps = static_cast<int>(num_experts < 32 ? num_experts : 32);
-  moe::route_topk_kernel<<<static_cast<unsigned>(num_tokens), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  auto kern = warps <= 8 ? moe::route_topk_kernel<16, 256> : moe::route_topk_kernel<8, 1024>;
+  kern<<<static_cast<unsigned>(num_tokens), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __half*>(x), static_cast<const __half*>(router_weight), expert_ids, expert_weights,
       static_cast<int>(hidden), static_cast<int>(num_experts), static_cast<int>(top_k));
   B200OPS_LAUNCH_CHECK("moe_route_topk");

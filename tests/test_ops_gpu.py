@@ -585,3 +585,17 @@ def test_paged_attention_nz_layout_fast_and_general_paths_agree(cabi, monkeypatc
     close(fast, general)
     close(fast, oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
                                        w["context_lens"]))
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 128, 128), (257, 256, 256), (32, 4096, 6144), (3000, 512, 768)])
+def test_dense_matmul_api(ops, m, k, n):
+    """The dense NT product of the reference's earlier interface (benchmark/test_matmul.py: seed 0,
+    x [m, k] and w [n, k] ~ N(0, 1), atol = rtol = 1e-3 there against an fp16 torch product; here
+    against the fp32-accumulated product, with the operator tolerance)."""
+    g = torch.Generator().manual_seed(0)
+    x = torch.randn(m, k, generator=g).half()
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).half()
+    y = ops.matmul(x.to(DEV), w.to(DEV)).cpu()
+    close(y, (x.float() @ w.float().T).half())
+    with pytest.raises(RuntimeError):
+        ops.matmul(x.to(DEV), w.to(DEV)[:, : k // 2])

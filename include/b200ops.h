@@ -162,10 +162,14 @@ int b200ops_paged_attention_static(const void* q, const void* key_cache, const v
  *   group_list : int64 [num_experts], inclusive cumulative row ends;  y : f16 [num_tokens, n]
  * Requires k % 64 == 0 and n % 64 == 0 (csrc/ffi/ops.cpp:173).  Rows past gl[E-1] are not
  * written.  Empty groups are skipped (grouped_mat_mul_ex.cpp:40).
- * Workspace: optional.  Shapes with fewer output tiles than SMs (decode batches) run split-K
- * when a workspace of b200ops_grouped_matmul_workspace_size() bytes is passed (the query
- * returns 0 for shapes that cannot benefit); the call zeroes the counters it needs itself.
- * With workspace == NULL the same result is computed without split-K.
+ * Workspace: optional.  Grouped shapes with fewer output tiles than SMs and a long k (expert
+ * projections of a decode batch) run split-K when a workspace of
+ * b200ops_grouped_matmul_workspace_size() bytes is passed (the query returns 0 for shapes that
+ * cannot benefit); the call zeroes the counters it needs itself.  With workspace == NULL the
+ * same result is computed without split-K.  A single group of at most 256 rows (a dense
+ * projection) splits k over thread-block clusters instead and needs no workspace either way.
+ * The kernel is chosen from the shape alone; every choice sums fp16 products in fp32 and
+ * rounds once, so results agree within the last fp16 bit.
  */
 size_t b200ops_grouped_matmul_workspace_size(int64_t num_tokens, int64_t k, int64_t num_experts,
                                              int64_t n);

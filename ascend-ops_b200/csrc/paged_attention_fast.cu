@@ -59,6 +59,10 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
   int* page_ids = reinterpret_cast<int*>(empty + kStages);
   int* abort_flag = page_ids + kMaxPagesPerChunk;
 
+  // Dispatch order: the chunks of one (sequence, kv head) first, then the kv heads, then the
+  // sequences.  (kv head fastest and chunk slowest -- neighbouring bytes side by side, the
+  // longest sequences' last chunks at the end -- was measured and is 3 % slower on the
+  // 64-sequence batch, equal elsewhere: every merge then falls into the kernel's tail.)
   const int chunk = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int group = a.num_heads / a.num_kv_heads;

@@ -232,8 +232,10 @@ Plan make_plan(int64_t bs, int64_t num_kv_heads, int64_t page_size, int64_t max_
     const long v = std::atol(s);
     if (v > 0) chunk = v;
   }
-  // Round up to whole pages so that a chunk never starts inside a page.
+  // Round up to whole pages so that a chunk never starts inside a page (and, for pages shorter
+  // than the 64-token tile of the TMA path, to whole tiles).
   chunk = (chunk + page_size - 1) / page_size * page_size;
+  if (page_size < 64 && 64 % page_size == 0) chunk = (chunk + 63) / 64 * 64;
   const int64_t cap = max_pages_per_seq * page_size;
   if (chunk > cap && cap > 0) chunk = cap;
   Plan p;

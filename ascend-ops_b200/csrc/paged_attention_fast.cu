@@ -1,6 +1,6 @@
-// Paged-attention decode, fast path for sm_100a: head_dim 128, page size a multiple of 64,
-// GQA group <= 16; caches [pages, P, Hkv, 128] (NHD) or [pages, Hkv*8, P, 16] (NZ, the
-// reference's layout).
+// Paged-attention decode, fast path for sm_100a: head_dim 128, GQA group <= 16; caches
+// [pages, P, Hkv, 128] (NHD; P a multiple of 64, or 16 or 32) or [pages, Hkv*8, P, 16] (NZ, the
+// reference's layout; P a multiple of 64).
 //
 // One CTA = one (sequence, kv head, context chunk).  A producer warp walks the chunk's pages
 // through the block table and streams 64-token K and V tiles into a ring of 128B-swizzled
@@ -32,7 +32,7 @@ namespace {
 using namespace tile;
 
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMaxPagesPerChunk = 64;
+constexpr int kMaxPagesPerChunk = 128;  // 2048-token chunks of 16-token pages
 constexpr int kErrProducerWait = 11;
 constexpr int kErrConsumerWait = 12;
 
@@ -48,7 +48,7 @@ __device__ int g_pa_status = 0;
 
 // kUpper: the GQA group has more than 8 query heads, so MMA rows 8..15 carry data.
 template <int kStages, bool kUpper, bool kNz>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, 2)
 paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, Args a) {
   extern __shared__ uint8_t smem_raw[];
@@ -77,8 +77,8 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
     const int pages_per_chunk = a.chunk_tokens / a.page_size;
     const int first_page = chunk * pages_per_chunk;
     const int32_t* table = a.block_tables + static_cast<size_t>(b) * a.max_pages_per_seq;
-    for (int i = lane; i < pages_per_chunk && first_page + i < a.max_pages_per_seq; i += 32) {
-      int pg = table[first_page + i];
+    for (int i = lane; i < pages_per_chunk; i += 32) {
+      int pg = first_page + i < a.max_pages_per_seq ? table[first_page + i] : 0;
       pg = pg < 0 ? 0 : (pg >= a.num_pages ? a.num_pages - 1 : pg);
       page_ids[i] = pg;
     }
@@ -118,11 +118,20 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
     if (kNz) {  // {256 halfs = 16 tokens, 4 such rows, the head's 8 chunks, 1 page}
       ptx::tma_load_4d(st, &map_k, &full[stage], 0, off / 16, kvh * (kD / 16), pg);
       ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, off / 16, kvh * (kD / 16), pg);
-    } else {    // {64 channels, 1 head, 64 tokens, 1 page}, twice
+    } else if (a.page_size >= kTile) {  // {64 channels, 1 head, 64 tokens, 1 page}, twice
       ptx::tma_load_4d(st, &map_k, &full[stage], 0, kvh, off, pg);
       ptx::tma_load_4d(st + kSubTileBytes, &map_k, &full[stage], 64, kvh, off, pg);
       ptx::tma_load_4d(st + kTensorTileBytes, &map_v, &full[stage], 0, kvh, off, pg);
       ptx::tma_load_4d(st + kTensorTileBytes + kSubTileBytes, &map_v, &full[stage], 64, kvh, off, pg);
+    } else {  // pages of 16 or 32 tokens: the tile is 4 or 2 pages, one set of boxes per page
+      for (int j = 0; j < kTile / a.page_size; ++j) {
+        const int pj = page_ids[tok / a.page_size + j];
+        uint8_t* dst = st + j * a.page_size * 128;  // whole 8-row swizzle groups: the pattern is kept
+        ptx::tma_load_4d(dst, &map_k, &full[stage], 0, kvh, 0, pj);
+        ptx::tma_load_4d(dst + kSubTileBytes, &map_k, &full[stage], 64, kvh, 0, pj);
+        ptx::tma_load_4d(dst + kTensorTileBytes, &map_v, &full[stage], 0, kvh, 0, pj);
+        ptx::tma_load_4d(dst + kTensorTileBytes + kSubTileBytes, &map_v, &full[stage], 64, kvh, 0, pj);
+      }
     }
   };
   const int prefill = min(kStages, n_tiles);
@@ -283,7 +292,10 @@ bool fast_path_supported(const Args& a) {
   // 3 = persistent tile-balanced kernel (paged_attention_stream.cu).
   if (env_int("B200OPS_PA_MODE", 0) == 2) return false;
   const int group = a.num_heads / a.num_kv_heads;
-  return a.head_dim == kD && a.page_size % kTile == 0 &&
+  const bool page_ok = a.page_size % kTile == 0 ||
+                       (a.layout == B200OPS_KV_LAYOUT_NHD && (a.page_size == 16 || a.page_size == 32) &&
+                        a.chunk_tokens % kTile == 0);
+  return a.head_dim == kD && page_ok &&
          group <= 16 && a.chunk_tokens % a.page_size == 0 &&
          a.chunk_tokens / a.page_size <= kMaxPagesPerChunk && a.page_size <= 256 * kTile;
 }
@@ -310,7 +322,7 @@ int launch_fast(const Args& a, cudaStream_t st) {
     const uint64_t strides[3] = {static_cast<uint64_t>(kD) * 2,
                                  static_cast<uint64_t>(a.num_kv_heads) * kD * 2,
                                  static_cast<uint64_t>(a.page_size) * a.num_kv_heads * kD * 2};
-    const uint32_t box[4] = {64, 1, kTile, 1};
+    const uint32_t box[4] = {64, 1, static_cast<uint32_t>(a.page_size < kTile ? a.page_size : kTile), 1};
     rc = encode_f16_map(&mk, a.k_cache, 4, dims, strides, box, "paged_attention(key_cache)");
     if (rc != B200OPS_OK) return rc;
     rc = encode_f16_map(&mv, a.v_cache, 4, dims, strides, box, "paged_attention(value_cache)");

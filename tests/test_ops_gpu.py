@@ -599,3 +599,26 @@ def test_dense_matmul_api(ops, m, k, n):
     close(y, (x.float() @ w.float().T).half())
     with pytest.raises(RuntimeError):
         ops.matmul(x.to(DEV), w.to(DEV)[:, : k // 2])
+
+
+@pytest.mark.parametrize("page", [16, 32])
+@pytest.mark.parametrize("chunk", ["", "64", "1000"])
+def test_paged_attention_small_pages_take_the_tma_path(cabi, monkeypatch, page, chunk):
+    """Pages shorter than the 64-token tile (the common 16 and 32): a tile is assembled from 4 or 2
+    pages.  NaN in every cache token no sequence owns; TMA path against the general path and the
+    oracle; chunk lengths that are and are not multiples of the tile."""
+    if chunk:
+        monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", chunk)
+    lens = [1, 15, 16, 17, 63, 64, 65, 100, 1000, 4097, 0, 2500, page * 3]
+    blocks = sum((l + page - 1) // page for l in lens) + 5
+    w = wl.paged_attention_inputs(heads=28, kv_heads=4, block_size=page, context_lens=lens, blocks=blocks,
+                                  seed=page + len(chunk))
+    w = poison_unused(w)
+    want = oracle.paged_attention(w["q"], w["key_cache_clean"], w["value_cache_clean"],
+                                  w["block_tables"], w["context_lens"])
+    monkeypatch.setenv("B200OPS_PA_MODE", "1")
+    fast = run_paged_attention(cabi, w)
+    monkeypatch.setenv("B200OPS_PA_MODE", "2")
+    general = run_paged_attention(cabi, w)
+    close(fast, want)
+    close(general, want)

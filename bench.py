@@ -31,7 +31,7 @@ import decode_workloads as wl  # noqa: E402
 # DRAM traffic of the attention kernel relative to its algorithmic bytes, from the ncu capture
 # summarised in profiles/paged_attention_fast_kernel__16seq_gqa7.md (dram read + write over
 # algorithmic bytes on a 16-sequence case; traffic grows in proportion to the context tokens).
-ATTENTION_TRAFFIC_RATIO = 1.06
+ATTENTION_TRAFFIC_RATIO = 1.05
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 L2_BYTES = 126 * 1024 * 1024

@@ -75,10 +75,11 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attention_general_kernel(Ar
         a.out[(static_cast<size_t>(b) * a.num_heads + h0) * D + i] = __float2half(0.f);
     return;
   }
-  const int start = chunk * a.chunk_tokens;
+  const int ct = seq_chunk_tokens(a.chunk_tokens, a.max_chunks, a.chunk_align, L);
+  const int start = chunk * ct;
   if (start >= L) return;
-  const int end = min(L, start + a.chunk_tokens);
-  const int n_chunks = (L + a.chunk_tokens - 1) / a.chunk_tokens;
+  const int end = min(L, start + ct);
+  const int n_chunks = (L + ct - 1) / ct;
 
   float qf[kHeadTile][DPL];
 #pragma unroll
@@ -197,7 +198,8 @@ __global__ void __launch_bounds__(kCombineWarps * 32) paged_attention_combine_ke
   const int cap = a.max_pages_per_seq * a.page_size;
   if (L > cap) L = cap;
   if (L <= 0) return;
-  const int n_chunks = (L + a.chunk_tokens - 1) / a.chunk_tokens;
+  const int ct = seq_chunk_tokens(a.chunk_tokens, a.max_chunks, a.chunk_align, L);
+  const int n_chunks = (L + ct - 1) / ct;
   if (n_chunks <= 1) return;
   combine_head(a, b, item - b * a.num_heads, n_chunks, lane);
 }
@@ -232,15 +234,25 @@ Plan make_plan(int64_t bs, int64_t num_kv_heads, int64_t page_size, int64_t max_
     const long v = std::atol(s);
     if (v > 0) chunk = v;
   }
-  // Round up to whole pages so that a chunk never starts inside a page (and, for pages shorter
-  // than the 64-token tile of the TMA path, to whole tiles).
-  chunk = (chunk + page_size - 1) / page_size * page_size;
-  if (page_size < 64 && 64 % page_size == 0) chunk = (chunk + 63) / 64 * 64;
-  const int64_t cap = max_pages_per_seq * page_size;
+  // Chunk lengths are whole pages, so that a chunk never starts inside a page, and (for the TMA
+  // path) whole 64-token tiles.
+  int64_t align = page_size;
+  while (align % 64 != 0 && align < 64 * page_size) align += page_size;
+  chunk = (chunk + align - 1) / align * align;
+  const int64_t cap = (max_pages_per_seq * page_size + align - 1) / align * align;
   if (chunk > cap && cap > 0) chunk = cap;
+  // Chunks per sequence: what the capacity asks for, but no more than keeps about eight CTAs
+  // per resident slot busy (and at least 8) -- see the note on block-table capacity in the header
+  // -- and no fewer than keeps the longest possible chunk within kMaxChunkPages pages.
+  int64_t max_chunks = cap > 0 ? (cap + chunk - 1) / chunk : 1;
+  int64_t limit = (2368 + pairs - 1) / (pairs > 0 ? pairs : 1);
+  if (limit < 8) limit = 8;
+  if (max_chunks > limit) max_chunks = limit;
+  while (((cap + max_chunks - 1) / max_chunks + align - 1) / align * align > kMaxChunkPages * page_size) ++max_chunks;
   Plan p;
   p.chunk_tokens = static_cast<int>(chunk);
-  p.max_chunks = static_cast<int>(cap > 0 ? (cap + chunk - 1) / chunk : 1);
+  p.max_chunks = static_cast<int>(max_chunks);
+  p.chunk_align = static_cast<int>(align);
   return p;
 }
 
@@ -352,6 +364,7 @@ extern "C" int b200ops_paged_attention(const void* q, const void* key_cache,
   a.layout = layout;
   a.chunk_tokens = plan.chunk_tokens;
   a.max_chunks = plan.max_chunks;
+  a.chunk_align = plan.chunk_align;
   a.scale_log2 = (1.0f / std::sqrt(static_cast<float>(head_dim))) * 1.44269504088896340736f;
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);

@@ -10,11 +10,17 @@ namespace pa {
 // How one launch cuts the work.  A sequence's context is cut into chunks of
 // `chunk_tokens`; one CTA handles one (sequence, kv head, chunk).  Chunk c of sequence b
 // exists iff c*chunk_tokens < context_len[b]; CTAs of absent chunks exit at once.
+// The block table's width is only a capacity (a host that replays CUDA graphs pads it to the
+// longest context the model allows), so the chunk count per sequence is capped at
+// `max_chunks` whatever the capacity: a sequence that would need more takes proportionally
+// longer chunks (seq_chunk_tokens).  Absent-chunk CTAs cost about 0.7 us of an SM slot each; a
+// grid sized for a 131072-token capacity made a 104 us call take 142 us.
 // When a sequence has a single chunk its CTA writes the final fp16 output directly;
 // otherwise every chunk writes a partial record and the combine kernel merges them.
 struct Plan {
-  int chunk_tokens;  // multiple of page_size (or of the tile size), > 0
-  int max_chunks;    // ceil(max_pages_per_seq * page_size / chunk_tokens)
+  int chunk_tokens;  // base chunk length: multiple of chunk_align, > 0
+  int max_chunks;    // chunks per sequence never exceed this (= grid extent, record stride)
+  int chunk_align;   // chunk lengths are multiples of this: of the page size and of the 64-token tile
 };
 
 // Partial record of one (sequence, query head, chunk), fp32:
@@ -36,9 +42,21 @@ struct Args {
   int bs, num_heads, num_kv_heads, head_dim;
   int num_pages, page_size, max_pages_per_seq;
   int layout;
-  int chunk_tokens, max_chunks;
+  int chunk_tokens, max_chunks, chunk_align;
   float scale_log2;  // 1/sqrt(head_dim) * log2(e)
 };
+
+// Block-table entries of one chunk that the TMA kernel keeps in shared memory; the plan makes
+// no chunk longer than this many pages.
+constexpr int kMaxChunkPages = 1024;
+
+// Chunk length of a sequence of L tokens: the base length, or the shortest multiple of
+// chunk_align that covers L in max_chunks chunks.
+__host__ __device__ inline int seq_chunk_tokens(int chunk_tokens, int max_chunks, int chunk_align, int L) {
+  if (static_cast<long long>(chunk_tokens) * max_chunks >= L) return chunk_tokens;
+  const int need = (L + max_chunks - 1) / max_chunks;
+  return (need + chunk_align - 1) / chunk_align * chunk_align;
+}
 
 #ifdef __CUDACC__
 // Merge the n_chunks partial records of (sequence b, query head h) and write the fp16 row.

@@ -32,7 +32,6 @@ namespace {
 using namespace tile;
 
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMaxPagesPerChunk = 128;  // 2048-token chunks of 16-token pages
 constexpr int kErrProducerWait = 11;
 constexpr int kErrConsumerWait = 12;
 
@@ -41,7 +40,7 @@ struct Smem {
   static constexpr size_t kTiles = static_cast<size_t>(kStages) * kStageBytes;
   static constexpr size_t kMerge = static_cast<size_t>(kConsumerWarps) * 16 * (kD + 2) * 4;
   static constexpr size_t kData = kTiles > kMerge ? kTiles : kMerge;
-  static constexpr size_t kBytes = 1024 + kData + 2 * kStages * 8 + kMaxPagesPerChunk * 4 + 16;
+  static constexpr size_t kBytes = 1024 + kData + 2 * kStages * 8 + kMaxChunkPages * 4 + 16;
 };
 
 __device__ int g_pa_status = 0;
@@ -57,7 +56,7 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + Smem<kStages>::kData);
   uint64_t* empty = full + kStages;
   int* page_ids = reinterpret_cast<int*>(empty + kStages);
-  int* abort_flag = page_ids + kMaxPagesPerChunk;
+  int* abort_flag = page_ids + kMaxChunkPages;
 
   // Dispatch order: the chunks of one (sequence, kv head) first, then the kv heads, then the
   // sequences.  (kv head fastest and chunk slowest -- neighbouring bytes side by side, the
@@ -71,17 +70,20 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
   // The producer warp starts the chunk's block-table reads before the sequence length is
   // known (entries past the sequence's end are clamped to valid pages and never used), and its
   // first lane sets up the barriers: three dependent global round trips (length, table, data)
-  // become two, and the first tiles are on their way before the CTA-wide barrier.
-  const int start = chunk * a.chunk_tokens;
-  if (warp == kConsumerWarps) {
-    const int pages_per_chunk = a.chunk_tokens / a.page_size;
+  // become two, and the first tiles are on their way before the CTA-wide barrier.  The reads
+  // assume the base chunk length; a sequence long enough to take longer chunks reads again.
+  const int32_t* table = a.block_tables + static_cast<size_t>(b) * a.max_pages_per_seq;
+  auto load_page_ids = [&](int chunk_tokens) {
+    const int pages_per_chunk = chunk_tokens / a.page_size;
     const int first_page = chunk * pages_per_chunk;
-    const int32_t* table = a.block_tables + static_cast<size_t>(b) * a.max_pages_per_seq;
     for (int i = lane; i < pages_per_chunk; i += 32) {
       int pg = first_page + i < a.max_pages_per_seq ? table[first_page + i] : 0;
       pg = pg < 0 ? 0 : (pg >= a.num_pages ? a.num_pages - 1 : pg);
       page_ids[i] = pg;
     }
+  };
+  if (warp == kConsumerWarps) {
+    load_page_ids(a.chunk_tokens);
     if (lane == 0) {
       for (int s = 0; s < kStages; ++s) {
         ptx::mbar_init(&full[s], 1);
@@ -103,10 +105,16 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
         a.out[(static_cast<size_t>(b) * a.num_heads + h0) * kD + i] = __float2half(0.f);
     return;
   }
+  const int ct = seq_chunk_tokens(a.chunk_tokens, a.max_chunks, a.chunk_align, L);
+  const int start = chunk * ct;
   if (start >= L) return;
-  const int end = min(L, start + a.chunk_tokens);
+  const int end = min(L, start + ct);
   const int n_tiles = (end - start + kTile - 1) / kTile;
-  const int n_chunks = (L + a.chunk_tokens - 1) / a.chunk_tokens;
+  const int n_chunks = (L + ct - 1) / ct;
+  if (ct != a.chunk_tokens && warp == kConsumerWarps) {
+    __syncwarp();
+    load_page_ids(ct);
+  }
 
   // One tile = K and V of 64 tokens of this kv head: four boxes of 64 channels.
   auto issue_tile = [&](int t, int stage) {
@@ -297,7 +305,7 @@ bool fast_path_supported(const Args& a) {
                         a.chunk_tokens % kTile == 0);
   return a.head_dim == kD && page_ok &&
          group <= 16 && a.chunk_tokens % a.page_size == 0 &&
-         a.chunk_tokens / a.page_size <= kMaxPagesPerChunk && a.page_size <= 256 * kTile;
+         a.chunk_tokens / a.page_size <= kMaxChunkPages && a.page_size <= 256 * kTile;
 }
 
 int launch_fast(const Args& a, cudaStream_t st) {

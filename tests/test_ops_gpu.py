@@ -622,3 +622,26 @@ def test_paged_attention_small_pages_take_the_tma_path(cabi, monkeypatch, page, 
     general = run_paged_attention(cabi, w)
     close(fast, want)
     close(general, want)
+
+
+@pytest.mark.parametrize("layout", [wl.KV_LAYOUT_NHD, wl.KV_LAYOUT_NZ])
+def test_paged_attention_wide_block_table_and_long_sequences(cabi, monkeypatch, layout):
+    """A block table padded far beyond the contexts (as a graph-replaying host passes it) and
+    sequences long enough that the chunk count per sequence is capped, so that they take longer
+    chunks than the short ones in the same batch.  TMA path, general path and oracle."""
+    monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", "128")  # small base chunk: the cap engages early
+    lens = [40000, 1, 129, 5000, 0, 128 * 8 * 7 + 3, 20011]
+    page = 128
+    blocks = sum((l + page - 1) // page for l in lens) + 4
+    w = wl.paged_attention_inputs(heads=16, kv_heads=2, block_size=page, context_lens=lens, blocks=blocks,
+                                  layout=layout, seed=41)
+    wide = torch.zeros(len(lens), 2048, dtype=torch.int32)  # capacity 262144 tokens
+    wide[:, : w["block_tables"].shape[1]] = w["block_tables"]
+    want = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"], w["context_lens"])
+    w = dict(w, block_tables=wide)
+    monkeypatch.setenv("B200OPS_PA_MODE", "1")
+    fast = run_paged_attention(cabi, w)
+    monkeypatch.setenv("B200OPS_PA_MODE", "2")
+    general = run_paged_attention(cabi, w)
+    close(fast, want)
+    close(general, want)

@@ -60,6 +60,11 @@ SIGNATURES = {
                                       c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p]),
     "b200ops_peer_barrier": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "b200ops_pipeline_status": (c_int, [ctypes.POINTER(c_int)]),
+    "b200ops_reload_options": (None, []),
+    "b200ops_matmul": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_void_p]),
+    "b200ops_moe_dispatch": (c_int, [c_void_p] * 7 + [c_int64] * 2 + [c_void_p] * 7 + [c_int64] * 8 + [c_void_p]),
+    "b200ops_moe_gather": (c_int, [c_void_p] * 9 + [c_int64] * 5 + [c_void_p]),
+    "b200ops_moe_combine": (c_int, [c_void_p] * 7 + [c_int64] * 5 + [c_void_p]),
 }
 
 _lib = None
@@ -177,6 +182,25 @@ def grouped_matmul_swiglu(x, w_storage, group_list, y, stream=None):
     e, n, k = w_storage.shape
     check(load().b200ops_grouped_matmul_swiglu(_ptr(x), _ptr(w_storage), _ptr(group_list), _ptr(y),
                                                x.shape[0], k, e, n, _stream(stream)))
+
+
+def matmul(x, w, y, stream=None):
+    """y [m, n] = x [m, k] . w [n, k]^T (any m, n, k)."""
+    check(load().b200ops_matmul(_ptr(x), _ptr(w), _ptr(y), x.shape[0], w.shape[0], x.shape[1], _stream(stream)))
+
+
+def reload_options() -> None:
+    """Make the library read its B200OPS_* tuning variables from the environment again."""
+    load().b200ops_reload_options()
+
+
+def set_option(name: str, value) -> None:
+    """Set (or with value None, unset) a B200OPS_* tuning variable for this process."""
+    if value is None:
+        os.environ.pop(name, None)
+    else:
+        os.environ[name] = str(value)
+    reload_options()
 
 
 def pipeline_status() -> int:

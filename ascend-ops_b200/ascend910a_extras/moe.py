@@ -18,3 +18,6 @@ push_rows = _C.moe.push_rows
 peer_barrier = _C.moe.peer_barrier
 grouped_matmul_scatter = _C.moe.grouped_matmul_scatter
 grouped_matmul_swiglu = _C.moe.grouped_matmul_swiglu
+dispatch = _C.moe.dispatch
+gather = _C.moe.gather
+combine = _C.moe.combine

@@ -26,6 +26,8 @@ add_rms_norm_kernel(const __half* __restrict__ x, const __half* __restrict__ res
                     __half* __restrict__ residual_out, int64_t num_tokens, int dim,
                     int warps_per_row, float eps, float inv_dim) {
   __shared__ float partial[32];
+  pdl_trigger();
+  pdl_wait();
 
   const int threads_per_row = warps_per_row * 32;
   const int rows_per_cta = blockDim.x / threads_per_row;
@@ -122,6 +124,8 @@ add_rms_norm_long_row_kernel(const __half* __restrict__ x, const __half* __restr
                              float inv_dim) {
   __shared__ float partial[32];
   __shared__ float total;
+  pdl_trigger();
+  pdl_wait();
   const int64_t row = blockIdx.x;
   const int vecs = dim >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + row * dim);
@@ -176,11 +180,6 @@ add_rms_norm_long_row_kernel(const __half* __restrict__ x, const __half* __restr
   }
 }
 
-int env_int(const char* name, int fallback) {
-  const char* s = std::getenv(name);
-  return (s && *s) ? std::atoi(s) : fallback;
-}
-
 }  // namespace
 }  // namespace b200ops
 
@@ -210,38 +209,38 @@ extern "C" int b200ops_add_rms_norm(const void* x, const void* residual, const v
   const float inv_dim = 1.0f / static_cast<float>(d);
 
   if (vecs > 1024 * kMaxVecPerThread) {
-    add_rms_norm_long_row_kernel<<<static_cast<unsigned>(num_tokens), 1024, 0, st>>>(
-        xp, rp, wp, yp, sp, d, eps, inv_dim);
-    B200OPS_LAUNCH_CHECK("add_rms_norm");
+    B200OPS_CUDA(launch_kernel(add_rms_norm_long_row_kernel, dim3(static_cast<unsigned>(num_tokens)), dim3(1024), 0, st,
+                        xp, rp, wp, yp, sp, d, eps, inv_dim));
     return B200OPS_OK;
   }
 
   // Two vectors per thread and tensor keep 64 B per thread in flight; rows shorter than a
   // warp's worth share a CTA so that small hidden sizes still fill the SMs.
-  int vpt = env_int("B200OPS_RMSNORM_VPT", 2);
+  int vpt = knob(kKnobRmsnormVpt, 2);
   if (vpt != 1 && vpt != 2 && vpt != 4 && vpt != 8) vpt = 2;
   int warps_per_row = (vecs + 32 * vpt - 1) / (32 * vpt);
   while (warps_per_row > 32) {
     vpt *= 2;
     warps_per_row = (vecs + 32 * vpt - 1) / (32 * vpt);
   }
-  const int cta_warps_target = env_int("B200OPS_RMSNORM_CTA_WARPS", 8);
+  const int cta_warps_target = knob(kKnobRmsnormCtaWarps, 8);
   int rows_per_cta = cta_warps_target / warps_per_row;
   if (rows_per_cta < 1) rows_per_cta = 1;
   const int threads = rows_per_cta * warps_per_row * 32;
   const int64_t grid = (num_tokens + rows_per_cta - 1) / rows_per_cta;
   B200OPS_REQUIRE(grid <= 0x7fffffffLL, "add_rms_norm: too many rows");
 
-#define LAUNCH(V)                                                                          \
-  add_rms_norm_kernel<V><<<static_cast<unsigned>(grid), threads, 0, st>>>(                 \
-      xp, rp, wp, yp, sp, num_tokens, d, warps_per_row, eps, inv_dim)
+#define LAUNCH(V)                                                                             \
+  launch_kernel(add_rms_norm_kernel<V>, dim3(static_cast<unsigned>(grid)), dim3(threads), 0, st, xp, \
+         rp, wp, yp, sp, num_tokens, d, warps_per_row, eps, inv_dim)
+  cudaError_t err;
   switch (vpt) {
-    case 1: LAUNCH(1); break;
-    case 2: LAUNCH(2); break;
-    case 4: LAUNCH(4); break;
-    default: LAUNCH(8); break;
+    case 1: err = LAUNCH(1); break;
+    case 2: err = LAUNCH(2); break;
+    case 4: err = LAUNCH(4); break;
+    default: err = LAUNCH(8); break;
   }
 #undef LAUNCH
-  B200OPS_LAUNCH_CHECK("add_rms_norm");
+  B200OPS_CUDA(err);
   return B200OPS_OK;
 }

@@ -7,6 +7,7 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <utility>
 
 #include "b200ops.h"
 
@@ -60,8 +61,77 @@ struct PeerTable {
 // Number of SMs of the current device (cached per device).
 int sm_count();
 
+// Tuning knobs.  Each is an environment variable read ONCE per process, at its first use (a
+// launch never calls getenv again); b200ops_reload_options() forgets what was read so that the
+// next use looks at the environment again.  `knob` returns `fallback` for an unset variable.
+enum Knob {
+  kKnobGmmPair,         // B200OPS_GMM_PAIR: 0 never use CTA pairs, 2 always, otherwise by shape
+  kKnobGmmKsplit,       // B200OPS_GMM_KSPLIT: 0 disables the cluster split-K kernel
+  kKnobGmmSwap,         // B200OPS_GMM_SWAP: 0 disables the weights-as-M decode kernel
+  kKnobPaMode,          // B200OPS_PA_MODE: 2 forces the general attention kernel
+  kKnobPaStages,        // B200OPS_PA_STAGES: ring depth of the TMA attention kernel (2, 3, 4, 6)
+  kKnobPaChunkTokens,   // B200OPS_PA_CHUNK_TOKENS: base chunk length of the split context
+  kKnobRmsnormVpt,      // B200OPS_RMSNORM_VPT: 16-byte vectors per thread
+  kKnobRmsnormCtaWarps, // B200OPS_RMSNORM_CTA_WARPS: warps per CTA
+  kKnobRacWarps,        // B200OPS_RAC_WARPS: warps per CTA of the reshape_and_cache row kernel
+  kKnobRacSplit,        // B200OPS_RAC_SPLIT: 1 = a token's K row and V row go to separate warps
+  kKnobPdl,             // B200OPS_PDL: 0 = plain stream-ordered launches (no programmatic dependent launch)
+  kKnobCount
+};
+int knob(Knob k, int fallback);
+
+// ---- kernel launch ---------------------------------------------------------------------
+// Every kernel of the library is launched through launch_kernel() / launch_cluster(), which ask for
+// programmatic dependent launch: the kernel may become resident while its predecessor on the
+// stream is still draining, so that its launch latency and its set-up (barrier initialisation,
+// TMEM allocation, descriptor prefetch) overlap the predecessor's tail.  The contract that makes
+// this safe: every kernel executes pdl_wait() before its first access to global memory that an
+// earlier kernel may have written or may still read -- in practice before its first global
+// access of any kind except L2 prefetches -- and pdl_trigger() as early as it likes.  Launched
+// without the attribute (B200OPS_PDL=0, or a predecessor that is not a kernel) both are no-ops
+// and the launch is an ordinary stream-ordered one.  Works under stream capture: the edges
+// become programmatic dependencies of the CUDA graph.
+#ifdef __CUDACC__
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_cluster(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                  unsigned cluster_x, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  unsigned n = 0;
+  if (knob(kKnobPdl, 1) != 0) {
+    attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n].val.programmaticStreamSerializationAllowed = 1;
+    ++n;
+  }
+  if (cluster_x > 1) {
+    attr[n].id = cudaLaunchAttributeClusterDimension;
+    attr[n].val.clusterDim.x = cluster_x;
+    attr[n].val.clusterDim.y = 1;
+    attr[n].val.clusterDim.z = 1;
+    ++n;
+  }
+  cfg.attrs = attr;
+  cfg.numAttrs = n;
+  return cudaLaunchKernelEx(&cfg, kern, std::forward<Args>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                          Args&&... args) {
+  return launch_cluster(kern, grid, block, smem, st, 1u, std::forward<Args>(args)...);
+}
+#endif
+
 // ---- device helpers --------------------------------------------------------------------
 #ifdef __CUDACC__
+
+// See launch_kernel() above.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll

@@ -1,9 +1,31 @@
 // Library-wide pieces of the C ABI: version, per-thread error text, device report.
 #include "common.cuh"
 
+#include <atomic>
+#include <cstdlib>
 #include <cstring>
 
 namespace b200ops {
+
+namespace {
+const char* const kKnobNames[kKnobCount] = {
+    "B200OPS_GMM_PAIR",      "B200OPS_GMM_KSPLIT",      "B200OPS_GMM_SWAP",    "B200OPS_PA_MODE",
+    "B200OPS_PA_STAGES",     "B200OPS_PA_CHUNK_TOKENS", "B200OPS_RMSNORM_VPT", "B200OPS_RMSNORM_CTA_WARPS",
+    "B200OPS_RAC_WARPS",     "B200OPS_RAC_SPLIT",       "B200OPS_PDL"};
+std::atomic<int> g_knob_state[kKnobCount];  // 0 not read yet, 1 unset, 2 set
+std::atomic<int> g_knob_value[kKnobCount];
+}  // namespace
+
+int knob(Knob k, int fallback) {
+  int st = g_knob_state[k].load(std::memory_order_acquire);
+  if (st == 0) {  // two threads may both get here; they store the same thing
+    const char* s = std::getenv(kKnobNames[k]);
+    st = (s && *s) ? 2 : 1;
+    g_knob_value[k].store(st == 2 ? std::atoi(s) : 0, std::memory_order_relaxed);
+    g_knob_state[k].store(st, std::memory_order_release);
+  }
+  return st == 2 ? g_knob_value[k].load(std::memory_order_relaxed) : fallback;
+}
 
 char* last_error_buffer() {
   static thread_local char buf[kLastErrorLen] = {0};
@@ -11,21 +33,25 @@ char* last_error_buffer() {
 }
 
 int sm_count() {
-  static int cached[64] = {0};
+  static std::atomic<int> cached[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
-  if (cached[dev] == 0) {
-    int n = 0;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n == 0) {
     if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
       n = 148;
-    cached[dev] = n;
+    cached[dev].store(n, std::memory_order_relaxed);
   }
-  return cached[dev];
+  return n;
 }
 
 }  // namespace b200ops
 
-extern "C" int b200ops_version(void) { return 100; }
+extern "C" int b200ops_version(void) { return 200; }
+
+extern "C" void b200ops_reload_options(void) {
+  for (int k = 0; k < b200ops::kKnobCount; ++k) b200ops::g_knob_state[k].store(0, std::memory_order_release);
+}
 
 extern "C" const char* b200ops_last_error(void) { return b200ops::last_error_buffer(); }
 
@@ -61,7 +87,7 @@ extern "C" int b200ops_print_info(int device_id, char* buf, size_t buf_len) {
 
 namespace b200ops {
 namespace gmm { int status_take(); }
-namespace pa { int fast_path_status_take(); int stream_status_take(); }
+namespace pa { int fast_path_status_take(); }
 }  // namespace b200ops
 
 // Codes 1-9 come from grouped_matmul's pipeline, 11-19 from paged_attention's TMA path.
@@ -71,8 +97,7 @@ extern "C" int b200ops_pipeline_status(int* status) {
   B200OPS_CUDA(cudaDeviceSynchronize());
   const int g = gmm::status_take();
   const int p = pa::fast_path_status_take();
-  const int s = pa::stream_status_take();
-  if (g < 0 || p < 0 || s < 0) return fail(B200OPS_ECUDA, "pipeline_status: could not read the status words");
-  *status = g != 0 ? g : (p != 0 ? p : s);
+  if (g < 0 || p < 0) return fail(B200OPS_ECUDA, "pipeline_status: could not read the status words");
+  *status = g != 0 ? g : p;
   return B200OPS_OK;
 }

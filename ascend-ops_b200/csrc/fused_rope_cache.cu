@@ -56,6 +56,8 @@ __device__ __forceinline__ size_t cache_vec(const FusedParams& p, int64_t slot, 
 __global__ void __launch_bounds__(kThreads) fused_qkv_rope_cache_kernel(FusedParams p) {
   // No early return: with the norm switched on, the lanes of a head reduce with shuffles, so
   // every lane of the warp stays (threads past the end work on the last item and store nothing).
+  pdl_trigger();
+  pdl_wait();
   const uint32_t raw_item = blockIdx.x * kThreads + threadIdx.x;
   const bool valid = raw_item < p.total_items;
   const uint32_t item = valid ? raw_item : p.total_items - 1;
@@ -227,7 +229,6 @@ extern "C" int b200ops_fused_qkv_norm_rope_cache(const void* qkv, const void* q_
   p.chunks = static_cast<uint32_t>(chunks);
   p.layout = layout;
   const unsigned grid = static_cast<unsigned>((total + kThreads - 1) / kThreads);
-  fused_qkv_rope_cache_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(p);
-  B200OPS_LAUNCH_CHECK("fused_qkv_rope_cache");
+  B200OPS_CUDA(launch_kernel(fused_qkv_rope_cache_kernel, dim3(grid), dim3(kThreads), 0, static_cast<cudaStream_t>(stream), p));
   return B200OPS_OK;
 }

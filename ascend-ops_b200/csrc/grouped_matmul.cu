@@ -40,7 +40,7 @@
 // time share the same w tile (read from HBM once, then from L2) while the group's x rows
 // stay L2-resident.  Work is 2*M*K*N flops; at the sizes of interest the kernel is bound by
 // the tensor pipe, at decode sizes (few rows per expert) by streaming w from HBM.
-#include <cstdlib>
+#include <atomic>
 
 #include "common.cuh"
 #include "sm100_ptx.cuh"
@@ -110,10 +110,7 @@ inline bool use_narrow_tiles(int64_t num_tokens, int64_t k, int64_t n, int sms) 
 // takes 45 us), hence also an absolute floor on it.
 // B200OPS_GMM_PAIR: 0 = never, 2 = always (tests), otherwise this rule.
 constexpr int64_t kMinRowsForPairs = 2048;
-inline int pair_mode() {
-  const char* s = std::getenv("B200OPS_GMM_PAIR");
-  return (s && *s) ? std::atoi(s) : 1;
-}
+inline int pair_mode() { return knob(kKnobGmmPair, 1); }
 
 inline bool use_cta_pairs(int64_t num_tokens, int64_t num_experts, int64_t n, int sms) {
   const int mode = pair_mode();
@@ -138,8 +135,7 @@ constexpr int kMaxClusterSplitHost = 8;
 
 inline int cluster_split_factor(int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n, int sms,
                                 int64_t* resident_tiles) {
-  const char* env = std::getenv("B200OPS_GMM_KSPLIT");
-  if (env && *env && std::atoi(env) == 0) return 0;
+  if (knob(kKnobGmmKsplit, 1) == 0) return 0;
   if (num_experts != 1) return 0;
   const int64_t n_tiles = (n + kWideBN - 1) / kWideBN;
   int64_t tiles;
@@ -213,7 +209,7 @@ struct TileCoord {
 struct RowScatter {
   const int32_t* index;
   PeerTable peers;
-  int cap, my_rank;
+  int cap, my_rank, world;
 };
 
 __device__ __forceinline__ __half* output_row(const RowScatter& sc, __half* y, int row, int N, bool& ok) {
@@ -224,6 +220,10 @@ __device__ __forceinline__ __half* output_row(const RowScatter& sc, __half* y, i
     return y;
   }
   const int peer = idx / sc.cap, off = idx - peer * sc.cap;
+  if (peer >= sc.world) {  // an index outside the exchange's geometry names no buffer
+    ok = false;
+    return y;
+  }
   return static_cast<__half*>(sc.peers.base[peer]) + (static_cast<size_t>(sc.my_rank) * sc.cap + off) * N;
 }
 
@@ -318,6 +318,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
   const int n_tiles = (n_out + kOutBN - 1) / kOutBN;
   const int k_blocks = K / BK;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(&ctl->full[s], 1);
@@ -336,10 +337,11 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
     ptx::tmem_alloc(&ctl->tmem_base, kTmemCols);
     ptx::tmem_relinquish_alloc_permit();
   }
+  pdl_wait();  // set-up done; from here on the kernel reads its inputs
   // Group table: clamp the cumulative ends into [0, M] and count m-tiles per group.
   for (int e = threadIdx.x; e < E; e += kThreads) {
-    long long s = e ? group_list[e - 1] : 0;
-    long long t = group_list[e];
+    long long s = (e && group_list) ? group_list[e - 1] : 0;
+    long long t = group_list ? group_list[e] : M;  // no group list: one group of all M rows
     s = s < 0 ? 0 : (s > M ? M : s);
     t = t < s ? s : (t > M ? M : t);
     ctl->row_start[e] = static_cast<int>(s);
@@ -609,6 +611,7 @@ extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_
   none.index = nullptr;
   none.cap = 1;
   none.my_rank = 0;
+  none.world = 0;
   for (int r = 0; r < b200ops::kMaxPeers; ++r) none.peers.base[r] = nullptr;
   B200OPS_REQUIRE(num_tokens <= 0 || y != nullptr, "grouped_matmul: null pointer");
   return b200ops::gmm::launch(x, w, group_list, y, num_tokens, k, num_experts, n, workspace, workspace_size,
@@ -622,6 +625,7 @@ extern "C" int b200ops_grouped_matmul_swiglu(const void* x, const void* w, const
   none.index = nullptr;
   none.cap = 1;
   none.my_rank = 0;
+  none.world = 0;
   for (int r = 0; r < b200ops::kMaxPeers; ++r) none.peers.base[r] = nullptr;
   B200OPS_REQUIRE(num_tokens <= 0 || y != nullptr, "grouped_matmul_swiglu: null pointer");
   return b200ops::gmm::launch(x, w, group_list, y, num_tokens, k, num_experts, two_d, nullptr, 0, none, true,
@@ -643,6 +647,7 @@ extern "C" int b200ops_grouped_matmul_scatter(const void* x, const void* w, cons
   sc.index = row_index;
   sc.cap = static_cast<int>(cap);
   sc.my_rank = static_cast<int>(my_rank);
+  sc.world = static_cast<int>(world);
   for (int r = 0; r < kMaxPeers; ++r) {
     sc.peers.base[r] = r < world ? peer_out[r] : nullptr;
     B200OPS_REQUIRE(r >= world || (sc.peers.base[r] != nullptr && aligned16(sc.peers.base[r])),
@@ -654,10 +659,88 @@ extern "C" int b200ops_grouped_matmul_scatter(const void* x, const void* w, cons
 
 namespace b200ops {
 namespace gmm {
+// y = x . w^T for shapes the tensor-core kernels do not take (k or n not a multiple of 64, or
+// pointers that are not 16-byte aligned): 64 x 64 output tiles, 16 x 16 threads with a 4 x 4
+// block each, operands staged through shared memory as fp32, element-wise bounds checks.  Same
+// arithmetic contract: fp16 products summed in fp32, one rounding.
+constexpr int kGenTile = 64, kGenK = 16;
+
+__global__ void __launch_bounds__(256) matmul_nt_general_kernel(const __half* __restrict__ x,
+                                                                const __half* __restrict__ w,
+                                                                __half* __restrict__ y, int m, int n, int k) {
+  __shared__ float xs[kGenK][kGenTile + 1];
+  __shared__ float ws[kGenK][kGenTile + 1];
+  pdl_trigger();
+  pdl_wait();
+  const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+  const int row0 = blockIdx.y * kGenTile, col0 = blockIdx.x * kGenTile;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < k; k0 += kGenK) {
+    for (int i = threadIdx.x; i < kGenTile * kGenK; i += 256) {
+      const int r = i / kGenK, c = i - r * kGenK;
+      const bool kin = k0 + c < k;
+      xs[c][r] = (kin && row0 + r < m) ? __half2float(x[static_cast<size_t>(row0 + r) * k + k0 + c]) : 0.f;
+      ws[c][r] = (kin && col0 + r < n) ? __half2float(w[static_cast<size_t>(col0 + r) * k + k0 + c]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int c = 0; c < kGenK; ++c) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        a[i] = xs[c][ty * 4 + i];
+        b[i] = ws[c][tx * 4 + i];
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int r = row0 + ty * 4 + i, c = col0 + tx * 4 + j;
+      if (r < m && c < n) y[static_cast<size_t>(r) * n + c] = __float2half_rn(acc[i][j]);
+    }
+}
+}  // namespace gmm
+}  // namespace b200ops
+
+extern "C" int b200ops_matmul(const void* x, const void* w, void* y, int64_t m, int64_t n, int64_t k,
+                              void* stream) {
+  using namespace b200ops;
+  B200OPS_REQUIRE(m >= 0 && n > 0 && k > 0 && m < (1LL << 30) && n < (1LL << 30) && k < (1LL << 30),
+                  "matmul: bad shape m=%lld n=%lld k=%lld", (long long)m, (long long)n, (long long)k);
+  if (m == 0) return B200OPS_OK;
+  B200OPS_REQUIRE(x && w && y, "matmul: null pointer");
+  if (k % 64 == 0 && n % 64 == 0 && aligned16(x) && aligned16(w) && aligned16(y)) {
+    gmm::RowScatter none;
+    none.index = nullptr;
+    none.cap = 1;
+    none.my_rank = 0;
+    none.world = 0;
+    for (int r = 0; r < kMaxPeers; ++r) none.peers.base[r] = nullptr;
+    return gmm::launch(x, w, nullptr, y, m, k, 1, n, nullptr, 0, none, false, stream);
+  }
+  const dim3 grid(static_cast<unsigned>((n + gmm::kGenTile - 1) / gmm::kGenTile),
+                  static_cast<unsigned>((m + gmm::kGenTile - 1) / gmm::kGenTile));
+  B200OPS_REQUIRE(grid.y <= 65535, "matmul: too many rows for the general kernel (%lld)", (long long)m);
+  B200OPS_CUDA(launch_kernel(gmm::matmul_nt_general_kernel, grid, dim3(256), 0, static_cast<cudaStream_t>(stream),
+                      static_cast<const __half*>(x), static_cast<const __half*>(w), static_cast<__half*>(y),
+                      static_cast<int>(m), static_cast<int>(n), static_cast<int>(k)));
+  return B200OPS_OK;
+}
+
+namespace b200ops {
+namespace gmm {
 // Clusters of two CTAs that the device can keep resident at once (cached per device).
 static int resident_pairs(int dev, int sms) {
-  static int cached[64] = {0};
-  if (dev >= 0 && dev < 64 && cached[dev] > 0) return cached[dev];
+  static std::atomic<int> cached[64];
+  if (dev >= 0 && dev < 64 && cached[dev].load(std::memory_order_relaxed) > 0)
+    return cached[dev].load(std::memory_order_relaxed);
   cudaLaunchConfig_t cfg = {};
   cudaLaunchAttribute attr[1];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -675,14 +758,15 @@ static int resident_pairs(int dev, int sms) {
     n = sms / 2;
   }
   if (n > sms / 2) n = sms / 2;
-  if (dev >= 0 && dev < 64) cached[dev] = n;
+  if (dev >= 0 && dev < 64) cached[dev].store(n, std::memory_order_relaxed);
   return n;
 }
 
 // Clusters of `splits` CTAs of the split-K kernel that the device keeps resident at once.
 static int resident_split_clusters(int dev, int splits) {
-  static int cached[64][kMaxClusterSplitHost + 1] = {{0}};
-  if (dev >= 0 && dev < 64 && cached[dev][splits] != 0) return cached[dev][splits];
+  static std::atomic<int> cached[64][kMaxClusterSplitHost + 1];
+  if (dev >= 0 && dev < 64 && cached[dev][splits].load(std::memory_order_relaxed) != 0)
+    return cached[dev][splits].load(std::memory_order_relaxed);
   // The query counts against the function's shared-memory limit, so raise that first.
   if (cudaFuncSetAttribute(grouped_matmul_ksplit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            static_cast<int>(kSplitSmemBytes)) != cudaSuccess) {
@@ -706,7 +790,7 @@ static int resident_split_clusters(int dev, int splits) {
     n = 0;
   }
   if (n <= 0) n = -1;  // cached as "none fit"
-  if (dev >= 0 && dev < 64) cached[dev][splits] = n;
+  if (dev >= 0 && dev < 64) cached[dev][splits].store(n, std::memory_order_relaxed);
   return n;
 }
 
@@ -732,32 +816,20 @@ static int launch_ksplit(const CUtensorMap& map_x, const void* w, const int64_t*
     const int rc = encode_f16_map(&map_w, w, 3, dims, strides, box, "grouped_matmul(w)");
     if (rc != B200OPS_OK) return rc;
   }
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];
   int dev = 0;
   B200OPS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     B200OPS_CUDA(cudaFuncSetAttribute(grouped_matmul_ksplit_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(kSplitSmemBytes)));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
   static_assert(kMaxClusterSplitHost == kMaxClusterSplit, "host and device agree on the cluster limit");
   const int64_t tiles = ((num_tokens + BM - 1) / BM) * ((n + kSplitBN - 1) / kSplitBN);
-  cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = static_cast<unsigned>(splits);
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.gridDim = dim3(static_cast<unsigned>(tiles * splits));
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = kSplitSmemBytes;
-  cfg.stream = st;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  B200OPS_CUDA(cudaLaunchKernelEx(&cfg, grouped_matmul_ksplit_kernel, map_x, map_w, group_list,
-                                  static_cast<__half*>(y), static_cast<int>(num_tokens), static_cast<int>(n),
-                                  static_cast<int>(k), static_cast<int>(num_experts), scatter));
-  B200OPS_LAUNCH_CHECK("grouped_matmul");
+  B200OPS_CUDA(launch_cluster(grouped_matmul_ksplit_kernel, dim3(static_cast<unsigned>(tiles * splits)),
+                              dim3(kThreads), kSplitSmemBytes, st, static_cast<unsigned>(splits), map_x, map_w,
+                              group_list, static_cast<__half*>(y), static_cast<int>(num_tokens),
+                              static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts), scatter));
   return B200OPS_OK;
 }
 
@@ -774,34 +846,21 @@ static int launch_pairs(const CUtensorMap& map_x, const void* w, const int64_t* 
     if (rc != B200OPS_OK) return rc;
   }
   auto kern = glu ? grouped_matmul_pair_kernel<true> : grouped_matmul_pair_kernel<false>;
-  static bool attr_set[2][64] = {{false}};
+  static std::atomic<bool> attr_set[2][64];
   int dev = 0;
   B200OPS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[glu][dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[glu][dev].load(std::memory_order_acquire)) {
     B200OPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(kPairSmemBytes)));
-    attr_set[glu][dev] = true;
+    attr_set[glu][dev].store(true, std::memory_order_release);
   }
   const int64_t n_tiles = (n + kPairBN - 1) / kPairBN;  // the same count with and without SwiGLU
   const int64_t max_items = (((num_tokens + BM - 1) / BM + 1) / 2 + num_experts) * n_tiles;
   const int64_t resident = resident_pairs(dev, launch_sms());
   const int pairs = static_cast<int>(max_items < resident ? max_items : resident);
-  cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.gridDim = dim3(static_cast<unsigned>(2 * pairs));
-  cfg.blockDim = dim3(kThreads);
-  cfg.dynamicSmemBytes = kPairSmemBytes;
-  cfg.stream = st;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  B200OPS_CUDA(cudaLaunchKernelEx(&cfg, kern, map_x, map_w, group_list,
-                                  static_cast<__half*>(y), static_cast<int>(num_tokens), static_cast<int>(n),
-                                  static_cast<int>(k), static_cast<int>(num_experts), scatter));
-  B200OPS_LAUNCH_CHECK("grouped_matmul");
+  B200OPS_CUDA(launch_cluster(kern, dim3(static_cast<unsigned>(2 * pairs)), dim3(kThreads), kPairSmemBytes, st, 2u,
+                              map_x, map_w, group_list, static_cast<__half*>(y), static_cast<int>(num_tokens),
+                              static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts), scatter));
   return B200OPS_OK;
 }
 }  // namespace gmm
@@ -824,7 +883,7 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   B200OPS_REQUIRE(!glu || n % 128 == 0,
                   "grouped_matmul_swiglu: w must have 2*d rows with d a multiple of 64, got %lld", (long long)n);
   if (num_tokens == 0) return B200OPS_OK;
-  B200OPS_REQUIRE(x && w && group_list && y, "grouped_matmul: null pointer");
+  B200OPS_REQUIRE(x && w && y && (group_list || num_experts == 1), "grouped_matmul: null pointer");
   B200OPS_REQUIRE(aligned16(x) && aligned16(w) && aligned16(y),
                   "grouped_matmul: pointers must be 16-byte aligned");
 
@@ -863,13 +922,13 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
                        : gmm::grouped_matmul_kernel<gmm::WideCfg>;
   const size_t smem = narrow ? gmm::NarrowCfg::kSmemBytes : gmm::WideCfg::kSmemBytes;
   const int variant = glu ? 2 : (narrow ? 1 : 0);
-  static bool attr_set[3][64] = {{false}};
+  static std::atomic<bool> attr_set[3][64];
   int dev = 0;
   B200OPS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[variant][dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[variant][dev].load(std::memory_order_acquire)) {
     B200OPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(smem)));
-    attr_set[variant][dev] = true;
+    attr_set[variant][dev].store(true, std::memory_order_release);
   }
   const int64_t n_tiles = (n + bn - 1) / bn;  // glu: n / 2 columns in tiles of bn / 2, the same count
   const int64_t max_tiles = ((num_tokens + gmm::BM - 1) / gmm::BM + num_experts) * n_tiles;
@@ -886,11 +945,9 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
     B200OPS_CUDA(cudaMemsetAsync(counters, 0, gmm::kCounterBytes, st));
     grid = sms;  // idle CTAs exit; the split factor needs the full grid
   }
-  kern<<<grid, gmm::kThreads, smem, st>>>(map_x, map_w, group_list, static_cast<__half*>(y),
-                                          static_cast<int>(num_tokens), static_cast<int>(n),
-                                          static_cast<int>(k), static_cast<int>(num_experts), counters,
-                                          partials, scatter);
-  B200OPS_LAUNCH_CHECK("grouped_matmul");
+  B200OPS_CUDA(launch_kernel(kern, dim3(grid), dim3(gmm::kThreads), smem, st, map_x, map_w, group_list,
+                      static_cast<__half*>(y), static_cast<int>(num_tokens), static_cast<int>(n),
+                      static_cast<int>(k), static_cast<int>(num_experts), counters, partials, scatter));
   return B200OPS_OK;
 }
 

@@ -122,6 +122,8 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   // present (an expert-parallel receive buffer), and idle clusters must cost next to nothing.
   const int m_tiles = (M + BM - 1) / BM;
   const int m_tile = tile / n_tiles;
+  pdl_trigger();
+  pdl_wait();  // the row count and the first loads below are inputs
   TileCoord tc;
   tc.group = 0;
   tc.n0 = (tile - m_tile * n_tiles) * kSplitBN;
@@ -130,7 +132,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   // splits <= k_blocks gives every rank at least one k-block; the host never asks otherwise.
   bool active = splits <= k_blocks && tile < m_tiles * n_tiles;
   if (m_tile > 0) {
-    long long rows = group_list[0];
+    long long rows = group_list ? group_list[0] : M;
     active = active && tc.row0 < (rows > M ? M : rows);
   }
   const int prefill = active ? min(kSplitStages, kb1 - kb0) : 0;
@@ -162,7 +164,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   const uint32_t tmem_base = active ? ctl->tmem_base : 0u;
   volatile int* abort_flag = &ctl->abort_flag;
   {
-    long long rows = group_list[0];
+    long long rows = group_list ? group_list[0] : M;
     rows = rows < 0 ? 0 : (rows > M ? M : rows);
     tc.row_end = static_cast<int>(rows);
   }

@@ -67,6 +67,7 @@ grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
   const int n_tiles = (n_out + kOutBN - 1) / kOutBN;
   const int k_blocks = K / BK;
 
+  pdl_trigger();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kPairStages; ++s) {
       ptx::mbar_init(&ctl->full[s], 1);   // used in the even CTA: its producer's expect_tx
@@ -85,9 +86,10 @@ grouped_matmul_pair_kernel(const __grid_constant__ CUtensorMap map_x,
     ptx::tmem_alloc_pair(&ctl->tmem_base, kPairTmemCols);
     ptx::tmem_relinquish_alloc_permit_pair();
   }
+  pdl_wait();  // set-up done; from here on the kernel reads its inputs
   for (int e = threadIdx.x; e < E; e += kThreads) {
-    long long s = e ? group_list[e - 1] : 0;
-    long long t = group_list[e];
+    long long s = (e && group_list) ? group_list[e - 1] : 0;
+    long long t = group_list ? group_list[e] : M;
     s = s < 0 ? 0 : (s > M ? M : s);
     t = t < s ? s : (t > M ? M : t);
     ctl->row_start[e] = static_cast<int>(s);

@@ -31,20 +31,19 @@ namespace {
 constexpr int kMaxExperts = 256;
 constexpr int kMaxTopK = 8;
 
-// One CTA per token, one warp per expert (warps loop when there are more experts than warps):
-// every warp forms its expert's dot product with 128-bit loads and eight independent
-// accumulators, so even a handful of tokens keeps hundreds of loads in flight.  Warp 0 then
-// does the softmax and the top-k selection.
+// Routing of one token by one CTA, one warp per expert (warps loop when there are more experts
+// than warps): every warp forms its expert's dot product with 128-bit loads and kBatch
+// independent accumulators, so even a handful of tokens keeps hundreds of loads in flight.
 // kBatch 16-byte loads of x and of w are in flight per lane: with 16, a hidden size of 4096 is
 // one batch, i.e. one memory round trip per expert, but that needs 128 registers for the loads
 // alone, so it is the variant for up to 8 experts (a CTA of at most 256 threads).
-template <int kBatch, int kMaxThreads>
-__global__ void __launch_bounds__(kMaxThreads)
-route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, int32_t* __restrict__ ids,
-                  float* __restrict__ weights, int hidden, int num_experts, int top_k) {
-  __shared__ float logits[kMaxExperts];
+// Leaves logits[e] (rounded to fp16 like a GEMM output, clamped to the finite fp16 range so that
+// an overflowing dot product or a NaN input cannot turn every probability into NaN) in shared
+// memory; the caller synchronises the CTA before route_select.
+template <int kBatch>
+__device__ __forceinline__ void route_logits(const __half* __restrict__ x, const __half* __restrict__ wr,
+                                             float* logits, int token, int hidden, int num_experts) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-  const int token = blockIdx.x;
   const int vecs = hidden >> 3;
   const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<size_t>(token) * hidden);
   for (int e = warp; e < num_experts; e += warps) {
@@ -82,11 +81,19 @@ route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, i
 #pragma unroll
     for (int u = 0; u < kBatch; u += 4) part += (acc[u] + acc[u + 1]) + (acc[u + 2] + acc[u + 3]);
     const float dot = warp_sum(part);
-    if (lane == 0) logits[e] = __half2float(__float2half_rn(dot));
+    if (lane == 0) {
+      float v = fminf(fmaxf(dot, -65504.f), 65504.f);  // fmaxf / fminf drop a NaN operand
+      if (!(dot == dot)) v = -65504.f;
+      logits[e] = __half2float(__float2half_rn(v));
+    }
   }
-  __syncthreads();
-  if (warp != 0) return;
-  // softmax over experts in fp32
+}
+
+// One warp: softmax over the experts in fp32, then top-k by repeated arg-max (ties go to the
+// lower expert index).  Lane 0 stores the choices.
+__device__ __forceinline__ void route_select(float* logits, int32_t* __restrict__ ids, float* __restrict__ weights,
+                                             int num_experts, int top_k) {
+  const int lane = threadIdx.x & 31;
   float mx = -INFINITY;
   for (int e = lane; e < num_experts; e += 32) mx = fmaxf(mx, logits[e]);
   mx = warp_max(mx);
@@ -97,7 +104,6 @@ route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, i
   __syncwarp();
   for (int e = lane; e < num_experts; e += 32) logits[e] = expf(logits[e] - mx) * inv;
   __syncwarp();
-  // top-k by repeated arg-max; ties go to the lower expert index
   for (int k = 0; k < top_k; ++k) {
     float best = -1.f;
     int best_e = 0x7fffffff;
@@ -117,13 +123,32 @@ route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, i
         best_e = oe;
       }
     }
+    if (best_e >= num_experts) {  // nothing compared greater than -1 (cannot happen with finite logits)
+      best_e = k;
+      best = 0.f;
+    }
     if (lane == 0) {
-      ids[static_cast<size_t>(token) * top_k + k] = best_e;
-      weights[static_cast<size_t>(token) * top_k + k] = best;
+      ids[k] = best_e;
+      weights[k] = best;
       logits[best_e] = -2.f;  // remove from the next round
     }
     __syncwarp();
   }
+}
+
+template <int kBatch, int kMaxThreads>
+__global__ void __launch_bounds__(kMaxThreads)
+route_topk_kernel(const __half* __restrict__ x, const __half* __restrict__ wr, int32_t* __restrict__ ids,
+                  float* __restrict__ weights, int hidden, int num_experts, int top_k) {
+  __shared__ float logits[kMaxExperts];
+  pdl_trigger();
+  pdl_wait();
+  const int token = blockIdx.x;
+  route_logits<kBatch>(x, wr, logits, token, hidden, num_experts);
+  __syncthreads();
+  if (threadIdx.x >= 32) return;
+  route_select(logits, ids + static_cast<size_t>(token) * top_k, weights + static_cast<size_t>(token) * top_k,
+               num_experts, top_k);
 }
 
 // Single CTA.  Warps own contiguous slices of the flat slot array; a slot's rank inside its
@@ -137,6 +162,8 @@ permute_kernel(const int32_t* __restrict__ ids, int32_t* __restrict__ pos, int32
                int64_t* __restrict__ group_list, int32_t* __restrict__ overflow, int num_slots,
                int num_experts, int experts_per_rank, int segment_rows) {
   extern __shared__ int hist[];  // [kPermuteWarps][num_experts], then base[num_experts], limit[num_experts]
+  pdl_trigger();
+  pdl_wait();
   int* base = hist + kPermuteWarps * num_experts;
   int* limit = base + num_experts;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -211,6 +238,8 @@ ep_plan_kernel(const int32_t* __restrict__ all_counts, int32_t* __restrict__ map
                int num_experts, int first_expert, int local_experts, int segment_rows) {
   __shared__ int dst_base[64 * 64];  // [local expert][source rank] start in grouped order
   __shared__ int src_base[64 * 64];  // same block's start inside the received buffer
+  pdl_trigger();
+  pdl_wait();
   if (threadIdx.x == 0) {
     int d = 0;
     for (int j = 0; j < local_experts; ++j) {
@@ -245,6 +274,8 @@ __global__ void __launch_bounds__(128)
 copy_rows_kernel(__half* __restrict__ dst, const __half* __restrict__ src,
                  const int32_t* __restrict__ dst_index, const int32_t* __restrict__ src_index,
                  int src_div, const int32_t* __restrict__ n_valid, int row_vecs) {
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   if (n_valid != nullptr && i >= *n_valid) return;
   int si = src_index ? src_index[i] : i;
@@ -259,6 +290,8 @@ copy_rows_kernel(__half* __restrict__ dst, const __half* __restrict__ src,
 __global__ void __launch_bounds__(128)
 finalize_kernel(const __half* __restrict__ rows, const int32_t* __restrict__ pos,
                 const float* __restrict__ weights, __half* __restrict__ y, int top_k, int row_vecs) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   for (int v = threadIdx.x; v < row_vecs; v += blockDim.x) {
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -305,10 +338,10 @@ extern "C" int b200ops_moe_route_topk(const void* x, const void* router_weight, 
   B200OPS_REQUIRE(aligned16(x) && aligned16(router_weight), "moe_route_topk: pointers must be 16-byte aligned");
   const int warps = static_cast<int>(num_experts < 32 ? num_experts : 32);
   auto kern = warps <= 8 ? moe::route_topk_kernel<16, 256> : moe::route_topk_kernel<8, 1024>;
-  kern<<<static_cast<unsigned>(num_tokens), warps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(x), static_cast<const __half*>(router_weight), expert_ids, expert_weights,
-      static_cast<int>(hidden), static_cast<int>(num_experts), static_cast<int>(top_k));
-  B200OPS_LAUNCH_CHECK("moe_route_topk");
+  B200OPS_CUDA(launch_kernel(kern, dim3(static_cast<unsigned>(num_tokens)), dim3(warps * 32), 0,
+                      static_cast<cudaStream_t>(stream), static_cast<const __half*>(x),
+                      static_cast<const __half*>(router_weight), expert_ids, expert_weights,
+                      static_cast<int>(hidden), static_cast<int>(num_experts), static_cast<int>(top_k)));
   return B200OPS_OK;
 }
 
@@ -326,11 +359,10 @@ extern "C" int b200ops_moe_permute(const int32_t* expert_ids, int32_t* slot_to_r
                   "moe_permute: bad segment capacity %lld", (long long)segment_rows);
   B200OPS_REQUIRE(slot_to_row && counts && group_list && (expert_ids || num_slots == 0), "moe_permute: null pointer");
   const size_t smem = (static_cast<size_t>(moe::kPermuteWarps) + 2) * num_experts * sizeof(int);
-  moe::permute_kernel<<<1, moe::kPermuteThreads, smem, static_cast<cudaStream_t>(stream)>>>(
-      expert_ids, slot_to_row, counts, group_list, overflow, static_cast<int>(num_slots),
-      static_cast<int>(num_experts),
-      static_cast<int>(num_experts / world), static_cast<int>(world == 1 ? 0 : segment_rows));
-  B200OPS_LAUNCH_CHECK("moe_permute");
+  B200OPS_CUDA(launch_kernel(moe::permute_kernel, dim3(1), dim3(moe::kPermuteThreads), smem,
+                      static_cast<cudaStream_t>(stream), expert_ids, slot_to_row, counts, group_list, overflow,
+                      static_cast<int>(num_slots), static_cast<int>(num_experts),
+                      static_cast<int>(num_experts / world), static_cast<int>(world == 1 ? 0 : segment_rows)));
   return B200OPS_OK;
 }
 
@@ -343,10 +375,10 @@ extern "C" int b200ops_moe_ep_plan(const int32_t* all_counts, int32_t* grouped_t
                   (long long)num_experts, (long long)rank);
   B200OPS_REQUIRE(all_counts && grouped_to_received && group_list && total_rows, "moe_ep_plan: null pointer");
   const int local = static_cast<int>(num_experts / world);
-  moe::ep_plan_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      all_counts, grouped_to_received, group_list, total_rows, static_cast<int>(world),
-      static_cast<int>(num_experts), static_cast<int>(rank) * local, local, static_cast<int>(segment_rows));
-  B200OPS_LAUNCH_CHECK("moe_ep_plan");
+  B200OPS_CUDA(launch_kernel(moe::ep_plan_kernel, dim3(1), dim3(256), 0, static_cast<cudaStream_t>(stream), all_counts,
+                      grouped_to_received, group_list, total_rows, static_cast<int>(world),
+                      static_cast<int>(num_experts), static_cast<int>(rank) * local, local,
+                      static_cast<int>(segment_rows)));
   return B200OPS_OK;
 }
 
@@ -358,10 +390,9 @@ extern "C" int b200ops_moe_copy_rows(void* dst, const void* src, const int32_t* 
                   (long long)src_div);
   if (n_max == 0) return B200OPS_OK;
   B200OPS_REQUIRE(dst && src && aligned16(dst) && aligned16(src), "moe_copy_rows: null or misaligned pointer");
-  moe::copy_rows_kernel<<<static_cast<unsigned>(n_max), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<__half*>(dst), static_cast<const __half*>(src), dst_index, src_index, static_cast<int>(src_div),
-      n_valid, static_cast<int>(row_elems / 8));
-  B200OPS_LAUNCH_CHECK("moe_copy_rows");
+  B200OPS_CUDA(launch_kernel(moe::copy_rows_kernel, dim3(static_cast<unsigned>(n_max)), dim3(128), 0,
+                      static_cast<cudaStream_t>(stream), static_cast<__half*>(dst), static_cast<const __half*>(src),
+                      dst_index, src_index, static_cast<int>(src_div), n_valid, static_cast<int>(row_elems / 8)));
   return B200OPS_OK;
 }
 
@@ -374,10 +405,10 @@ extern "C" int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row
   if (num_tokens == 0) return B200OPS_OK;
   B200OPS_REQUIRE(rows && slot_to_row && expert_weights && y && aligned16(rows) && aligned16(y),
                   "moe_finalize: null or misaligned pointer");
-  moe::finalize_kernel<<<static_cast<unsigned>(num_tokens), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(rows), slot_to_row, expert_weights, static_cast<__half*>(y),
-      static_cast<int>(top_k), static_cast<int>(row_elems / 8));
-  B200OPS_LAUNCH_CHECK("moe_finalize");
+  B200OPS_CUDA(launch_kernel(moe::finalize_kernel, dim3(static_cast<unsigned>(num_tokens)), dim3(128), 0,
+                      static_cast<cudaStream_t>(stream), static_cast<const __half*>(rows), slot_to_row,
+                      expert_weights, static_cast<__half*>(y), static_cast<int>(top_k),
+                      static_cast<int>(row_elems / 8)));
   return B200OPS_OK;
 }
 
@@ -405,6 +436,8 @@ __global__ void __launch_bounds__(128)
 push_rows_kernel(const __half* __restrict__ src, const int32_t* __restrict__ index, int src_div,
                  const int32_t* __restrict__ n_valid, PeerTable rows, int cap, int my_rank, int row_vecs,
                  const int32_t* __restrict__ counts, int num_counts, PeerTable count_tables, int world) {
+  pdl_trigger();
+  pdl_wait();
   const int i = blockIdx.x;
   if (i == 0 && counts != nullptr) {
     for (int t = threadIdx.x; t < num_counts * world; t += blockDim.x) {
@@ -416,6 +449,7 @@ push_rows_kernel(const __half* __restrict__ src, const int32_t* __restrict__ ind
   const int idx = index[i];
   if (idx < 0) return;
   const int peer = idx / cap, off = idx - peer * cap;
+  if (peer >= world) return;  // an index outside the exchange's geometry names no buffer
   const uint4* s = reinterpret_cast<const uint4*>(src) + static_cast<size_t>(i / src_div) * row_vecs;
   uint4* d = static_cast<uint4*>(rows.base[peer]) + (static_cast<size_t>(my_rank) * cap + off) * row_vecs;
   for (int v = threadIdx.x; v < row_vecs; v += blockDim.x) d[v] = s[v];
@@ -439,6 +473,8 @@ __global__ void __launch_bounds__(kMaxPeers)
 peer_barrier_kernel(PeerTable flag_arrays, uint32_t* __restrict__ my_flags, uint32_t* __restrict__ state,
                     int world, int my_rank) {
   __shared__ uint32_t step_s;
+  pdl_trigger();
+  pdl_wait();
   if (threadIdx.x == 0) step_s = state[0] + 1;
   __syncthreads();
   const uint32_t step = step_s;
@@ -495,11 +531,11 @@ extern "C" int b200ops_moe_push_rows(const void* src, const int32_t* index, int6
                     "moe_push_rows: peer %d has no buffer", r);
   }
   const unsigned grid = static_cast<unsigned>(n_max > 0 ? n_max : 1);
-  moe::push_rows_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(src), index, static_cast<int>(src_div), n_max > 0 ? n_valid : nullptr, rows,
-      static_cast<int>(cap), static_cast<int>(my_rank), static_cast<int>(row_elems / 8), counts,
-      static_cast<int>(num_counts), cnt, static_cast<int>(world));
-  B200OPS_LAUNCH_CHECK("moe_push_rows");
+  B200OPS_CUDA(launch_kernel(moe::push_rows_kernel, dim3(grid), dim3(128), 0, static_cast<cudaStream_t>(stream),
+                      static_cast<const __half*>(src), index, static_cast<int>(src_div),
+                      n_max > 0 ? n_valid : nullptr, rows, static_cast<int>(cap), static_cast<int>(my_rank),
+                      static_cast<int>(row_elems / 8), counts, static_cast<int>(num_counts), cnt,
+                      static_cast<int>(world)));
   return B200OPS_OK;
 }
 
@@ -513,9 +549,455 @@ extern "C" int b200ops_peer_barrier(void* const* peer_flags, void* my_flags, voi
     flags.base[r] = r < world ? peer_flags[r] : nullptr;
     B200OPS_REQUIRE(r >= world || flags.base[r] != nullptr, "peer_barrier: peer %d has no flag array", r);
   }
-  moe::peer_barrier_kernel<<<1, kMaxPeers, 0, static_cast<cudaStream_t>(stream)>>>(
-      flags, static_cast<uint32_t*>(my_flags), static_cast<uint32_t*>(state), static_cast<int>(world),
-      static_cast<int>(my_rank));
-  B200OPS_LAUNCH_CHECK("peer_barrier");
+  B200OPS_CUDA(launch_kernel(moe::peer_barrier_kernel, dim3(1), dim3(kMaxPeers), 0, static_cast<cudaStream_t>(stream), flags,
+                      static_cast<uint32_t*>(my_flags), static_cast<uint32_t*>(state), static_cast<int>(world),
+                      static_cast<int>(my_rank)));
+  return B200OPS_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Fused expert-parallel step: three launches around the two expert GEMMs instead of eight.
+//
+//   moe_dispatch   one CTA per token: route it (or take the given expert ids), pick the slot
+//                  that holds the expert (a replica by token index when an expert has several),
+//                  claim a row of the (this rank, slot) sub-segment in the owner's receive buffer
+//                  with an atomic cursor, store the token's row there through the peer mapping
+//                  and remember where the result will come back.  The last CTA to finish sends
+//                  each peer the row counts of that peer's slots and announces "step n
+//                  dispatched" in every peer's flag array.
+//   moe_gather     every CTA waits (bounded) until all peers have announced step n, derives the
+//                  expert-major order from the counts, and the CTAs together copy the received
+//                  rows into that order (the input of grouped_matmul) with the map back.
+//   moe_combine    runs after the down projection whose epilogue stored the result rows into
+//                  the peers' return buffers: the first CTA to run announces "step n returned"
+//                  to every peer, every CTA waits (bounded) for all peers' announcements, then
+//                  forms y[t] = sum_k weight[t,k] * returned_row(t,k).
+//
+// Layout.  Slots are placed contiguously on ranks, `spr` per rank.  Rank d's receive buffer is
+// [world sources][spr slots][cap rows]; rank s's return buffer is [world*spr slots][cap rows]: the
+// row claimed as number p of (source s, slot e) travels to row (s*spr + e%spr)*cap + p of rank
+// e/spr and its result comes back to row e*cap + p of rank s.  A sub-segment holds `cap` rows;
+// rows that do not fit are left out of the result and counted.
+//
+// Waiting.  A kernel only ever waits for announcements made by kernels of OTHER GPUs, which wait
+// for nothing themselves before announcing; each wait gives up after two seconds, records
+// 100 + peer in the state's error word and carries on, so a missing peer cannot hang the GPU.
+// Step numbers only grow and live on the device, so the launches replay from a CUDA graph.
+//
+// state (uint32, local memory, zero-initialised once): [0] step, [1] error word, [2] CTAs of
+// the running dispatch that have finished, [3] CTAs of the running combine that have started,
+// [4] ... that have finished.  overflow (int32 [2], may be NULL): [0] rows dispatch could not
+// place, [1] rows gather could not fit.
+namespace b200ops {
+namespace moe {
+namespace {
+
+constexpr int kMaxFusedBlocks = 1024;  // world * slots per rank
+constexpr uint64_t kPeerWaitNs = 2000000000ull;
+
+struct DispatchParams {
+  const __half* x;
+  const __half* router_weight;     // null: expert ids and weights are given
+  const int32_t* ids_in;           // [T, top_k] when router_weight is null
+  int32_t* ids_out;                // [T, top_k] when routing here
+  float* weights_out;              // [T, top_k] when routing here
+  const int32_t* expert_slots;     // [E, max_replicas] slots of each expert, or null (slot = expert)
+  const int32_t* num_replicas;     // [E]
+  int32_t* pos;                    // [T * top_k] row of the return buffer, -1 = left out
+  int32_t* cursor;                 // [num_slots] rows claimed so far (zero between launches)
+  uint32_t* state;
+  int32_t* overflow;
+  PeerTable recv, counts, flags;
+  int hidden, num_experts, top_k, max_replicas, token_offset;
+  int num_slots, spr, cap, world, my_rank;
+};
+
+__device__ __forceinline__ bool wait_for_peer(const uint32_t* flag, uint32_t step) {
+  // step numbers only grow; compare with wrap-around in mind
+  if (static_cast<int32_t>(ld_acquire_sys(flag) - step) >= 0) return true;
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  uint32_t spins = 0;
+  while (static_cast<int32_t>(ld_acquire_sys(flag) - step) < 0) {
+    if ((++spins & 0xffu) == 0) {
+      uint64_t now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (now - t0 > kPeerWaitNs) return false;
+    }
+  }
+  return true;
+}
+
+template <int kBatch>
+__global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams p) {
+  __shared__ float logits[kMaxExperts];
+  __shared__ int32_t chosen[kMaxTopK];
+  __shared__ float chosen_w[kMaxTopK];
+  __shared__ int dest_peer[kMaxTopK];
+  __shared__ int dest_row[kMaxTopK];
+  __shared__ int is_last, dropped;
+  pdl_trigger();
+  pdl_wait();
+  const int token = blockIdx.x;
+  const int tid = threadIdx.x;
+  if (tid == 0) dropped = 0;
+  if (p.router_weight != nullptr) {
+    route_logits<kBatch>(p.x, p.router_weight, logits, token, p.hidden, p.num_experts);
+    __syncthreads();
+    if (tid < 32) {
+      route_select(logits, chosen, chosen_w, p.num_experts, p.top_k);
+      __syncwarp();
+      if (tid < p.top_k) {
+        p.ids_out[static_cast<size_t>(token) * p.top_k + tid] = chosen[tid];
+        p.weights_out[static_cast<size_t>(token) * p.top_k + tid] = chosen_w[tid];
+      }
+    }
+  } else if (tid < p.top_k) {
+    chosen[tid] = p.ids_in[static_cast<size_t>(token) * p.top_k + tid];
+  }
+  __syncthreads();
+  if (tid < p.top_k) {
+    const int e = chosen[tid];
+    int slot = -1;
+    if (e >= 0 && e < p.num_experts) {
+      slot = e;
+      if (p.expert_slots != nullptr) {
+        const int reps = max(p.num_replicas[e], 1);
+        slot = p.expert_slots[e * p.max_replicas + (p.token_offset + token) % reps];
+      }
+    }
+    int row = -1, peer = 0, back = -1;
+    if (slot >= 0 && slot < p.num_slots) {
+      const int claimed = atomicAdd(&p.cursor[slot], 1);
+      if (claimed < p.cap) {
+        peer = slot / p.spr;
+        row = (p.my_rank * p.spr + (slot - peer * p.spr)) * p.cap + claimed;
+        back = slot * p.cap + claimed;
+      }
+    }
+    p.pos[static_cast<size_t>(token) * p.top_k + tid] = back;
+    dest_peer[tid] = peer;
+    dest_row[tid] = row;
+  }
+  __syncthreads();
+  const int row_vecs = p.hidden >> 3;
+  const uint4* src = reinterpret_cast<const uint4*>(p.x) + static_cast<size_t>(token) * row_vecs;
+  for (int v = tid; v < row_vecs; v += blockDim.x) {
+    const uint4 val = __ldg(src + v);
+    for (int k = 0; k < p.top_k; ++k) {
+      if (dest_row[k] < 0) continue;
+      uint4* dst = static_cast<uint4*>(p.recv.base[dest_peer[k]]) + static_cast<size_t>(dest_row[k]) * row_vecs;
+      dst[v] = val;
+    }
+  }
+  // Publish: this CTA's stores, then its arrival; the CTA that finds all others arrived finishes
+  // the step for the rank.
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();
+    is_last = atomicAdd(&p.state[2], 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence_system();
+  const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.state) + 1u;
+  int lost = 0;
+  for (int slot = tid; slot < p.num_slots; slot += blockDim.x) {
+    const int claimed = atomicExch(&p.cursor[slot], 0);  // read at L2 and reset for the next launch
+    const int kept = min(claimed, p.cap);
+    lost += claimed - kept;
+    const int peer = slot / p.spr;
+    static_cast<int32_t*>(p.counts.base[peer])[p.my_rank * p.spr + (slot - peer * p.spr)] = kept;
+  }
+  if (lost) atomicAdd(&dropped, lost);
+  __threadfence_system();
+  __syncthreads();
+  if (tid < p.world) st_release_sys(static_cast<uint32_t*>(p.flags.base[tid]) + p.my_rank, step);
+  if (tid == 0) {
+    if (p.overflow != nullptr) p.overflow[0] = dropped;
+    p.state[0] = step;
+    p.state[2] = 0;
+  }
+}
+
+struct GatherParams {
+  const __half* recv;        // [world][spr][cap][hidden], local
+  const int32_t* counts;     // [world][spr], local, written by the peers
+  const uint32_t* flags;     // [world] dispatch announcements, local
+  uint32_t* state;
+  int32_t* overflow;
+  __half* grouped;           // [max_rows][hidden]
+  int32_t* map;              // [max_rows] grouped row -> received row
+  int64_t* group_list;       // [spr]
+  int32_t* total;            // [1]
+  int hidden, world, spr, cap, max_rows;
+};
+
+// Exclusive prefix sums of n <= kMaxFusedBlocks values held in shared memory, by one CTA of 256
+// threads; returns the total.  `v` is overwritten with the prefix, v[n] receives the total.
+__device__ __forceinline__ int block_exclusive_scan(int* v, int n, int* warp_sums) {
+  constexpr int kPer = kMaxFusedBlocks / 256;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  int local[kPer], sum = 0;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int idx = tid * kPer + i;
+    local[i] = idx < n ? v[idx] : 0;
+    sum += local[i];
+  }
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_sums[warp] = incl;
+  __syncthreads();
+  int base = 0, total = 0;
+  for (int w = 0; w < 8; ++w) {
+    const int ws = warp_sums[w];
+    if (w < warp) base += ws;
+    total += ws;
+  }
+  int run = base + incl - sum;
+#pragma unroll
+  for (int i = 0; i < kPer; ++i) {
+    const int idx = tid * kPer + i;
+    if (idx < n) v[idx] = run;
+    run += local[i];
+  }
+  if (tid == 0) v[n] = total;
+  __syncthreads();
+  return total;
+}
+
+__global__ void __launch_bounds__(256) moe_gather_kernel(const GatherParams p) {
+  __shared__ int dst_base[kMaxFusedBlocks + 1];  // [slot j][source r] start in grouped order; [n] = total
+  __shared__ int warp_sums[8];
+  pdl_trigger();
+  pdl_wait();
+  const int tid = threadIdx.x;
+  const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.state);
+  if (tid < p.world && !wait_for_peer(p.flags + tid, step))
+    atomicCAS(reinterpret_cast<unsigned int*>(p.state + 1), 0u, 100u + static_cast<unsigned>(tid));
+  __syncthreads();
+  const int blocks = p.world * p.spr;
+  for (int blk = tid; blk < blocks; blk += blockDim.x) {
+    const int j = blk / p.world, r = blk - j * p.world;
+    int n = __ldcg(p.counts + r * p.spr + j);
+    dst_base[blk] = n < 0 ? 0 : (n > p.cap ? p.cap : n);
+  }
+  __syncthreads();
+  const int all_rows = block_exclusive_scan(dst_base, blocks, warp_sums);
+  const int total = min(all_rows, p.max_rows);
+  if (blockIdx.x == 0) {
+    for (int j = tid; j < p.spr; j += blockDim.x) p.group_list[j] = min(dst_base[(j + 1) * p.world], p.max_rows);
+    if (tid == 0) {
+      *p.total = total;
+      if (p.overflow != nullptr) p.overflow[1] = all_rows - total;
+    }
+  }
+  const int row_vecs = p.hidden >> 3;
+  for (int d = blockIdx.x; d < total; d += gridDim.x) {
+    int lo = 0, hi = blocks - 1;  // last block whose start is <= d (empty blocks share a start)
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (dst_base[mid] <= d) lo = mid; else hi = mid - 1;
+    }
+    const int j = lo / p.world, r = lo - j * p.world;
+    const int src_row = (r * p.spr + j) * p.cap + (d - dst_base[lo]);
+    if (tid == 0) p.map[d] = src_row;
+    const uint4* s = reinterpret_cast<const uint4*>(p.recv) + static_cast<size_t>(src_row) * row_vecs;
+    uint4* o = reinterpret_cast<uint4*>(p.grouped) + static_cast<size_t>(d) * row_vecs;
+    for (int v = tid; v < row_vecs; v += blockDim.x) o[v] = __ldcg(s + v);
+  }
+}
+
+struct CombineParams {
+  const __half* ret;         // [world*spr][cap][hidden_out], local, written by the peers
+  const int32_t* pos;
+  const float* weights;
+  __half* y;
+  uint32_t* my_flags;        // [world] return announcements, local
+  uint32_t* state;
+  PeerTable flags;
+  int top_k, row_vecs, world, my_rank;
+};
+
+__global__ void __launch_bounds__(128) moe_combine_kernel(const CombineParams p) {
+  __shared__ unsigned ticket;
+  pdl_trigger();
+  pdl_wait();  // the down projection before this kernel has completed: its peer stores are done
+  const int tid = threadIdx.x;
+  const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.state);
+  if (tid == 0) ticket = atomicAdd(&p.state[3], 1u);
+  __syncthreads();
+  if (ticket == 0 && tid < p.world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(p.flags.base[tid]) + p.my_rank, step);
+  }
+  if (tid < p.world && !wait_for_peer(p.my_flags + tid, step))
+    atomicCAS(reinterpret_cast<unsigned int*>(p.state + 1), 0u, 100u + static_cast<unsigned>(tid));
+  __syncthreads();
+  const int t = blockIdx.x;
+  for (int v = tid; v < p.row_vecs; v += blockDim.x) {
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < p.top_k; ++k) {
+      const int row = p.pos[t * p.top_k + k];
+      if (row < 0) continue;
+      const float w = p.weights[t * p.top_k + k];
+      const uint4 r = __ldcg(reinterpret_cast<const uint4*>(p.ret) + static_cast<size_t>(row) * p.row_vecs + v);
+      const uint32_t* rs = reinterpret_cast<const uint32_t*>(&r);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = h2_to_f2(rs[j]);
+        acc[2 * j] = fmaf(w, f.x, acc[2 * j]);
+        acc[2 * j + 1] = fmaf(w, f.y, acc[2 * j + 1]);
+      }
+    }
+    uint4 o;
+    o.x = f2_to_h2(acc[0], acc[1]);
+    o.y = f2_to_h2(acc[2], acc[3]);
+    o.z = f2_to_h2(acc[4], acc[5]);
+    o.w = f2_to_h2(acc[6], acc[7]);
+    reinterpret_cast<uint4*>(p.y)[static_cast<size_t>(t) * p.row_vecs + v] = o;
+  }
+  __syncthreads();
+  if (tid == 0 && atomicAdd(&p.state[4], 1u) == gridDim.x - 1) {  // every CTA has its ticket by now
+    p.state[3] = 0;
+    p.state[4] = 0;
+  }
+}
+
+int fill_peers(PeerTable& t, void* const* ptrs, int64_t world, const char* what) {
+  for (int r = 0; r < kMaxPeers; ++r) {
+    t.base[r] = (ptrs != nullptr && r < world) ? ptrs[r] : nullptr;
+    B200OPS_REQUIRE(r >= world || (t.base[r] != nullptr && aligned16(t.base[r])), "%s: peer %d has no buffer", what, r);
+  }
+  return B200OPS_OK;
+}
+
+}  // namespace
+}  // namespace moe
+}  // namespace b200ops
+
+extern "C" int b200ops_moe_dispatch(const void* x, const void* router_weight, const int32_t* expert_ids_in,
+                                    int32_t* expert_ids_out, float* expert_weights_out,
+                                    const int32_t* expert_slots, const int32_t* num_replicas,
+                                    int64_t max_replicas, int64_t token_offset, int32_t* slot_to_row,
+                                    void* const* peer_recv, void* const* peer_counts, void* const* peer_flags,
+                                    int32_t* cursor, void* state, int32_t* overflow, int64_t num_tokens,
+                                    int64_t hidden, int64_t num_experts, int64_t top_k, int64_t num_slots,
+                                    int64_t world, int64_t cap, int64_t my_rank, void* stream) {
+  B200OPS_REQUIRE(num_tokens > 0 && num_tokens < (1LL << 30) && hidden > 0 && hidden % 8 == 0,
+                  "moe_dispatch: bad shape [%lld, %lld]", (long long)num_tokens, (long long)hidden);
+  B200OPS_REQUIRE(num_experts >= 1 && num_experts <= moe::kMaxExperts && top_k >= 1 && top_k <= moe::kMaxTopK &&
+                      top_k <= num_experts,
+                  "moe_dispatch: 1..%d experts and top_k in 1..min(%d, experts), got %lld and %lld",
+                  moe::kMaxExperts, moe::kMaxTopK, (long long)num_experts, (long long)top_k);
+  B200OPS_REQUIRE(world >= 1 && world <= kMaxPeers && my_rank >= 0 && my_rank < world && num_slots >= 1 &&
+                      num_slots % world == 0 && num_slots <= moe::kMaxFusedBlocks && cap > 0 &&
+                      num_slots * cap < (1LL << 31),
+                  "moe_dispatch: bad geometry world=%lld rank=%lld slots=%lld cap=%lld", (long long)world,
+                  (long long)my_rank, (long long)num_slots, (long long)cap);
+  B200OPS_REQUIRE(x && slot_to_row && cursor && state && aligned16(x), "moe_dispatch: null or misaligned pointer");
+  B200OPS_REQUIRE(router_weight ? (expert_ids_out && expert_weights_out && aligned16(router_weight))
+                                : expert_ids_in != nullptr,
+                  "moe_dispatch: give router_weight with the two outputs, or expert_ids_in");
+  B200OPS_REQUIRE(expert_slots == nullptr || (num_replicas != nullptr && max_replicas >= 1),
+                  "moe_dispatch: expert_slots needs num_replicas");
+  moe::DispatchParams p;
+  p.x = static_cast<const __half*>(x);
+  p.router_weight = static_cast<const __half*>(router_weight);
+  p.ids_in = expert_ids_in;
+  p.ids_out = expert_ids_out;
+  p.weights_out = expert_weights_out;
+  p.expert_slots = expert_slots;
+  p.num_replicas = num_replicas;
+  p.pos = slot_to_row;
+  p.cursor = cursor;
+  p.state = static_cast<uint32_t*>(state);
+  p.overflow = overflow;
+  int rc = moe::fill_peers(p.recv, peer_recv, world, "moe_dispatch(recv)");
+  if (rc == B200OPS_OK) rc = moe::fill_peers(p.counts, peer_counts, world, "moe_dispatch(counts)");
+  if (rc == B200OPS_OK) rc = moe::fill_peers(p.flags, peer_flags, world, "moe_dispatch(flags)");
+  if (rc != B200OPS_OK) return rc;
+  p.hidden = static_cast<int>(hidden);
+  p.num_experts = static_cast<int>(num_experts);
+  p.top_k = static_cast<int>(top_k);
+  p.max_replicas = static_cast<int>(max_replicas);
+  p.token_offset = static_cast<int>(token_offset);
+  p.num_slots = static_cast<int>(num_slots);
+  p.spr = static_cast<int>(num_slots / world);
+  p.cap = static_cast<int>(cap);
+  p.world = static_cast<int>(world);
+  p.my_rank = static_cast<int>(my_rank);
+  auto kern = num_experts <= 8 ? moe::moe_dispatch_kernel<16> : moe::moe_dispatch_kernel<8>;
+  B200OPS_CUDA(launch_kernel(kern, dim3(static_cast<unsigned>(num_tokens)), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
+  return B200OPS_OK;
+}
+
+extern "C" int b200ops_moe_gather(const void* recv, const int32_t* counts, const void* flags, void* state,
+                                  int32_t* overflow, void* grouped, int32_t* grouped_to_received,
+                                  int64_t* group_list, int32_t* total_rows, int64_t hidden, int64_t world,
+                                  int64_t slots_per_rank, int64_t cap, int64_t max_rows, void* stream) {
+  B200OPS_REQUIRE(world >= 1 && world <= kMaxPeers && slots_per_rank >= 1 &&
+                      world * slots_per_rank <= moe::kMaxFusedBlocks && cap > 0 && max_rows > 0 &&
+                      world * slots_per_rank * cap < (1LL << 31) && max_rows < (1LL << 31),
+                  "moe_gather: bad geometry world=%lld slots=%lld cap=%lld rows=%lld", (long long)world,
+                  (long long)slots_per_rank, (long long)cap, (long long)max_rows);
+  B200OPS_REQUIRE(hidden > 0 && hidden % 8 == 0, "moe_gather: bad row length %lld", (long long)hidden);
+  B200OPS_REQUIRE(recv && counts && flags && state && grouped && grouped_to_received && group_list && total_rows &&
+                      aligned16(recv) && aligned16(grouped),
+                  "moe_gather: null or misaligned pointer");
+  moe::GatherParams p;
+  p.recv = static_cast<const __half*>(recv);
+  p.counts = counts;
+  p.flags = static_cast<const uint32_t*>(flags);
+  p.state = static_cast<uint32_t*>(state);
+  p.overflow = overflow;
+  p.grouped = static_cast<__half*>(grouped);
+  p.map = grouped_to_received;
+  p.group_list = group_list;
+  p.total = total_rows;
+  p.hidden = static_cast<int>(hidden);
+  p.world = static_cast<int>(world);
+  p.spr = static_cast<int>(slots_per_rank);
+  p.cap = static_cast<int>(cap);
+  p.max_rows = static_cast<int>(max_rows);
+  const int64_t ctas = 4LL * sm_count();
+  const unsigned grid = static_cast<unsigned>(max_rows < ctas ? max_rows : ctas);
+  B200OPS_CUDA(launch_kernel(moe::moe_gather_kernel, dim3(grid), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
+  return B200OPS_OK;
+}
+
+extern "C" int b200ops_moe_combine(const void* returned, const int32_t* slot_to_row, const float* expert_weights,
+                                   void* y, void* const* peer_flags, void* my_flags, void* state,
+                                   int64_t num_tokens, int64_t top_k, int64_t row_elems, int64_t world,
+                                   int64_t my_rank, void* stream) {
+  B200OPS_REQUIRE(num_tokens > 0 && num_tokens < (1LL << 31) && top_k >= 1 && row_elems > 0 && row_elems % 8 == 0,
+                  "moe_combine: bad shape tokens=%lld top_k=%lld row=%lld", (long long)num_tokens,
+                  (long long)top_k, (long long)row_elems);
+  B200OPS_REQUIRE(world >= 1 && world <= kMaxPeers && my_rank >= 0 && my_rank < world,
+                  "moe_combine: bad geometry world=%lld rank=%lld", (long long)world, (long long)my_rank);
+  B200OPS_REQUIRE(returned && slot_to_row && expert_weights && y && my_flags && state && aligned16(returned) &&
+                      aligned16(y),
+                  "moe_combine: null or misaligned pointer");
+  moe::CombineParams p;
+  p.ret = static_cast<const __half*>(returned);
+  p.pos = slot_to_row;
+  p.weights = expert_weights;
+  p.y = static_cast<__half*>(y);
+  p.my_flags = static_cast<uint32_t*>(my_flags);
+  p.state = static_cast<uint32_t*>(state);
+  const int rc = moe::fill_peers(p.flags, peer_flags, world, "moe_combine(flags)");
+  if (rc != B200OPS_OK) return rc;
+  p.top_k = static_cast<int>(top_k);
+  p.row_vecs = static_cast<int>(row_elems / 8);
+  p.world = static_cast<int>(world);
+  p.my_rank = static_cast<int>(my_rank);
+  B200OPS_CUDA(launch_kernel(moe::moe_combine_kernel, dim3(static_cast<unsigned>(num_tokens)), dim3(128), 0,
+                      static_cast<cudaStream_t>(stream), p));
   return B200OPS_OK;
 }

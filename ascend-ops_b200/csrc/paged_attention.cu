@@ -10,8 +10,8 @@
 // tokens count.  Scores, softmax and the PV sum are fp32; the output is rounded once.
 #include "paged_attention.cuh"
 
+#include <atomic>
 #include <cmath>
-#include <cstdlib>
 
 namespace b200ops {
 namespace pa {
@@ -55,6 +55,8 @@ __device__ __forceinline__ size_t kv_offset(int layout, int page, int off, int h
 template <int DPL>
 __global__ void __launch_bounds__(kWarps * 32) paged_attention_general_kernel(Args a) {
   extern __shared__ float smem[];
+  pdl_trigger();
+  pdl_wait();
   const int D = a.head_dim;
   const int chunk = blockIdx.x;
   const int group = a.num_heads / a.num_kv_heads;
@@ -190,6 +192,8 @@ __global__ void __launch_bounds__(kWarps * 32) paged_attention_general_kernel(Ar
 constexpr int kCombineWarps = 4;
 
 __global__ void __launch_bounds__(kCombineWarps * 32) paged_attention_combine_kernel(Args a) {
+  pdl_trigger();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const int item = blockIdx.x * kCombineWarps + (threadIdx.x >> 5);
   if (item >= a.bs * a.num_heads) return;
@@ -230,10 +234,7 @@ Plan make_plan(int64_t bs, int64_t num_kv_heads, int64_t page_size, int64_t max_
   const int64_t cap_tokens = max_pages_per_seq * page_size;
   int64_t chunk = (pairs * cap_tokens + 1183) / 1184;
   chunk = chunk < 256 ? 256 : (chunk > 2048 ? 2048 : chunk);
-  if (const char* s = std::getenv("B200OPS_PA_CHUNK_TOKENS")) {
-    const long v = std::atol(s);
-    if (v > 0) chunk = v;
-  }
+  if (const int v = knob(kKnobPaChunkTokens, 0); v > 0) chunk = v;
   // Chunk lengths are whole pages, so that a chunk never starts inside a page, and (for the TMA
   // path) whole 64-token tiles.
   int64_t align = page_size;
@@ -263,24 +264,24 @@ int launch_general(const Args& a, cudaStream_t st) {
   const size_t smem = static_cast<size_t>(kWarps) * kHeadTile * (a.head_dim + 2) * sizeof(float);
   B200OPS_REQUIRE(grid.y <= 65535 && grid.z <= 65535,
                   "paged_attention: batch or head count too large for one launch");
+  const dim3 block(kWarps * 32);
   switch (a.head_dim / 32) {
-    case 1: paged_attention_general_kernel<1><<<grid, kWarps * 32, smem, st>>>(a); break;
-    case 2: paged_attention_general_kernel<2><<<grid, kWarps * 32, smem, st>>>(a); break;
-    case 4: paged_attention_general_kernel<4><<<grid, kWarps * 32, smem, st>>>(a); break;
-    case 8: paged_attention_general_kernel<8><<<grid, kWarps * 32, smem, st>>>(a); break;
+    case 1: B200OPS_CUDA(launch_kernel(paged_attention_general_kernel<1>, grid, block, smem, st, a)); break;
+    case 2: B200OPS_CUDA(launch_kernel(paged_attention_general_kernel<2>, grid, block, smem, st, a)); break;
+    case 4: B200OPS_CUDA(launch_kernel(paged_attention_general_kernel<4>, grid, block, smem, st, a)); break;
+    case 8: B200OPS_CUDA(launch_kernel(paged_attention_general_kernel<8>, grid, block, smem, st, a)); break;
     default:
       return fail(B200OPS_EUNSUPPORTED, "paged_attention: head_dim %d not in {32,64,128,256}",
                   a.head_dim);
   }
-  B200OPS_LAUNCH_CHECK("paged_attention");
   return B200OPS_OK;
 }
 
 int launch_combine(const Args& a, cudaStream_t st) {
   if (a.max_chunks <= 1) return B200OPS_OK;
   const int items = a.bs * a.num_heads;
-  paged_attention_combine_kernel<<<(items + kCombineWarps - 1) / kCombineWarps, kCombineWarps * 32, 0, st>>>(a);
-  B200OPS_LAUNCH_CHECK("paged_attention combine");
+  B200OPS_CUDA(launch_kernel(paged_attention_combine_kernel, dim3((items + kCombineWarps - 1) / kCombineWarps),
+                      dim3(kCombineWarps * 32), 0, st, a));
   return B200OPS_OK;
 }
 
@@ -295,15 +296,9 @@ extern "C" size_t b200ops_paged_attention_workspace_size(int64_t bs, int64_t num
   if (bs <= 0 || num_heads <= 0 || num_kv_heads <= 0 || head_dim <= 0 || page_size <= 0 ||
       max_pages_per_seq <= 0)
     return 0;
-  // The layout is not part of the query, so the answer covers whichever path the launch takes:
-  // chunk partials of the split-context kernels, or prefix sums + segment records of the
-  // tile-balanced kernel.
+  // Chunk partials plus one counter per (sequence, kv head); 0 when no sequence can be split.
   const pa::Plan p = pa::make_plan(bs, num_kv_heads, page_size, max_pages_per_seq);
-  const size_t chunked = pa::chunk_workspace_bytes(bs, num_heads, num_kv_heads, head_dim, p.max_chunks);
-  const size_t stream = num_heads % num_kv_heads == 0
-                            ? pa::stream_workspace_bytes(bs, num_heads, num_kv_heads, head_dim)
-                            : 0;
-  return chunked > stream ? chunked : stream;
+  return pa::chunk_workspace_bytes(bs, num_heads, num_kv_heads, head_dim, p.max_chunks);
 }
 
 extern "C" int b200ops_paged_attention(const void* q, const void* key_cache,
@@ -369,7 +364,6 @@ extern "C" int b200ops_paged_attention(const void* q, const void* key_cache,
 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   a.pair_counters = nullptr;
-  if (pa::stream_path_supported(a)) return pa::launch_stream(a, workspace, st);
   if (pa::fast_path_supported(a)) {
     // The split-context TMA kernel merges a pair's chunks itself: the CTA that finishes the
     // pair's last outstanding chunk (a counter per pair, zeroed here) does the merge, so no
@@ -405,19 +399,20 @@ constexpr size_t kStaticScratchBytes = B200OPS_PAGED_ATTENTION_STATIC_SCRATCH_BY
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
 // `g_static_scratch` named in host code is only the host-side handle of the symbol, never
-// a device address; the address on the current device comes from the runtime, once.
+// a device address; the address on the current device comes from the runtime, once per device.
+// Host threads may race to be first: they look up the same address, and the slot is atomic.
 int static_scratch_address(void** out) {
-  static void* address[64] = {nullptr};
+  static std::atomic<void*> address[64];
   int dev = -1;
   B200OPS_CUDA(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(B200OPS_EUNSUPPORTED, "paged_attention_static: device index %d", dev);
-  if (address[dev] == nullptr) {
-    void* p = nullptr;
+  void* p = address[dev].load(std::memory_order_acquire);
+  if (p == nullptr) {
     B200OPS_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
     if (p == nullptr) return fail(B200OPS_ECUDA, "paged_attention_static: scratch symbol has no device address");
-    address[dev] = p;
+    address[dev].store(p, std::memory_order_release);
   }
-  *out = address[dev];
+  *out = p;
   return B200OPS_OK;
 }
 
@@ -440,11 +435,11 @@ extern "C" int b200ops_paged_attention_static(const void* q, const void* key_cac
                 "paged_attention_static: this shape needs %zu bytes of scratch but the built-in "
                 "array holds %zu; use b200ops_paged_attention with a caller-owned workspace",
                 need, pa::kStaticScratchBytes);
+  // Looked up on every call, also for shapes that need no scratch: the first call on a device is
+  // the documented warm-up that makes the runtime load this module (and claim the array's memory).
   void* scratch = nullptr;
-  if (need > 0) {
-    const int rc = pa::static_scratch_address(&scratch);
-    if (rc != B200OPS_OK) return rc;
-  }
+  const int rc = pa::static_scratch_address(&scratch);
+  if (rc != B200OPS_OK) return rc;
   // The partial records are fully written by the attention kernel before the combine
   // kernel reads them, so nothing in the array has to start at zero.
   return b200ops_paged_attention(q, key_cache, value_cache, block_tables, context_lens, out, bs,

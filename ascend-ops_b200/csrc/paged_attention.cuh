@@ -142,10 +142,5 @@ bool fast_path_supported(const Args& a);
 int launch_fast(const Args& a, cudaStream_t st);
 int launch_combine(const Args& a, cudaStream_t st);
 
-// Persistent tile-balanced path (paged_attention_stream.cu): plan + main + combine in one call.
-bool stream_path_supported(const Args& a);
-size_t stream_workspace_bytes(int64_t bs, int64_t num_heads, int64_t num_kv_heads, int64_t head_dim);
-int launch_stream(const Args& a, void* workspace, cudaStream_t st);
-
 }  // namespace pa
 }  // namespace b200ops

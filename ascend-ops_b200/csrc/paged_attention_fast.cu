@@ -23,7 +23,7 @@
 #include "paged_attention_tile.cuh"
 #include "tma_host.cuh"
 
-#include <cstdlib>
+#include <atomic>
 
 namespace b200ops {
 namespace pa {
@@ -68,7 +68,8 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
   const int h0 = kvh * group;
 
   // The producer warp starts the chunk's block-table reads before the sequence length is
-  // known (entries past the sequence's end are clamped to valid pages and never used), and its
+  // known (entries that name no page -- past the sequence's end, or invalid inside it -- are
+  // fetched from page 0 and their tokens left out, as the general kernel leaves them out), and its
   // first lane sets up the barriers: three dependent global round trips (length, table, data)
   // become two, and the first tiles are on their way before the CTA-wide barrier.  The reads
   // assume the base chunk length; a sequence long enough to take longer chunks reads again.
@@ -77,24 +78,23 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
     const int pages_per_chunk = chunk_tokens / a.page_size;
     const int first_page = chunk * pages_per_chunk;
     for (int i = lane; i < pages_per_chunk; i += 32) {
-      int pg = first_page + i < a.max_pages_per_seq ? table[first_page + i] : 0;
-      pg = pg < 0 ? 0 : (pg >= a.num_pages ? a.num_pages - 1 : pg);
-      page_ids[i] = pg;
+      const int pg = first_page + i < a.max_pages_per_seq ? table[first_page + i] : 0;
+      page_ids[i] = (pg < 0 || pg >= a.num_pages) ? -1 : pg;  // -1: loaded from page 0, never used
     }
   };
-  if (warp == kConsumerWarps) {
-    load_page_ids(a.chunk_tokens);
-    if (lane == 0) {
-      for (int s = 0; s < kStages; ++s) {
-        ptx::mbar_init(&full[s], 1);
-        ptx::mbar_init(&empty[s], kConsumerWarps);
-      }
-      *abort_flag = 0;
-      ptx::fence_barrier_init();
-      ptx::prefetch_tensormap(&map_k);
-      ptx::prefetch_tensormap(&map_v);
+  pdl_trigger();
+  if (warp == kConsumerWarps && lane == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(&full[s], 1);
+      ptx::mbar_init(&empty[s], kConsumerWarps);
     }
+    *abort_flag = 0;
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&map_k);
+    ptx::prefetch_tensormap(&map_v);
   }
+  pdl_wait();  // everything below reads what earlier kernels wrote (the cache, the tables)
+  if (warp == kConsumerWarps) load_page_ids(a.chunk_tokens);
 
   int L = a.context_lens[b];
   const int cap = a.max_pages_per_seq * a.page_size;
@@ -119,7 +119,7 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
   // One tile = K and V of 64 tokens of this kv head: four boxes of 64 channels.
   auto issue_tile = [&](int t, int stage) {
     const int tok = t * kTile;  // relative to the chunk start (a page boundary)
-    const int pg = page_ids[tok / a.page_size];
+    const int pg = max(page_ids[tok / a.page_size], 0);
     const int off = tok % a.page_size;
     uint8_t* st = smem + stage * kStageBytes;
     ptx::mbar_arrive_expect_tx(&full[stage], kStageBytes);
@@ -133,7 +133,7 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
       ptx::tma_load_4d(st + kTensorTileBytes + kSubTileBytes, &map_v, &full[stage], 64, kvh, off, pg);
     } else {  // pages of 16 or 32 tokens: the tile is 4 or 2 pages, one set of boxes per page
       for (int j = 0; j < kTile / a.page_size; ++j) {
-        const int pj = page_ids[tok / a.page_size + j];
+        const int pj = max(page_ids[tok / a.page_size + j], 0);
         uint8_t* dst = st + j * a.page_size * 128;  // whole 8-row swizzle groups: the pattern is kept
         ptx::tma_load_4d(dst, &map_k, &full[stage], 0, kvh, 0, pj);
         ptx::tma_load_4d(dst + kSubTileBytes, &map_k, &full[stage], 64, kvh, 0, pj);
@@ -184,8 +184,10 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
         atomicCAS(&g_pa_status, 0, kErrConsumerWait);
         break;
       }
-      consume_slice<kUpper, kNz>(st, qa, smem + stage * kStageBytes, row0, start + t * kTile + row0, end, lane,
-                            a.scale_log2);
+      // A warp's 16 tokens lie inside one page (pages hold a multiple of 16 tokens).
+      if (page_ids[(t * kTile + row0) / a.page_size] >= 0)
+        consume_slice<kUpper, kNz>(st, qa, smem + stage * kStageBytes, row0, start + t * kTile + row0, end, lane,
+                                   a.scale_log2);
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&empty[stage]);
       if (++stage == kStages) {
@@ -261,24 +263,18 @@ paged_attention_fast_kernel(const __grid_constant__ CUtensorMap map_k,
   }
 }
 
-int env_int(const char* name, int fallback) {
-  const char* s = std::getenv(name);
-  return (s && *s) ? std::atoi(s) : fallback;
-}
-
 template <int kStages, bool kUpper, bool kNz>
 int launch_variant(const CUtensorMap& mk, const CUtensorMap& mv, const Args& a, dim3 grid, cudaStream_t st) {
   auto kern = paged_attention_fast_kernel<kStages, kUpper, kNz>;
-  static bool attr_set[64] = {false};
+  static std::atomic<bool> attr_set[64];
   int dev = 0;
   B200OPS_CUDA(cudaGetDevice(&dev));
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+  if (dev >= 0 && dev < 64 && !attr_set[dev].load(std::memory_order_acquire)) {
     B200OPS_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                       static_cast<int>(Smem<kStages>::kBytes)));
-    attr_set[dev] = true;
+    attr_set[dev].store(true, std::memory_order_release);
   }
-  kern<<<grid, kThreads, Smem<kStages>::kBytes, st>>>(mk, mv, a);
-  B200OPS_LAUNCH_CHECK("paged_attention");
+  B200OPS_CUDA(launch_kernel(kern, grid, dim3(kThreads), Smem<kStages>::kBytes, st, mk, mv, a));
   return B200OPS_OK;
 }
 
@@ -296,9 +292,8 @@ int launch_with_stages(const CUtensorMap& mk, const CUtensorMap& mv, const Args&
 }  // namespace
 
 bool fast_path_supported(const Args& a) {
-  // B200OPS_PA_MODE: 0/1 = this split-context TMA path (default), 2 = general kernel,
-  // 3 = persistent tile-balanced kernel (paged_attention_stream.cu).
-  if (env_int("B200OPS_PA_MODE", 0) == 2) return false;
+  // B200OPS_PA_MODE: 2 = general kernel, anything else = this split-context TMA path.
+  if (knob(kKnobPaMode, 0) == 2) return false;
   const int group = a.num_heads / a.num_kv_heads;
   const bool page_ok = a.page_size % kTile == 0 ||
                        (a.layout == B200OPS_KV_LAYOUT_NHD && (a.page_size == 16 || a.page_size == 32) &&
@@ -339,7 +334,7 @@ int launch_fast(const Args& a, cudaStream_t st) {
   const dim3 grid(a.max_chunks, a.num_kv_heads, a.bs);
   B200OPS_REQUIRE(grid.y <= 65535 && grid.z <= 65535,
                   "paged_attention: batch or head count too large for one launch");
-  switch (env_int("B200OPS_PA_STAGES", 3)) {
+  switch (knob(kKnobPaStages, 3)) {
     case 2: return launch_with_stages<2>(mk, mv, a, grid, st);
     case 4: return launch_with_stages<4>(mk, mv, a, grid, st);
     case 6: return launch_with_stages<6>(mk, mv, a, grid, st);

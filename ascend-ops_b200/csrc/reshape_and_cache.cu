@@ -8,9 +8,13 @@
 // Slots outside [0, pages*P) are skipped, as the reference kernel does (:50).  Where the
 // reference lets every core copy all tokens element by element, here a warp moves one token's
 // K and V rows in 32-byte pieces (rows of whole sectors), or each thread one 16-byte vector of
-// K and the matching vector of V (other rows that are multiples of 8), or single elements.  If two tokens name the same slot the
-// reference keeps the later token; here the winner is unspecified (callers never do this:
-// a slot is one cache position).
+// K and the matching vector of V (other rows that are multiples of 8), or single elements.
+//
+// A slot named by two tokens: the reference walks the tokens in order, so the later token's
+// row stays (:47-61).  Batches of up to kDedupMaxTokens tokens (every decode step) reproduce
+// that: a token is skipped when a later token of the batch names its slot.  Larger batches do
+// not pay for the check; there one of the rows that name the slot ends up in it, whole for the
+// row-per-warp kernel (callers never do this: a slot is one cache position).
 #include "common.cuh"
 
 namespace b200ops {
@@ -30,16 +34,28 @@ struct ScatterParams {
   int64_t num_slots;    // pages * P
   uint32_t page_size;   // P
   uint32_t chunks;      // NZ: C
+  bool dedup;           // small batch: a token whose slot a later token names again is skipped
 };
+
+// The per-thread form of the check for the fallback kernels (odd row sizes; never on a hot path).
+__device__ __forceinline__ bool thread_named_again(const int32_t* __restrict__ slots, uint32_t token,
+                                                   uint32_t num_tokens, int32_t slot) {
+  for (uint32_t t = token + 1; t < num_tokens; ++t)
+    if (__ldg(slots + t) == slot) return true;
+  return false;
+}
 
 // NHD: a token's destination is one contiguous row of row_elems halfs at slot * row_elems.
 __global__ void __launch_bounds__(kThreads) scatter_nhd_vec_kernel(ScatterParams p) {
+  pdl_trigger();
+  pdl_wait();
   const uint32_t item = blockIdx.x * kThreads + threadIdx.x;
   const uint32_t token = item / p.items_per_token;
   if (token >= p.num_tokens) return;
   const uint32_t v = item - token * p.items_per_token;
   const int64_t slot = p.slots[token];
   if (slot < 0 || slot >= p.num_slots) return;
+  if (p.dedup && thread_named_again(p.slots, token, p.num_tokens, static_cast<int32_t>(slot))) return;
   const size_t src = static_cast<size_t>(token) * p.items_per_token + v;
   const size_t dst = static_cast<size_t>(slot) * p.items_per_token + v;
   const uint4 kv = ld_stream(reinterpret_cast<const uint4*>(p.key) + src);
@@ -52,6 +68,8 @@ __global__ void __launch_bounds__(kThreads) scatter_nhd_vec_kernel(ScatterParams
 
 // NZ: vector v of the flat row belongs to chunk c = v/2 (16 halfs = two vectors per chunk).
 __global__ void __launch_bounds__(kThreads) scatter_nz_vec_kernel(ScatterParams p) {
+  pdl_trigger();
+  pdl_wait();
   const uint32_t item = blockIdx.x * kThreads + threadIdx.x;
   const uint32_t token = item / p.items_per_token;
   if (token >= p.num_tokens) return;
@@ -60,6 +78,7 @@ __global__ void __launch_bounds__(kThreads) scatter_nz_vec_kernel(ScatterParams 
   if (c >= p.chunks) return;
   const int64_t slot = p.slots[token];
   if (slot < 0 || slot >= p.num_slots) return;
+  if (p.dedup && thread_named_again(p.slots, token, p.num_tokens, static_cast<int32_t>(slot))) return;
   const uint32_t page = static_cast<uint32_t>(slot / p.page_size);
   const uint32_t off = static_cast<uint32_t>(slot - static_cast<int64_t>(page) * p.page_size);
   const size_t src = static_cast<size_t>(token) * p.items_per_token + v;
@@ -73,32 +92,51 @@ __global__ void __launch_bounds__(kThreads) scatter_nz_vec_kernel(ScatterParams 
   reinterpret_cast<uint4*>(p.key_cache)[dst] = kv;
 }
 
-// Row-per-warp kernels for rows that are whole 32-byte sectors (row_elems % 16 == 0): a warp
-// owns one token, every lane moves 32-byte pieces of the K row and of the V row.  All loads
-// (including the slot) are issued before anything depends on them, so one DRAM round trip
-// covers them; stores are one full sector each.  kMaxPieces bounds the pieces a lane holds.
-constexpr int kRowWarps = 4;
+// True if a token after `token` names the same slot (the warp scans the rest of the batch; the
+// slot array of a decode step is a few KB and stays in L1).
+__device__ __forceinline__ bool named_again(const int32_t* __restrict__ slots, uint32_t token,
+                                            uint32_t num_tokens, int32_t slot, uint32_t lane) {
+  bool later = false;
+#pragma unroll 4
+  for (uint32_t t = token + 1 + lane; t < num_tokens; t += 32) later |= (__ldg(slots + t) == slot);
+  return __any_sync(0xffffffffu, later);
+}
+
+constexpr int kDedupMaxTokens = 4096;
+
+// Row-per-warp kernel for rows that are whole 32-byte sectors (row_elems % 16 == 0): a warp
+// owns one token (kSplit: one token's K row or its V row), every lane moves 32-byte pieces.
+// All loads (including the slot) are issued before anything depends on them, so one DRAM round
+// trip covers them; stores are one full sector each.  kMaxPieces bounds the pieces a lane holds.
 constexpr int kMaxPieces = 4;  // 32 lanes x 4 pieces x 32 B = rows up to 4 KB
 
-template <bool kNz>
-__global__ void __launch_bounds__(kRowWarps * 32) scatter_rows_kernel(ScatterParams p) {
-  const uint32_t token = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+template <bool kNz, bool kDedup, bool kSplit>
+__global__ void __launch_bounds__(512) scatter_rows_kernel(ScatterParams p) {
+  pdl_trigger();
+  pdl_wait();
+  const uint32_t warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const uint32_t token = kSplit ? warp_id >> 1 : warp_id;
   if (token >= p.num_tokens) return;
+  const bool do_k = !kSplit || (warp_id & 1u) == 0;
+  const bool do_v = p.value != nullptr && (!kSplit || (warp_id & 1u) == 1);
+  if (!do_k && !do_v) return;
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t pieces = p.row_elems >> 4;  // 32-byte pieces (= NZ chunks) per row
   const char* ks = reinterpret_cast<const char*>(p.key) + static_cast<size_t>(token) * p.row_elems * 2;
   const char* vs = reinterpret_cast<const char*>(p.value) + static_cast<size_t>(token) * p.row_elems * 2;
-  const int64_t slot = p.slots[token];
+  const int32_t slot32 = p.slots[token];
   Vec256 kb[kMaxPieces], vb[kMaxPieces];
 #pragma unroll
   for (int i = 0; i < kMaxPieces; ++i) {
     const uint32_t c = lane + i * 32;
     if (c < pieces) {
-      kb[i] = ld_stream256(ks + c * 32);
-      if (p.value != nullptr) vb[i] = ld_stream256(vs + c * 32);
+      if (do_k) kb[i] = ld_stream256(ks + c * 32);
+      if (do_v) vb[i] = ld_stream256(vs + c * 32);
     }
   }
+  const int64_t slot = slot32;
   if (slot < 0 || slot >= p.num_slots) return;
+  if (kDedup && named_again(p.slots, token, p.num_tokens, slot32, lane)) return;
   size_t base, stride;  // byte offset of piece 0 and distance between pieces in the cache
   uint32_t limit = pieces;
   if (kNz) {
@@ -117,8 +155,8 @@ __global__ void __launch_bounds__(kRowWarps * 32) scatter_rows_kernel(ScatterPar
   for (int i = 0; i < kMaxPieces; ++i) {
     const uint32_t c = lane + i * 32;
     if (c < limit) {
-      st256(kc + c * stride, kb[i]);
-      if (p.value != nullptr) st256(vc + c * stride, vb[i]);
+      if (do_k) st256(kc + c * stride, kb[i]);
+      if (do_v) st256(vc + c * stride, vb[i]);
     }
   }
 }
@@ -126,12 +164,16 @@ __global__ void __launch_bounds__(kRowWarps * 32) scatter_rows_kernel(ScatterPar
 // Any shape / alignment: one 16-bit element per item.
 template <bool kNz>
 __global__ void __launch_bounds__(kThreads) scatter_scalar_kernel(ScatterParams p) {
+  pdl_trigger();
+  pdl_wait();
   const uint64_t item = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
   const uint64_t token = item / p.row_elems;
   if (token >= p.num_tokens) return;
   const uint32_t e = static_cast<uint32_t>(item - token * p.row_elems);
   const int64_t slot = p.slots[token];
   if (slot < 0 || slot >= p.num_slots) return;
+  if (p.dedup && thread_named_again(p.slots, static_cast<uint32_t>(token), p.num_tokens, static_cast<int32_t>(slot)))
+    return;
   size_t dst;
   if (kNz) {
     const uint32_t c = e >> 4;
@@ -208,13 +250,27 @@ extern "C" int b200ops_reshape_and_cache(const void* key, const void* value, voi
                            (with_value ? reinterpret_cast<uintptr_t>(value) |
                                              reinterpret_cast<uintptr_t>(value_cache)
                                        : 0)) & 31u) == 0;
+  p.dedup = num_tokens <= kDedupMaxTokens;
   if (row_elems % 16 == 0 && row_elems <= 16 * 32 * kMaxPieces && aligned32) {
-    const unsigned grid = static_cast<unsigned>((num_tokens + kRowWarps - 1) / kRowWarps);
-    if (layout == B200OPS_KV_LAYOUT_NZ)
-      scatter_rows_kernel<true><<<grid, kRowWarps * 32, 0, st>>>(p);
+    // Warps per CTA and whether a token's K and V rows go to separate warps (twice the warps,
+    // half the loads each holds) are tuning knobs; a decode step is one DRAM round trip long.
+    int warps = knob(kKnobRacWarps, 4);
+    if (warps != 2 && warps != 4 && warps != 8 && warps != 16) warps = 4;
+    const bool split = with_value && knob(kKnobRacSplit, 0) != 0;
+    const int64_t n_warps = split ? 2 * num_tokens : num_tokens;
+    const unsigned grid = static_cast<unsigned>((n_warps + warps - 1) / warps);
+    const bool nz = layout == B200OPS_KV_LAYOUT_NZ;
+#define RAC_LAUNCH(NZ, DD, SP) \
+  launch_kernel(scatter_rows_kernel<NZ, DD, SP>, dim3(grid), dim3(warps * 32), 0, st, p)
+    cudaError_t err;
+    if (nz)
+      err = p.dedup ? (split ? RAC_LAUNCH(true, true, true) : RAC_LAUNCH(true, true, false))
+                    : (split ? RAC_LAUNCH(true, false, true) : RAC_LAUNCH(true, false, false));
     else
-      scatter_rows_kernel<false><<<grid, kRowWarps * 32, 0, st>>>(p);
-    B200OPS_LAUNCH_CHECK("reshape_and_cache");
+      err = p.dedup ? (split ? RAC_LAUNCH(false, true, true) : RAC_LAUNCH(false, true, false))
+                    : (split ? RAC_LAUNCH(false, false, true) : RAC_LAUNCH(false, false, false));
+#undef RAC_LAUNCH
+    B200OPS_CUDA(err);
     return B200OPS_OK;
   }
   const bool vec_ok = row_elems % 8 == 0 && aligned16(key) && aligned16(key_cache) &&
@@ -223,20 +279,16 @@ extern "C" int b200ops_reshape_and_cache(const void* key, const void* value, voi
   if (vec_ok && vec_items < 0x7fffff00LL) {
     p.items_per_token = static_cast<uint32_t>(row_elems / 8);
     const unsigned grid = static_cast<unsigned>((vec_items + kThreads - 1) / kThreads);
-    if (layout == B200OPS_KV_LAYOUT_NZ)
-      scatter_nz_vec_kernel<<<grid, kThreads, 0, st>>>(p);
-    else
-      scatter_nhd_vec_kernel<<<grid, kThreads, 0, st>>>(p);
+    B200OPS_CUDA(launch_kernel(layout == B200OPS_KV_LAYOUT_NZ ? scatter_nz_vec_kernel : scatter_nhd_vec_kernel, dim3(grid),
+                        dim3(kThreads), 0, st, p));
+    return B200OPS_OK;
   } else {
     p.items_per_token = 0;
     const int64_t items = num_tokens * row_elems;
     const int64_t grid = (items + kThreads - 1) / kThreads;
     B200OPS_REQUIRE(grid <= 0x7fffffffLL, "reshape_and_cache: key too large");
-    if (layout == B200OPS_KV_LAYOUT_NZ)
-      scatter_scalar_kernel<true><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(p);
-    else
-      scatter_scalar_kernel<false><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(p);
+    B200OPS_CUDA(launch_kernel(layout == B200OPS_KV_LAYOUT_NZ ? scatter_scalar_kernel<true> : scatter_scalar_kernel<false>,
+                        dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0, st, p));
   }
-  B200OPS_LAUNCH_CHECK("reshape_and_cache");
   return B200OPS_OK;
 }

@@ -21,6 +21,8 @@ rope_kernel(const __half* __restrict__ q, const __half* __restrict__ k,
             const __half* __restrict__ sin_cache, __half* __restrict__ out_q,
             __half* __restrict__ out_k, uint32_t total_items, uint32_t items_per_token,
             uint32_t vecs_per_half, uint32_t num_heads, uint32_t num_kv_heads, int max_pos) {
+  pdl_trigger();
+  pdl_wait();
   const uint32_t item = blockIdx.x * kThreads + threadIdx.x;
   if (item >= total_items) return;
   const uint32_t token = item / items_per_token;
@@ -96,13 +98,12 @@ extern "C" int b200ops_rope(const void* q, const void* k, const int32_t* positio
   const int64_t total = bs * items_per_token;
   B200OPS_REQUIRE(total < 0x7fffff00LL, "rope: tensor too large");
   const unsigned grid = static_cast<unsigned>((total + kThreads - 1) / kThreads);
-  rope_kernel<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __half*>(q), static_cast<const __half*>(k), position_ids,
-      static_cast<const __half*>(cos_cache), static_cast<const __half*>(sin_cache),
-      static_cast<__half*>(out_q), static_cast<__half*>(out_k), static_cast<uint32_t>(total),
-      static_cast<uint32_t>(items_per_token), static_cast<uint32_t>(vecs_per_half),
-      static_cast<uint32_t>(num_heads), static_cast<uint32_t>(num_kv_heads),
-      static_cast<int>(max_pos));
-  B200OPS_LAUNCH_CHECK("rope");
+  B200OPS_CUDA(launch_kernel(rope_kernel, dim3(grid), dim3(kThreads), 0, static_cast<cudaStream_t>(stream),
+                      static_cast<const __half*>(q), static_cast<const __half*>(k), position_ids,
+                      static_cast<const __half*>(cos_cache), static_cast<const __half*>(sin_cache),
+                      static_cast<__half*>(out_q), static_cast<__half*>(out_k), static_cast<uint32_t>(total),
+                      static_cast<uint32_t>(items_per_token), static_cast<uint32_t>(vecs_per_half),
+                      static_cast<uint32_t>(num_heads), static_cast<uint32_t>(num_kv_heads),
+                      static_cast<int>(max_pos)));
   return B200OPS_OK;
 }

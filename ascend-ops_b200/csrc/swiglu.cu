@@ -15,6 +15,8 @@ template <typename index_t>
 __global__ void __launch_bounds__(kThreads)
 swiglu_kernel(const __half* __restrict__ x, __half* __restrict__ y, index_t total_vecs,
               index_t vecs_per_row) {
+  pdl_trigger();
+  pdl_wait();
   const uint4* xin = reinterpret_cast<const uint4*>(x);
   uint4* yout = reinterpret_cast<uint4*>(y);
   const index_t base = static_cast<index_t>(blockIdx.x) * (kThreads * kUnroll) + threadIdx.x;
@@ -73,13 +75,12 @@ extern "C" int b200ops_swiglu(const void* x, void* y, int64_t num_tokens, int64_
   __half* yp = static_cast<__half*>(y);
   // Input vector indices reach 2*total: stay in 32-bit arithmetic when that fits.
   if (2 * total + per_cta < 0x7fffffffLL) {
-    swiglu_kernel<uint32_t><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(
-        xp, yp, static_cast<uint32_t>(total), static_cast<uint32_t>(vecs_per_row));
+    B200OPS_CUDA(launch_kernel(swiglu_kernel<uint32_t>, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0, st, xp, yp,
+                        static_cast<uint32_t>(total), static_cast<uint32_t>(vecs_per_row)));
   } else {
-    swiglu_kernel<unsigned long long><<<static_cast<unsigned>(grid), kThreads, 0, st>>>(
-        xp, yp, static_cast<unsigned long long>(total),
-        static_cast<unsigned long long>(vecs_per_row));
+    B200OPS_CUDA(launch_kernel(swiglu_kernel<unsigned long long>, dim3(static_cast<unsigned>(grid)), dim3(kThreads), 0, st,
+                        xp, yp, static_cast<unsigned long long>(total),
+                        static_cast<unsigned long long>(vecs_per_row)));
   }
-  B200OPS_LAUNCH_CHECK("swiglu");
   return B200OPS_OK;
 }

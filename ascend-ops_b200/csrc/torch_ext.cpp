@@ -7,6 +7,7 @@
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
 #include <torch/extension.h>
+#include <torch/library.h>
 
 #include <tuple>
 #include <vector>
@@ -287,6 +288,26 @@ at::Tensor paged_attention(at::Tensor q, at::Tensor key_cache, at::Tensor value_
   return y;
 }
 
+// Mirrors native::matmul of the reference's earlier interface (_csrc/ffi.cpp:408-442): the same
+// three argument checks and messages, float16 only, output allocated here.
+at::Tensor matmul(const at::Tensor& x, const at::Tensor& w) {
+  TORCH_CHECK(x.dim() == 2 && w.dim() == 2, "matmul: input tensors must be 2D");
+  TORCH_CHECK(x.size(1) == w.size(1), "matmul: last dimension of x must match last dimension of w, got ",
+              x.size(1), " and ", w.size(1));
+  TORCH_CHECK(x.is_contiguous() && w.is_contiguous(), "matmul: x and w must be contiguous tensors");
+  TORCH_CHECK(x.scalar_type() == at::kHalf && w.scalar_type() == at::kHalf,
+              "matmul: only float16 is supported, got ", x.scalar_type());
+  TORCH_CHECK(x.is_cuda() && w.is_cuda(), "matmul: x and w must be CUDA tensors (there is no CPU path)");
+  check_same_device(x, w, "matmul");
+  TORCH_CHECK(w.size(0) > 0 && x.size(1) > 0, "matmul: empty weight");
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor y = at::empty({x.size(0), w.size(0)}, x.options());
+  check_status(b200ops_matmul(x.data_ptr(), w.data_ptr(), y.data_ptr(), x.size(0), w.size(0), x.size(1),
+                              current_stream()),
+               "matmul");
+  return y;
+}
+
 int print_info(int device_id) {
   check_status(b200ops_print_info(device_id, nullptr, 0), "print_info");
   return 0;
@@ -537,7 +558,142 @@ void peer_barrier(std::vector<int64_t> peer_flags, at::Tensor my_flags, at::Tens
                "peer_barrier");
 }
 
+namespace {
+std::vector<void*> as_pointers(const std::vector<int64_t>& v) {
+  std::vector<void*> out(v.size());
+  for (size_t i = 0; i < v.size(); ++i) out[i] = reinterpret_cast<void*>(v[i]);
+  return out;
+}
+}  // namespace
+
+// Fused dispatch of the expert-parallel step (see b200ops_moe_dispatch).  Routes with
+// router_weight, or takes expert_ids (then returns them unchanged with an empty weight tensor).
+// Returns (slot_to_row, expert_ids, expert_weights).
+std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_dispatch(
+    at::Tensor x, c10::optional<at::Tensor> router_weight, c10::optional<at::Tensor> expert_ids, int64_t top_k,
+    c10::optional<at::Tensor> expert_slots, c10::optional<at::Tensor> num_replicas, int64_t token_offset,
+    std::vector<int64_t> peer_recv, std::vector<int64_t> peer_counts, std::vector<int64_t> peer_flags,
+    at::Tensor cursor, at::Tensor state, c10::optional<at::Tensor> overflow, int64_t num_experts, int64_t cap,
+    int64_t my_rank) {
+  TORCH_CHECK(x.dim() == 2 && x.is_contiguous(), "moe_dispatch: x must be contiguous [T, H]");
+  check_f16_cuda(x, "moe_dispatch", "x");
+  TORCH_CHECK(router_weight.has_value() != expert_ids.has_value(),
+              "moe_dispatch: give either router_weight or expert_ids");
+  check_i32_cuda(cursor, "moe_dispatch", "cursor");
+  TORCH_CHECK(state.is_cuda() && state.element_size() == 4 && state.numel() >= 5 && state.is_contiguous(),
+              "moe_dispatch: state must be a contiguous 32-bit CUDA tensor of at least 5 elements");
+  TORCH_CHECK(peer_recv.size() == peer_counts.size() && peer_recv.size() == peer_flags.size(),
+              "moe_dispatch: one receive buffer, count table and flag array per rank");
+  const int64_t world = static_cast<int64_t>(peer_recv.size());
+  const int64_t num_slots = cursor.numel();
+  const int64_t tokens = x.size(0);
+  const c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor pos = at::empty({tokens * top_k}, x.options().dtype(at::kInt));
+  at::Tensor ids, wts;
+  if (router_weight) {
+    TORCH_CHECK(router_weight->dim() == 2 && router_weight->size(1) == x.size(1) && router_weight->is_contiguous(),
+                "moe_dispatch: router_weight must be contiguous [E, H]");
+    check_f16_cuda(*router_weight, "moe_dispatch", "router_weight");
+    TORCH_CHECK(router_weight->size(0) == num_experts, "moe_dispatch: router_weight rows must equal num_experts");
+    ids = at::empty({tokens, top_k}, x.options().dtype(at::kInt));
+    wts = at::empty({tokens, top_k}, x.options().dtype(at::kFloat));
+  } else {
+    check_i32_cuda(*expert_ids, "moe_dispatch", "expert_ids");
+    TORCH_CHECK(expert_ids->numel() == tokens * top_k, "moe_dispatch: expert_ids must be [T, top_k]");
+    ids = *expert_ids;
+    wts = at::empty({0}, x.options().dtype(at::kFloat));
+  }
+  int64_t max_rep = 0;
+  if (expert_slots) {
+    TORCH_CHECK(num_replicas.has_value(), "moe_dispatch: expert_slots needs num_replicas");
+    check_i32_cuda(*expert_slots, "moe_dispatch", "expert_slots");
+    check_i32_cuda(*num_replicas, "moe_dispatch", "num_replicas");
+    TORCH_CHECK(expert_slots->dim() == 2 && expert_slots->size(0) == num_experts &&
+                    num_replicas->numel() == num_experts,
+                "moe_dispatch: expert_slots [E, max_replicas], num_replicas [E]");
+    max_rep = expert_slots->size(1);
+  }
+  if (overflow) {
+    check_i32_cuda(*overflow, "moe_dispatch", "overflow");
+    TORCH_CHECK(overflow->numel() >= 2, "moe_dispatch: overflow must hold 2 counters");
+  }
+  if (tokens == 0) return {pos, ids, wts};
+  auto recv = as_pointers(peer_recv), cnt = as_pointers(peer_counts), flg = as_pointers(peer_flags);
+  check_status(b200ops_moe_dispatch(
+                   x.data_ptr(), router_weight ? router_weight->data_ptr() : nullptr,
+                   router_weight ? nullptr : ids.data_ptr<int32_t>(),
+                   router_weight ? ids.data_ptr<int32_t>() : nullptr, router_weight ? wts.data_ptr<float>() : nullptr,
+                   expert_slots ? expert_slots->data_ptr<int32_t>() : nullptr,
+                   num_replicas ? num_replicas->data_ptr<int32_t>() : nullptr, max_rep, token_offset,
+                   pos.data_ptr<int32_t>(), recv.data(), cnt.data(), flg.data(), cursor.data_ptr<int32_t>(),
+                   state.data_ptr(), overflow ? overflow->data_ptr<int32_t>() : nullptr, tokens, x.size(1),
+                   num_experts, top_k, num_slots, world, cap, my_rank, current_stream()),
+               "moe_dispatch");
+  return {pos, ids, wts};
+}
+
+// Receiving side of the fused step (see b200ops_moe_gather): returns (grouped rows [max_rows, H],
+// grouped_to_received [max_rows], group_list [slots_per_rank], total [1]).
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> moe_gather(at::Tensor recv, at::Tensor counts,
+                                                                     at::Tensor flags, at::Tensor state,
+                                                                     c10::optional<at::Tensor> overflow,
+                                                                     int64_t cap, int64_t max_rows) {
+  TORCH_CHECK(recv.dim() == 2 && recv.is_contiguous(), "moe_gather: recv must be contiguous [rows, H]");
+  check_f16_cuda(recv, "moe_gather", "recv");
+  check_i32_cuda(counts, "moe_gather", "counts");
+  TORCH_CHECK(counts.dim() == 2, "moe_gather: counts must be [world, slots_per_rank]");
+  TORCH_CHECK(flags.is_cuda() && flags.element_size() == 4 && flags.numel() >= counts.size(0) &&
+                  state.is_cuda() && state.element_size() == 4 && state.numel() >= 5,
+              "moe_gather: flags [world] and state [5] must be 32-bit CUDA tensors");
+  const int64_t world = counts.size(0), spr = counts.size(1);
+  TORCH_CHECK(recv.size(0) >= world * spr * cap, "moe_gather: recv holds fewer than world * slots * cap rows");
+  const c10::cuda::CUDAGuard guard(recv.device());
+  at::Tensor grouped = at::empty({max_rows, recv.size(1)}, recv.options());
+  at::Tensor map = at::empty({max_rows}, recv.options().dtype(at::kInt));
+  at::Tensor gl = at::empty({spr}, recv.options().dtype(at::kLong));
+  at::Tensor total = at::empty({1}, recv.options().dtype(at::kInt));
+  check_status(b200ops_moe_gather(recv.data_ptr(), counts.data_ptr<int32_t>(), flags.data_ptr(), state.data_ptr(),
+                                  overflow ? overflow->data_ptr<int32_t>() : nullptr, grouped.data_ptr(),
+                                  map.data_ptr<int32_t>(), gl.data_ptr<int64_t>(), total.data_ptr<int32_t>(),
+                                  recv.size(1), world, spr, cap, max_rows, current_stream()),
+               "moe_gather");
+  return {grouped, map, gl, total};
+}
+
+// Last launch of the fused step (see b200ops_moe_combine).
+at::Tensor moe_combine(at::Tensor returned, at::Tensor slot_to_row, at::Tensor expert_weights,
+                       std::vector<int64_t> peer_flags, at::Tensor my_flags, at::Tensor state, int64_t my_rank) {
+  TORCH_CHECK(returned.dim() == 2 && returned.is_contiguous() && expert_weights.dim() == 2 &&
+                  expert_weights.is_contiguous() && slot_to_row.numel() == expert_weights.numel(),
+              "moe_combine: returned [R, H], expert_weights [T, k], slot_to_row [T*k]");
+  check_f16_cuda(returned, "moe_combine", "returned");
+  check_i32_cuda(slot_to_row, "moe_combine", "slot_to_row");
+  TORCH_CHECK(expert_weights.is_cuda() && expert_weights.scalar_type() == at::kFloat,
+              "moe_combine: expert_weights must be a CUDA float32 tensor");
+  TORCH_CHECK(my_flags.is_cuda() && my_flags.element_size() == 4 &&
+                  my_flags.numel() >= static_cast<int64_t>(peer_flags.size()) && state.is_cuda() &&
+                  state.element_size() == 4 && state.numel() >= 5,
+              "moe_combine: flags [world] and state [5] must be 32-bit CUDA tensors");
+  const c10::cuda::CUDAGuard guard(returned.device());
+  at::Tensor y = at::empty({expert_weights.size(0), returned.size(1)}, returned.options());
+  if (expert_weights.size(0) == 0) return y;
+  auto flg = as_pointers(peer_flags);
+  check_status(b200ops_moe_combine(returned.data_ptr(), slot_to_row.data_ptr<int32_t>(),
+                                   expert_weights.data_ptr<float>(), y.data_ptr(), flg.data(), my_flags.data_ptr(),
+                                   state.data_ptr(), expert_weights.size(0), expert_weights.size(1),
+                                   returned.size(1), static_cast<int64_t>(flg.size()), my_rank, current_stream()),
+               "moe_combine");
+  return y;
+}
+
 void init_ffi_moe(py::module_&& m) {
+  m.def("dispatch", &moe_dispatch, py::arg("x"), py::arg("router_weight"), py::arg("expert_ids"), py::arg("top_k"),
+        py::arg("expert_slots"), py::arg("num_replicas"), py::arg("token_offset"), py::arg("peer_recv"),
+        py::arg("peer_counts"), py::arg("peer_flags"), py::arg("cursor"), py::arg("state"), py::arg("overflow"),
+        py::arg("num_experts"), py::arg("cap"), py::arg("my_rank"));
+  m.def("gather", &moe_gather, py::arg("recv"), py::arg("counts"), py::arg("flags"), py::arg("state"),
+        py::arg("overflow"), py::arg("cap"), py::arg("max_rows"));
+  m.def("combine", &moe_combine);
   m.def("push_rows", &moe_push_rows, py::arg("src"), py::arg("index"), py::arg("src_div"),
         py::arg("n_valid"), py::arg("n_max"), py::arg("peer_rows"), py::arg("cap"), py::arg("my_rank"),
         py::arg("counts") = py::none(), py::arg("peer_counts") = std::vector<int64_t>());
@@ -565,9 +721,25 @@ void init_ffi_ops(py::module_&& m) {
   m.def("add_rms_norm", &add_rms_norm, "AddRMSNorm");
   m.def("reshape_and_cache", &reshape_and_cache, "ReshapeAndCache");
   m.def("paged_attention", &paged_attention, "PagedAttention");
+  m.def("matmul", &matmul, "MatMul (dense NT product of the reference's earlier interface)");
 }
 
 }  // namespace native
+
+// The reference's earlier interface also registers its operators with the dispatcher
+// (TORCH_LIBRARY(ascend910a, ...), _csrc/ffi.cpp:473-482): torch.ops.ascend910a.{swiglu,
+// grouped_matmul, matmul}.  Same schemas here, bound to the CUDA key.
+TORCH_LIBRARY(ascend910a, m) {
+  m.def("swiglu(Tensor x) -> Tensor");
+  m.def("grouped_matmul(Tensor x, Tensor w, Tensor group_list) -> Tensor");
+  m.def("matmul(Tensor x, Tensor w) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(ascend910a, CUDA, m) {
+  m.impl("swiglu", &native::swiglu);
+  m.impl("grouped_matmul", &native::grouped_matmul);
+  m.impl("matmul", &native::matmul);
+}
 
 PYBIND11_MODULE(ascend910a_extras_C, m) {
   m.def("print_info", &native::print_info, "Print info about the device");

@@ -96,6 +96,7 @@ class MoEDecodeLayer:
         self.cfg, self.ops, self.device, self.group, self.moe = cfg, ops, device, group, moe
         self.segment_rows = segment_rows  # rows each rank sends each peer under expert parallelism
         self.exchange = exchange  # a moe_parallel.PeerExchange: NVLink peer-memory dispatch/combine
+        self.local_only = False  # True: all experts are here; ignore any process group
         self.fuse_return = True  # down projection stores into the peers' buffers in its epilogue
         self.fuse_rope_cache = True  # False: split + ops.rope + ops.reshape_and_cache separately
         self.fuse_swiglu = True  # False: ops.grouped_matmul then ops.swiglu
@@ -176,13 +177,14 @@ class MoEDecodeLayer:
         h2, res2 = ops.add_rms_norm(o, res1, self.ln2, cfg.eps)
         if on_residual is not None:
             on_residual(res2)
-        ids, wts = self.moe.route_topk(h2, self.wrouter, cfg.top_k)
-        if self.exchange is not None:
-            y = self.exchange.mlp(h2, ids, wts, self._local_mlp,
-                                  local_mlp_scatter=self._local_mlp_scatter if self.fuse_return else None)
+        if self.exchange is not None:  # the router runs inside the dispatch launch
+            y, ids, wts = self.exchange.mlp(h2, None, None, self._local_mlp,
+                                            local_mlp_scatter=self._local_mlp_scatter if self.fuse_return else None,
+                                            router_weight=self.wrouter, top_k=cfg.top_k, return_routing=True)
         else:
+            ids, wts = self.moe.route_topk(h2, self.wrouter, cfg.top_k)
             y = moe_parallel.expert_parallel_mlp_device(self.moe, h2, ids, wts, cfg.experts, self._local_mlp,
-                                                        self.group, self.segment_rows)
+                                                        self.group, self.segment_rows, local=self.local_only)
         if return_routing:
             return y, res2, ids, wts
         return y, res2
@@ -190,11 +192,11 @@ class MoEDecodeLayer:
     # number of this library's kernels one single-GPU forward launches (for the benchmark's
     # accounting): 2 add_rms_norm, 2 dense GEMMs, fused rope+cache, attention (one kernel: the
     # chunk merge is fused), route, permute, copy_rows, gate/up GEMM with SwiGLU epilogue, down GEMM,
-    # finalize.  Under expert parallelism with the peer-memory exchange the MoE part is route,
-    # permute, push_rows, barrier, ep_plan, copy_rows, gate/up GEMM with SwiGLU epilogue, down GEMM
-    # with scatter epilogue, barrier, finalize.
+    # finalize.  Under expert parallelism with the peer-memory exchange the MoE part is dispatch
+    # (router inside), gather, gate/up GEMM with SwiGLU epilogue, down GEMM with scatter epilogue,
+    # combine.
     KERNEL_LAUNCHES = 12
-    KERNEL_LAUNCHES_EP = 16
+    KERNEL_LAUNCHES_EP = 11
 
 
 class CapturedDecodeStep:

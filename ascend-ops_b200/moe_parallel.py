@@ -132,7 +132,7 @@ def expert_parallel_mlp(x, expert_ids, expert_weights, num_experts, local_mlp, g
 
 
 def expert_parallel_mlp_device(moe, x, expert_ids, expert_weights, num_experts, local_mlp, group=None,
-                               segment_rows=None, overflow_out=None):
+                               segment_rows=None, overflow_out=None, local=False):
     """Same contract as expert_parallel_mlp, built from the library's own glue kernels
     (`ascend910a_extras.moe`) with every piece of metadata on the device: no host
     synchronisation anywhere in the step.
@@ -146,10 +146,13 @@ def expert_parallel_mlp_device(moe, x, expert_ids, expert_weights, num_experts, 
     `segment_rows`.  A capacity below T*top_k can overflow: rows that do not fit are left out of
     the result and counted in a device int32 that is appended to `overflow_out` (a list) for the
     caller to inspect later -- reading it here would be the host sync this path exists to avoid.
+    `local=True` runs the single-GPU form whatever process group exists (this rank then needs
+    every expert's weights behind `local_mlp`).
     """
     t, top_k = expert_ids.shape
     slots, hidden = t * top_k, x.shape[1]
-    distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+    distributed = (not local and dist.is_available() and dist.is_initialized()
+                   and dist.get_world_size(group) > 1)
     if not distributed:
         pos, _, group_list, _ = moe.permute(expert_ids, num_experts, 1, 0)
         rows = x.new_empty(slots, hidden)
@@ -195,6 +198,14 @@ class Placement:
     def local_slot_experts(self, rank):
         s = self.slots_per_rank
         return self.slot_expert[rank * s:(rank + 1) * s].tolist()
+
+    def to(self, device):
+        """The tables on `device` (also as the int32 tensors `moe.dispatch` reads)."""
+        self.expert_slots = self.expert_slots.to(device)
+        self.num_replicas = self.num_replicas.to(device)
+        self.expert_slots_i32 = self.expert_slots.to(torch.int32).contiguous()
+        self.num_replicas_i32 = self.num_replicas.to(torch.int32).contiguous()
+        return self
 
 
 def balanced_placement(load, world: int, slots_per_rank: int) -> Placement:
@@ -256,33 +267,48 @@ class PeerExchange:
     """Expert-parallel dispatch/combine over NVLink peer memory instead of NCCL collectives.
 
     Each rank holds, in symmetric memory its peers have mapped, a receive buffer and a return
-    buffer of `world` segments of `segment_rows` rows, a table of every rank's per-expert
-    counts, and a flag array.  `moe.push_rows` gathers the routed rows and stores them straight
-    into the owners' receive buffers (and the counts into their tables); `moe.peer_barrier`
-    tells the peers and waits for them (bounded).  The way back works the same with the return
-    buffers.  Compared with the NCCL path this removes the send-side staging copy, the count
-    all-gather and two collective launches from the step.
+    buffer, a table of row counts and two flag arrays.  A step is three launches around the two
+    expert GEMMs (`moe.dispatch`, `moe.gather`, `moe.combine`):
 
-    Buffer reuse across steps is safe without extra synchronisation: a rank passes the second
-    barrier of step n only after every peer has finished reading its receive buffer, and a
-    peer writes into this rank's return buffer only after this rank's first barrier of step
-    n+1, which its stream issues after the `finalize` of step n.
-    All ranks must construct the object together and call `mlp` the same number of times.
+    * dispatch routes every token (or takes the given expert ids), claims a row of the
+      (this rank, slot) sub-segment in the slot owner's receive buffer and stores the token's row
+      there through the peer mapping; its last CTA sends the counts and announces the step;
+    * gather waits (bounded) for every peer's announcement and compacts the received rows into
+      expert-major order for `grouped_matmul`;
+    * the down projection stores its result rows straight into the owners' return buffers
+      (`moe.grouped_matmul_scatter`), and combine announces "returned", waits (bounded) for the
+      peers and forms the weighted sum.
+
+    `slots_per_rank` slots live on every rank (an expert, or a replica of a replicated expert: pass
+    a `Placement` to `mlp`); a (source, slot) sub-segment holds `segment_rows` rows; rows that do
+    not fit are left out and counted in `overflow` (device int32 [2]: at dispatch, at gather).
+
+    Buffer reuse across steps needs no extra synchronisation: a rank starts dispatching step
+    n+1 only after its combine of step n, which waited for every peer's "returned" of step n, and
+    a peer sends that only after its own gather of step n has read its receive buffer; a peer's
+    down projection of step n+1 writes into this rank's return buffer only after that peer's
+    gather of step n+1, which waited for this rank's dispatch of step n+1, which its stream issues
+    after the combine of step n.  All ranks must construct the object together and call `mlp` the
+    same number of times.
     """
 
-    def __init__(self, moe, group, device, segment_rows, hidden, hidden_out, num_experts):
+    def __init__(self, moe, group, device, segment_rows, hidden, hidden_out, num_slots, max_rows=None):
         import torch.distributed._symmetric_memory as symm
 
         self.moe, self.group = moe, group
         self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        self.cap, self.num_experts = int(segment_rows), int(num_experts)
-        rows = self.world * self.cap
+        self.cap, self.num_slots = int(segment_rows), int(num_slots)
+        assert self.num_slots % self.world == 0, "slots must divide evenly over ranks"
+        self.spr = self.num_slots // self.world
+        rows = self.num_slots * self.cap  # world * spr * cap, both for receiving and for returning
+        self.max_rows = rows if max_rows is None else min(int(max_rows), rows)
         align = lambda n: (n + 255) // 256 * 256
         o_recv = 0
         o_ret = o_recv + align(rows * hidden * 2)
         o_counts = o_ret + align(rows * hidden_out * 2)
-        o_flags = o_counts + align(self.world * num_experts * 4)
-        total = o_flags + align(self.world * 4)
+        o_flags_d = o_counts + align(self.world * self.spr * 4)
+        o_flags_r = o_flags_d + align(self.world * 4)
+        total = o_flags_r + align(self.world * 4)
         self.buf = symm.empty(total, dtype=torch.uint8, device=device)
         self.handle = symm.rendezvous(self.buf, group.group_name)
         self.buf.zero_()
@@ -290,40 +316,59 @@ class PeerExchange:
         self.peer_recv = [p + o_recv for p in ptrs]
         self.peer_ret = [p + o_ret for p in ptrs]
         self.peer_counts = [p + o_counts for p in ptrs]
-        self.peer_flags = [p + o_flags for p in ptrs]
+        self.peer_flags_d = [p + o_flags_d for p in ptrs]
+        self.peer_flags_r = [p + o_flags_r for p in ptrs]
         self.recv = self.buf[o_recv:o_recv + rows * hidden * 2].view(torch.float16).view(rows, hidden)
         self.ret = self.buf[o_ret:o_ret + rows * hidden_out * 2].view(torch.float16).view(rows, hidden_out)
-        self.counts_all = self.buf[o_counts:o_counts + self.world * num_experts * 4].view(torch.int32).view(
-            self.world, num_experts)
-        self.flags = self.buf[o_flags:o_flags + self.world * 4].view(torch.int32)
-        self.state = torch.zeros(2, dtype=torch.int32, device=device)
+        self.counts = self.buf[o_counts:o_counts + self.world * self.spr * 4].view(torch.int32).view(
+            self.world, self.spr)
+        self.flags_d = self.buf[o_flags_d:o_flags_d + self.world * 4].view(torch.int32)
+        self.flags_r = self.buf[o_flags_r:o_flags_r + self.world * 4].view(torch.int32)
+        self.cursor = torch.zeros(self.num_slots, dtype=torch.int32, device=device)
+        self.state = torch.zeros(8, dtype=torch.int32, device=device)
+        self.overflow = torch.zeros(2, dtype=torch.int32, device=device)
         torch.cuda.synchronize(device)
-        dist.barrier(group)  # everyone's flags are zero before anyone pushes
+        dist.barrier(group)  # everyone's flags are zero before anyone announces
 
     def barrier_error(self) -> int:
-        """0, or 100 + the rank that did not arrive within the barrier's time limit (synchronises)."""
+        """0, or 100 + the rank whose announcement did not arrive within the time limit (synchronises)."""
         return int(self.state[1].item())
 
-    def mlp(self, x, expert_ids, expert_weights, local_mlp, overflow_out=None, local_mlp_scatter=None):
+    def mlp(self, x, expert_ids, expert_weights, local_mlp, overflow_out=None, local_mlp_scatter=None,
+            router_weight=None, top_k=None, placement=None, token_offset=0, num_experts=None,
+            return_routing=False):
         """Same contract as expert_parallel_mlp_device for world > 1.
 
+        Either `expert_ids` [T, top_k] int32 with `expert_weights` [T, top_k] float32, or
+        `router_weight` [E, H] with `top_k` (the routing then happens inside the dispatch launch).
+        `placement` (a `Placement` whose tables are on the device) maps experts to slots.
         `local_mlp_scatter(rows, group_list, scatter)`, if given, replaces `local_mlp` plus the
         return push: it must end in `moe.grouped_matmul_scatter(..., *scatter)`, whose epilogue
         stores the result rows into the peers' return buffers itself."""
-        moe, world, rank, cap = self.moe, self.world, self.rank, self.cap
-        t, top_k = expert_ids.shape
-        pos, counts, _, overflow = moe.permute(expert_ids, self.num_experts, world, cap)
+        moe, rank = self.moe, self.rank
+        if num_experts is None:
+            num_experts = router_weight.shape[0] if router_weight is not None else (
+                placement.num_replicas.numel() if placement is not None else self.num_slots)
+        k = top_k if router_weight is not None else expert_ids.shape[1]
+        slots_tab = placement.expert_slots_i32 if placement is not None else None
+        reps_tab = placement.num_replicas_i32 if placement is not None else None
+        pos, ids, wts = moe.dispatch(x, router_weight, None if router_weight is not None else expert_ids, k,
+                                     slots_tab, reps_tab, token_offset, self.peer_recv, self.peer_counts,
+                                     self.peer_flags_d, self.cursor, self.state, self.overflow, num_experts,
+                                     self.cap, rank)
+        if router_weight is None:
+            wts = expert_weights
         if overflow_out is not None:
-            overflow_out.append(overflow)
-        moe.push_rows(x, pos, top_k, None, t * top_k, self.peer_recv, cap, rank, counts, self.peer_counts)
-        moe.peer_barrier(self.peer_flags, self.flags, self.state, rank)
-        grouped_to_received, group_list, total = moe.ep_plan(self.counts_all, rank, cap)
-        grouped = x.new_empty(world * cap, x.shape[1])
-        moe.copy_rows(grouped, self.recv, src_index=grouped_to_received, n_valid=total, n_max=world * cap)
+            overflow_out.append(self.overflow)
+        grouped, to_received, group_list, total = moe.gather(self.recv, self.counts, self.flags_d, self.state,
+                                                             self.overflow, self.cap, self.max_rows)
+        seg = self.spr * self.cap  # rows one source owns in a receive buffer
         if local_mlp_scatter is not None:
-            local_mlp_scatter(grouped, group_list, (grouped_to_received, self.peer_ret, cap, rank))
+            local_mlp_scatter(grouped, group_list, (to_received, self.peer_ret, seg, rank))
         else:
             res = local_mlp(grouped, group_list)
-            moe.push_rows(res, grouped_to_received, 1, total, world * cap, self.peer_ret, cap, rank)
-        moe.peer_barrier(self.peer_flags, self.flags, self.state, rank)
-        return moe.finalize(self.ret, pos, expert_weights)
+            moe.push_rows(res, to_received, 1, total, self.max_rows, self.peer_ret, seg, rank)
+        y = moe.combine(self.ret, pos, wts, self.peer_flags_r, self.flags_r, self.state, rank)
+        if return_routing:
+            return y, ids, wts
+        return y

@@ -3,10 +3,14 @@
     python bench.py --gpus N --steps K --warmup W          this implementation (GPU)
     python bench.py --impl reference ...                    the CPU golden path, for the ratio
 
-Prints ONE JSON line on rank 0: `value` is device-timed with inputs resident in HBM, `e2e` goes through the public
-`ascend910a_extras.ops` API from pinned host buffers with the copies inside the timed
-region, `roofline` is the dominant kernel against the measured peak, `per_op` lists every
-operator of the path, and `cpu_baseline` times the CPU oracle on a bounded sample.
+Prints ONE JSON line on rank 0: `value` is device-timed with inputs resident in HBM, `e2e` goes
+through the public `ascend910a_extras.ops` API from pinned host buffers with the copies inside
+the timed region, `roofline` is the dominant kernel against the measured peak, `cpu_baseline`
+times the CPU oracle's layer step, `ep_check` (more than one GPU) compares the exchanged result
+with the single-GPU path, and `per_op` holds one short row per operator (columns in
+`per_op_cols`: device time, achieved rate, fraction of the measured peak, the CPU oracle's time
+on all host threads, and the GPU result's error against it).  Shapes, byte counts and the other
+details of every row go to gpurun_out/bench_detail_n<N>.json.
 """
 from __future__ import annotations
 
@@ -28,9 +32,9 @@ import torch  # noqa: E402
 
 import decode_workloads as wl  # noqa: E402
 
-# DRAM traffic of the attention kernel relative to its algorithmic bytes, from the ncu capture
-# summarised in profiles/paged_attention_fast_kernel__16seq_gqa7.md (dram read + write over
-# algorithmic bytes on a 16-sequence case; traffic grows in proportion to the context tokens).
+# DRAM traffic of the attention kernel relative to its algorithmic bytes (dram read + write over
+# algorithmic bytes in an ncu capture of a 16-sequence case; the traffic grows in proportion to
+# the context tokens, so the ratio carries over to the full batch).
 ATTENTION_TRAFFIC_RATIO = 1.05
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
@@ -167,6 +171,51 @@ def sets_for(bytes_per_set, minimum=2, maximum=16):
 
 
 # --------------------------------------------------------------------------- per-op cases
+# Every case returns one row: device time and roofline fraction of the operator at its benchmark
+# size, and beside it the CPU oracle on the same tensors -- its time on all host threads and the
+# error of the GPU result against it (max |got - want|, and the largest |got - want| /
+# (atol + rtol * |want|) with the operator's tolerance rtol 1e-2 / atol 1e-3: <= 1 passes).
+RTOL, ATOL = 1e-2, 1e-3
+
+
+def _oracle():
+    from oracle import decode_ops_oracle as oracle
+
+    torch.set_num_threads(len(os.sched_getaffinity(0)))
+    return oracle
+
+
+def cpu_run(fn, repeats=1):
+    best, out = None, None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        out = fn()
+        dt = (time.perf_counter() - t0) * 1e6
+        best = dt if best is None else min(best, dt)
+    return out, best
+
+
+def errors(got, want):
+    d = (got.float() - want.float()).abs()
+    return float(d.max()), float((d / (ATOL + RTOL * want.float().abs())).max())
+
+
+def op_record(name, us, work, peaks, bound, cpu_us=None, err=None, launches=1, cpu_sample=None, **detail):
+    if bound == "hbm":
+        achieved, unit, peak = work / us / 1e3, "GB/s", peaks["hbm_gbs"]
+    else:
+        achieved, unit, peak = work / us / 1e6, "TFLOP/s", peaks["bf16_tflops"]
+    rec = {"op": name, "us": round(us, 2), "achieved": round(achieved, 1), "unit": unit, "peak": peak,
+           "frac": round(achieved / peak, 4), "bound": bound, "launches": launches,
+           "work": int(work), "cpu_us": None if cpu_us is None else round(cpu_us, 1),
+           "max_abs_err": None if err is None else float(f"{err[0]:.3g}"),
+           "err_over_tol": None if err is None else float(f"{err[1]:.3g}")}
+    if cpu_sample is not None:
+        rec["cpu_sample"] = cpu_sample
+    rec.update(detail)
+    return rec
+
+
 def case_add_rms_norm(ops, dev, steps, warmup, peaks):
     d = wl.add_rms_norm_inputs()
     t, h = d["x"].shape
@@ -176,15 +225,25 @@ def case_add_rms_norm(ops, dev, steps, warmup, peaks):
     rs = [d["residual"].to(dev).clone() for _ in range(n)]
     w = d["weight"].to(dev)
     us, _ = time_graph(lambda i: ops.add_rms_norm(xs[i], rs[i], w, d["eps"]), n, 2 * n, steps, warmup, dev)
-    return op_record("add_rms_norm", f"[{t},{h}] f16", nbytes, us, peaks, "hbm", launches=1)
+    y, res = ops.add_rms_norm(xs[0], rs[0], w, d["eps"])
+    oracle = _oracle()
+    (ey, eres), cpu_us = cpu_run(lambda: oracle.add_rms_norm(d["x"], d["residual"], d["weight"], d["eps"]), 2)
+    err = errors(y.cpu(), ey)
+    if not torch.equal(res.cpu(), eres):
+        err = (float("inf"), float("inf"))  # residual_out is a bit-exact contract
+    return op_record("add_rms_norm", us, nbytes, peaks, "hbm", cpu_us, err, shape=f"[{t},{h}] f16")
 
 
 def case_swiglu(ops, dev, steps, warmup, peaks):
     t, dd = 8192, 14336
-    x = wl.swiglu_inputs(t, dd)["x"].to(dev)
+    xc = wl.swiglu_inputs(t, dd)["x"]
+    x = xc.to(dev)
     nbytes = 6 * t * dd
     us, _ = time_launches(lambda i: ops.swiglu(x), 1, steps, warmup, dev)
-    return op_record("swiglu", f"[{t},{2 * dd}] f16", nbytes, us, peaks, "hbm", launches=1)
+    oracle = _oracle()
+    want, cpu_us = cpu_run(lambda: oracle.swiglu(xc))
+    return op_record("swiglu", us, nbytes, peaks, "hbm", cpu_us, errors(ops.swiglu(x).cpu(), want),
+                     shape=f"[{t},{2 * dd}] f16")
 
 
 def case_rope(ops, dev, steps, warmup, peaks):
@@ -197,7 +256,13 @@ def case_rope(ops, dev, steps, warmup, peaks):
     ks = [r["k"].to(dev).clone() for _ in range(n)]
     pos, cos, sin = r["position_ids"].to(dev), r["cos_cache"].to(dev), r["sin_cache"].to(dev)
     us, _ = time_graph(lambda i: ops.rope(qs[i], ks[i], pos, cos, sin), n, 2 * n, steps, warmup, dev)
-    return op_record("rope", f"q[{t},{hq},{d}] k[{t},{hkv},{d}] f16", nbytes, us, peaks, "hbm", launches=1)
+    oq, ok = ops.rope(qs[0], ks[0], pos, cos, sin)
+    oracle = _oracle()
+    (eq, ek), cpu_us = cpu_run(lambda: oracle.rope(r["q"], r["k"], r["position_ids"], r["cos_cache"],
+                                                   r["sin_cache"]), 2)
+    e1, e2 = errors(oq.cpu(), eq), errors(ok.cpu(), ek)
+    return op_record("rope", us, nbytes, peaks, "hbm", cpu_us, (max(e1[0], e2[0]), max(e1[1], e2[1])),
+                     shape=f"q[{t},{hq},{d}] k[{t},{hkv},{d}] f16")
 
 
 def case_reshape_and_cache(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_NHD, tokens=2048):
@@ -216,8 +281,19 @@ def case_reshape_and_cache(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_N
                        steps, warmup, dev)
     name = "reshape_and_cache" + ("" if layout == wl.KV_LAYOUT_NHD else "_nz") + (
         "" if tokens == 2048 else f"_{tokens}tok")
-    return op_record(name, f"{t} tokens -> cache {list(c['cache_shape'])} f16", nbytes, us, peaks, "hbm",
-                     launches=1)
+    cpu_us, err = None, None
+    if tokens == 2048:  # the benchmark size: bit-exact against the oracle on fresh caches
+        kc.zero_()
+        vc.zero_()
+        ops.reshape_and_cache(keys[0], vals[0], kc, vc, c["slot_indices"].to(dev))
+        oracle = _oracle()
+        ekc = torch.zeros(c["cache_shape"], dtype=torch.float16)
+        evc = torch.zeros(c["cache_shape"], dtype=torch.float16)
+        _, cpu_us = cpu_run(lambda: oracle.reshape_and_cache(c["key"], ekc, c["slot_indices"], c["value"], evc))
+        same = torch.equal(kc.cpu(), ekc) and torch.equal(vc.cpu(), evc)
+        err = (0.0, 0.0) if same else (float("inf"), float("inf"))
+    return op_record(name, us, nbytes, peaks, "hbm", cpu_us, err,
+                     shape=f"{t} tokens -> cache {list(c['cache_shape'])} f16")
 
 
 def case_paged_attention(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_NHD):
@@ -227,11 +303,13 @@ def case_paged_attention(ops, dev, steps, warmup, peaks, layout=wl.KV_LAYOUT_NHD
     bt, cl = a["block_tables"].to(dev), a["context_lens"].to(dev)
     us, _ = time_launches(lambda i: ops.paged_attention(q, kc, vc, bt, cl), 1, steps, warmup, dev)
     nz = layout == wl.KV_LAYOUT_NZ
-    rec = op_record("paged_attention_nz" if nz else "paged_attention",
-                    "B=64 28q/4kv D=128 L~U[512,8192] page 128" + (", cache [blocks, 32, 128, 16]" if nz else ""),
-                    nbytes, us, peaks, "hbm", launches=1)
-    rec["sum_context"] = int(a["context_lens"].sum())
-    return rec
+    oracle = _oracle()
+    want, cpu_us = cpu_run(lambda: oracle.paged_attention(a["q"], a["key_cache"], a["value_cache"],
+                                                          a["block_tables"], a["context_lens"]))
+    return op_record("paged_attention_nz" if nz else "paged_attention", us, nbytes, peaks, "hbm", cpu_us,
+                     errors(ops.paged_attention(q, kc, vc, bt, cl).cpu(), want),
+                     shape="B=64 28q/4kv D=128 L~U[512,8192] page 128" + (", cache [blocks, 32, 128, 16]" if nz else ""),
+                     sum_context=int(a["context_lens"].sum()))
 
 
 def case_grouped_matmul(ops, dev, steps, warmup, peaks, which="gate_up"):
@@ -241,14 +319,25 @@ def case_grouped_matmul(ops, dev, steps, warmup, peaks, which="gate_up"):
     wv = ws.transpose(1, 2)
     flops = 2 * 8192 * k * n
     us, _ = time_launches(lambda i: ops.grouped_matmul(x, wv, gl), 1, steps, warmup, dev)
-    tf = flops / us / 1e6
-    peak = peaks["bf16_tflops"]
-    return {"op": f"grouped_matmul_{which}", "shape": f"8 experts, 8192 rows, {k}->{n} f16",
-            "flops": flops, "us": round(us, 2), "achieved": round(tf, 1), "unit": "TFLOP/s",
-            "peak": peak, "frac": round(tf / peak, 4),
-            "frac_of_sustained": round(tf / peaks.get("bf16_tflops_sustained", peak), 4),
-            "bound": "tensor", "launches": 1,
-            "group_rows": torch.diff(w["group_list"], prepend=torch.zeros(1, dtype=torch.int64)).tolist()}
+    # CPU oracle on every 4th row of every group (the full product is about ten seconds of host
+    # time per shape); its time is scaled by 4 and the errors are those of the sampled rows.
+    y = ops.grouped_matmul(x, wv, gl)
+    ends = w["group_list"].tolist()
+    rows, sample_ends, lo = [], [], 0
+    for e in ends:
+        rows.extend(range(lo, e, 4))
+        sample_ends.append(len(rows))
+        lo = e
+    idx = torch.tensor(rows, dtype=torch.long)
+    oracle = _oracle()
+    want, cpu_us = cpu_run(lambda: oracle.grouped_matmul(w["x"][idx], w["w_storage"].transpose(1, 2),
+                                                         torch.tensor(sample_ends, dtype=torch.int64)))
+    rec = op_record(f"grouped_matmul_{which}", us, flops, peaks, "tensor", cpu_us * 4,
+                    errors(y[idx.to(dev)].cpu(), want), cpu_sample="every 4th row of each group, time x4",
+                    shape=f"8 experts, 8192 rows, {k}->{n} f16",
+                    group_rows=torch.diff(w["group_list"], prepend=torch.zeros(1, dtype=torch.int64)).tolist())
+    rec["frac_of_sustained"] = round(rec["achieved"] / peaks.get("bf16_tflops_sustained", rec["peak"]), 4)
+    return rec
 
 
 def case_dense_projection(ops, dev, steps, warmup, peaks, rows=256, k=4096, n=6144):
@@ -262,14 +351,11 @@ def case_dense_projection(ops, dev, steps, warmup, peaks, rows=256, k=4096, n=61
           for _ in range(sets)]
     gl = torch.tensor([rows], dtype=torch.int64, device=dev)
     us, _ = time_graph(lambda i: ops.grouped_matmul(x, ws[i], gl), sets, 2 * sets, steps, warmup, dev)
-    return op_record("dense_projection_qkv", f"[{rows},{k}] x [{k},{n}] f16", nbytes, us, peaks, "hbm", launches=1)
-
-
-def op_record(name, shape, nbytes, us, peaks, bound, launches):
-    gbs = nbytes / us / 1e3
-    return {"op": name, "shape": shape, "bytes": int(nbytes), "us": round(us, 3),
-            "achieved": round(gbs, 1), "unit": "GB/s", "peak": peaks["hbm_gbs"],
-            "frac": round(gbs / peaks["hbm_gbs"], 4), "bound": bound, "launches": launches}
+    oracle = _oracle()
+    xc, wc = x.cpu(), ws[0].cpu()
+    want, cpu_us = cpu_run(lambda: oracle.grouped_matmul(xc, wc, gl.cpu()), 2)
+    return op_record("dense_projection_qkv", us, nbytes, peaks, "hbm", cpu_us,
+                     errors(ops.grouped_matmul(x, ws[0], gl).cpu(), want), shape=f"[{rows},{k}] x [{k},{n}] f16")
 
 
 # --------------------------------------------------------------------------- the layer step
@@ -280,14 +366,14 @@ LAYER_WORKLOAD = ("MoE decoder layer, decode step: batch 256, hidden 4096, 32q/8
 EXCHANGE = "peer"  # "peer": NVLink peer-memory pushes (moe_parallel.PeerExchange); "nccl": collectives
 
 
-def make_exchange(group, dev, segment_rows, hidden, hidden_out, num_experts):
+def make_exchange(group, dev, segment_rows, hidden, hidden_out, num_slots, max_rows=None):
     """The expert-parallel exchange object for this run (None = NCCL collectives or 1 GPU)."""
     if group is None or EXCHANGE != "peer":
         return None
     import ascend910a_extras.moe as moe
     import moe_parallel
 
-    return moe_parallel.PeerExchange(moe, group, dev, segment_rows, hidden, hidden_out, num_experts)
+    return moe_parallel.PeerExchange(moe, group, dev, segment_rows, hidden, hidden_out, num_slots, max_rows)
 
 
 def balanced_sequence_shard(positions, world, rank):
@@ -324,6 +410,40 @@ def build_layer(ops, dev, rank, world, group):
     k_cache = torch.randn(batch["cache_shape"], generator=g, device=dev, dtype=torch.float16)
     v_cache = torch.randn(batch["cache_shape"], generator=g, device=dev, dtype=torch.float16)
     return cfg, layer, batch, k_cache, v_cache, int(pos.long().sum()) + 256
+
+
+def gather_check(ok, max_err, rows, group, dev):
+    """Combine the ranks' value checks: all must pass; the largest error and the row total."""
+    t = torch.tensor([0.0 if ok else 1.0, max_err, float(rows)], device=dev, dtype=torch.float64)
+    if group is not None:
+        worst = t[:2].clone()
+        torch.distributed.all_reduce(worst, op=torch.distributed.ReduceOp.MAX, group=group)
+        total = t[2:].clone()
+        torch.distributed.all_reduce(total, op=torch.distributed.ReduceOp.SUM, group=group)
+        t = torch.cat([worst, total])
+    return {"ok": bool(t[0] == 0), "max_abs_err": float(f"{float(t[1]):.3g}"), "rows": int(t[2])}
+
+
+def check_layer_against_single_gpu(ops, dev, layer, inp, k_cache, v_cache, y_ep, res_ep, group):
+    """Value check of the expert-parallel step that was just timed: the same layer with ALL
+    experts on this GPU and no exchange (the single-GPU path) runs this rank's sequences, and its
+    output must match the exchanged result (residual bit for bit; y within the operators'
+    tolerance, since the GEMM kernels chosen for the local row counts differ)."""
+    import moe_decode_layer as mdl
+
+    cfg = layer.cfg
+    w_all = mdl.make_weights(cfg, seed=7, device=dev)
+    solo = mdl.MoEDecodeLayer(cfg, w_all, dev, ops, group=None)
+    solo.local_only = True
+    y, res = solo.forward(inp["x"], inp["residual"], inp["positions"], inp["slots"], inp["block_tables"],
+                          inp["context_lens"], k_cache, v_cache)
+    torch.cuda.synchronize(dev)
+    d = (y.float() - y_ep.float()).abs()
+    ok = bool(torch.equal(res, res_ep)) and bool((d <= 2e-3 + 1e-2 * y.float().abs()).all())
+    out = gather_check(ok, float(d.max()), y.shape[0], group, dev)
+    del solo, w_all
+    torch.cuda.empty_cache()
+    return out
 
 
 def run_layer(ops, dev, rank, world, group, steps, warmup, peaks):
@@ -400,6 +520,12 @@ def run_layer(ops, dev, rank, world, group, steps, warmup, peaks):
     torch.cuda.synchronize(dev)
     if not (torch.equal(hosted.host_y, y_dev.cpu()) and torch.equal(hosted.host_res, res_dev.cpu())):
         raise RuntimeError("host-to-host step and device-resident step disagree")
+    ep_check = None
+    if world > 1:
+        sync_all()
+        if layer.exchange is not None and layer.exchange.barrier_error() != 0:
+            raise RuntimeError(f"a peer announcement timed out: {layer.exchange.barrier_error()}")
+        ep_check = check_layer_against_single_gpu(ops, dev, layer, devt, k_cache, v_cache, y_dev, res_dev, group)
 
     local_ctx = int(batch["context_lens"].long().sum())
     attn_bytes = wl.paged_attention_bytes(batch["context_lens"], cfg.kv_heads, cfg.head_dim, cfg.heads,
@@ -408,7 +534,8 @@ def run_layer(ops, dev, rank, world, group, steps, warmup, peaks):
     return {
         "layer_us": layer_us, "eager_us": eager_us, "e2e_us": e2e_us, "h2d": h2d, "d2h": d2h,
         "attention": {"us": attn_us, "bytes": attn_bytes, "gbs": gbs, "local_context": local_ctx},
-        "launches": 3 * steps * (layer.KERNEL_LAUNCHES if world == 1 else layer.KERNEL_LAUNCHES_EP), "total_context": total_context,
+        "launches": 3 * steps * (layer.KERNEL_LAUNCHES if world == 1 else layer.KERNEL_LAUNCHES_EP),
+        "total_context": total_context, "ep_check": ep_check,
     }
 
 
@@ -419,10 +546,12 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
     [14336 -> 4096].  Tokens are sharded over ranks.  Experts are placed by load: every rank has
     ceil(E/G) + 2 slots, hot experts are replicated into the spare slots and their rows spread
     over the replicas (moe_parallel.balanced_placement), because with one expert per GPU the
-    busiest expert (47 % of the rows here) would bound the step.  Rows travel with the
-    fixed-capacity all-to-all at twice the balanced share per peer; an overflow is detected on
-    the device and the measurement repeated at full capacity.  Reports whole-job TFLOP/s of the
-    two GEMMs (everything else in the step is overhead counted against them)."""
+    busiest expert (47 % of the rows here) would bound the step.  Rows travel through bounded
+    sub-segments (twice the expected rows per source and slot) into a bounded row buffer (1.25
+    times a rank's expected rows); an overflow is detected on the device and the measurement
+    repeated at full capacity.  Reports whole-job TFLOP/s of the two GEMMs (everything else in
+    the step is overhead counted against them).  At more than one GPU the result of a sample
+    of every rank's tokens is checked against the single-GPU path with all experts local."""
     import ascend910a_extras.moe as moe
     import moe_decode_layer as mdl
     import moe_parallel
@@ -434,9 +563,7 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
     load = torch.bincount(ids_flat, minlength=cfg.experts).tolist()
     per = tokens // world
     spr = -(-cfg.experts // world) + (2 if world > 1 else 0)
-    placement = moe_parallel.balanced_placement(load, world, spr)
-    placement.expert_slots = placement.expert_slots.to(dev)
-    placement.num_replicas = placement.num_replicas.to(dev)
+    placement = moe_parallel.balanced_placement(load, world, spr).to(dev)
     my_ids = ids[rank * per:(rank + 1) * per].contiguous().to(dev)
     g = torch.Generator(device=dev).manual_seed(40 + rank)
     x = torch.randn(per, cfg.hidden, generator=g, device=dev, dtype=torch.float16)
@@ -444,20 +571,33 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
     w = mdl.make_weights(cfg, seed=7, experts=placement.local_slot_experts(rank), device=dev)
     w_gu, w_dn = w["w_gate_up"].transpose(1, 2), w["w_down"].transpose(1, 2)
     full_cap = per * top_k
-    # twice the share a peer is owed under perfect balance, rounded up to 64 rows
-    cap = min(full_cap, (-(-2 * full_cap // world) + 63) // 64 * 64) if world > 1 else full_cap
+    up = lambda v, m: -(-int(v) // m) * m
+    slot_rows = [load[e] / int(placement.num_replicas[e]) for e in placement.slot_expert.tolist()]
+    rank_rows = [sum(slot_rows[r * spr:(r + 1) * spr]) for r in range(world)]
+    if world > 1 and EXCHANGE == "peer":  # rows of one (source, slot) sub-segment; rows of the grouped buffer
+        cap = min(full_cap, up(2 * max(slot_rows) / world, 64))
+        max_rows = up(1.25 * max(rank_rows), 128)
+    elif world > 1:  # NCCL form: one segment per peer, twice the balanced share
+        cap, max_rows = min(full_cap, up(2 * full_cap / world, 64)), None
+    else:
+        cap, max_rows = full_cap, None
 
     def local_mlp(rows, gl):
         return ops.grouped_matmul(moe.grouped_matmul_swiglu(rows, w_gu, gl), w_dn, gl)
 
-    def measure(capacity):
+    def local_mlp_scatter(rows, gl, scatter):
+        moe.grouped_matmul_scatter(moe.grouped_matmul_swiglu(rows, w_gu, gl), w_dn, gl, *scatter)
+
+    def measure(capacity, rows_bound):
         flags = []
-        exchange = make_exchange(group, dev, capacity, cfg.hidden, cfg.hidden, placement.num_slots)
+        exchange = make_exchange(group, dev, capacity, cfg.hidden, cfg.hidden, placement.num_slots, rows_bound)
 
         def step():
-            slot_ids = moe_parallel.to_slot_ids(my_ids, placement, rank * per)
             if exchange is not None:
-                return exchange.mlp(x, slot_ids, wts, local_mlp, overflow_out=flags)
+                return exchange.mlp(x, my_ids, wts, local_mlp, overflow_out=flags,
+                                    local_mlp_scatter=local_mlp_scatter, placement=placement,
+                                    token_offset=rank * per, num_experts=cfg.experts)
+            slot_ids = moe_parallel.to_slot_ids(my_ids, placement, rank * per)
             return moe_parallel.expert_parallel_mlp_device(moe, x, slot_ids, wts, placement.num_slots, local_mlp,
                                                            group, capacity, overflow_out=flags)
 
@@ -472,7 +612,7 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
         del flags[:]
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=side):
-            step()
+            y_graph = step()
         torch.cuda.current_stream(dev).wait_stream(side)
         for _ in range(warmup):
             graph.replay()
@@ -485,27 +625,44 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
             graph.replay()
         t1.record()
         torch.cuda.synchronize(dev)
-        t = torch.tensor([t0.elapsed_time(t1), float(flags[-1].item()) if flags else 0.0], device=dev)
+        dropped = float(flags[-1].sum().item()) if flags else 0.0
+        t = torch.tensor([t0.elapsed_time(t1), dropped], device=dev)
         if world > 1:
             torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX, group=group)
-        return float(t[0]) * 1e3 / steps, int(t[1])
+        if exchange is not None and exchange.barrier_error() != 0:
+            raise RuntimeError(f"a peer announcement timed out: {exchange.barrier_error()}")
+        return float(t[0]) * 1e3 / steps, int(t[1]), y_graph
 
-    us, dropped = measure(cap)
-    used_cap = cap
+    us, dropped, y_ep = measure(cap, max_rows)
+    used_cap, used_rows = cap, max_rows
     if dropped > 0:
-        us, dropped = measure(full_cap)
-        used_cap = full_cap
+        us, dropped, y_ep = measure(full_cap, None)
+        used_cap, used_rows = full_cap, None
+    ep_check = None
+    if world > 1:  # the first 64 tokens of every rank through the single-GPU path, all experts local
+        n = min(64, per)
+        w_all = mdl.make_weights(cfg, seed=7, device=dev)
+        a_gu, a_dn = w_all["w_gate_up"].transpose(1, 2), w_all["w_down"].transpose(1, 2)
+        want = moe_parallel.expert_parallel_mlp_device(
+            moe, x[:n].contiguous(), my_ids[:n].contiguous(), wts[:n].contiguous(), cfg.experts,
+            lambda rows, gl: ops.grouped_matmul(moe.grouped_matmul_swiglu(rows, a_gu, gl), a_dn, gl), local=True)
+        torch.cuda.synchronize(dev)
+        d = (want.float() - y_ep[:n].float()).abs()
+        ok = bool((d <= 2e-3 + 1e-2 * want.float().abs()).all()) and bool(want.float().abs().max() > 0)
+        ep_check = gather_check(ok, float(d.max()), n, group, dev)
+        del w_all, a_gu, a_dn
+        torch.cuda.empty_cache()
     flops = 2 * tokens * top_k * cfg.hidden * 3 * cfg.intermediate
-    tf = flops / us / 1e6
-    return {"op": "moe_mlp_expert_parallel", "shape": "4096 tokens top-2 of 8 experts, 4096->2x14336->4096 f16",
-            "flops": flops, "us": round(us, 1), "achieved": round(tf, 1), "unit": "TFLOP/s",
-            "peak": peaks["bf16_tflops"] * world, "frac": round(tf / (peaks["bf16_tflops"] * world), 4),
-            "bound": "tensor", "launches": 7 if world == 1 else 10, "rows_per_expert": load,
-            "slots_per_rank": spr, "replicas_per_expert": placement.num_replicas.tolist(),
-            "balance": round(moe_parallel.placement_balance(load, placement, world), 3),
-            "one_expert_per_slot_balance": round(sum(load) / (cfg.experts * max(load)), 3),
-            "segment_rows": used_cap, "dropped_rows": dropped,
-            "includes": "slot remap, permutation, SwiGLU (in the gate/up GEMM's epilogue) and (for >1 GPU) dispatch/combine"}
+    rec = op_record("moe_mlp_expert_parallel", us, flops, {"bf16_tflops": peaks["bf16_tflops"] * world}, "tensor",
+                    launches=5 if (world == 1 or EXCHANGE == "peer") else 8,
+                    shape="4096 tokens top-2 of 8 experts, 4096->2x14336->4096 f16", rows_per_expert=load,
+                    slots_per_rank=spr, replicas_per_expert=placement.num_replicas.tolist(),
+                    balance=round(moe_parallel.placement_balance(load, placement, world), 3),
+                    one_expert_per_slot_balance=round(sum(load) / (cfg.experts * max(load)), 3),
+                    segment_rows=used_cap, row_bound=used_rows, dropped_rows=dropped,
+                    includes="slot choice, dispatch, SwiGLU (in the gate/up GEMM's epilogue) and (for >1 GPU) gather/combine")
+    rec["ep_check"] = ep_check
+    return rec
 
 
 # --------------------------------------------------------------------------- CPU baseline
@@ -616,6 +773,28 @@ def profile_case(name, ops, dev):
 
 
 # --------------------------------------------------------------------------- main
+PER_OP_COLS = ["us", "achieved", "frac_of_peak", "cpu_us", "max_abs_err", "err_over_tol"]
+
+
+def compact(rec):
+    """One per-op row of the printed line, in the order of PER_OP_COLS (the full rows go to the
+    detail file)."""
+    return [rec["us"], rec["achieved"], rec["frac"], rec["cpu_us"], rec["max_abs_err"], rec["err_over_tol"]]
+
+
+def write_detail(n_gpus, detail):
+    """Everything the printed line leaves out (shapes, byte counts, group sizes, placement), as
+    gpurun_out/bench_detail_n<N>.json next to this file, if that directory can be written."""
+    try:
+        out = REPO / "gpurun_out"
+        out.mkdir(exist_ok=True)
+        path = out / f"bench_detail_n{n_gpus}.json"
+        path.write_text(json.dumps(detail, indent=1))
+        return str(path.relative_to(REPO))
+    except OSError:
+        return None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -625,6 +804,7 @@ def main():
     ap.add_argument("--ops", default="auto",
                     help="per-op cases: comma list, 'all', 'none', or 'auto' (all at 1 GPU, none otherwise)")
     ap.add_argument("--no-layer", action="store_true", help="skip the layer step (per-op cases only)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline of the layer step")
     ap.add_argument("--cpu-seqs", type=int, default=256,
                     help="sequences in the CPU-baseline sample (256 = the whole batch, no extrapolation)")
     ap.add_argument("--exchange", default="peer", choices=["peer", "nccl"],
@@ -644,11 +824,11 @@ def main():
         "metric": "moe_decode_layer_latency", "unit": "us", "n_gpus": ns.gpus, "higher_is_better": False,
         "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": LAYER_WORKLOAD, "parallelism": f"ep{ns.gpus}+batch-sharded attention",
-                   "exchange": ("none (1 GPU)" if ns.gpus == 1 else
-                                "NVLink peer-memory pushes + flag barrier" if ns.exchange == "peer" else
+                   "exchange": ("none" if ns.gpus == 1 else
+                                "NVLink peer pushes, flag waits in the kernels" if ns.exchange == "peer" else
                                 "NCCL all-gather + all-to-all"),
-                   "execution": "step replayed from a CUDA graph; eager_us is the same step launched op by op",
-                   "l2": "inputs larger than L2 (the step streams GBs of KV cache and expert weights)"},
+                   "execution": "CUDA graph replay (eager_us: op by op)",
+                   "l2": "inputs larger than L2 (GBs of KV cache and expert weights per step)"},
     }
 
     if ns.impl == "reference":
@@ -723,8 +903,10 @@ def main():
     if rank != 0:
         return
 
+    # Key order: the contract's keys first, the per-op table last (a reader that keeps only the
+    # end of a long line still sees every operator's row).
     line = dict(base)
-    line.update({"steps": ns.steps, "warmup": ns.warmup, "clocks": clocks, "per_op": per_op})
+    line.update({"steps": ns.steps, "warmup": ns.warmup, "clocks": clocks})
     launches = sum(r["launches"] * max(5, ns.steps // 2) for r in per_op)
     if layer is not None:
         att = layer["attention"]
@@ -734,19 +916,27 @@ def main():
             "eager_us": round(layer["eager_us"], 1),
             "e2e": {"value": round(layer["e2e_us"], 1), "unit": "us",
                     "h2d_bytes_per_step": layer["h2d"], "d2h_bytes_per_step": layer["d2h"]},
-            "roofline": {"bound": "hbm", "kernel": "paged_attention_fast_kernel (chunk merge fused) inside the step",
+            "roofline": {"bound": "hbm", "kernel": "paged_attention_fast_kernel inside the step",
                          "achieved": round(att["gbs"], 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
                          "frac": round(att["gbs"] / peaks["hbm_gbs"], 4),
                          "traffic": int(att["bytes"] * ATTENTION_TRAFFIC_RATIO),
-                         "traffic_source": "ncu capture of a 16-sequence case, scaled by context tokens",
                          "us": round(att["us"], 1), "bytes": att["bytes"], "peak_source": peaks["source"]},
         })
         launches += layer["launches"]
-        if world == 1:
+        if not ns.no_cpu:
             us, dt, seqs = cpu_layer_sample(ns.cpu_seqs)
             line["cpu_baseline"] = {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
                                     "sample": cpu_sample_text(seqs, dt)}
+        if layer["ep_check"] is not None:
+            line["ep_check"] = {"layer": layer["ep_check"], "moe_mlp": mlp["ep_check"] if mlp else None,
+                                "against": "single-GPU path, all experts local"}
+            if not (layer["ep_check"]["ok"] and (mlp is None or mlp["ep_check"]["ok"])):
+                print(json.dumps(line))
+                raise SystemExit("expert-parallel result differs from the single-GPU path")
     line["gpu_launches"] = launches
+    line["detail_file"] = write_detail(ns.gpus, {"per_op": per_op, "layer": layer})
+    line["per_op_cols"] = PER_OP_COLS
+    line["per_op"] = {r["op"]: compact(r) for r in per_op}
     print(json.dumps(line))
 
 

@@ -49,6 +49,15 @@ int b200ops_version(void);
 const char* b200ops_last_error(void);
 
 /*
+ * Tuning variables (B200OPS_GMM_PAIR, B200OPS_PA_MODE, ... listed in INTEGRATION.md) are read
+ * from the environment once per process, at their first use; no launch calls getenv after
+ * that.  This call forgets what was read, so that the next use looks at the environment again
+ * (for tests and tuning sessions that change a variable mid-process).  No counterpart in the
+ * reference.
+ */
+void b200ops_reload_options(void);
+
+/*
  * Device report: SM count, shared memory, L2, memory size/clock/bus, printed to stdout.
  * Replaces native::print_info (csrc/ffi/bind.cpp:26-51).  If `buf` is non-NULL the same
  * text is also copied there (truncated to buf_len, always NUL-terminated).
@@ -102,6 +111,10 @@ int b200ops_rope(const void* q, const void* k, const int32_t* position_ids,
  * `value_cache` may both be NULL (key-only form, ascend910a_extras/ops.py:40-43); if only
  * one of them is NULL values are not written, as in the reference kernel (:24-25,62-64).
  * Bit-exact copy.  No workspace.
+ * A slot named by several tokens: with num_tokens <= 4096 the LAST of them is kept, as in the
+ * reference's sequential loop (:47-61).  Larger batches skip that check: the slot then holds
+ * the row of one of those tokens (a whole row when Hkv*D is a multiple of 16), not
+ * necessarily the last.
  */
 int b200ops_reshape_and_cache(const void* key, const void* value, void* key_cache,
                               void* value_cache, const int32_t* slot_indices,
@@ -116,8 +129,11 @@ int b200ops_reshape_and_cache(const void* key, const void* value, void* key_cach
  *   q, out : f16 [bs, num_heads, head_dim];  block_tables : int32 [bs, max_pages_per_seq]
  *   context_lens : int32 [bs];  caches in `layout` with `num_pages` pages of `page_size` tokens
  *   out[b,h] = softmax(q[b,h] . K[b, h/(Hq/Hkv), :L_b]^T / sqrt(head_dim)) . V[b, h/(Hq/Hkv), :L_b]
- * A sequence with context_len <= 0 gets zeros.  Scratch (split-context partials) lives in
- * `workspace`; ask b200ops_paged_attention_workspace_size() for the minimum size.
+ * A sequence with context_len <= 0 gets zeros.  A block-table entry outside [0, num_pages)
+ * that lies inside a sequence's context names no page: the tokens of that page are left out
+ * of the softmax (every kernel path behaves the same; the reference validates nothing here).
+ * Scratch (split-context partials) lives in `workspace`; ask
+ * b200ops_paged_attention_workspace_size() for the minimum size.
  */
 size_t b200ops_paged_attention_workspace_size(int64_t bs, int64_t num_heads,
                                               int64_t num_kv_heads, int64_t head_dim,
@@ -140,7 +156,13 @@ int b200ops_paged_attention(const void* q, const void* key_cache, const void* va
  * on every GPU that loads the library until the process exits.  Shapes whose
  * b200ops_paged_attention_workspace_size() exceeds that return B200OPS_EWORKSPACE.
  * The first call on each device looks up the array's device address (with that device
- * current); make that first call before starting any stream capture.  All calls share the
+ * current); make that first call before starting any stream capture.  That first call is also
+ * when the CUDA runtime may load the library's device code and set the array's memory aside
+ * (module loading is lazy by default): a host that is about to claim all remaining HBM for
+ * its own arena must make one warm-up call per device BEFORE it does so (any small valid
+ * shape will do), or run with CUDA_MODULE_LOADING=EAGER; otherwise that first call can fail
+ * with an out-of-memory error.  The array's bytes are charged to every CUDA context that
+ * loads the library, whether or not this entry point is ever called.  All calls share the
  * one array, which keeps whatever the previous call left in it: two calls whose kernels
  * overlap on the GPU (different streams, no ordering) race on it -- order them on one
  * stream or with events.  Calls no cudaMalloc/cudaFree and no allocating library routine.
@@ -176,6 +198,18 @@ size_t b200ops_grouped_matmul_workspace_size(int64_t num_tokens, int64_t k, int6
 int b200ops_grouped_matmul(const void* x, const void* w, const int64_t* group_list, void* y,
                            int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n,
                            void* workspace, size_t workspace_size, void* stream);
+
+/*
+ * Dense NT product y = x . w^T:  x f16 [m, k], w f16 [n, k], y f16 [m, n], all contiguous.
+ * Replaces matmul_impl(stream, x, w, y, m, n, k) of the reference's earlier single-call
+ * interface (_csrc/ffi.cpp:71-75, called from native::matmul :408-442; kernel
+ * _csrc/kernels/matmul.cpp:3-28 over csrc/opdev/op_kernel/matmul_core.h).  Like the reference
+ * (whose multiple-of-64 check is commented out, _csrc/ffi.cpp:423-424) any m, n, k >= 1 is
+ * accepted: with k and n multiples of 64 (and 16-byte aligned pointers) the product runs on the
+ * tensor-core kernels of b200ops_grouped_matmul as a single group; every other shape runs a
+ * plain tiled kernel.  fp32 accumulation, one rounding.  No workspace, nothing allocated.
+ */
+int b200ops_matmul(const void* x, const void* w, void* y, int64_t m, int64_t n, int64_t k, void* stream);
 
 /*
  * Split + rotary embedding + KV-cache scatter in one launch, for the decode step
@@ -306,6 +340,53 @@ int b200ops_moe_push_rows(const void* src, const int32_t* index, int64_t src_div
                           void* const* peer_counts, void* stream);
 int b200ops_peer_barrier(void* const* peer_flags, void* my_flags, void* state, int64_t world,
                          int64_t my_rank, void* stream);
+
+/*
+ * The same exchange as three launches around the two expert GEMMs (no counterpart in the
+ * reference).  Slots (an expert, or one replica of a replicated expert) are placed
+ * contiguously on ranks, num_slots / world per rank ("spr").  Buffers every rank provides in
+ * memory its peers have mapped: a receive buffer [world][spr][cap] rows of `hidden` f16, a return
+ * buffer [num_slots][cap] rows of the MLP's output width, a count table int32 [world][spr], and
+ * two flag arrays uint32 [world] (dispatched, returned), all zero-initialised once.  Local only:
+ * cursor int32 [num_slots] and state uint32 [5], zero-initialised once; overflow int32 [2] (may
+ * be NULL).  Arrays of peer addresses are HOST arrays of `world` entries (entry my_rank = the
+ * local buffer).
+ *
+ * dispatch: one CTA per token.  With router_weight: route as b200ops_moe_route_topk does and
+ *   store the choices in expert_ids_out / expert_weights_out; otherwise read expert_ids_in
+ *   [num_tokens, top_k].  An expert id becomes a slot: the id itself, or, with expert_slots
+ *   int32 [num_experts, max_replicas] and num_replicas int32 [num_experts], replica
+ *   (token_offset + t) % num_replicas[e] of the expert.  The token's row is stored into the
+ *   slot owner's receive buffer, in the sub-segment (my_rank, slot), at the next free row;
+ *   slot_to_row[t*top_k+k] = row of the LOCAL return buffer where the result will arrive
+ *   (-1: invalid id, or the sub-segment was full; overflow[0] counts the latter).  Row order
+ *   inside a sub-segment depends on scheduling; results do not.  The last CTA to finish
+ *   sends every peer its counts and announces the step in every peer's `dispatched` flags.
+ * gather: waits (at most two seconds per peer, then state[1] = 100 + peer) until every peer
+ *   has announced the step, then copies the received rows into expert-major order:
+ *   grouped [max_rows, hidden], grouped_to_received[d] = receive-buffer row of grouped row d,
+ *   group_list int64 [spr], total_rows int32 [1].  Rows beyond max_rows are left out and
+ *   counted in overflow[1].
+ * (expert MLP: b200ops_grouped_matmul_swiglu on `grouped`, then b200ops_grouped_matmul_scatter
+ *   with row_index = grouped_to_received, peer_out = the return buffers, cap = spr * cap.)
+ * combine: announces "returned" to every peer, waits for every peer's announcement (same
+ *   limit), then y[t] = sum_k expert_weights[t,k] * returned[slot_to_row[t*top_k+k]].
+ * All ranks must run the three calls the same number of times, in this order.
+ */
+int b200ops_moe_dispatch(const void* x, const void* router_weight, const int32_t* expert_ids_in,
+                         int32_t* expert_ids_out, float* expert_weights_out, const int32_t* expert_slots,
+                         const int32_t* num_replicas, int64_t max_replicas, int64_t token_offset,
+                         int32_t* slot_to_row, void* const* peer_recv, void* const* peer_counts,
+                         void* const* peer_flags, int32_t* cursor, void* state, int32_t* overflow,
+                         int64_t num_tokens, int64_t hidden, int64_t num_experts, int64_t top_k,
+                         int64_t num_slots, int64_t world, int64_t cap, int64_t my_rank, void* stream);
+int b200ops_moe_gather(const void* recv, const int32_t* counts, const void* flags, void* state,
+                       int32_t* overflow, void* grouped, int32_t* grouped_to_received, int64_t* group_list,
+                       int32_t* total_rows, int64_t hidden, int64_t world, int64_t slots_per_rank, int64_t cap,
+                       int64_t max_rows, void* stream);
+int b200ops_moe_combine(const void* returned, const int32_t* slot_to_row, const float* expert_weights, void* y,
+                        void* const* peer_flags, void* my_flags, void* state, int64_t num_tokens, int64_t top_k,
+                        int64_t row_elems, int64_t world, int64_t my_rank, void* stream);
 
 /*
  * Health word of the pipelined kernels (grouped_matmul, paged_attention's TMA path).  Their

@@ -35,6 +35,27 @@ def bits(t: torch.Tensor) -> np.ndarray:
     return t.detach().cpu().contiguous().view(torch.int16).numpy().view(np.uint16)
 
 
+def knob(monkeypatch, name, value):
+    """Set (value None: unset) a B200OPS_* tuning variable for the rest of the test.  The library
+    reads its variables once per process, so it is told to read them again."""
+    if value is None:
+        monkeypatch.delenv(name, raising=False)
+    else:
+        monkeypatch.setenv(name, str(value))
+    from ascend910a_extras import cabi as m
+    m.reload_options()
+
+
+@pytest.fixture(autouse=True)
+def _fresh_tuning_options():
+    """A test's tuning variables end with it (monkeypatch restores the environment first)."""
+    yield
+    lib = os.path.join(str(REPO), "ascend-ops_b200", "ascend910a_extras", "lib", "libb200ops.so")
+    if os.path.exists(lib):
+        from ascend910a_extras import cabi as m
+        m.reload_options()
+
+
 @pytest.fixture(scope="session")
 def golden():
     def load(name):

@@ -6,6 +6,8 @@ import ctypes
 import pytest
 import torch
 
+from conftest import knob
+
 import decode_workloads as wl
 
 pytestmark = pytest.mark.gpu
@@ -83,7 +85,7 @@ def test_attention_and_gemm_stay_inside_their_outputs(cabi):
 
 @pytest.mark.parametrize("ksplit", ["1", "0"])  # cluster split-K / split-K through the workspace
 def test_split_k_paths_stay_inside_their_outputs(cabi, monkeypatch, ksplit):
-    monkeypatch.setenv("B200OPS_GMM_KSPLIT", ksplit)
+    knob(monkeypatch, "B200OPS_GMM_KSPLIT", ksplit)
     g2 = wl.grouped_matmul_inputs(rows=70, k=8192, n=320, experts=1, seed=7)
     nb = cabi.grouped_matmul_workspace_size(70, 8192, 1, 320)
     assert nb > 0
@@ -98,7 +100,7 @@ def test_split_k_paths_stay_inside_their_outputs(cabi, monkeypatch, ksplit):
 
 @pytest.mark.parametrize("pairs", ["0", "2"])  # single-CTA kernel / CTA-pair kernel
 def test_pair_and_swiglu_epilogues_stay_inside_their_outputs(cabi, monkeypatch, pairs):
-    monkeypatch.setenv("B200OPS_GMM_PAIR", pairs)
+    knob(monkeypatch, "B200OPS_GMM_PAIR", pairs)
     g = wl.grouped_matmul_inputs(rows=301, k=256, n=384, experts=5, seed=6)
     x, w, gl = g["x"].to(DEV), g["w_storage"].to(DEV), g["group_list"].to(DEV)
     y, act = Guarded((301, 384)), Guarded((301, 192))

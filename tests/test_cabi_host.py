@@ -55,6 +55,18 @@ def test_argument_checks_run_before_any_cuda_call(cabi):
     assert "multiple of num_kv_heads" in cabi.last_error()
     assert lib.b200ops_paged_attention(one, one, one, one, one, one, 2, 8, 4, 48, 8, 16, 4,
                                        cabi.KV_LAYOUT_NHD, null, 0, null) == cabi.EINVAL
+    assert lib.b200ops_matmul(one, one, one, 4, 0, 64, null) == cabi.EINVAL
+    assert lib.b200ops_matmul(null, one, one, 4, 64, 64, null) == cabi.EINVAL
+    assert lib.b200ops_matmul(null, null, null, 0, 64, 64, null) == cabi.OK
+    # the fused expert-parallel launches: geometry is checked before anything is dereferenced
+    peers = (ctypes.c_void_p * 2)(256, 512)
+    assert lib.b200ops_moe_dispatch(one, None, one, None, None, None, None, 0, 0, one, peers, peers, peers, one, one,
+                                    None, 4, 64, 8, 2, 7, 2, 16, 0, null) == cabi.EINVAL  # 7 slots over 2 ranks
+    assert "geometry" in cabi.last_error()
+    assert lib.b200ops_moe_dispatch(one, None, None, None, None, None, None, 0, 0, one, peers, peers, peers, one, one,
+                                    None, 4, 64, 8, 2, 8, 2, 16, 0, null) == cabi.EINVAL  # neither router nor ids
+    assert lib.b200ops_moe_gather(one, one, one, one, None, one, one, one, one, 60, 2, 4, 16, 128, null) == cabi.EINVAL
+    assert lib.b200ops_moe_combine(one, one, one, one, peers, one, one, 4, 2, 64, 2, 2, null) == cabi.EINVAL
     # zero-size problems succeed without a device
     assert lib.b200ops_swiglu(null, null, 0, 64, null) == cabi.OK
     assert lib.b200ops_add_rms_norm(null, null, null, 1e-6, null, null, 0, 64, null) == cabi.OK
@@ -65,7 +77,8 @@ def test_workspace_queries(cabi):
     assert lib.b200ops_grouped_matmul_workspace_size(8192, 4096, 8, 28672) == 0  # plenty of tiles
     assert lib.b200ops_grouped_matmul_workspace_size(64, 14336, 1, 4096) > 0  # few tiles, long K: split-K
     assert lib.b200ops_grouped_matmul_workspace_size(256, 4096, 1, 6144) == 0  # K too short to pay off
-    small = lib.b200ops_paged_attention_workspace_size(4, 8, 2, 128, 128, 2)
+    assert lib.b200ops_paged_attention_workspace_size(4, 8, 2, 128, 128, 2) == 0  # one chunk per sequence
+    small = lib.b200ops_paged_attention_workspace_size(4, 8, 2, 128, 128, 16)
     n = lib.b200ops_paged_attention_workspace_size(64, 28, 4, 128, 128, 64)
     assert 0 < small < n
     # grows with the batch, covers the chunk partials of the split-context path
@@ -111,3 +124,36 @@ def test_ops_module_keeps_the_reference_signatures(ops):
     for name, params in expect.items():
         assert list(inspect.signature(getattr(ops, name)).parameters) == params
     assert inspect.signature(ops.add_rms_norm).parameters["epsilon"].default == 1e-5
+
+
+def test_matmul_of_the_earlier_interface_is_exposed(ops):
+    """ops.matmul(x, w) and the dispatcher registration of the reference's earlier interface
+    (TORCH_LIBRARY(ascend910a, ...), _csrc/ffi.cpp:473-482), with its argument checks (:409-414)."""
+    import inspect
+    assert list(inspect.signature(ops.matmul).parameters) == ["x", "w"]
+    for name in ("swiglu", "grouped_matmul", "matmul"):
+        assert hasattr(torch.ops.ascend910a, name)
+    h = torch.float16
+    with pytest.raises(RuntimeError, match="must be 2D"):
+        ops.matmul(torch.zeros(4, 4, 64, dtype=h), torch.zeros(8, 64, dtype=h))
+    with pytest.raises(RuntimeError, match="last dimension of x must match"):
+        ops.matmul(torch.zeros(4, 64, dtype=h), torch.zeros(8, 32, dtype=h))
+    with pytest.raises(RuntimeError, match="only float16"):
+        ops.matmul(torch.zeros(4, 64), torch.zeros(8, 64))
+    with pytest.raises(RuntimeError, match="no CPU path"):
+        ops.matmul(torch.zeros(4, 64, dtype=h), torch.zeros(8, 64, dtype=h))
+
+
+def test_tuning_variables_are_read_once_and_can_be_reloaded(cabi, monkeypatch):
+    """Launch-time knobs come from the environment at first use only; reload_options() is the
+    hook that makes a changed variable visible (what conftest.knob calls)."""
+    lib = cabi.load()
+    monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", "4096")
+    cabi.reload_options()
+    big = lib.b200ops_paged_attention_workspace_size(64, 28, 4, 128, 128, 64)
+    monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", "256")
+    unchanged = lib.b200ops_paged_attention_workspace_size(64, 28, 4, 128, 128, 64)
+    assert unchanged == big  # not re-read
+    cabi.reload_options()
+    small_chunks = lib.b200ops_paged_attention_workspace_size(64, 28, 4, 128, 128, 64)
+    assert small_chunks > big  # shorter chunks, more partial records

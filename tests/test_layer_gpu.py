@@ -1,5 +1,6 @@
 """The MoE decoder layer (decode step) on the GPU against the CPU oracle's layer, stage by
-stage, at a reduced size; and the expert-parallel path on two GPUs when two are present."""
+stage, at a reduced size; the expert-parallel paths on every visible GPU when there are at least
+two; and a step at the benchmark's full dimensions against the oracle on sampled sequences."""
 import os
 import subprocess
 import sys
@@ -66,17 +67,21 @@ def test_layer_is_deterministic_and_cache_update_is_idempotent(ops):
     assert torch.equal(y1, y2) and torch.equal(r1, r2) and torch.equal(k_after, kd)
 
 
-@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_expert_parallel_two_gpus_matches_single_gpu(tmp_path):
-    """Two ranks, experts split 2+2, sequences split 6+6: each rank's output rows must equal
-    the single-GPU layer's rows for the same sequences."""
-    script = Path(__file__).with_name("ep_two_rank_check.py")
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs at least two GPUs")
+def test_expert_parallel_ranks_match_single_gpu(tmp_path):
+    """One rank per visible GPU (2, 4 or 8): the layer over the NCCL exchange and over the fused
+    peer-memory exchange, and the MoE MLP with replicated experts, each rank's rows against the
+    single-GPU path (tests/ep_ranks_check.py).  NVLS stays off: a rank that died while bound to an
+    NVLink multicast object would fault its peers."""
+    n = torch.cuda.device_count()
+    ranks = 8 if n >= 8 else (4 if n >= 4 else 2)
+    script = Path(__file__).with_name("ep_ranks_check.py")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
-    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={ranks}",
                         "--master-addr", "127.0.0.1", "--master-port", "29611", str(script)],
-                       env=env, capture_output=True, text=True, timeout=600)
-    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
-    assert "EP_CHECK_OK" in r.stdout
+                       env=env, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.stdout.count("EP_CHECK_OK") == ranks
 
 
 @pytest.mark.parametrize("nz", [False, True])
@@ -213,3 +218,62 @@ def test_fused_qk_norm_head_sizes(head_dim, heads, kv_heads):
     torch.testing.assert_close(flat_k[slots.long()].float(), k_ref.float(), rtol=1e-2, atol=2e-3)
     flat_v = vc.cpu().view(-1, kv_heads, head_dim)
     assert torch.equal(flat_v[slots.long()], qkv[:, nq + nkv:].reshape(t, kv_heads, head_dim))
+
+
+def test_layer_step_at_benchmark_dimensions_on_sampled_sequences(ops):
+    """The step the benchmark reports (batch 256, hidden 4096, 32 q / 8 kv heads, positions
+    U[1024, 16384], 8 experts of 14336) against the CPU oracle on eight of its sequences, the
+    longest and the shortest among them.  Every operator of the layer acts on a sequence by
+    itself, so the oracle runs on just those sequences: their pages are gathered out of the
+    9 GB cache (as it was before the step) into a small cache with a renumbered block table."""
+    cfg = mdl.LayerConfig()
+    w = mdl.make_weights(cfg, seed=7, device=DEV)
+    batch = mdl.make_decode_batch(cfg, seed=8)
+    g = torch.Generator(device=DEV).manual_seed(90)
+    k_cache = torch.randn(batch["cache_shape"], generator=g, device=DEV, dtype=torch.float16)
+    v_cache = torch.randn(batch["cache_shape"], generator=g, device=DEV, dtype=torch.float16)
+    lens = batch["context_lens"].long()
+    sample = sorted({0, 17, 101, 200, 255, int(lens.argmax()), int(lens.argmin()), 128})
+    bs = cfg.block_size
+    # the sampled sequences' pages, before the step writes the new tokens into them
+    tables, new_slots, page_ids, o = [], [], [], 0
+    for b in sample:
+        n = int((lens[b] + bs - 1) // bs)
+        ids = batch["block_tables"][b, :n].long()
+        page_ids.append(ids)
+        row = torch.zeros(batch["block_tables"].shape[1], dtype=torch.int32)
+        row[:n] = torch.arange(o, o + n, dtype=torch.int32)
+        tables.append(row)
+        p = int(batch["positions"][b])
+        new_slots.append((o + p // bs) * bs + p % bs)
+        o += n
+    gather = torch.cat(page_ids).to(DEV)
+    k_small, v_small = k_cache[gather].cpu(), v_cache[gather].cpu()
+    layer = mdl.MoEDecodeLayer(cfg, w, DEV, ops)
+    names = ("x", "residual", "positions", "slots", "block_tables", "context_lens")
+    y, res, ids, wts = layer.forward(*(batch[n].to(DEV) for n in names), k_cache, v_cache, return_routing=True)
+    torch.cuda.synchronize()
+    from ascend910a_extras import cabi
+    assert cabi.pipeline_status() == 0
+    sub = {"x": batch["x"][sample], "residual": batch["residual"][sample], "positions": batch["positions"][sample],
+           "context_lens": batch["context_lens"][sample], "block_tables": torch.stack(tables),
+           "slots": torch.tensor(new_slots, dtype=torch.int32)}
+    w_cpu = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in w.items()}
+    cos, sin = oracle.cos_sin_cache(16385, cfg.head_dim, cfg.rope_theta)
+    ey, eres, _, _, st = oracle.moe_decode_layer(
+        w_cpu, sub, k_small, v_small, heads=cfg.heads, kv_heads=cfg.kv_heads, head_dim=cfg.head_dim,
+        experts=cfg.experts, top_k=cfg.top_k, eps=cfg.eps, cos_cache=cos, sin_cache=sin,
+        expert_ids=ids[sample].cpu().long(), expert_weights=wts[sample].cpu())
+    # the new tokens' rotated keys landed in the right cache rows
+    flat_k = k_cache.view(-1, cfg.kv_heads, cfg.head_dim)
+    got_k = flat_k[batch["slots"][sample].long().to(DEV)].cpu()
+    torch.testing.assert_close(got_k.float(), st["k_rot"].float(), rtol=1e-2, atol=2e-3)
+    # routing: the same experts, except where two probabilities are within rounding of each other
+    prob = torch.softmax(st["logits"].float(), -1)
+    mine, theirs = ids[sample].cpu().long(), st["own_ids"]
+    differs = mine.sort(1).values != theirs.sort(1).values
+    if differs.any():
+        gap = (prob.gather(1, mine).sort(1).values - prob.gather(1, theirs).sort(1).values).abs()
+        assert float(gap.max()) < 5e-3
+    torch.testing.assert_close(res[sample].cpu().float(), eres.float(), rtol=1e-2, atol=2e-3)
+    torch.testing.assert_close(y[sample].cpu().float(), ey.float(), rtol=2e-2, atol=3e-3)

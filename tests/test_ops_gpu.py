@@ -9,7 +9,7 @@ import pytest
 import torch
 
 import decode_workloads as wl
-from conftest import bits, f16
+from conftest import bits, f16, knob
 from oracle import decode_ops_oracle as oracle
 
 pytestmark = pytest.mark.gpu
@@ -338,21 +338,17 @@ def test_grouped_matmul_moe_shape_sampled_rows(cabi):
 
 
 def test_paged_attention_benchmark_size_all_paths_agree(cabi, monkeypatch):
-    """Full benchmark batch (64 sequences, lengths U[512, 8192], 8192 pages): the tile-balanced
-    persistent kernel, the split-context TMA kernel, the general kernel and the CPU oracle."""
+    """Full benchmark batch (64 sequences, lengths U[512, 8192], 8192 pages): the split-context
+    TMA kernel, the general kernel and the CPU oracle."""
     w = wl.paged_attention_inputs()
-    monkeypatch.setenv("B200OPS_PA_MODE", "3")
-    stream = run_paged_attention(cabi, w)
-    monkeypatch.setenv("B200OPS_PA_MODE", "1")
+    knob(monkeypatch, "B200OPS_PA_MODE", "1")
     chunked = run_paged_attention(cabi, w)
-    monkeypatch.setenv("B200OPS_PA_MODE", "2")
+    knob(monkeypatch, "B200OPS_PA_MODE", "2")
     general = run_paged_attention(cabi, w)
-    monkeypatch.delenv("B200OPS_PA_MODE")
-    close(stream, general)
+    knob(monkeypatch, "B200OPS_PA_MODE", None)
     close(chunked, general)
     want = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
                                   w["context_lens"])
-    close(stream, want)
     close(chunked, want)
 
 
@@ -362,9 +358,9 @@ def test_paged_attention_benchmark_size_all_paths_agree(cabi, monkeypatch):
 def test_paged_attention_split_context_path_pipeline_depths(cabi, monkeypatch, stages, chunk, layout):
     """The TMA path on both cache layouts, every ring depth, short and long chunks, with NaN in
     every cache token that no sequence owns."""
-    monkeypatch.setenv("B200OPS_PA_MODE", "1")
-    monkeypatch.setenv("B200OPS_PA_STAGES", stages)
-    monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", chunk)
+    knob(monkeypatch, "B200OPS_PA_MODE", "1")
+    knob(monkeypatch, "B200OPS_PA_STAGES", stages)
+    knob(monkeypatch, "B200OPS_PA_CHUNK_TOKENS", chunk)
     lens = [1, 63, 64, 65, 127, 128, 129, 1000, 4097, 0, 2048]
     w = wl.paged_attention_inputs(heads=32, kv_heads=4, context_lens=lens, blocks=80, seed=int(stages),
                                   layout=layout)
@@ -380,10 +376,9 @@ def test_paged_attention_split_context_path_pipeline_depths(cabi, monkeypatch, s
     (16, 1, 256, [33000]),                                 # one long sequence spread over all CTAs
     (64, 4, 128, [3000] * 3 + [17] * 40),                  # group of 16 (upper MMA rows in use)
     (8, 8, 128, list(range(1, 400, 7))),                   # many short sequences, group 1
-    (8, 2, 64, [(i * 37) % 300 for i in range(700)]),      # batch beyond the in-kernel plan limit
+    (8, 2, 64, [(i * 37) % 300 for i in range(700)]),      # a large batch of short sequences
 ])
-def test_paged_attention_tile_balanced_path(cabi, monkeypatch, heads, kv_heads, page, lens):
-    monkeypatch.setenv("B200OPS_PA_MODE", "3")
+def test_paged_attention_ragged_batches(cabi, heads, kv_heads, page, lens):
     blocks = sum((l + page - 1) // page for l in lens) + 2
     w = wl.paged_attention_inputs(heads=heads, kv_heads=kv_heads, block_size=page, context_lens=lens,
                                   blocks=blocks, seed=heads + page)
@@ -401,7 +396,7 @@ def test_paged_attention_tile_balanced_path(cabi, monkeypatch, heads, kv_heads, 
     ([256], 16384, 1024),              # dense projection with a long K
 ])
 def test_grouped_matmul_split_k(cabi, monkeypatch, counts, k, n):
-    monkeypatch.setenv("B200OPS_GMM_KSPLIT", "0")  # single-group shapes would take the cluster path
+    knob(monkeypatch, "B200OPS_GMM_KSPLIT", "0")  # single-group shapes would take the cluster path
     g = torch.Generator().manual_seed(sum(counts) + k)
     m = sum(counts)
     x = torch.randn(m, k, generator=g).half()
@@ -427,7 +422,7 @@ def test_grouped_matmul_split_k(cabi, monkeypatch, counts, k, n):
 def test_grouped_matmul_narrow_tiles(cabi, monkeypatch, counts, k, n):
     """At most 128 rows in total and few output columns: the 128 x 64 tile configuration
     (reached by single-group shapes only when the cluster split-K path is switched off)."""
-    monkeypatch.setenv("B200OPS_GMM_KSPLIT", "0")
+    knob(monkeypatch, "B200OPS_GMM_KSPLIT", "0")
     g = torch.Generator().manual_seed(sum(counts) + k + n)
     m = sum(counts)
     x = torch.randn(m, k, generator=g).half()
@@ -456,9 +451,9 @@ def test_grouped_matmul_cta_pairs(cabi, monkeypatch, counts, k, n):
     w_storage = (torch.randn(len(counts), n, k, generator=g) * 0.05).half()
     gl = torch.tensor(counts).cumsum(0).to(torch.int64)
     want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
-    monkeypatch.setenv("B200OPS_GMM_PAIR", "2")
+    knob(monkeypatch, "B200OPS_GMM_PAIR", "2")
     pairs = run_grouped_matmul(cabi, x, w_storage, gl, fill=3.0, split_k=False)
-    monkeypatch.setenv("B200OPS_GMM_PAIR", "0")
+    knob(monkeypatch, "B200OPS_GMM_PAIR", "0")
     single = run_grouped_matmul(cabi, x, w_storage, gl, fill=3.0, split_k=False)
     close(pairs, want)
     assert torch.equal(pairs, single)
@@ -468,9 +463,9 @@ def test_grouped_matmul_cta_pairs_engage_at_benchmark_scale(cabi, monkeypatch):
     """A problem of several tile waves takes the pair kernel by default; sampled rows of every
     group are checked against the oracle, all rows against the single-CTA kernel."""
     w = wl.grouped_matmul_inputs(rows=8192, k=1024, n=4096, experts=8, seed=12)
-    monkeypatch.delenv("B200OPS_GMM_PAIR", raising=False)
+    knob(monkeypatch, "B200OPS_GMM_PAIR", None)
     auto = run_grouped_matmul(cabi, w["x"], w["w_storage"], w["group_list"])
-    monkeypatch.setenv("B200OPS_GMM_PAIR", "0")
+    knob(monkeypatch, "B200OPS_GMM_PAIR", "0")
     single = run_grouped_matmul(cabi, w["x"], w["w_storage"], w["group_list"])
     assert torch.equal(auto, single)
     rows = torch.arange(0, 8192, 61)
@@ -499,12 +494,12 @@ def test_grouped_matmul_cluster_split_k(cabi, monkeypatch, counts, k, n):
     w_storage = (torch.randn(1, n, k, generator=g) * 0.05).half()
     gl = torch.tensor(counts).cumsum(0).to(torch.int64)
     want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
-    monkeypatch.delenv("B200OPS_GMM_KSPLIT", raising=False)
+    knob(monkeypatch, "B200OPS_GMM_KSPLIT", None)
     got = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False)
     close(got, want)
     again = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False)
     assert torch.equal(got, again)  # fixed summation order: bitwise repeatable
-    monkeypatch.setenv("B200OPS_GMM_KSPLIT", "0")
+    knob(monkeypatch, "B200OPS_GMM_KSPLIT", "0")
     close(run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False), want)
 
 
@@ -531,7 +526,7 @@ def test_grouped_matmul_cluster_split_k_fewer_rows_than_the_bound(cabi):
 def test_grouped_matmul_swiglu_equals_the_two_operators(cabi, monkeypatch, counts, k, d, pair_mode):
     """SwiGLU in the GEMM's epilogue: the same bits as grouped_matmul followed by swiglu (the
     accumulators are rounded to fp16 in between, as the intermediate tensor would be)."""
-    monkeypatch.setenv("B200OPS_GMM_PAIR", pair_mode)
+    knob(monkeypatch, "B200OPS_GMM_PAIR", pair_mode)
     g = torch.Generator().manual_seed(sum(counts) + k + d)
     m = sum(counts)
     x = torch.randn(m, k, generator=g).half().to(DEV)
@@ -577,11 +572,11 @@ def test_paged_attention_nz_layout_fast_and_general_paths_agree(cabi, monkeypatc
     """The reference's own cache layout [blocks, Hkv*D/16, P, 16] at a 16-sequence slice of the
     benchmark batch with 16 query heads per kv head: TMA path, general path and the oracle."""
     w = wl.paged_attention_inputs(bs=16, heads=32, kv_heads=2, blocks=16 * 64, layout=wl.KV_LAYOUT_NZ, seed=13)
-    monkeypatch.setenv("B200OPS_PA_MODE", "1")
+    knob(monkeypatch, "B200OPS_PA_MODE", "1")
     fast = run_paged_attention(cabi, w)
-    monkeypatch.setenv("B200OPS_PA_MODE", "2")
+    knob(monkeypatch, "B200OPS_PA_MODE", "2")
     general = run_paged_attention(cabi, w)
-    monkeypatch.delenv("B200OPS_PA_MODE")
+    knob(monkeypatch, "B200OPS_PA_MODE", None)
     close(fast, general)
     close(fast, oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
                                        w["context_lens"]))
@@ -608,7 +603,7 @@ def test_paged_attention_small_pages_take_the_tma_path(cabi, monkeypatch, page, 
     pages.  NaN in every cache token no sequence owns; TMA path against the general path and the
     oracle; chunk lengths that are and are not multiples of the tile."""
     if chunk:
-        monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", chunk)
+        knob(monkeypatch, "B200OPS_PA_CHUNK_TOKENS", chunk)
     lens = [1, 15, 16, 17, 63, 64, 65, 100, 1000, 4097, 0, 2500, page * 3]
     blocks = sum((l + page - 1) // page for l in lens) + 5
     w = wl.paged_attention_inputs(heads=28, kv_heads=4, block_size=page, context_lens=lens, blocks=blocks,
@@ -616,9 +611,9 @@ def test_paged_attention_small_pages_take_the_tma_path(cabi, monkeypatch, page, 
     w = poison_unused(w)
     want = oracle.paged_attention(w["q"], w["key_cache_clean"], w["value_cache_clean"],
                                   w["block_tables"], w["context_lens"])
-    monkeypatch.setenv("B200OPS_PA_MODE", "1")
+    knob(monkeypatch, "B200OPS_PA_MODE", "1")
     fast = run_paged_attention(cabi, w)
-    monkeypatch.setenv("B200OPS_PA_MODE", "2")
+    knob(monkeypatch, "B200OPS_PA_MODE", "2")
     general = run_paged_attention(cabi, w)
     close(fast, want)
     close(general, want)
@@ -629,7 +624,7 @@ def test_paged_attention_wide_block_table_and_long_sequences(cabi, monkeypatch, 
     """A block table padded far beyond the contexts (as a graph-replaying host passes it) and
     sequences long enough that the chunk count per sequence is capped, so that they take longer
     chunks than the short ones in the same batch.  TMA path, general path and oracle."""
-    monkeypatch.setenv("B200OPS_PA_CHUNK_TOKENS", "128")  # small base chunk: the cap engages early
+    knob(monkeypatch, "B200OPS_PA_CHUNK_TOKENS", "128")  # small base chunk: the cap engages early
     lens = [40000, 1, 129, 5000, 0, 128 * 8 * 7 + 3, 20011]
     page = 128
     blocks = sum((l + page - 1) // page for l in lens) + 4
@@ -639,9 +634,117 @@ def test_paged_attention_wide_block_table_and_long_sequences(cabi, monkeypatch, 
     wide[:, : w["block_tables"].shape[1]] = w["block_tables"]
     want = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"], w["context_lens"])
     w = dict(w, block_tables=wide)
-    monkeypatch.setenv("B200OPS_PA_MODE", "1")
+    knob(monkeypatch, "B200OPS_PA_MODE", "1")
     fast = run_paged_attention(cabi, w)
-    monkeypatch.setenv("B200OPS_PA_MODE", "2")
+    knob(monkeypatch, "B200OPS_PA_MODE", "2")
     general = run_paged_attention(cabi, w)
     close(fast, want)
     close(general, want)
+
+
+# ---------------------------------------------------------------------------------------
+# Benchmark-size grouped GEMMs, the repeated-slot rule, invalid block-table entries, matmul
+def _sampled_rows(ends, per_group=32):
+    """First, last and evenly spaced rows of every non-empty group, with their expert."""
+    rows, experts, lo = [], [], 0
+    for e, hi in enumerate(ends):
+        if hi > lo:
+            pick = sorted(set([lo, hi - 1] + [lo + (hi - lo) * i // per_group for i in range(per_group)]))
+            rows.extend(pick)
+            experts.extend([e] * len(pick))
+        lo = hi
+    return rows, experts
+
+
+@pytest.mark.parametrize("which,k,n,seed", [("gate_up", 4096, 28672, 4), ("down", 14336, 4096, 5)])
+def test_grouped_matmul_benchmark_size(cabi, which, k, n, seed):
+    """The two grouped GEMMs at the size the benchmark times (8192 rows in 8 skewed groups, weight
+    tensors of 0.9 and 0.5 G elements): at least 256 rows spread over every group, the first and
+    the last row of each group among them, against the fp32 product of the same fp16 operands
+    (tolerance convention of the reference's own check, benchmark/test_grouped_matmul.py:52-60:
+    assert_close on the fp16 result; rtol 1e-2 / atol 1e-3 as for every fp16 operator here)."""
+    w = wl.grouped_matmul_inputs(rows=8192, k=k, n=n, seed=seed)
+    y = run_grouped_matmul(cabi, w["x"], w["w_storage"], w["group_list"])
+    rows, experts = _sampled_rows(w["group_list"].tolist())
+    assert len(rows) >= 256
+    x32 = w["x"][rows].float()
+    want = torch.empty(len(rows), n)
+    for e in sorted(set(experts)):
+        sel = [i for i, ee in enumerate(experts) if ee == e]
+        want[sel] = x32[sel] @ w["w_storage"][e].float().T
+    close(y[rows], want.half())
+    assert torch.isfinite(y.float()).all()
+
+
+@pytest.mark.parametrize("layout", [wl.KV_LAYOUT_NHD, wl.KV_LAYOUT_NZ])
+@pytest.mark.parametrize("tokens,hkv,d", [(2048, 8, 128), (23, 2, 64), (9, 1, 24), (40, 3, 40)])
+def test_reshape_and_cache_repeated_slot_keeps_the_later_token(cabi, layout, tokens, hkv, d):
+    """The reference walks the tokens in order (reshape_and_cache_ex.cpp:47-61), so when several
+    tokens name one slot the last of them stays.  Every kernel form (row per warp, 16-byte
+    vectors, single elements) is covered by the head sizes."""
+    if layout == wl.KV_LAYOUT_NZ and (hkv * d) % 16 != 0:
+        pytest.skip("the NZ cache holds rows in chunks of 16 elements")
+    blocks, p = 12, 16
+    c = wl.reshape_and_cache_inputs(tokens, hkv, d, blocks=max(blocks, tokens // p + 2), block_size=p,
+                                    layout=layout, seed=tokens)
+    slots = c["slot_indices"].clone()
+    g = torch.Generator().manual_seed(tokens + d)
+    dup = torch.randperm(tokens, generator=g)[: max(2, tokens // 3)]
+    slots[dup] = slots[dup[0]]          # a third of the batch piles onto one slot ...
+    slots[tokens // 2] = slots[0]       # ... and one more pair
+    last = {}
+    for t, s_ in enumerate(slots.tolist()):
+        last[s_] = t
+    keep = torch.tensor([last[s_] == t for t, s_ in enumerate(slots.tolist())])
+    only_last = torch.where(keep, slots, torch.full_like(slots, -1))
+    kc = torch.full(c["cache_shape"], 3.0, dtype=torch.float16)
+    vc = torch.full(c["cache_shape"], 4.0, dtype=torch.float16)
+    ekc, evc = kc.clone(), vc.clone()
+    oracle.reshape_and_cache(c["key"], ekc, only_last, c["value"], evc, layout=layout)
+    kd, vd = kc.to(DEV), vc.to(DEV)
+    cabi.reshape_and_cache(c["key"].to(DEV), c["value"].to(DEV), kd, vd, slots.to(DEV), layout)
+    torch.cuda.synchronize()
+    assert torch.equal(kd.cpu(), ekc) and torch.equal(vd.cpu(), evc)
+
+
+@pytest.mark.parametrize("layout,page", [(wl.KV_LAYOUT_NHD, 128), (wl.KV_LAYOUT_NHD, 16), (wl.KV_LAYOUT_NZ, 64)])
+def test_paged_attention_invalid_block_table_entry_is_left_out(cabi, monkeypatch, layout, page):
+    """A block-table entry outside [0, num_pages) inside a sequence's context names no page: its
+    tokens take no part, on the TMA path and on the general path alike.  Expected value: the
+    same sequence with that page removed from its table."""
+    lens = [5 * page + 7, 3 * page, 9 * page + 1]
+    w = wl.paged_attention_inputs(heads=8, kv_heads=2, block_size=page, context_lens=lens, blocks=40, seed=page,
+                                  layout=layout)
+    bad = w["block_tables"].clone()
+    bad[0, 2] = -1
+    bad[1, 0] = 40          # == num_pages
+    bad[2, 4] = 1 << 30
+    ref_table = w["block_tables"].clone()
+    ref_lens = w["context_lens"].clone()
+    for b, col in ((0, 2), (1, 0), (2, 4)):
+        ref_table[b, col:-1] = w["block_tables"][b, col + 1:]
+        ref_lens[b] -= page
+    want = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], ref_table, ref_lens)
+    w_bad = dict(w, block_tables=bad)
+    knob(monkeypatch, "B200OPS_PA_MODE", "1")
+    fast = run_paged_attention(cabi, w_bad)
+    knob(monkeypatch, "B200OPS_PA_MODE", "2")
+    general = run_paged_attention(cabi, w_bad)
+    close(fast, want)
+    close(general, want)
+
+
+@pytest.mark.parametrize("m,k,n", [(128, 128, 128), (256, 4096, 6144), (1, 64, 64), (37, 100, 72), (300, 257, 65),
+                                   (5, 8, 3), (2100, 512, 768)])
+def test_matmul_c_abi_any_shape(cabi, m, k, n):
+    """b200ops_matmul replaces the reference's matmul_impl (_csrc/ffi.cpp:71-75), which takes any
+    m, n, k (its multiple-of-64 check is commented out, :423-424): tensor-core path for k and n
+    multiples of 64, plain tiled kernel otherwise; same torch golden as benchmark/test_matmul.py."""
+    g = torch.Generator().manual_seed(m + k + n)
+    x = torch.randn(m, k, generator=g).half()
+    w = (torch.randn(n, k, generator=g) * 0.1).half()
+    y = torch.full((m, n), float("nan"), dtype=torch.float16, device=DEV)
+    cabi.matmul(x.to(DEV), w.to(DEV), y)
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    close(y.cpu(), (x.float() @ w.float().T).half())

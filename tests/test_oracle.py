@@ -159,3 +159,38 @@ def test_head_rms_norm_is_add_rms_norm_without_residual():
     got = oracle.head_rms_norm(x, w, 1e-6)
     want, _ = oracle.add_rms_norm(x.view(-1, 128), torch.zeros(35, 128, dtype=torch.float16), w, 1e-6)
     assert torch.equal(got.view(-1, 128), want)
+
+
+def test_paged_attention_oracle_against_an_independent_statement():
+    """The attention oracle has no reference golden to pin it (the reference's kernel is
+    unfinished and its check calls a third-party NPU library), so this does not pin it either.
+    It removes one risk: that oracle and kernel share one author's misreading.  A second
+    statement of decode attention written differently -- gather each sequence's pages into a
+    dense [kv_heads, L, D] tensor and call torch's scaled_dot_product_attention in fp32 with
+    grouped-query broadcasting -- must agree with the oracle on the benchmark recipe (64
+    sequences, 28 query / 4 kv heads, lengths U[512, 8192], random distinct pages), on both
+    cache layouts."""
+    import torch.nn.functional as F
+
+    import decode_workloads as wl
+    from oracle import decode_ops_oracle as oracle
+
+    for layout in (wl.KV_LAYOUT_NHD, wl.KV_LAYOUT_NZ):
+        w = wl.paged_attention_inputs(blocks=2400, layout=layout, seed=3)
+        got = oracle.paged_attention(w["q"], w["key_cache"], w["value_cache"], w["block_tables"],
+                                     w["context_lens"])
+        kc, vc = w["key_cache"], w["value_cache"]
+        if layout == wl.KV_LAYOUT_NZ:  # [pages, Hkv*D/16, P, 16] -> [pages, P, Hkv, D]
+            pages, chunks, p, _ = kc.shape
+            kc = kc.permute(0, 2, 1, 3).reshape(pages, p, 4, 128)
+            vc = vc.permute(0, 2, 1, 3).reshape(pages, p, 4, 128)
+        want = torch.empty_like(w["q"])
+        for b in range(w["q"].shape[0]):
+            n = int(w["context_lens"][b])
+            ids = w["block_tables"][b, : (n + 127) // 128].long()
+            k = kc[ids].reshape(-1, 4, 128)[:n].permute(1, 0, 2).float()   # [Hkv, L, D]
+            v = vc[ids].reshape(-1, 4, 128)[:n].permute(1, 0, 2).float()
+            q = w["q"][b].float()[:, None, :]                              # [Hq, 1, D]
+            o = F.scaled_dot_product_attention(q[None], k[None], v[None], enable_gqa=True)
+            want[b] = o[0, :, 0, :].half()
+        torch.testing.assert_close(got.float(), want.float(), rtol=1e-2, atol=1e-3)

@@ -45,6 +45,29 @@ def test_static_scratch_entry_matches_workspace_entry_twice(cabi):
     assert cabi.pipeline_status() == 0
 
 
+def test_static_scratch_entry_allocates_nothing(cabi):
+    """What the name promises: once the warm-up call has made the runtime load the library's
+    device code (its documented first call), further calls leave the device's free memory
+    exactly where it was -- including memory torch's allocator holds, which is read with it."""
+    w = wl.paged_attention_inputs(bs=6, blocks=6 * 64, min_len=4000, max_len=8192, seed=73)
+    q = w["q"].to(DEV)
+    kc, vc = w["key_cache"].to(DEV), w["value_cache"].to(DEV)
+    bt, cl = w["block_tables"].to(DEV), w["context_lens"].to(DEV)
+    out = torch.empty_like(q)
+    call = lambda: cabi.paged_attention_static(q, kc, vc, bt, cl, out, w["kv_heads"], w["block_size"], w["layout"])
+    call()  # warm-up
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    reserved_before = torch.cuda.memory_reserved()
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert torch.cuda.memory_reserved() == reserved_before
+    assert torch.isfinite(out.float()).all()
+
+
 def test_static_scratch_entry_rejects_shapes_beyond_its_array(cabi):
     lib = cabi.load()
     null = ctypes.c_void_p(None)

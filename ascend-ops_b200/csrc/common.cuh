@@ -74,7 +74,6 @@ enum Knob {
   kKnobRmsnormVpt,      // B200OPS_RMSNORM_VPT: 16-byte vectors per thread
   kKnobRmsnormCtaWarps, // B200OPS_RMSNORM_CTA_WARPS: warps per CTA
   kKnobRacWarps,        // B200OPS_RAC_WARPS: warps per CTA of the reshape_and_cache row kernel
-  kKnobRacSplit,        // B200OPS_RAC_SPLIT: 1 = a token's K row and V row go to separate warps
   kKnobPdl,             // B200OPS_PDL: 0 = plain stream-ordered launches (no programmatic dependent launch)
   kKnobCount
 };

@@ -35,6 +35,7 @@ struct ScatterParams {
   uint32_t page_size;   // P
   uint32_t chunks;      // NZ: C
   bool dedup;           // small batch: a token whose slot a later token names again is skipped
+  bool slots_vec;       // the slot array is 16-byte aligned
 };
 
 // The per-thread form of the check for the fallback kernels (odd row sizes; never on a hot path).
@@ -92,34 +93,58 @@ __global__ void __launch_bounds__(kThreads) scatter_nz_vec_kernel(ScatterParams 
   reinterpret_cast<uint4*>(p.key_cache)[dst] = kv;
 }
 
-// True if a token after `token` names the same slot (the warp scans the rest of the batch; the
-// slot array of a decode step is a few KB and stays in L1).
+// True if a token after `token` names the same slot.  The warp scans the rest of the batch's
+// slots, four per load and kScanBatch loads per lane in flight, so the check is one or two L2/L1
+// round trips that pass while the token's own rows are still on their way from DRAM.
+// `vec_ok`: the slot array is 16-byte aligned (otherwise single loads).
+constexpr int kScanBatch = 8;
+
 __device__ __forceinline__ bool named_again(const int32_t* __restrict__ slots, uint32_t token,
-                                            uint32_t num_tokens, int32_t slot, uint32_t lane) {
+                                            uint32_t num_tokens, int32_t slot, uint32_t lane, bool vec_ok) {
   bool later = false;
+  if (!vec_ok) {
 #pragma unroll 4
-  for (uint32_t t = token + 1 + lane; t < num_tokens; t += 32) later |= (__ldg(slots + t) == slot);
+    for (uint32_t t = token + 1 + lane; t < num_tokens; t += 32) later |= (__ldg(slots + t) == slot);
+    return __any_sync(0xffffffffu, later);
+  }
+  const uint32_t full = num_tokens >> 2;  // complete groups of four slots
+  const int4* s4 = reinterpret_cast<const int4*>(slots);
+#pragma unroll 1
+  for (uint32_t base = (token + 1) >> 2; base < full; base += 32 * kScanBatch) {
+    int4 v[kScanBatch];
+#pragma unroll
+    for (int i = 0; i < kScanBatch; ++i) {
+      const uint32_t g = base + lane + 32 * i;
+      v[i] = g < full ? __ldg(s4 + g) : make_int4(-1, -1, -1, -1);  // -1 equals no valid slot
+    }
+#pragma unroll
+    for (int i = 0; i < kScanBatch; ++i) {
+      const uint32_t idx = (base + lane + 32 * i) << 2;  // only the first group can hold earlier tokens
+      later |= (v[i].x == slot && idx > token) | (v[i].y == slot && idx + 1 > token) |
+               (v[i].z == slot && idx + 2 > token) | (v[i].w == slot && idx + 3 > token);
+    }
+  }
+  const uint32_t tail = (full << 2) + lane;  // the last one to three slots
+  if (lane < (num_tokens & 3u) && tail > token) later |= (__ldg(slots + tail) == slot);
   return __any_sync(0xffffffffu, later);
 }
 
 constexpr int kDedupMaxTokens = 4096;
 
 // Row-per-warp kernel for rows that are whole 32-byte sectors (row_elems % 16 == 0): a warp
-// owns one token (kSplit: one token's K row or its V row), every lane moves 32-byte pieces.
-// All loads (including the slot) are issued before anything depends on them, so one DRAM round
-// trip covers them; stores are one full sector each.  kMaxPieces bounds the pieces a lane holds.
+// owns one token, every lane moves 32-byte pieces of the K row and of the V row.  All loads
+// (including the slot) are issued before anything depends on them, so one DRAM round trip
+// covers them; stores are one full sector each.  kMaxPieces bounds the pieces a lane holds.
+// (Giving a token's K row and V row to separate warps, and CTAs of 8 or 16 warps, were measured
+// and are slower at a decode batch of 2048 tokens.)
 constexpr int kMaxPieces = 4;  // 32 lanes x 4 pieces x 32 B = rows up to 4 KB
 
-template <bool kNz, bool kDedup, bool kSplit>
+template <bool kNz, bool kDedup>
 __global__ void __launch_bounds__(512) scatter_rows_kernel(ScatterParams p) {
   pdl_trigger();
   pdl_wait();
-  const uint32_t warp_id = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const uint32_t token = kSplit ? warp_id >> 1 : warp_id;
+  const uint32_t token = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (token >= p.num_tokens) return;
-  const bool do_k = !kSplit || (warp_id & 1u) == 0;
-  const bool do_v = p.value != nullptr && (!kSplit || (warp_id & 1u) == 1);
-  if (!do_k && !do_v) return;
   const uint32_t lane = threadIdx.x & 31;
   const uint32_t pieces = p.row_elems >> 4;  // 32-byte pieces (= NZ chunks) per row
   const char* ks = reinterpret_cast<const char*>(p.key) + static_cast<size_t>(token) * p.row_elems * 2;
@@ -130,13 +155,13 @@ __global__ void __launch_bounds__(512) scatter_rows_kernel(ScatterParams p) {
   for (int i = 0; i < kMaxPieces; ++i) {
     const uint32_t c = lane + i * 32;
     if (c < pieces) {
-      if (do_k) kb[i] = ld_stream256(ks + c * 32);
-      if (do_v) vb[i] = ld_stream256(vs + c * 32);
+      kb[i] = ld_stream256(ks + c * 32);
+      if (p.value != nullptr) vb[i] = ld_stream256(vs + c * 32);
     }
   }
   const int64_t slot = slot32;
   if (slot < 0 || slot >= p.num_slots) return;
-  if (kDedup && named_again(p.slots, token, p.num_tokens, slot32, lane)) return;
+  if (kDedup && named_again(p.slots, token, p.num_tokens, slot32, lane, p.slots_vec)) return;
   size_t base, stride;  // byte offset of piece 0 and distance between pieces in the cache
   uint32_t limit = pieces;
   if (kNz) {
@@ -155,8 +180,8 @@ __global__ void __launch_bounds__(512) scatter_rows_kernel(ScatterParams p) {
   for (int i = 0; i < kMaxPieces; ++i) {
     const uint32_t c = lane + i * 32;
     if (c < limit) {
-      if (do_k) st256(kc + c * stride, kb[i]);
-      if (do_v) st256(vc + c * stride, vb[i]);
+      st256(kc + c * stride, kb[i]);
+      if (p.value != nullptr) st256(vc + c * stride, vb[i]);
     }
   }
 }
@@ -251,26 +276,15 @@ extern "C" int b200ops_reshape_and_cache(const void* key, const void* value, voi
                                              reinterpret_cast<uintptr_t>(value_cache)
                                        : 0)) & 31u) == 0;
   p.dedup = num_tokens <= kDedupMaxTokens;
+  p.slots_vec = aligned16(slot_indices);
   if (row_elems % 16 == 0 && row_elems <= 16 * 32 * kMaxPieces && aligned32) {
-    // Warps per CTA and whether a token's K and V rows go to separate warps (twice the warps,
-    // half the loads each holds) are tuning knobs; a decode step is one DRAM round trip long.
-    int warps = knob(kKnobRacWarps, 4);
+    int warps = knob(kKnobRacWarps, 4);  // warps (= tokens) per CTA
     if (warps != 2 && warps != 4 && warps != 8 && warps != 16) warps = 4;
-    const bool split = with_value && knob(kKnobRacSplit, 0) != 0;
-    const int64_t n_warps = split ? 2 * num_tokens : num_tokens;
-    const unsigned grid = static_cast<unsigned>((n_warps + warps - 1) / warps);
+    const unsigned grid = static_cast<unsigned>((num_tokens + warps - 1) / warps);
     const bool nz = layout == B200OPS_KV_LAYOUT_NZ;
-#define RAC_LAUNCH(NZ, DD, SP) \
-  launch_kernel(scatter_rows_kernel<NZ, DD, SP>, dim3(grid), dim3(warps * 32), 0, st, p)
-    cudaError_t err;
-    if (nz)
-      err = p.dedup ? (split ? RAC_LAUNCH(true, true, true) : RAC_LAUNCH(true, true, false))
-                    : (split ? RAC_LAUNCH(true, false, true) : RAC_LAUNCH(true, false, false));
-    else
-      err = p.dedup ? (split ? RAC_LAUNCH(false, true, true) : RAC_LAUNCH(false, true, false))
-                    : (split ? RAC_LAUNCH(false, false, true) : RAC_LAUNCH(false, false, false));
-#undef RAC_LAUNCH
-    B200OPS_CUDA(err);
+    auto kern = nz ? (p.dedup ? scatter_rows_kernel<true, true> : scatter_rows_kernel<true, false>)
+                   : (p.dedup ? scatter_rows_kernel<false, true> : scatter_rows_kernel<false, false>);
+    B200OPS_CUDA(launch_kernel(kern, dim3(grid), dim3(warps * 32), 0, st, p));
     return B200OPS_OK;
   }
   const bool vec_ok = row_elems % 8 == 0 && aligned16(key) && aligned16(key_cache) &&

@@ -677,7 +677,7 @@ def test_grouped_matmul_benchmark_size(cabi, which, k, n, seed):
 
 
 @pytest.mark.parametrize("layout", [wl.KV_LAYOUT_NHD, wl.KV_LAYOUT_NZ])
-@pytest.mark.parametrize("tokens,hkv,d", [(2048, 8, 128), (23, 2, 64), (9, 1, 24), (40, 3, 40)])
+@pytest.mark.parametrize("tokens,hkv,d", [(2048, 8, 128), (23, 2, 64), (9, 1, 24), (40, 3, 40), (7, 1, 12), (2047, 4, 128)])
 def test_reshape_and_cache_repeated_slot_keeps_the_later_token(cabi, layout, tokens, hkv, d):
     """The reference walks the tokens in order (reshape_and_cache_ex.cpp:47-61), so when several
     tokens name one slot the last of them stays.  Every kernel form (row per warp, 16-byte
@@ -690,8 +690,8 @@ def test_reshape_and_cache_repeated_slot_keeps_the_later_token(cabi, layout, tok
     slots = c["slot_indices"].clone()
     g = torch.Generator().manual_seed(tokens + d)
     dup = torch.randperm(tokens, generator=g)[: max(2, tokens // 3)]
-    slots[dup] = slots[dup[0]]          # a third of the batch piles onto one slot ...
-    slots[tokens // 2] = slots[0]       # ... and one more pair
+    slots[dup] = int(slots[dup[0]])     # a third of the batch piles onto one slot ...
+    slots[tokens // 2] = int(slots[0])  # ... and one more pair
     last = {}
     for t, s_ in enumerate(slots.tolist()):
         last[s_] = t

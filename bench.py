@@ -588,8 +588,7 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
     def local_mlp_scatter(rows, gl, scatter):
         moe.grouped_matmul_scatter(moe.grouped_matmul_swiglu(rows, w_gu, gl), w_dn, gl, *scatter)
 
-    def measure(capacity, rows_bound):
-        flags = []
+    def make_step(capacity, rows_bound, flags):
         exchange = make_exchange(group, dev, capacity, cfg.hidden, cfg.hidden, placement.num_slots, rows_bound)
 
         def step():
@@ -600,6 +599,15 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
             slot_ids = moe_parallel.to_slot_ids(my_ids, placement, rank * per)
             return moe_parallel.expert_parallel_mlp_device(moe, x, slot_ids, wts, placement.num_slots, local_mlp,
                                                            group, capacity, overflow_out=flags)
+
+        return step, exchange
+
+    if steps == 0:  # for a per-kernel timeline: hand back the eager step at the bounded capacity
+        return make_step(cap, max_rows, [])[0]
+
+    def measure(capacity, rows_bound):
+        flags = []
+        step, exchange = make_step(capacity, rows_bound, flags)
 
         # Recorded once into a CUDA graph (fixed shapes, no host sync, NCCL included), like the
         # layer step: at 8 GPUs the step is shorter than the host time to launch it op by op.

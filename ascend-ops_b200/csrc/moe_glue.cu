@@ -690,17 +690,18 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams 
       dst[v] = val;
     }
   }
-  // Publish: this CTA's stores, then its arrival; the CTA that finds all others arrived finishes
-  // the step for the rank.
-  __threadfence_system();
+  // Publish: this CTA's stores (ordered before thread 0's fence by the CTA barrier), then its
+  // arrival; the CTA that finds all others arrived finishes the step for the rank.  One thread
+  // fences: a system-scope fence waits for the peer stores to be acknowledged over NVLink, and
+  // 256 threads doing so one after the other cost tens of microseconds.
   __syncthreads();
   if (tid == 0) {
     __threadfence_system();
     is_last = atomicAdd(&p.state[2], 1u) == gridDim.x - 1;
+    if (is_last) __threadfence_system();
   }
   __syncthreads();
   if (!is_last) return;
-  __threadfence_system();
   const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.state) + 1u;
   int lost = 0;
   for (int slot = tid; slot < p.num_slots; slot += blockDim.x) {
@@ -711,9 +712,11 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams 
     static_cast<int32_t*>(p.counts.base[peer])[p.my_rank * p.spr + (slot - peer * p.spr)] = kept;
   }
   if (lost) atomicAdd(&dropped, lost);
-  __threadfence_system();
-  __syncthreads();
-  if (tid < p.world) st_release_sys(static_cast<uint32_t*>(p.flags.base[tid]) + p.my_rank, step);
+  __syncthreads();  // the count stores of all threads precede the fences of the announcing threads
+  if (tid < p.world) {
+    __threadfence_system();
+    st_release_sys(static_cast<uint32_t*>(p.flags.base[tid]) + p.my_rank, step);
+  }
   if (tid == 0) {
     if (p.overflow != nullptr) p.overflow[0] = dropped;
     p.state[0] = step;

@@ -401,7 +401,9 @@ def build_layer(ops, dev, rank, world, group):
     mine = moe_parallel.local_experts(cfg.experts, world, rank).tolist()
     weights = mdl.make_weights(cfg, seed=7, experts=mine, device=dev)
     per = 256 // world
-    exchange = make_exchange(group, dev, per * cfg.top_k, cfg.hidden, cfg.hidden, cfg.experts)
+    # a rank can receive at most every routed row of the batch: the bound the GEMMs are sized by
+    exchange = make_exchange(group, dev, per * cfg.top_k, cfg.hidden, cfg.hidden, cfg.experts,
+                             max_rows=256 * cfg.top_k)
     layer = mdl.MoEDecodeLayer(cfg, weights, dev, ops, group, segment_rows=per * cfg.top_k, exchange=exchange)
     pos = mdl.draw_positions(256)
     mine_seq = balanced_sequence_shard(pos, world, rank)

@@ -43,7 +43,7 @@ SIGNATURES = {
     "b200ops_grouped_matmul_workspace_size": (c_size_t, [c_int64] * 4),
     "b200ops_grouped_matmul": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p, c_size_t,
                                                                         c_void_p]),
-    "b200ops_grouped_matmul_swiglu": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p]),
+    "b200ops_grouped_matmul_swiglu": (c_int, [c_void_p] * 4 + [c_int64] * 4 + [c_void_p, c_size_t, c_void_p]),
     "b200ops_fused_qkv_rope_cache": (c_int, [c_void_p] * 8 + [c_int64] * 5 + [ctypes.POINTER(c_int64), c_int,
                                                                               c_void_p]),
     "b200ops_fused_qkv_norm_rope_cache": (c_int, [c_void_p] * 3 + [c_float] + [c_void_p] * 7 + [c_int64] * 5 +
@@ -177,11 +177,13 @@ def grouped_matmul(x, w_storage, group_list, y, workspace=None, stream=None):
                                         x.shape[0], k, e, n, _ptr(workspace), ws_size, _stream(stream)))
 
 
-def grouped_matmul_swiglu(x, w_storage, group_list, y, stream=None):
-    """`w_storage` [E, 2*d, K]: gate rows then up rows; y [M, d] = swiglu(x @ w)."""
+def grouped_matmul_swiglu(x, w_storage, group_list, y, workspace=None, stream=None):
+    """`w_storage` [E, 2*d, K]: gate rows then up rows; y [M, d] = swiglu(x @ w).  `workspace` as
+    for grouped_matmul (size from grouped_matmul_workspace_size with n = 2*d)."""
     e, n, k = w_storage.shape
+    ws_size = 0 if workspace is None else workspace.numel() * workspace.element_size()
     check(load().b200ops_grouped_matmul_swiglu(_ptr(x), _ptr(w_storage), _ptr(group_list), _ptr(y),
-                                               x.shape[0], k, e, n, _stream(stream)))
+                                               x.shape[0], k, e, n, _ptr(workspace), ws_size, _stream(stream)))
 
 
 def matmul(x, w, y, stream=None):

@@ -17,13 +17,15 @@
 //               predicated on the group's row end (an M-tail tile never writes into the next
 //               group's rows; reading them is harmless)
 //
-// Split-K.  When the problem has fewer output tiles than SMs (decode batches: one m-tile per
-// expert; a down projection with N = 4096 has 16 n-tiles) each CTA can only stream its own
-// operands at about 100 GB/s and most SMs idle.  If the caller passes a workspace, every CTA
-// derives the same split factor s = floor(CTAs / tiles) from the tile count it computed on
-// the device, a work item becomes (tile, k-slice), and the s CTAs of a tile write fp32
-// partial tiles to the workspace.  A counter per tile identifies the last CTA to finish; it
-// alone sums the partials and writes the fp16 rows.  Nobody waits on another CTA.
+// Balanced schedule.  Tiles handed out whole leave a ragged last wave (160 tiles of a long k on
+// 148 SMs take two waves), and a problem with fewer tiles than SMs leaves SMs idle while each
+// busy CTA streams its operands at the rate one SM can ingest.  If the caller passes a
+// workspace, every CTA derives the same decision from the tile count it computed on the device:
+// the (tile, k-block) units are cut into one contiguous range per CTA; whole tiles inside a range
+// are stored directly, the incomplete tiles at its ends go to the workspace as fp32 partial
+// tiles.  A counter per tile identifies the last CTA to publish a part; it alone sums the parts
+// in CTA order and writes the fp16 rows (with SwiGLU applied for the fused gate/up form).
+// Nobody waits on another CTA.
 //
 // CTA pairs.  Problems of a wave of tiles or more run grouped_matmul_pair_kernel instead
 // (grouped_matmul_pair.cuh): clusters of two CTAs issue one 256 x 256 x 16 MMA (cta_group::2), each
@@ -67,30 +69,19 @@ constexpr int kErrMmaWaitTmem = 3;
 constexpr int kErrEpilogueWait = 4;
 constexpr int kMinKBlocksPerSplit = 4;  // keep every k-slice long enough to fill the ring
 
-// Workspace layout (only used when split-K engages): [kMaxGrid] tile counters, then
-// [kMaxGrid] fp32 partial tiles of BM x BN.  With s > 1 there is at most one work item per CTA.
+// Workspace layout (used by the balanced schedule): one counter per tile, then two fp32 partial
+// tiles of BM x BN per CTA (a CTA's range has at most two incomplete tiles, see partial_slot).
 constexpr int kMaxGrid = 256;
+constexpr int kBalancedWaves = 16;  // the host offers the workspace below this many waves of tiles (by its row bound)
 constexpr size_t kPartialTileBytes = static_cast<size_t>(BM) * kWideBN * sizeof(float);
-constexpr size_t kCounterBytes = kMaxGrid * sizeof(int);
+constexpr size_t kCounterBytes = static_cast<size_t>(kBalancedWaves) * kMaxGrid * sizeof(int);
 
-// Host-side gate, shared by the size query and the launch.  Split-K adds a serial tail of
-// about 12 us (publish the partial tile, count, reduce), so it only pays when a tile's k-loop is
-// long: measured on B200, K = 14336 with 16-32 tiles drops from 92-98 us to 47-70 us, while
-// K = 4096 with 32-48 tiles gets slower (29-32 us -> 35-37 us).  Hence K >= 8192, and at least
-// half of the SMs left without a tile even by the densest packing of the rows.  (Narrower
-// output tiles were also tried for these shapes and lost: with BN = 64 two thirds of every
-// stage is the re-read activation tile, and an 8-expert down projection went from 152 to 262 us.)
+// A k range shorter than this does not amortise the publish-and-sum tail of split-K proper
+// (fewer tiles than half the CTAs).
 constexpr int64_t kMinSplitK = 8192;
 
-inline bool split_k_possible(int64_t num_tokens, int64_t k, int64_t n, int sms) {
-  const int64_t n_tiles = (n + kWideBN - 1) / kWideBN;
-  const int64_t min_tiles = ((num_tokens + BM - 1) / BM) * n_tiles;
-  return min_tiles * 2 <= sms && k >= kMinSplitK;
-}
-
 // Narrow tiles: one m-tile of rows at most, wide tiles would occupy under a quarter of the SMs,
-// and K too short for split-K (which wins where both apply: 51 us against 71 us for a
-// 70-row, K = 14336, N = 4096 projection).
+// and K too short for split-K (which wins where both apply).
 inline bool use_narrow_tiles(int64_t num_tokens, int64_t k, int64_t n, int sms) {
   return num_tokens <= BM && ((n + kWideBN - 1) / kWideBN) * 4 <= sms && k < kMinSplitK;
 }
@@ -98,17 +89,9 @@ inline bool use_narrow_tiles(int64_t num_tokens, int64_t k, int64_t n, int sms) 
 // CTA pairs (grouped_matmul_pair.cuh): for problems bound by the tensor pipe and not by streaming
 // the weights once -- at least one wave of 128 x 256 output tiles, and two m-tiles per expert on
 // average (with one m-tile per expert the second CTA of every pair would multiply nothing useful).
-// Measured on B200 against the single-CTA kernel, interleaved on one GPU: 4096^3 dense 102 us
-// against 112 us; 2048 rows x 4096 x 4096 (1.7 waves) 94 against 97 us; the 8192-row, 8-expert
-// benchmark shapes 1525 against 1555 us and 806 against 824 us on a cool GPU, and 1686 against
-// 1854 us and 830 against 903 us once the 1 kW power cap has pulled the clocks down -- a pair
-// moves a third less operand data per flop, and under the cap that is clock speed.
-// (Running the odd last m-tile of a group in a launch of its own instead of pairing it with a
-// tile past the group's end was tried and is no faster: 1677 / 929 us.)
-// The row count the host sees is only a bound (an expert-parallel receive buffer of 1536 rows
-// holds about 128 at decode time, and the pair kernel then takes 54 us where the single-CTA kernel
-// takes 45 us), hence also an absolute floor on it.
-// B200OPS_GMM_PAIR: 0 = never, 2 = always (tests), otherwise this rule.
+// The row count the host sees is only a bound (an expert-parallel receive buffer holds a fraction
+// of it at decode time, where the pair kernel is slower than the single-CTA one), hence also an
+// absolute floor on it.  B200OPS_GMM_PAIR: 0 = never, 2 = always (tests), otherwise this rule.
 constexpr int64_t kMinRowsForPairs = 2048;
 inline int pair_mode() { return knob(kKnobGmmPair, 1); }
 
@@ -154,7 +137,16 @@ inline int cluster_split_factor(int64_t num_tokens, int64_t k, int64_t num_exper
 
 inline int launch_sms() { return sm_count() < kMaxGrid ? sm_count() : kMaxGrid; }
 
-inline size_t workspace_bytes() { return kCounterBytes + launch_sms() * kPartialTileBytes; }
+inline size_t workspace_bytes() { return kCounterBytes + 2 * static_cast<size_t>(launch_sms()) * kPartialTileBytes; }
+
+// Host-side gate of the balanced schedule, shared by the size query and the launch: a workspace
+// is worth having when the tile count (by the host's row bound, an upper bound of the real
+// one) is within kBalancedWaves waves.  The kernel decides with the real count.
+inline bool balanced_possible(int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n, int sms) {
+  const int64_t n_tiles = (n + kWideBN - 1) / kWideBN;
+  const int64_t max_tiles = ((num_tokens + BM - 1) / BM + num_experts) * n_tiles;
+  return k >= 1024 && max_tiles < static_cast<int64_t>(kBalancedWaves) * sms;
+}
 
 struct Control {
   uint64_t full[kMaxStages];
@@ -163,7 +155,8 @@ struct Control {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  int split_rank;  // arrival order of this CTA among the k-slices of its tile
+  int split_rank;  // arrival order of this CTA among the parts of its tile
+  int part_slot[kMaxGrid];  // workspace slots of a tile's parts, in CTA order (reducing CTA only)
   int tile_prefix[kMaxExperts + 1];  // first tile id of each group; [E] = total tiles
   int row_start[kMaxExperts];
   int row_end[kMaxExperts];
@@ -227,19 +220,86 @@ __device__ __forceinline__ __half* output_row(const RowScatter& sc, __half* y, i
   return static_cast<__half*>(sc.peers.base[peer]) + (static_cast<size_t>(sc.my_rank) * sc.cap + off) * N;
 }
 
-// Work item -> (tile, k-slice).  Items of one tile are adjacent so its CTAs run together.
-struct WorkItem {
-  int tile, kb0, kb1, split;
+// Work decomposition.  A unit is one k-block of one tile; tiles are numbered as locate_tile
+// numbers them.  Two schedules:
+//   by tiles    CTA c takes tiles c, c + G, ... whole (no workspace needed);
+//   balanced    the units are cut into G equal contiguous ranges, CTA c takes range c.  A range
+//               covers the end of one tile, whole tiles, and the start of another: whole tiles are
+//               stored directly, parts go through the workspace (see the epilogue).  Chosen when
+//               a workspace is given and the tile count leaves a ragged last wave that matters
+//               (fewer than 8 waves, not a multiple of the grid): 160 tiles of a long k on 148 SMs
+//               are two waves by tiles, 1.08 waves balanced.  With fewer tiles than CTAs this is
+//               split-K; ranges are kept at least kMinKBlocksPerSplit k-blocks long.
+struct Segment {
+  int tile, kb0, kb1;
 };
 
-__device__ __forceinline__ WorkItem locate_item(int item, int splits, int k_blocks) {
-  WorkItem w;
-  w.tile = item / splits;
-  w.split = item - w.tile * splits;
-  w.kb0 = static_cast<int>(static_cast<long long>(w.split) * k_blocks / splits);
-  w.kb1 = static_cast<int>(static_cast<long long>(w.split + 1) * k_blocks / splits);
-  return w;
+struct Schedule {
+  long long units;   // total_tiles * k_blocks
+  int k_blocks, total_tiles;
+  int ctas;          // CTAs that take part (balanced: ranges; by tiles: the grid)
+  bool balanced;
+  __device__ __forceinline__ long long first_unit(int c) const { return units * c / ctas; }
+  // The CTA whose range holds unit u: the largest c with first_unit(c) <= u.
+  __device__ __forceinline__ int cta_of(long long u) const {
+    return static_cast<int>(((u + 1) * ctas + units - 1) / units) - 1;
+  }
+};
+
+__device__ __forceinline__ Schedule make_schedule(int total_tiles, int k_blocks, int grid, bool have_workspace) {
+  Schedule s;
+  s.k_blocks = k_blocks;
+  s.total_tiles = total_tiles;
+  s.units = static_cast<long long>(total_tiles) * k_blocks;
+  s.ctas = grid;
+  // Fewer tiles than half the CTAs is split-K proper, whose publish-and-sum tail only pays for a
+  // long k (kMinSplitK); beyond that the tail is a few percent of a CTA's range.
+  s.balanced = have_workspace && total_tiles > 0 && total_tiles % grid != 0 && total_tiles < 8 * grid &&
+               (2 * total_tiles > grid || k_blocks * BK >= kMinSplitK);
+  if (s.balanced) {
+    const long long most = s.units / kMinKBlocksPerSplit;
+    if (most < grid) s.ctas = most < 1 ? 1 : static_cast<int>(most);
+  }
+  return s;
 }
+
+// Workspace slot of a part: a CTA has at most one part that starts inside a tile (the first
+// segment of its range) and at most one that starts a tile without finishing it (the last).
+__device__ __forceinline__ int partial_slot(int cta, int kb0) { return 2 * cta + (kb0 == 0 ? 1 : 0); }
+
+struct Walk {
+  const Schedule& s;
+  long long lo, hi;  // balanced: remaining units; by tiles: next tile, tile count
+  int stride;
+  __device__ __forceinline__ Walk(const Schedule& sched, int cta) : s(sched) {
+    if (s.balanced) {
+      lo = cta < s.ctas ? s.first_unit(cta) : 0;
+      hi = cta < s.ctas ? s.first_unit(cta + 1) : 0;
+      stride = 0;
+    } else {
+      lo = cta;
+      hi = s.total_tiles;
+      stride = s.ctas;
+    }
+  }
+  __device__ __forceinline__ bool next(Segment& g) {
+    if (lo >= hi) return false;
+    if (!s.balanced) {
+      g.tile = static_cast<int>(lo);
+      g.kb0 = 0;
+      g.kb1 = s.k_blocks;
+      lo += stride;
+      return true;
+    }
+    g.tile = static_cast<int>(lo / s.k_blocks);
+    const long long t0 = static_cast<long long>(g.tile) * s.k_blocks;
+    const long long end = hi < t0 + s.k_blocks ? hi : t0 + s.k_blocks;
+    g.kb0 = static_cast<int>(lo - t0);
+    g.kb1 = static_cast<int>(end - t0);
+    lo = end;
+    return true;
+  }
+};
 
 // Tiles of one group are numbered m-fastest.  `g` is carried between calls: tile ids only
 // grow within a CTA, so the search is amortised O(1).
@@ -284,6 +344,89 @@ __device__ __forceinline__ void glu_epilogue(uint32_t taddr, __half* yrow, bool 
         o[j] = f2_to_h2(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
       }
       dst[v] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
+// Sum the parts of one output tile (fp32 partial tiles in the workspace, `slots` in CTA order) and
+// store its rows.  Run by the 128 epilogue threads of the CTA that published the tile's last
+// part.  Warp `quarter` takes rows quarter, quarter + 4, ...; a row is read and written by one
+// warp, coalesced.  Four rows and two parts are loaded before anything is added, so each lane
+// keeps sixteen 16-byte loads in flight: the step is a chain of L2 round trips otherwise.
+// kGlu: the tile's first BN / 2 columns are gate columns, the rest the up columns of the same
+// outputs; sums are rounded to fp16 and SwiGLU applied as in glu_epilogue.
+template <int BN, bool kGlu>
+__device__ __forceinline__ void reduce_parts(const float* __restrict__ partials, const int* slots, int parts,
+                                             int rows_here, int quarter, int lane, const TileCoord& tc,
+                                             __half* y, int y_cols, const RowScatter& scatter) {
+  constexpr int kPerLane = kGlu ? 4 : 8;           // accumulator columns per lane and operand half
+  constexpr int kHalves = kGlu ? 2 : 1;            // gate + up, or one run of columns
+  constexpr int kVecs = kPerLane / 4;              // float4 loads per half
+  const int col = lane * kPerLane;
+  if (col >= (kGlu ? BN / 2 : BN) || tc.n0 + col >= y_cols) return;  // widths are multiples of 64
+  for (int r0 = quarter; r0 < rows_here; r0 += 16) {
+    float acc[4][kHalves][kPerLane];
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) acc[j][h][i] = 0.f;
+    for (int s0 = 0; s0 < parts; s0 += 2) {
+      float4 v[2][4][kHalves][kVecs];
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int rr = r0 + 4 * j;
+          const bool live = s0 + u < parts && rr < rows_here;
+          const float* base =
+              live ? partials + static_cast<size_t>(slots[s0 + u]) * (BM * BN) + rr * BN + col : nullptr;
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+            for (int q = 0; q < kVecs; ++q)
+              v[u][j][h][q] = live ? __ldcg(reinterpret_cast<const float4*>(base + h * (BN / 2)) + q)
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+          for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+            for (int q = 0; q < kVecs; ++q) {
+              acc[j][h][4 * q + 0] += v[u][j][h][q].x;
+              acc[j][h][4 * q + 1] += v[u][j][h][q].y;
+              acc[j][h][4 * q + 2] += v[u][j][h][q].z;
+              acc[j][h][4 * q + 3] += v[u][j][h][q].w;
+            }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int rr = r0 + 4 * j;
+      bool out_ok = rr < rows_here;
+      __half* out_row = output_row(scatter, y, tc.row0 + rr, y_cols, out_ok);
+      if (!out_ok) continue;
+      if constexpr (kGlu) {
+        uint32_t o[2];
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const float2 gf = h2_to_f2(f2_to_h2(acc[j][0][2 * q], acc[j][0][2 * q + 1]));
+          const float2 uf = h2_to_f2(f2_to_h2(acc[j][1][2 * q], acc[j][1][2 * q + 1]));
+          o[q] = f2_to_h2(silu_mul(gf.x, uf.x), silu_mul(gf.y, uf.y));
+        }
+        *reinterpret_cast<uint2*>(out_row + tc.n0 + col) = make_uint2(o[0], o[1]);
+      } else {
+        uint4 o;
+        o.x = f2_to_h2(acc[j][0][0], acc[j][0][1]);
+        o.y = f2_to_h2(acc[j][0][2], acc[j][0][3]);
+        o.z = f2_to_h2(acc[j][0][4], acc[j][0][5]);
+        o.w = f2_to_h2(acc[j][0][6], acc[j][0][7]);
+        *reinterpret_cast<uint4*>(out_row + tc.n0 + col) = o;
+      }
     }
   }
 }
@@ -364,14 +507,9 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
   const int total_tiles = ctl->tile_prefix[E];
   const uint32_t tmem_base = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
-  // Split factor: identical in every CTA because it depends only on the tile count.
-  int splits = 1;
-  if (partials != nullptr && total_tiles > 0) {
-    splits = static_cast<int>(gridDim.x) / total_tiles;
-    splits = min(splits, k_blocks / kMinKBlocksPerSplit);
-    splits = max(splits, 1);
-  }
-  const int total_items = total_tiles * splits;
+  // Every role walks the same sequence of segments (tile, k-blocks [kb0, kb1)); the schedule
+  // depends only on the tile count, so all CTAs agree on it.
+  const Schedule sched = make_schedule(total_tiles, k_blocks, static_cast<int>(gridDim.x), partials != nullptr);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
@@ -379,10 +517,11 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       int stage = 0, g = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x) {
-        const WorkItem wi = locate_item(item, splits, k_blocks);
-        const TileCoord tc = locate_tile(ctl, wi.tile, g, kOutBN);
-        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
+      Walk walk(sched, static_cast<int>(blockIdx.x));
+      Segment sg;
+      while (ok && walk.next(sg)) {
+        const TileCoord tc = locate_tile(ctl, sg.tile, g, kOutBN);
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
             *abort_flag = 1;
             atomicCAS(&g_pipeline_status, 0, kErrProducerWait);
@@ -413,8 +552,9 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       uint32_t phase = 0;
       bool ok = true;
       int iter = 0;
-      for (int item = blockIdx.x; ok && item < total_items; item += gridDim.x, ++iter) {
-        const WorkItem wi = locate_item(item, splits, k_blocks);
+      Walk walk(sched, static_cast<int>(blockIdx.x));
+      Segment sg;
+      for (; ok && walk.next(sg); ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (iter >> 1) & 1;
         if (!ptx::mbar_wait(&ctl->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
@@ -424,7 +564,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
         }
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = wi.kb0; kb < wi.kb1; ++kb) {
+        for (int kb = sg.kb0; kb < sg.kb1; ++kb) {
           if (!ptx::mbar_wait(&ctl->full[stage], phase, abort_flag)) {
             *abort_flag = 1;
             atomicCAS(&g_pipeline_status, 0, kErrMmaWaitFull);
@@ -439,7 +579,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
             // Inside a 128-byte swizzle row the k-th 16-element slice starts 32 bytes on.
             const uint64_t a_desc = ptx::make_sw128_kmajor_desc(a_addr + k * UMMA_K * 2);
             const uint64_t b_desc = ptx::make_sw128_kmajor_desc(b_addr + k * UMMA_K * 2);
-            ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb != wi.kb0 || k != 0) ? 1u : 0u);
+            ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
           }
           ptx::umma_commit(&ctl->empty[stage]);  // frees the stage once these MMAs retire
           if (++stage == kStages) {
@@ -454,9 +594,11 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
     // ---------------- epilogue (warps 2..5) ----------------
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32)
     int g = 0, iter = 0;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++iter) {
-      const WorkItem wi = locate_item(item, splits, k_blocks);
-      const TileCoord tc = locate_tile(ctl, wi.tile, g, kOutBN);
+    Walk walk(sched, static_cast<int>(blockIdx.x));
+    Segment sg;
+    for (; walk.next(sg); ++iter) {
+      const TileCoord tc = locate_tile(ctl, sg.tile, g, kOutBN);
+      const bool whole = sg.kb0 == 0 && sg.kb1 == k_blocks;
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1;
       if (!ptx::mbar_wait(&ctl->tmem_full[acc], acc_phase, abort_flag)) {
@@ -468,110 +610,70 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
       const int tile_row = quarter * 32 + lane;
       const int row = tc.row0 + tile_row;
       bool row_ok = row < tc.row_end;
-      __half* yrow = output_row(scatter, y, row, n_out, row_ok) + tc.n0;
-      float* prow = splits > 1 ? partials + static_cast<size_t>(item) * (BM * BN) + tile_row * BN : nullptr;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
-      if constexpr (kGlu) {
-        glu_epilogue<kOutBN>(taddr, yrow, row_ok, tc.n0, n_out);
-      } else {
-#pragma unroll 1
-      for (int c = 0; c < BN / 32; ++c) {
-        if (tc.n0 + c * 32 >= N) break;  // N is a multiple of 64, so chunks are all-or-nothing
-        uint32_t r[32];
-        ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
-        ptx::tmem_ld_wait();
-        if (!row_ok) continue;
-        if (splits == 1) {
-          uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
-#pragma unroll
-          for (int v = 0; v < 4; ++v) {
-            uint4 o;
-            o.x = f2_to_h2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
-            o.y = f2_to_h2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
-            o.z = f2_to_h2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
-            o.w = f2_to_h2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
-            dst[v] = o;
-          }
+      if (whole) {
+        __half* yrow = output_row(scatter, y, row, n_out, row_ok) + tc.n0;
+        if constexpr (kGlu) {
+          glu_epilogue<kOutBN>(taddr, yrow, row_ok, tc.n0, n_out);
         } else {
+#pragma unroll 1
+          for (int c = 0; c < BN / 32; ++c) {
+            if (tc.n0 + c * 32 >= N) break;  // N is a multiple of 64, so chunks are all-or-nothing
+            uint32_t r[32];
+            ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+            ptx::tmem_ld_wait();
+            if (!row_ok) continue;
+            uint4* dst = reinterpret_cast<uint4*>(yrow + c * 32);
+#pragma unroll
+            for (int v = 0; v < 4; ++v) {
+              uint4 o;
+              o.x = f2_to_h2(__uint_as_float(r[v * 8 + 0]), __uint_as_float(r[v * 8 + 1]));
+              o.y = f2_to_h2(__uint_as_float(r[v * 8 + 2]), __uint_as_float(r[v * 8 + 3]));
+              o.z = f2_to_h2(__uint_as_float(r[v * 8 + 4]), __uint_as_float(r[v * 8 + 5]));
+              o.w = f2_to_h2(__uint_as_float(r[v * 8 + 6]), __uint_as_float(r[v * 8 + 7]));
+              dst[v] = o;
+            }
+          }
+        }
+      } else {
+        // Part of a tile's k range: the fp32 accumulator goes to this CTA's slot of the workspace.
+        float* prow = partials + static_cast<size_t>(partial_slot(blockIdx.x, sg.kb0)) * (BM * BN) + tile_row * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+          ptx::tmem_ld_wait();
+          if (!row_ok) continue;
           uint4* dst = reinterpret_cast<uint4*>(prow + c * 32);
 #pragma unroll
           for (int v = 0; v < 8; ++v) dst[v] = make_uint4(r[v * 4], r[v * 4 + 1], r[v * 4 + 2], r[v * 4 + 3]);
         }
       }
-      }
       ptx::tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(&ctl->tmem_empty[acc]);
-      if (splits > 1) {
-        // Publish this k-slice; the CTA that finds the other s-1 slices already published
-        // reduces all of them.  Counters were zeroed by the host before the launch.
+      if (!whole) {
+        // Publish this part; the CTA that finds all other parts of the tile already published
+        // sums them (in CTA order, so the result does not depend on timing) and writes the rows.
+        // Counters were zeroed by the host before the launch.  Nobody waits.
+        const int c_first = sched.cta_of(static_cast<long long>(sg.tile) * k_blocks);
+        const int c_last = sched.cta_of(static_cast<long long>(sg.tile + 1) * k_blocks - 1);
+        const int parts = c_last - c_first + 1;
         __threadfence();
         asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (threadIdx.x == 64) ctl->split_rank = atomicAdd(&tile_counters[wi.tile], 1);
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (ctl->split_rank == splits - 1) {
-          __threadfence();
-          const float* first = partials + static_cast<size_t>(wi.tile) * splits * (BM * BN);
-          const int rows_here = min(BM, tc.row_end - tc.row0);
-          const int cols_here = min(BN, N - tc.n0);
-          // Warp `quarter` reduces rows quarter, quarter+4, ...; a row is read and written by one
-          // warp, 8 columns per lane, coalesced.  Four rows and two k-slices are loaded before
-          // anything is added, so each lane keeps sixteen 16-byte loads in flight: the step is a
-          // chain of L2 round trips otherwise.
-          const int col = lane * 8;
-          if (col < cols_here) {
-            for (int r0 = quarter; r0 < rows_here; r0 += 16) {
-              float acc8[4][8];
-#pragma unroll
-              for (int j = 0; j < 4; ++j)
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc8[j][i] = 0.f;
-              for (int s0 = 0; s0 < splits; s0 += 2) {
-                float4 v[2][4][2];
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    const int rr = r0 + 4 * j;
-                    if (s0 + u < splits && rr < rows_here) {
-                      const float4* p = reinterpret_cast<const float4*>(
-                          first + static_cast<size_t>(s0 + u) * (BM * BN) + rr * BN + col);
-                      v[u][j][0] = __ldcg(p);
-                      v[u][j][1] = __ldcg(p + 1);
-                    } else {
-                      v[u][j][0] = make_float4(0.f, 0.f, 0.f, 0.f);
-                      v[u][j][1] = make_float4(0.f, 0.f, 0.f, 0.f);
-                    }
-                  }
-                }
-#pragma unroll
-                for (int u = 0; u < 2; ++u) {
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    acc8[j][0] += v[u][j][0].x; acc8[j][1] += v[u][j][0].y;
-                    acc8[j][2] += v[u][j][0].z; acc8[j][3] += v[u][j][0].w;
-                    acc8[j][4] += v[u][j][1].x; acc8[j][5] += v[u][j][1].y;
-                    acc8[j][6] += v[u][j][1].z; acc8[j][7] += v[u][j][1].w;
-                  }
-                }
-              }
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const int rr = r0 + 4 * j;
-                bool out_ok = rr < rows_here;
-                __half* out_row = output_row(scatter, y, tc.row0 + rr, N, out_ok);
-                if (out_ok) {
-                  uint4 o;
-                  o.x = f2_to_h2(acc8[j][0], acc8[j][1]);
-                  o.y = f2_to_h2(acc8[j][2], acc8[j][3]);
-                  o.z = f2_to_h2(acc8[j][4], acc8[j][5]);
-                  o.w = f2_to_h2(acc8[j][6], acc8[j][7]);
-                  *reinterpret_cast<uint4*>(out_row + tc.n0 + col) = o;
-                }
-              }
-            }
-          }
+        if (threadIdx.x == 64) ctl->split_rank = atomicAdd(&tile_counters[sg.tile], 1);
+        for (int i = threadIdx.x - 64; i < parts; i += 128) {
+          const long long begin = sched.first_unit(c_first + i) - static_cast<long long>(sg.tile) * k_blocks;
+          ctl->part_slot[i] = partial_slot(c_first + i, begin > 0 ? static_cast<int>(begin) : 0);
         }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (ctl->split_rank == parts - 1) {
+          __threadfence();
+          const int rows_here = min(BM, tc.row_end - tc.row0);
+          reduce_parts<BN, kGlu>(partials, ctl->part_slot, parts, rows_here, quarter, lane, tc, y, kGlu ? n_out : N,
+                                 scatter);
+        }
+        asm volatile("bar.sync 2, 128;" ::: "memory");  // part_slot is reused by the next segment
       }
     }
   }
@@ -593,7 +695,7 @@ extern "C" size_t b200ops_grouped_matmul_workspace_size(int64_t num_tokens, int6
                                                         int64_t n) {
   using namespace b200ops;
   if (num_tokens <= 0 || k <= 0 || num_experts <= 0 || n <= 0) return 0;
-  return gmm::split_k_possible(num_tokens, k, n, gmm::launch_sms()) ? gmm::workspace_bytes() : 0;
+  return gmm::balanced_possible(num_tokens, k, num_experts, n, gmm::launch_sms()) ? gmm::workspace_bytes() : 0;
 }
 
 namespace b200ops {
@@ -620,7 +722,7 @@ extern "C" int b200ops_grouped_matmul(const void* x, const void* w, const int64_
 
 extern "C" int b200ops_grouped_matmul_swiglu(const void* x, const void* w, const int64_t* group_list, void* y,
                                              int64_t num_tokens, int64_t k, int64_t num_experts, int64_t two_d,
-                                             void* stream) {
+                                             void* workspace, size_t workspace_size, void* stream) {
   b200ops::gmm::RowScatter none;
   none.index = nullptr;
   none.cap = 1;
@@ -628,8 +730,8 @@ extern "C" int b200ops_grouped_matmul_swiglu(const void* x, const void* w, const
   none.world = 0;
   for (int r = 0; r < b200ops::kMaxPeers; ++r) none.peers.base[r] = nullptr;
   B200OPS_REQUIRE(num_tokens <= 0 || y != nullptr, "grouped_matmul_swiglu: null pointer");
-  return b200ops::gmm::launch(x, w, group_list, y, num_tokens, k, num_experts, two_d, nullptr, 0, none, true,
-                              stream);
+  return b200ops::gmm::launch(x, w, group_list, y, num_tokens, k, num_experts, two_d, workspace, workspace_size,
+                              none, true, stream);
 }
 
 extern "C" int b200ops_grouped_matmul_scatter(const void* x, const void* w, const int64_t* group_list,
@@ -935,7 +1037,7 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   int* counters = nullptr;
   float* partials = nullptr;
   int grid = static_cast<int>(max_tiles < sms ? max_tiles : sms);
-  if (!glu && workspace != nullptr && gmm::split_k_possible(num_tokens, k, n, sms)) {
+  if (!narrow && workspace != nullptr && gmm::balanced_possible(num_tokens, k, num_experts, n, sms)) {
     if (workspace_size < gmm::workspace_bytes())
       return fail(B200OPS_EWORKSPACE, "grouped_matmul: workspace of %zu bytes needed, got %zu",
                   gmm::workspace_bytes(), workspace_size);
@@ -943,7 +1045,7 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
     counters = static_cast<int*>(workspace);
     partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + gmm::kCounterBytes);
     B200OPS_CUDA(cudaMemsetAsync(counters, 0, gmm::kCounterBytes, st));
-    grid = sms;  // idle CTAs exit; the split factor needs the full grid
+    grid = sms;  // the schedule cuts the work into one range per SM; CTAs without one exit
   }
   B200OPS_CUDA(launch_kernel(kern, dim3(grid), dim3(gmm::kThreads), smem, st, map_x, map_w, group_list,
                       static_cast<__half*>(y), static_cast<int>(num_tokens), static_cast<int>(n),

@@ -538,9 +538,11 @@ at::Tensor grouped_matmul_swiglu(at::Tensor x, at::Tensor w, at::Tensor group_li
   check_same_device(x, group_list, "grouped_matmul_swiglu");
   const c10::cuda::CUDAGuard guard(x.device());
   at::Tensor y = at::empty({x.size(0), w.size(2) / 2}, x.options());
+  const size_t ws = b200ops_grouped_matmul_workspace_size(x.size(0), x.size(1), w.size(0), w.size(2));
+  at::Tensor workspace = at::empty({static_cast<int64_t>(ws)}, x.options().dtype(at::kByte));
   check_status(b200ops_grouped_matmul_swiglu(x.data_ptr(), w.data_ptr(), group_list.data_ptr<int64_t>(),
                                              y.data_ptr(), x.size(0), x.size(1), w.size(0), w.size(2),
-                                             current_stream()),
+                                             ws ? workspace.data_ptr() : nullptr, ws, current_stream()),
                "grouped_matmul_swiglu");
   return y;
 }

@@ -184,14 +184,16 @@ int b200ops_paged_attention_static(const void* q, const void* key_cache, const v
  *   group_list : int64 [num_experts], inclusive cumulative row ends;  y : f16 [num_tokens, n]
  * Requires k % 64 == 0 and n % 64 == 0 (csrc/ffi/ops.cpp:173).  Rows past gl[E-1] are not
  * written.  Empty groups are skipped (grouped_mat_mul_ex.cpp:40).
- * Workspace: optional.  Grouped shapes with fewer output tiles than SMs and a long k (expert
- * projections of a decode batch) run split-K when a workspace of
- * b200ops_grouped_matmul_workspace_size() bytes is passed (the query returns 0 for shapes that
- * cannot benefit); the call zeroes the counters it needs itself.  With workspace == NULL the
- * same result is computed without split-K.  A single group of at most 256 rows (a dense
- * projection) splits k over thread-block clusters instead and needs no workspace either way.
- * The kernel is chosen from the shape alone; every choice sums fp16 products in fp32 and
- * rounds once, so results agree within the last fp16 bit.
+ * Workspace: optional.  With a workspace of b200ops_grouped_matmul_workspace_size() bytes (0 for
+ * shapes that cannot benefit: many waves of output tiles by the row bound) the kernel may
+ * spread the work evenly over the SMs instead of handing out whole output tiles: tiles cut by
+ * a range boundary are summed from fp32 partial tiles in the workspace (a problem with fewer
+ * tiles than SMs thereby runs split-K, one whose tiles do not fill the last wave loses no
+ * wave).  The call zeroes the counters it needs itself.  With workspace == NULL the same result
+ * is computed tile by tile.  A single group of at most 256 rows (a dense projection) splits k
+ * over thread-block clusters instead and needs no workspace either way.  The kernel is chosen
+ * from the shape alone; every choice sums fp16 products in fp32 and rounds once, so results
+ * agree within the last fp16 bit, and each choice by itself is bitwise repeatable.
  */
 size_t b200ops_grouped_matmul_workspace_size(int64_t num_tokens, int64_t k, int64_t num_experts,
                                              int64_t n);
@@ -294,11 +296,14 @@ int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row, const flo
  * (csrc/ffi/ops.cpp:126-154) on its result, without the [num_tokens, two_d] intermediate.
  * w [num_experts, two_d, k] f16, k contiguous: rows [0, d) are the gate projection, rows
  * [d, 2d) the up projection, d = two_d / 2 a multiple of 64.  y [num_tokens, d] f16.  The
- * accumulators are rounded to f16 before SwiGLU, so the result equals the two-call form bit for bit.
+ * accumulators are rounded to f16 before SwiGLU, so the result equals the two-call form bit for
+ * bit (both forms given, or both not given, a workspace).  Workspace: optional, as for
+ * b200ops_grouped_matmul; b200ops_grouped_matmul_workspace_size(num_tokens, k, num_experts,
+ * two_d) gives its size.
  */
 int b200ops_grouped_matmul_swiglu(const void* x, const void* w, const int64_t* group_list, void* y,
                                   int64_t num_tokens, int64_t k, int64_t num_experts, int64_t two_d,
-                                  void* stream);
+                                  void* workspace, size_t workspace_size, void* stream);
 
 /*
  * grouped_matmul whose epilogue performs the return leg of the expert-parallel exchange

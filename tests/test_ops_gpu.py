@@ -748,3 +748,56 @@ def test_matmul_c_abi_any_shape(cabi, m, k, n):
     torch.cuda.synchronize()
     assert cabi.pipeline_status() == 0
     close(y.cpu(), (x.float() @ w.float().T).half())
+
+
+@pytest.mark.parametrize("counts,k,n", [
+    ([350, 340, 410], 2048, 4096),       # 160 tiles on 148 SMs: the ragged second wave is spread out
+    ([1024], 1024, 256 * 146),           # 7.9 waves: ranges of several whole tiles with cut ends
+    ([64] * 8, 14336, 4096),             # decode down projection: 128 tiles, under one wave
+    ([40, 0, 3, 90, 7, 64, 1, 128], 8192, 1024),  # fewer tiles than half the SMs, long k: split-K proper
+    ([200, 100], 1024, 320),             # N tail (320 = 256 + 64) in cut tiles
+])
+def test_grouped_matmul_balanced_schedule(cabi, counts, k, n):
+    """With a workspace the kernel cuts the (tile, k-block) units into equal ranges per SM; tiles
+    cut by a range boundary are summed from partial tiles.  Against the oracle, and against the
+    same call without a workspace (tile by tile): the two may differ in the last bit only."""
+    g = torch.Generator().manual_seed(sum(counts) + k)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half()
+    w_storage = (torch.randn(len(counts), n, k, generator=g) * 0.03).half()
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64)
+    assert cabi.grouped_matmul_workspace_size(m, k, len(counts), n) > 0
+    balanced = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0)
+    by_tiles = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False)
+    again = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0)
+    assert torch.equal(balanced, again)  # repeatable bit for bit
+    close(balanced, by_tiles)
+    rows, experts = _sampled_rows(gl.tolist(), per_group=24)
+    want = torch.stack([x[r].float() @ w_storage[e].float().T for r, e in zip(rows, experts)])
+    close(balanced[rows], want.half())
+
+
+@pytest.mark.parametrize("counts,k,d", [([350, 340, 410], 1024, 1792), ([64] * 8, 4096, 2048), ([1, 127, 129], 2048, 640)])
+def test_grouped_matmul_swiglu_balanced_schedule(cabi, counts, k, d):
+    """The fused gate/up form under the balanced schedule: the CTA that sums a cut tile applies
+    SwiGLU to the rounded sums, so the result still equals grouped_matmul followed by swiglu bit
+    for bit when both run the same schedule, and the oracle within tolerance."""
+    g = torch.Generator().manual_seed(sum(counts) + d)
+    m = sum(counts)
+    x = torch.randn(m, k, generator=g).half().to(DEV)
+    w = (torch.randn(len(counts), 2 * d, k, generator=g) * 0.03).half().to(DEV)
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64).to(DEV)
+    nbytes = cabi.grouped_matmul_workspace_size(m, k, len(counts), 2 * d)
+    assert nbytes > 0
+    ws = torch.full((nbytes,), 0xCD, dtype=torch.uint8, device=DEV)
+    fused = torch.full((m, d), float("nan"), dtype=torch.float16, device=DEV)
+    cabi.grouped_matmul_swiglu(x, w, gl, fused, ws)
+    h = torch.empty(m, 2 * d, dtype=torch.float16, device=DEV)
+    cabi.grouped_matmul(x, w, gl, h, ws)
+    two = torch.empty(m, d, dtype=torch.float16, device=DEV)
+    cabi.swiglu(h, two)
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    assert torch.equal(fused, two)
+    want = oracle.swiglu(oracle.grouped_matmul(x.cpu(), w.cpu().transpose(1, 2), gl.cpu()))
+    close(fused.cpu(), want)

@@ -296,10 +296,10 @@ int b200ops_moe_finalize(const void* rows, const int32_t* slot_to_row, const flo
  * (csrc/ffi/ops.cpp:126-154) on its result, without the [num_tokens, two_d] intermediate.
  * w [num_experts, two_d, k] f16, k contiguous: rows [0, d) are the gate projection, rows
  * [d, 2d) the up projection, d = two_d / 2 a multiple of 64.  y [num_tokens, d] f16.  The
- * accumulators are rounded to f16 before SwiGLU, so the result equals the two-call form bit for
- * bit (both forms given, or both not given, a workspace).  Workspace: optional, as for
- * b200ops_grouped_matmul; b200ops_grouped_matmul_workspace_size(num_tokens, k, num_experts,
- * two_d) gives its size.
+ * accumulators are rounded to f16 before SwiGLU, so without a workspace the result equals the
+ * two-call form bit for bit.  Workspace: optional, as for b200ops_grouped_matmul;
+ * b200ops_grouped_matmul_workspace_size(num_tokens, k, num_experts, two_d) gives its size (with
+ * it, sums of cut tiles may differ from the two-call form in the last bit).
  */
 int b200ops_grouped_matmul_swiglu(const void* x, const void* w, const int64_t* group_list, void* y,
                                   int64_t num_tokens, int64_t k, int64_t num_experts, int64_t two_d,

@@ -75,8 +75,9 @@ def test_argument_checks_run_before_any_cuda_call(cabi):
 def test_workspace_queries(cabi):
     lib = cabi.load()
     assert lib.b200ops_grouped_matmul_workspace_size(8192, 4096, 8, 28672) == 0  # plenty of tiles
-    assert lib.b200ops_grouped_matmul_workspace_size(64, 14336, 1, 4096) > 0  # few tiles, long K: split-K
-    assert lib.b200ops_grouped_matmul_workspace_size(256, 4096, 1, 6144) == 0  # K too short to pay off
+    assert lib.b200ops_grouped_matmul_workspace_size(64, 14336, 1, 4096) > 0  # few tiles: split-K
+    assert lib.b200ops_grouped_matmul_workspace_size(1100, 14336, 3, 4096) > 0  # a ragged second wave
+    assert lib.b200ops_grouped_matmul_workspace_size(256, 512, 1, 6144) == 0  # k too short to cut
     assert lib.b200ops_paged_attention_workspace_size(4, 8, 2, 128, 128, 2) == 0  # one chunk per sequence
     small = lib.b200ops_paged_attention_workspace_size(4, 8, 2, 128, 128, 16)
     n = lib.b200ops_paged_attention_workspace_size(64, 28, 4, 128, 128, 64)

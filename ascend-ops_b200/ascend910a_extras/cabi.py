@@ -62,8 +62,8 @@ SIGNATURES = {
     "b200ops_pipeline_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200ops_reload_options": (None, []),
     "b200ops_matmul": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_void_p]),
-    "b200ops_moe_dispatch": (c_int, [c_void_p] * 7 + [c_int64] * 2 + [c_void_p] * 7 + [c_int64] * 8 + [c_void_p]),
-    "b200ops_moe_gather": (c_int, [c_void_p] * 9 + [c_int64] * 5 + [c_void_p]),
+    "b200ops_moe_dispatch": (c_int, [c_void_p] * 7 + [c_int64] * 2 + [c_void_p] * 6 + [c_int64] * 8 + [c_void_p]),
+    "b200ops_moe_gather": (c_int, [c_void_p] * 8 + [c_int64] * 5 + [c_void_p]),
     "b200ops_moe_combine": (c_int, [c_void_p] * 7 + [c_int64] * 5 + [c_void_p]),
 }
 

@@ -156,6 +156,7 @@ struct Control {
   uint32_t tmem_base;
   int abort_flag;
   int split_rank;  // arrival order of this CTA among the parts of its tile
+  int live_groups;  // groups that hold rows
   int part_slot[kMaxGrid];  // workspace slots of a tile's parts, in CTA order (reducing CTA only)
   int tile_prefix[kMaxExperts + 1];  // first tile id of each group; [E] = total tiles
   int row_start[kMaxExperts];
@@ -227,9 +228,9 @@ __device__ __forceinline__ __half* output_row(const RowScatter& sc, __half* y, i
 //               covers the end of one tile, whole tiles, and the start of another: whole tiles are
 //               stored directly, parts go through the workspace (see the epilogue).  Chosen when
 //               a workspace is given and the tile count leaves a ragged last wave that matters
-//               (fewer than 8 waves, not a multiple of the grid): 160 tiles of a long k on 148 SMs
-//               are two waves by tiles, 1.08 waves balanced.  With fewer tiles than CTAs this is
-//               split-K; ranges are kept at least kMinKBlocksPerSplit k-blocks long.
+//               (see make_schedule): 160 tiles of a long k on 148 SMs are two waves by tiles, 1.08
+//               waves balanced.  With fewer tiles than CTAs this is split-K; ranges are kept at
+//               least kMinKBlocksPerSplit k-blocks long.
 struct Segment {
   int tile, kb0, kb1;
 };
@@ -246,16 +247,22 @@ struct Schedule {
   }
 };
 
-__device__ __forceinline__ Schedule make_schedule(int total_tiles, int k_blocks, int grid, bool have_workspace) {
+__device__ __forceinline__ Schedule make_schedule(int total_tiles, int k_blocks, int grid, bool have_workspace,
+                                                  int weight_tiles) {
   Schedule s;
   s.k_blocks = k_blocks;
   s.total_tiles = total_tiles;
   s.units = static_cast<long long>(total_tiles) * k_blocks;
   s.ctas = grid;
   // Fewer tiles than half the CTAs is split-K proper, whose publish-and-sum tail only pays for a
-  // long k (kMinSplitK); beyond that the tail is a few percent of a CTA's range.
-  s.balanced = have_workspace && total_tiles > 0 && total_tiles % grid != 0 && total_tiles < 8 * grid &&
-               (2 * total_tiles > grid || k_blocks * BK >= kMinSplitK);
+  // long k (kMinSplitK).  With more tiles the balanced schedule pays when CTAs run at their own
+  // pace, i.e. when the tensor pipe is the limit: every weight tile (`weight_tiles` of them: one per
+  // group with rows and column block) is used by two m-tiles or more on average.  With one m-tile
+  // per weight tile (decode batches) the kernel streams weights at the HBM rate, the CTAs of a
+  // ragged last wave simply run faster, and cutting tiles only adds traffic.
+  const bool split_k = 2 * total_tiles <= grid && k_blocks * BK >= kMinSplitK;
+  const bool even_out = 2 * total_tiles > grid && total_tiles < 8 * grid && total_tiles >= 2 * weight_tiles;
+  s.balanced = have_workspace && total_tiles > 0 && total_tiles % grid != 0 && (split_k || even_out);
   if (s.balanced) {
     const long long most = s.units / kMinKBlocksPerSplit;
     if (most < grid) s.ctas = most < 1 ? 1 : static_cast<int>(most);
@@ -492,13 +499,15 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int acc = 0;
+    int acc = 0, live = 0;
     ctl->tile_prefix[0] = 0;
     for (int e = 0; e < E; ++e) {
       const int rows = ctl->row_end[e] - ctl->row_start[e];
       acc += ((rows + BM - 1) / BM) * n_tiles;
+      live += rows > 0;
       ctl->tile_prefix[e + 1] = acc;
     }
+    ctl->live_groups = live;
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
@@ -509,7 +518,8 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
   volatile int* abort_flag = &ctl->abort_flag;
   // Every role walks the same sequence of segments (tile, k-blocks [kb0, kb1)); the schedule
   // depends only on the tile count, so all CTAs agree on it.
-  const Schedule sched = make_schedule(total_tiles, k_blocks, static_cast<int>(gridDim.x), partials != nullptr);
+  const Schedule sched = make_schedule(total_tiles, k_blocks, static_cast<int>(gridDim.x), partials != nullptr,
+                                       n_tiles * ctl->live_groups);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------

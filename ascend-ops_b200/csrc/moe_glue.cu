@@ -563,11 +563,12 @@ extern "C" int b200ops_peer_barrier(void* const* peer_flags, void* my_flags, voi
 //                  claim a row of the (this rank, slot) sub-segment in the owner's receive buffer
 //                  with an atomic cursor, store the token's row there through the peer mapping
 //                  and remember where the result will come back.  The last CTA to finish sends
-//                  each peer the row counts of that peer's slots and announces "step n
-//                  dispatched" in every peer's flag array.
-//   moe_gather     every CTA waits (bounded) until all peers have announced step n, derives the
-//                  expert-major order from the counts, and the CTAs together copy the received
-//                  rows into that order (the input of grouped_matmul) with the map back.
+//                  each peer the row counts of that peer's slots; a count word carries the step
+//                  number in its upper bits, so the counts ARE the announcement "step n
+//                  dispatched" (one NVLink round trip instead of counts, fence, flags).
+//   moe_gather     every CTA waits (bounded) until the count words of all sources carry step n,
+//                  derives the expert-major order from the counts, and the CTAs together copy the
+//                  received rows into that order (the input of grouped_matmul) with the map back.
 //   moe_combine    runs after the down projection whose epilogue stored the result rows into
 //                  the peers' return buffers: the first CTA to run announces "step n returned"
 //                  to every peer, every CTA waits (bounded) for all peers' announcements, then
@@ -594,6 +595,12 @@ namespace {
 
 constexpr int kMaxFusedBlocks = 1024;  // world * slots per rank
 constexpr uint64_t kPeerWaitNs = 2000000000ull;
+// A count word: rows in the low kCountBits bits, the step number (mod 2^12) above them.  A
+// source's word for step n replaces its word for step n - 1 and no source can be a step ahead
+// (it waits for this rank's "returned" of step n first), so equality of the tag is the test.
+constexpr int kCountBits = 20;
+constexpr uint32_t kCountMask = (1u << kCountBits) - 1u;
+__device__ __forceinline__ uint32_t step_tag(uint32_t step) { return (step & 0xfffu) << kCountBits; }
 
 struct DispatchParams {
   const __half* x;
@@ -607,7 +614,7 @@ struct DispatchParams {
   int32_t* cursor;                 // [num_slots] rows claimed so far (zero between launches)
   uint32_t* state;
   int32_t* overflow;
-  PeerTable recv, counts, flags;
+  PeerTable recv, counts;
   int hidden, num_experts, top_k, max_replicas, token_offset;
   int num_slots, spr, cap, world, my_rank;
 };
@@ -626,6 +633,27 @@ __device__ __forceinline__ bool wait_for_peer(const uint32_t* flag, uint32_t ste
     }
   }
   return true;
+}
+
+// Waits until the count word carries `tag`; `word` receives it (0 rows if the wait ran out).
+__device__ __forceinline__ bool wait_for_count(const uint32_t* p, uint32_t tag, uint32_t& word) {
+  word = ld_acquire_sys(p);
+  if ((word & ~kCountMask) == tag) return true;
+  uint64_t t0;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+  uint32_t spins = 0;
+  while (true) {
+    word = ld_acquire_sys(p);
+    if ((word & ~kCountMask) == tag) return true;
+    if ((++spins & 0xffu) == 0) {
+      uint64_t now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (now - t0 > kPeerWaitNs) {
+        word = 0;
+        return false;
+      }
+    }
+  }
 }
 
 template <int kBatch>
@@ -709,14 +737,13 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams 
     const int kept = min(claimed, p.cap);
     lost += claimed - kept;
     const int peer = slot / p.spr;
-    static_cast<int32_t*>(p.counts.base[peer])[p.my_rank * p.spr + (slot - peer * p.spr)] = kept;
+    // thread 0's fence above ordered every CTA's row stores before this point; the release makes
+    // them visible to whoever sees the word
+    st_release_sys(static_cast<uint32_t*>(p.counts.base[peer]) + p.my_rank * p.spr + (slot - peer * p.spr),
+                   step_tag(step) | static_cast<uint32_t>(kept));
   }
   if (lost) atomicAdd(&dropped, lost);
-  __syncthreads();  // the count stores of all threads precede the fences of the announcing threads
-  if (tid < p.world) {
-    __threadfence_system();
-    st_release_sys(static_cast<uint32_t*>(p.flags.base[tid]) + p.my_rank, step);
-  }
+  __syncthreads();
   if (tid == 0) {
     if (p.overflow != nullptr) p.overflow[0] = dropped;
     p.state[0] = step;
@@ -726,8 +753,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams 
 
 struct GatherParams {
   const __half* recv;        // [world][spr][cap][hidden], local
-  const int32_t* counts;     // [world][spr], local, written by the peers
-  const uint32_t* flags;     // [world] dispatch announcements, local
+  const uint32_t* counts;    // [world][spr] count words, local, written by the peers
   uint32_t* state;
   int32_t* overflow;
   __half* grouped;           // [max_rows][hidden]
@@ -781,15 +807,15 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(const GatherParams p) {
   pdl_trigger();
   pdl_wait();
   const int tid = threadIdx.x;
-  const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.state);
-  if (tid < p.world && !wait_for_peer(p.flags + tid, step))
-    atomicCAS(reinterpret_cast<unsigned int*>(p.state + 1), 0u, 100u + static_cast<unsigned>(tid));
-  __syncthreads();
+  const uint32_t tag = step_tag(*reinterpret_cast<volatile uint32_t*>(p.state));
   const int blocks = p.world * p.spr;
   for (int blk = tid; blk < blocks; blk += blockDim.x) {
     const int j = blk / p.world, r = blk - j * p.world;
-    int n = __ldcg(p.counts + r * p.spr + j);
-    dst_base[blk] = n < 0 ? 0 : (n > p.cap ? p.cap : n);
+    uint32_t word = 0;
+    if (!wait_for_count(p.counts + r * p.spr + j, tag, word))
+      atomicCAS(reinterpret_cast<unsigned int*>(p.state + 1), 0u, 100u + static_cast<unsigned>(r));
+    const int n = static_cast<int>(word & kCountMask);
+    dst_base[blk] = n > p.cap ? p.cap : n;
   }
   __syncthreads();
   const int all_rows = block_exclusive_scan(dst_base, blocks, warp_sums);
@@ -889,7 +915,7 @@ extern "C" int b200ops_moe_dispatch(const void* x, const void* router_weight, co
                                     int32_t* expert_ids_out, float* expert_weights_out,
                                     const int32_t* expert_slots, const int32_t* num_replicas,
                                     int64_t max_replicas, int64_t token_offset, int32_t* slot_to_row,
-                                    void* const* peer_recv, void* const* peer_counts, void* const* peer_flags,
+                                    void* const* peer_recv, void* const* peer_counts,
                                     int32_t* cursor, void* state, int32_t* overflow, int64_t num_tokens,
                                     int64_t hidden, int64_t num_experts, int64_t top_k, int64_t num_slots,
                                     int64_t world, int64_t cap, int64_t my_rank, void* stream) {
@@ -901,7 +927,7 @@ extern "C" int b200ops_moe_dispatch(const void* x, const void* router_weight, co
                   moe::kMaxExperts, moe::kMaxTopK, (long long)num_experts, (long long)top_k);
   B200OPS_REQUIRE(world >= 1 && world <= kMaxPeers && my_rank >= 0 && my_rank < world && num_slots >= 1 &&
                       num_slots % world == 0 && num_slots <= moe::kMaxFusedBlocks && cap > 0 &&
-                      num_slots * cap < (1LL << 31),
+                      cap <= moe::kCountMask && num_slots * cap < (1LL << 31),
                   "moe_dispatch: bad geometry world=%lld rank=%lld slots=%lld cap=%lld", (long long)world,
                   (long long)my_rank, (long long)num_slots, (long long)cap);
   B200OPS_REQUIRE(x && slot_to_row && cursor && state && aligned16(x), "moe_dispatch: null or misaligned pointer");
@@ -924,7 +950,6 @@ extern "C" int b200ops_moe_dispatch(const void* x, const void* router_weight, co
   p.overflow = overflow;
   int rc = moe::fill_peers(p.recv, peer_recv, world, "moe_dispatch(recv)");
   if (rc == B200OPS_OK) rc = moe::fill_peers(p.counts, peer_counts, world, "moe_dispatch(counts)");
-  if (rc == B200OPS_OK) rc = moe::fill_peers(p.flags, peer_flags, world, "moe_dispatch(flags)");
   if (rc != B200OPS_OK) return rc;
   p.hidden = static_cast<int>(hidden);
   p.num_experts = static_cast<int>(num_experts);
@@ -941,8 +966,7 @@ extern "C" int b200ops_moe_dispatch(const void* x, const void* router_weight, co
   return B200OPS_OK;
 }
 
-extern "C" int b200ops_moe_gather(const void* recv, const int32_t* counts, const void* flags, void* state,
-                                  int32_t* overflow, void* grouped, int32_t* grouped_to_received,
+extern "C" int b200ops_moe_gather(const void* recv, const void* counts, void* state, int32_t* overflow, void* grouped, int32_t* grouped_to_received,
                                   int64_t* group_list, int32_t* total_rows, int64_t hidden, int64_t world,
                                   int64_t slots_per_rank, int64_t cap, int64_t max_rows, void* stream) {
   B200OPS_REQUIRE(world >= 1 && world <= kMaxPeers && slots_per_rank >= 1 &&
@@ -951,13 +975,12 @@ extern "C" int b200ops_moe_gather(const void* recv, const int32_t* counts, const
                   "moe_gather: bad geometry world=%lld slots=%lld cap=%lld rows=%lld", (long long)world,
                   (long long)slots_per_rank, (long long)cap, (long long)max_rows);
   B200OPS_REQUIRE(hidden > 0 && hidden % 8 == 0, "moe_gather: bad row length %lld", (long long)hidden);
-  B200OPS_REQUIRE(recv && counts && flags && state && grouped && grouped_to_received && group_list && total_rows &&
+  B200OPS_REQUIRE(recv && counts && state && grouped && grouped_to_received && group_list && total_rows &&
                       aligned16(recv) && aligned16(grouped),
                   "moe_gather: null or misaligned pointer");
   moe::GatherParams p;
   p.recv = static_cast<const __half*>(recv);
-  p.counts = counts;
-  p.flags = static_cast<const uint32_t*>(flags);
+  p.counts = static_cast<const uint32_t*>(counts);
   p.state = static_cast<uint32_t*>(state);
   p.overflow = overflow;
   p.grouped = static_cast<__half*>(grouped);

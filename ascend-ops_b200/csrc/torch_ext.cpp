@@ -574,8 +574,7 @@ std::vector<void*> as_pointers(const std::vector<int64_t>& v) {
 std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_dispatch(
     at::Tensor x, c10::optional<at::Tensor> router_weight, c10::optional<at::Tensor> expert_ids, int64_t top_k,
     c10::optional<at::Tensor> expert_slots, c10::optional<at::Tensor> num_replicas, int64_t token_offset,
-    std::vector<int64_t> peer_recv, std::vector<int64_t> peer_counts, std::vector<int64_t> peer_flags,
-    at::Tensor cursor, at::Tensor state, c10::optional<at::Tensor> overflow, int64_t num_experts, int64_t cap,
+    std::vector<int64_t> peer_recv, std::vector<int64_t> peer_counts, at::Tensor cursor, at::Tensor state, c10::optional<at::Tensor> overflow, int64_t num_experts, int64_t cap,
     int64_t my_rank) {
   TORCH_CHECK(x.dim() == 2 && x.is_contiguous(), "moe_dispatch: x must be contiguous [T, H]");
   check_f16_cuda(x, "moe_dispatch", "x");
@@ -584,8 +583,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_dispatch(
   check_i32_cuda(cursor, "moe_dispatch", "cursor");
   TORCH_CHECK(state.is_cuda() && state.element_size() == 4 && state.numel() >= 5 && state.is_contiguous(),
               "moe_dispatch: state must be a contiguous 32-bit CUDA tensor of at least 5 elements");
-  TORCH_CHECK(peer_recv.size() == peer_counts.size() && peer_recv.size() == peer_flags.size(),
-              "moe_dispatch: one receive buffer, count table and flag array per rank");
+  TORCH_CHECK(peer_recv.size() == peer_counts.size(), "moe_dispatch: one receive buffer and count table per rank");
   const int64_t world = static_cast<int64_t>(peer_recv.size());
   const int64_t num_slots = cursor.numel();
   const int64_t tokens = x.size(0);
@@ -620,14 +618,14 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_dispatch(
     TORCH_CHECK(overflow->numel() >= 2, "moe_dispatch: overflow must hold 2 counters");
   }
   if (tokens == 0) return {pos, ids, wts};
-  auto recv = as_pointers(peer_recv), cnt = as_pointers(peer_counts), flg = as_pointers(peer_flags);
+  auto recv = as_pointers(peer_recv), cnt = as_pointers(peer_counts);
   check_status(b200ops_moe_dispatch(
                    x.data_ptr(), router_weight ? router_weight->data_ptr() : nullptr,
                    router_weight ? nullptr : ids.data_ptr<int32_t>(),
                    router_weight ? ids.data_ptr<int32_t>() : nullptr, router_weight ? wts.data_ptr<float>() : nullptr,
                    expert_slots ? expert_slots->data_ptr<int32_t>() : nullptr,
                    num_replicas ? num_replicas->data_ptr<int32_t>() : nullptr, max_rep, token_offset,
-                   pos.data_ptr<int32_t>(), recv.data(), cnt.data(), flg.data(), cursor.data_ptr<int32_t>(),
+                   pos.data_ptr<int32_t>(), recv.data(), cnt.data(), cursor.data_ptr<int32_t>(),
                    state.data_ptr(), overflow ? overflow->data_ptr<int32_t>() : nullptr, tokens, x.size(1),
                    num_experts, top_k, num_slots, world, cap, my_rank, current_stream()),
                "moe_dispatch");
@@ -637,16 +635,15 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_dispatch(
 // Receiving side of the fused step (see b200ops_moe_gather): returns (grouped rows [max_rows, H],
 // grouped_to_received [max_rows], group_list [slots_per_rank], total [1]).
 std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> moe_gather(at::Tensor recv, at::Tensor counts,
-                                                                     at::Tensor flags, at::Tensor state,
+                                                                     at::Tensor state,
                                                                      c10::optional<at::Tensor> overflow,
                                                                      int64_t cap, int64_t max_rows) {
   TORCH_CHECK(recv.dim() == 2 && recv.is_contiguous(), "moe_gather: recv must be contiguous [rows, H]");
   check_f16_cuda(recv, "moe_gather", "recv");
   check_i32_cuda(counts, "moe_gather", "counts");
   TORCH_CHECK(counts.dim() == 2, "moe_gather: counts must be [world, slots_per_rank]");
-  TORCH_CHECK(flags.is_cuda() && flags.element_size() == 4 && flags.numel() >= counts.size(0) &&
-                  state.is_cuda() && state.element_size() == 4 && state.numel() >= 5,
-              "moe_gather: flags [world] and state [5] must be 32-bit CUDA tensors");
+  TORCH_CHECK(state.is_cuda() && state.element_size() == 4 && state.numel() >= 5,
+              "moe_gather: state [5] must be a 32-bit CUDA tensor");
   const int64_t world = counts.size(0), spr = counts.size(1);
   TORCH_CHECK(recv.size(0) >= world * spr * cap, "moe_gather: recv holds fewer than world * slots * cap rows");
   const c10::cuda::CUDAGuard guard(recv.device());
@@ -654,7 +651,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor> moe_gather(at::Tensor
   at::Tensor map = at::empty({max_rows}, recv.options().dtype(at::kInt));
   at::Tensor gl = at::empty({spr}, recv.options().dtype(at::kLong));
   at::Tensor total = at::empty({1}, recv.options().dtype(at::kInt));
-  check_status(b200ops_moe_gather(recv.data_ptr(), counts.data_ptr<int32_t>(), flags.data_ptr(), state.data_ptr(),
+  check_status(b200ops_moe_gather(recv.data_ptr(), counts.data_ptr(), state.data_ptr(),
                                   overflow ? overflow->data_ptr<int32_t>() : nullptr, grouped.data_ptr(),
                                   map.data_ptr<int32_t>(), gl.data_ptr<int64_t>(), total.data_ptr<int32_t>(),
                                   recv.size(1), world, spr, cap, max_rows, current_stream()),
@@ -691,9 +688,9 @@ at::Tensor moe_combine(at::Tensor returned, at::Tensor slot_to_row, at::Tensor e
 void init_ffi_moe(py::module_&& m) {
   m.def("dispatch", &moe_dispatch, py::arg("x"), py::arg("router_weight"), py::arg("expert_ids"), py::arg("top_k"),
         py::arg("expert_slots"), py::arg("num_replicas"), py::arg("token_offset"), py::arg("peer_recv"),
-        py::arg("peer_counts"), py::arg("peer_flags"), py::arg("cursor"), py::arg("state"), py::arg("overflow"),
+        py::arg("peer_counts"), py::arg("cursor"), py::arg("state"), py::arg("overflow"),
         py::arg("num_experts"), py::arg("cap"), py::arg("my_rank"));
-  m.def("gather", &moe_gather, py::arg("recv"), py::arg("counts"), py::arg("flags"), py::arg("state"),
+  m.def("gather", &moe_gather, py::arg("recv"), py::arg("counts"), py::arg("state"),
         py::arg("overflow"), py::arg("cap"), py::arg("max_rows"));
   m.def("combine", &moe_combine);
   m.def("push_rows", &moe_push_rows, py::arg("src"), py::arg("index"), py::arg("src_div"),

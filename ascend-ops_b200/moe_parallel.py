@@ -267,13 +267,13 @@ class PeerExchange:
     """Expert-parallel dispatch/combine over NVLink peer memory instead of NCCL collectives.
 
     Each rank holds, in symmetric memory its peers have mapped, a receive buffer and a return
-    buffer, a table of row counts and two flag arrays.  A step is three launches around the two
+    buffer, a table of count words and a flag array.  A step is three launches around the two
     expert GEMMs (`moe.dispatch`, `moe.gather`, `moe.combine`):
 
     * dispatch routes every token (or takes the given expert ids), claims a row of the
       (this rank, slot) sub-segment in the slot owner's receive buffer and stores the token's row
-      there through the peer mapping; its last CTA sends the counts and announces the step;
-    * gather waits (bounded) for every peer's announcement and compacts the received rows into
+      there through the peer mapping; its last CTA sends the counts, tagged with the step number;
+    * gather waits (bounded) for every source's counts of the step and compacts the received rows into
       expert-major order for `grouped_matmul`;
     * the down projection stores its result rows straight into the owners' return buffers
       (`moe.grouped_matmul_scatter`), and combine announces "returned", waits (bounded) for the
@@ -306,8 +306,7 @@ class PeerExchange:
         o_recv = 0
         o_ret = o_recv + align(rows * hidden * 2)
         o_counts = o_ret + align(rows * hidden_out * 2)
-        o_flags_d = o_counts + align(self.world * self.spr * 4)
-        o_flags_r = o_flags_d + align(self.world * 4)
+        o_flags_r = o_counts + align(self.world * self.spr * 4)
         total = o_flags_r + align(self.world * 4)
         self.buf = symm.empty(total, dtype=torch.uint8, device=device)
         self.handle = symm.rendezvous(self.buf, group.group_name)
@@ -316,13 +315,11 @@ class PeerExchange:
         self.peer_recv = [p + o_recv for p in ptrs]
         self.peer_ret = [p + o_ret for p in ptrs]
         self.peer_counts = [p + o_counts for p in ptrs]
-        self.peer_flags_d = [p + o_flags_d for p in ptrs]
         self.peer_flags_r = [p + o_flags_r for p in ptrs]
         self.recv = self.buf[o_recv:o_recv + rows * hidden * 2].view(torch.float16).view(rows, hidden)
         self.ret = self.buf[o_ret:o_ret + rows * hidden_out * 2].view(torch.float16).view(rows, hidden_out)
         self.counts = self.buf[o_counts:o_counts + self.world * self.spr * 4].view(torch.int32).view(
             self.world, self.spr)
-        self.flags_d = self.buf[o_flags_d:o_flags_d + self.world * 4].view(torch.int32)
         self.flags_r = self.buf[o_flags_r:o_flags_r + self.world * 4].view(torch.int32)
         self.cursor = torch.zeros(self.num_slots, dtype=torch.int32, device=device)
         self.state = torch.zeros(8, dtype=torch.int32, device=device)
@@ -354,14 +351,13 @@ class PeerExchange:
         reps_tab = placement.num_replicas_i32 if placement is not None else None
         pos, ids, wts = moe.dispatch(x, router_weight, None if router_weight is not None else expert_ids, k,
                                      slots_tab, reps_tab, token_offset, self.peer_recv, self.peer_counts,
-                                     self.peer_flags_d, self.cursor, self.state, self.overflow, num_experts,
-                                     self.cap, rank)
+                                     self.cursor, self.state, self.overflow, num_experts, self.cap, rank)
         if router_weight is None:
             wts = expert_weights
         if overflow_out is not None:
             overflow_out.append(self.overflow)
-        grouped, to_received, group_list, total = moe.gather(self.recv, self.counts, self.flags_d, self.state,
-                                                             self.overflow, self.cap, self.max_rows)
+        grouped, to_received, group_list, total = moe.gather(self.recv, self.counts, self.state, self.overflow,
+                                                             self.cap, self.max_rows)
         seg = self.spr * self.cap  # rows one source owns in a receive buffer
         if local_mlp_scatter is not None:
             local_mlp_scatter(grouped, group_list, (to_received, self.peer_ret, seg, rank))

@@ -351,8 +351,10 @@ int b200ops_peer_barrier(void* const* peer_flags, void* my_flags, void* state, i
  * reference).  Slots (an expert, or one replica of a replicated expert) are placed
  * contiguously on ranks, num_slots / world per rank ("spr").  Buffers every rank provides in
  * memory its peers have mapped: a receive buffer [world][spr][cap] rows of `hidden` f16, a return
- * buffer [num_slots][cap] rows of the MLP's output width, a count table int32 [world][spr], and
- * two flag arrays uint32 [world] (dispatched, returned), all zero-initialised once.  Local only:
+ * buffer [num_slots][cap] rows of the MLP's output width, a table of count words uint32
+ * [world][spr] (rows in the low 20 bits, the step number above them: the counts double as the
+ * "dispatched" announcement) and a flag array uint32 [world] ("returned"), all zero-initialised
+ * once; cap < 2^20.  Local only:
  * cursor int32 [num_slots] and state uint32 [5], zero-initialised once; overflow int32 [2] (may
  * be NULL).  Arrays of peer addresses are HOST arrays of `world` entries (entry my_rank = the
  * local buffer).
@@ -366,9 +368,9 @@ int b200ops_peer_barrier(void* const* peer_flags, void* my_flags, void* state, i
  *   slot_to_row[t*top_k+k] = row of the LOCAL return buffer where the result will arrive
  *   (-1: invalid id, or the sub-segment was full; overflow[0] counts the latter).  Row order
  *   inside a sub-segment depends on scheduling; results do not.  The last CTA to finish
- *   sends every peer its counts and announces the step in every peer's `dispatched` flags.
- * gather: waits (at most two seconds per peer, then state[1] = 100 + peer) until every peer
- *   has announced the step, then copies the received rows into expert-major order:
+ *   sends every peer the count words of that peer's slots for this step.
+ * gather: waits (at most two seconds per source, then state[1] = 100 + source) until every
+ *   source's count words carry the step, then copies the received rows into expert-major order:
  *   grouped [max_rows, hidden], grouped_to_received[d] = receive-buffer row of grouped row d,
  *   group_list int64 [spr], total_rows int32 [1].  Rows beyond max_rows are left out and
  *   counted in overflow[1].
@@ -382,11 +384,10 @@ int b200ops_moe_dispatch(const void* x, const void* router_weight, const int32_t
                          int32_t* expert_ids_out, float* expert_weights_out, const int32_t* expert_slots,
                          const int32_t* num_replicas, int64_t max_replicas, int64_t token_offset,
                          int32_t* slot_to_row, void* const* peer_recv, void* const* peer_counts,
-                         void* const* peer_flags, int32_t* cursor, void* state, int32_t* overflow,
+                         int32_t* cursor, void* state, int32_t* overflow,
                          int64_t num_tokens, int64_t hidden, int64_t num_experts, int64_t top_k,
                          int64_t num_slots, int64_t world, int64_t cap, int64_t my_rank, void* stream);
-int b200ops_moe_gather(const void* recv, const int32_t* counts, const void* flags, void* state,
-                       int32_t* overflow, void* grouped, int32_t* grouped_to_received, int64_t* group_list,
+int b200ops_moe_gather(const void* recv, const void* counts, void* state, int32_t* overflow, void* grouped, int32_t* grouped_to_received, int64_t* group_list,
                        int32_t* total_rows, int64_t hidden, int64_t world, int64_t slots_per_rank, int64_t cap,
                        int64_t max_rows, void* stream);
 int b200ops_moe_combine(const void* returned, const int32_t* slot_to_row, const float* expert_weights, void* y,

@@ -60,12 +60,12 @@ def test_argument_checks_run_before_any_cuda_call(cabi):
     assert lib.b200ops_matmul(null, null, null, 0, 64, 64, null) == cabi.OK
     # the fused expert-parallel launches: geometry is checked before anything is dereferenced
     peers = (ctypes.c_void_p * 2)(256, 512)
-    assert lib.b200ops_moe_dispatch(one, None, one, None, None, None, None, 0, 0, one, peers, peers, peers, one, one,
+    assert lib.b200ops_moe_dispatch(one, None, one, None, None, None, None, 0, 0, one, peers, peers, one, one,
                                     None, 4, 64, 8, 2, 7, 2, 16, 0, null) == cabi.EINVAL  # 7 slots over 2 ranks
     assert "geometry" in cabi.last_error()
-    assert lib.b200ops_moe_dispatch(one, None, None, None, None, None, None, 0, 0, one, peers, peers, peers, one, one,
+    assert lib.b200ops_moe_dispatch(one, None, None, None, None, None, None, 0, 0, one, peers, peers, one, one,
                                     None, 4, 64, 8, 2, 8, 2, 16, 0, null) == cabi.EINVAL  # neither router nor ids
-    assert lib.b200ops_moe_gather(one, one, one, one, None, one, one, one, one, 60, 2, 4, 16, 128, null) == cabi.EINVAL
+    assert lib.b200ops_moe_gather(one, one, one, None, one, one, one, one, 60, 2, 4, 16, 128, null) == cabi.EINVAL
     assert lib.b200ops_moe_combine(one, one, one, one, peers, one, one, 4, 2, 64, 2, 2, null) == cabi.EINVAL
     # zero-size problems succeed without a device
     assert lib.b200ops_swiglu(null, null, 0, 64, null) == cabi.OK

@@ -272,14 +272,13 @@ class EmulatedRanks:
         self.recv = [z(rows, hidden, dt=torch.float16) for _ in range(world)]
         self.ret = [z(rows, hidden_out, dt=torch.float16) for _ in range(world)]
         self.counts = [z(world, spr) for _ in range(world)]
-        self.flags_d = [z(world) for _ in range(world)]
         self.flags_r = [z(world) for _ in range(world)]
         self.cursor = [z(self.slots) for _ in range(world)]
         self.state = [z(8) for _ in range(world)]
         self.overflow = [z(2) for _ in range(world)]
         arr = lambda bufs: _ptr_array([b.data_ptr() for b in bufs])
         self.p_recv, self.p_ret, self.p_counts = arr(self.recv), arr(self.ret), arr(self.counts)
-        self.p_flags_d, self.p_flags_r = arr(self.flags_d), arr(self.flags_r)
+        self.p_flags_r = arr(self.flags_r)
 
     def step(self, cabi, xs, ids, wts, weights, router=None, top_k=None, tables=None, offsets=None):
         """One exchange step of all ranks.  weights[r] = [spr, n, k] f16 of rank r's slots (a plain
@@ -299,7 +298,7 @@ class EmulatedRanks:
                 p(oi) if router is not None else None, p(ow) if router is not None else None,
                 p(tables[0]) if tables else None, p(tables[1]) if tables else None,
                 tables[0].shape[1] if tables else 0, offsets[r] if offsets else 0, p(pr), self.p_recv,
-                self.p_counts, self.p_flags_d, p(self.cursor[r]), p(self.state[r]), p(self.overflow[r]), t,
+                self.p_counts, p(self.cursor[r]), p(self.state[r]), p(self.overflow[r]), t,
                 self.h, router.shape[0] if router is not None else (tables[1].numel() if tables else self.slots),
                 k, self.slots, w_, cap, r, stream()))
             pos.append(pr)
@@ -311,7 +310,7 @@ class EmulatedRanks:
             back = torch.full((self.max_rows,), -9, dtype=torch.int32, device=DEV)
             gl = torch.zeros(spr, dtype=torch.int64, device=DEV)
             total = torch.zeros(1, dtype=torch.int32, device=DEV)
-            cabi.check(lib.b200ops_moe_gather(p(self.recv[r]), p(self.counts[r]), p(self.flags_d[r]),
+            cabi.check(lib.b200ops_moe_gather(p(self.recv[r]), p(self.counts[r]),
                                               p(self.state[r]), p(self.overflow[r]), p(grouped), p(back), p(gl),
                                               p(total), self.h, w_, spr, cap, self.max_rows, stream()))
             n = weights[r].shape[1]
@@ -441,8 +440,8 @@ def test_fused_step_counts_rows_that_do_not_fit(cabi):
 
 
 def test_fused_gather_gives_up_when_a_peer_never_announces(cabi):
-    """The wait inside the gather launch is bounded like the barrier's: with one peer's
-    announcement missing it records 100 + peer, carries on, and the context stays usable."""
+    """The wait inside the gather launch is bounded like the barrier's: with one source's count
+    words missing it records 100 + source, carries on, and the context stays usable."""
     import time
 
     lib = cabi.load()
@@ -451,14 +450,14 @@ def test_fused_gather_gives_up_when_a_peer_never_announces(cabi):
     ids = torch.zeros(3, 1, dtype=torch.int32, device=DEV)
     pos = torch.empty(3, dtype=torch.int32, device=DEV)
     cabi.check(lib.b200ops_moe_dispatch(p(x), None, p(ids), None, None, None, None, 0, 0, p(pos), em.p_recv,
-                                        em.p_counts, em.p_flags_d, p(em.cursor[0]), p(em.state[0]), None, 3, 64, 2,
+                                        em.p_counts, p(em.cursor[0]), p(em.state[0]), None, 3, 64, 2,
                                         1, 2, 2, 4, 0, stream()))  # rank 0 only: rank 1 never dispatches
     grouped = torch.zeros(8, 64, dtype=torch.float16, device=DEV)
     back = torch.zeros(8, dtype=torch.int32, device=DEV)
     gl = torch.zeros(1, dtype=torch.int64, device=DEV)
     total = torch.zeros(1, dtype=torch.int32, device=DEV)
     t0 = time.perf_counter()
-    cabi.check(lib.b200ops_moe_gather(p(em.recv[0]), p(em.counts[0]), p(em.flags_d[0]), p(em.state[0]), None,
+    cabi.check(lib.b200ops_moe_gather(p(em.recv[0]), p(em.counts[0]), p(em.state[0]), None,
                                       p(grouped), p(back), p(gl), p(total), 64, 2, 1, 4, 8, stream()))
     torch.cuda.synchronize()
     waited = time.perf_counter() - t0

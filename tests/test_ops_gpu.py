@@ -753,7 +753,8 @@ def test_matmul_c_abi_any_shape(cabi, m, k, n):
 @pytest.mark.parametrize("counts,k,n", [
     ([350, 340, 410], 2048, 4096),       # 160 tiles on 148 SMs: the ragged second wave is spread out
     ([1024], 1024, 256 * 146),           # 7.9 waves: ranges of several whole tiles with cut ends
-    ([64] * 8, 14336, 4096),             # decode down projection: 128 tiles, under one wave
+    ([64] * 8, 14336, 4096),             # decode down projection: one m-tile per expert, stays tile by tile
+    ([200] * 4, 14336, 4096),            # 128 tiles of two m-tiles per expert: under one wave, evened out
     ([40, 0, 3, 90, 7, 64, 1, 128], 8192, 1024),  # fewer tiles than half the SMs, long k: split-K proper
     ([200, 100], 1024, 320),             # N tail (320 = 256 + 64) in cut tiles
 ])

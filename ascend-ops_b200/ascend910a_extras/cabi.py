@@ -61,7 +61,6 @@ SIGNATURES = {
     "b200ops_peer_barrier": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
     "b200ops_pipeline_status": (c_int, [ctypes.POINTER(c_int)]),
     "b200ops_reload_options": (None, []),
-    "b200ops_prefetch_l2": (c_int, [c_void_p, c_size_t, c_void_p]),
     "b200ops_matmul": (c_int, [c_void_p] * 3 + [c_int64] * 3 + [c_void_p]),
     "b200ops_moe_dispatch": (c_int, [c_void_p] * 7 + [c_int64] * 2 + [c_void_p] * 6 + [c_int64] * 8 + [c_void_p]),
     "b200ops_moe_gather": (c_int, [c_void_p] * 8 + [c_int64] * 5 + [c_void_p]),

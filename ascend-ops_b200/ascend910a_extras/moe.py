@@ -21,4 +21,3 @@ grouped_matmul_swiglu = _C.moe.grouped_matmul_swiglu
 dispatch = _C.moe.dispatch
 gather = _C.moe.gather
 combine = _C.moe.combine
-prefetch_l2 = _C.moe.prefetch_l2

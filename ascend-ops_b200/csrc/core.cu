@@ -86,36 +86,6 @@ extern "C" int b200ops_print_info(int device_id, char* buf, size_t buf_len) {
 }
 
 namespace b200ops {
-namespace {
-// One bulk prefetch instruction per thread and chunk: the copy engine brings the lines into L2,
-// no SM waits for them.
-constexpr size_t kPrefetchChunk = 32768;
-__global__ void __launch_bounds__(128) prefetch_l2_kernel(const char* base, size_t bytes) {
-  pdl_trigger();
-  pdl_wait();
-  const size_t chunk = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const size_t off = chunk * kPrefetchChunk;
-  if (off >= bytes) return;
-  const size_t n = bytes - off < kPrefetchChunk ? bytes - off : kPrefetchChunk;
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(base + off), "r"(static_cast<uint32_t>(n)) : "memory");
-}
-}  // namespace
-}  // namespace b200ops
-
-extern "C" int b200ops_prefetch_l2(const void* ptr, size_t bytes, void* stream) {
-  using namespace b200ops;
-  if (bytes == 0) return B200OPS_OK;
-  B200OPS_REQUIRE(ptr != nullptr && aligned16(ptr), "prefetch_l2: null or misaligned pointer");
-  bytes &= ~static_cast<size_t>(15);
-  if (bytes == 0) return B200OPS_OK;
-  const size_t chunks = (bytes + kPrefetchChunk - 1) / kPrefetchChunk;
-  B200OPS_REQUIRE(chunks < (1ull << 31), "prefetch_l2: range too large");
-  B200OPS_CUDA(launch_kernel(prefetch_l2_kernel, dim3(static_cast<unsigned>((chunks + 127) / 128)), dim3(128), 0,
-                             static_cast<cudaStream_t>(stream), static_cast<const char*>(ptr), bytes));
-  return B200OPS_OK;
-}
-
-namespace b200ops {
 namespace gmm { int status_take(); }
 namespace pa { int fast_path_status_take(); }
 }  // namespace b200ops

@@ -685,18 +685,7 @@ at::Tensor moe_combine(at::Tensor returned, at::Tensor slot_to_row, at::Tensor e
   return y;
 }
 
-// L2 prefetch hint over the first `bytes` bytes of a tensor's storage (see b200ops_prefetch_l2).
-void prefetch_l2(at::Tensor t, int64_t bytes) {
-  TORCH_CHECK(t.is_cuda(), "prefetch_l2: CUDA tensor expected");
-  const int64_t have = static_cast<int64_t>(t.numel()) * t.element_size();
-  const c10::cuda::CUDAGuard guard(t.device());
-  check_status(b200ops_prefetch_l2(t.data_ptr(), static_cast<size_t>(std::max<int64_t>(0, std::min(bytes, have))),
-                                   current_stream()),
-               "prefetch_l2");
-}
-
 void init_ffi_moe(py::module_&& m) {
-  m.def("prefetch_l2", &prefetch_l2);
   m.def("dispatch", &moe_dispatch, py::arg("x"), py::arg("router_weight"), py::arg("expert_ids"), py::arg("top_k"),
         py::arg("expert_slots"), py::arg("num_replicas"), py::arg("token_offset"), py::arg("peer_recv"),
         py::arg("peer_counts"), py::arg("cursor"), py::arg("state"), py::arg("overflow"),

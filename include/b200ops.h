@@ -395,14 +395,6 @@ int b200ops_moe_combine(const void* returned, const int32_t* slot_to_row, const 
                         int64_t row_elems, int64_t world, int64_t my_rank, void* stream);
 
 /*
- * Hint: bring `bytes` bytes starting at `ptr` (device memory, 16-byte aligned) into L2.  For
- * a decode step whose exchange phases leave HBM idle: launched on a side stream, it fetches the
- * head of the weights the next GEMM will stream (L2 holds about 100 MB).  Changes no result.
- * No counterpart in the reference.
- */
-int b200ops_prefetch_l2(const void* ptr, size_t bytes, void* stream);
-
-/*
  * Health word of the pipelined kernels (grouped_matmul, paged_attention's TMA path).  Their
  * producer/consumer waits are bounded; a wait that runs out ends the kernel and leaves a
  * non-zero code here.  This call synchronises the device, returns the code in *status

@@ -123,20 +123,15 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   const int m_tiles = (M + BM - 1) / BM;
   const int m_tile = tile / n_tiles;
   pdl_trigger();
-  pdl_wait();  // the row count and the first loads below are inputs
   TileCoord tc;
   tc.group = 0;
   tc.n0 = (tile - m_tile * n_tiles) * kSplitBN;
   tc.row0 = m_tile * BM;
   tc.row_end = 0;  // first m-tile: read after the first loads are on their way
   // splits <= k_blocks gives every rank at least one k-block; the host never asks otherwise.
-  bool active = splits <= k_blocks && tile < m_tiles * n_tiles;
-  if (m_tile > 0) {
-    long long rows = group_list ? group_list[0] : M;
-    active = active && tc.row0 < (rows > M ? M : rows);
-  }
-  const int prefill = active ? min(kSplitStages, kb1 - kb0) : 0;
-
+  const bool may_run = splits <= k_blocks && tile < m_tiles * n_tiles;
+  // Set-up that needs no input runs before the wait for the previous kernel, so that it overlaps
+  // that kernel's tail: the barriers, and the TMEM allocation (warp 1, in parallel).
   if (threadIdx.x == 0) {
     for (int s = 0; s < kSplitStages; ++s) {
       ptx::mbar_init(&ctl->full[s], 1);
@@ -145,23 +140,32 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
     ptx::mbar_init(&ctl->tmem_full[0], 1);
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
-    // The first ring-full of loads needs nobody else: issue it before the CTA-wide set-up so
-    // that its latency (about 2 us from HBM) overlaps the TMEM allocation and the barrier.
+  }
+  if (may_run && warp == 1) {
+    ptx::tmem_alloc(&ctl->tmem_base, kSplitTmemCols);
+    ptx::tmem_relinquish_alloc_permit();
+  }
+  pdl_wait();  // the row count and the loads below are inputs
+  bool active = may_run;
+  if (m_tile > 0) {
+    long long rows = group_list ? group_list[0] : M;
+    active = active && tc.row0 < (rows > M ? M : rows);
+  }
+  const int prefill = active ? min(kSplitStages, kb1 - kb0) : 0;
+  if (threadIdx.x == 0) {
+    // The first ring-full of loads needs nobody else: issue it before the CTA-wide barrier so
+    // that its latency (about 2 us from HBM) overlaps it.
     for (int i = 0; i < prefill; ++i) {
       ptx::mbar_arrive_expect_tx(&ctl->full[i], kSplitStageBytes);
       ptx::tma_load_2d(a_tiles + i * kABytes, &map_x, &ctl->full[i], (kb0 + i) * BK, tc.row0);
       ptx::tma_load_3d(b_tiles + i * kSplitBBytes, &map_w, &ctl->full[i], (kb0 + i) * BK, tc.n0, 0);
     }
   }
-  if (active && warp == 1) {
-    ptx::tmem_alloc(&ctl->tmem_base, kSplitTmemCols);
-    ptx::tmem_relinquish_alloc_permit();
-  }
   ptx::tcgen05_fence_before();
   __syncthreads();
   ptx::tcgen05_fence_after();
 
-  const uint32_t tmem_base = active ? ctl->tmem_base : 0u;
+  const uint32_t tmem_base = may_run ? ctl->tmem_base : 0u;
   volatile int* abort_flag = &ctl->abort_flag;
   {
     long long rows = group_list ? group_list[0] : M;
@@ -261,7 +265,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   // Nobody leaves (and frees its shared memory) while a peer may still be reading it.
   __syncthreads();
   ptx::cluster_sync();
-  if (active && warp == 1) {
+  if (may_run && warp == 1) {
     ptx::tcgen05_fence_after();
     ptx::tmem_dealloc(tmem_base, kSplitTmemCols);
   }

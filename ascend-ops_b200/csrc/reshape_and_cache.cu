@@ -275,7 +275,7 @@ extern "C" int b200ops_reshape_and_cache(const void* key, const void* value, voi
                            (with_value ? reinterpret_cast<uintptr_t>(value) |
                                              reinterpret_cast<uintptr_t>(value_cache)
                                        : 0)) & 31u) == 0;
-  p.dedup = num_tokens <= kDedupMaxTokens;
+  p.dedup = num_tokens <= kDedupMaxTokens && knob(kKnobRacDedup, 1) != 0;
   p.slots_vec = aligned16(slot_indices);
   if (row_elems % 16 == 0 && row_elems <= 16 * 32 * kMaxPieces && aligned32) {
     int warps = knob(kKnobRacWarps, 4);  // warps (= tokens) per CTA

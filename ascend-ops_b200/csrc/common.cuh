@@ -73,7 +73,6 @@ enum Knob {
   kKnobPaChunkTokens,   // B200OPS_PA_CHUNK_TOKENS: base chunk length of the split context
   kKnobRmsnormVpt,      // B200OPS_RMSNORM_VPT: 16-byte vectors per thread
   kKnobRmsnormCtaWarps, // B200OPS_RMSNORM_CTA_WARPS: warps per CTA
-  kKnobRacWarps,        // B200OPS_RAC_WARPS: warps per CTA of the reshape_and_cache row kernel
   kKnobRacDedup,        // B200OPS_RAC_DEDUP: 0 = skip the repeated-slot check (measurement only)
   kKnobPdl,             // B200OPS_PDL: 0 = plain stream-ordered launches (no programmatic dependent launch)
   kKnobCount

@@ -94,66 +94,50 @@ __global__ void __launch_bounds__(kThreads) scatter_nz_vec_kernel(ScatterParams 
 }
 
 // The repeated-slot check of one warp: is the token's slot named again by a later token?  The
-// warp scans the rest of the batch's slots four per load.  The loads of the first kScanBatch
-// groups per lane (the next 1024 tokens) are issued together with the token's row loads, before
-// anything depends on them, so for most tokens the check costs no extra round trip; what lies
-// further on is read in a loop.  (Sixteen groups per lane cost 143 registers and a CTA per SM.)
-// Needs a 16-byte aligned slot array (`vec_ok`); otherwise single loads after the fact.
+// warp scans the rest of the batch's slots, four per load and kScanBatch loads per lane in
+// flight, while the token's own rows are still on their way from DRAM.  The price is the extra
+// load traffic (every warp reads up to the whole slot array through L1): about 1 us on a decode
+// batch of 2048 tokens, 0.4 us on the NZ layout.  Issuing the scan loads before the slot is known
+// does not help (measured), the volume is what costs.  `vec_ok`: the slot array is 16-byte
+// aligned (otherwise single loads).
 constexpr int kScanBatch = 8;
 
-struct SlotScan {
-  int4 v[kScanBatch];
-  uint32_t base;  // first group of four slots this warp looks at
-};
-
-__device__ __forceinline__ void scan_issue(SlotScan& sc, const int32_t* __restrict__ slots, uint32_t token,
-                                           uint32_t num_tokens, uint32_t lane) {
+__device__ __forceinline__ bool named_again(const int32_t* __restrict__ slots, uint32_t token,
+                                            uint32_t num_tokens, int32_t slot, uint32_t lane, bool vec_ok) {
+  bool later = false;
+  if (!vec_ok) {
+#pragma unroll 4
+    for (uint32_t t = token + 1 + lane; t < num_tokens; t += 32) later |= (__ldg(slots + t) == slot);
+    return __any_sync(0xffffffffu, later);
+  }
   const uint32_t full = num_tokens >> 2;  // complete groups of four slots
   const int4* s4 = reinterpret_cast<const int4*>(slots);
-  sc.base = (token + 1) >> 2;
-#pragma unroll
-  for (int i = 0; i < kScanBatch; ++i) {
-    const uint32_t g = sc.base + lane + 32 * i;
-    sc.v[i] = g < full ? __ldg(s4 + g) : make_int4(-1, -1, -1, -1);  // -1 equals no valid slot
-  }
-}
-
-__device__ __forceinline__ bool group_hit(const int4& v, uint32_t idx, uint32_t token, int32_t slot) {
-  // only the first group can hold tokens that are not later than `token`
-  return (v.x == slot && idx > token) | (v.y == slot && idx + 1 > token) | (v.z == slot && idx + 2 > token) |
-         (v.w == slot && idx + 3 > token);
-}
-
-__device__ __forceinline__ bool scan_named_again(const SlotScan& sc, const int32_t* __restrict__ slots,
-                                                 uint32_t token, uint32_t num_tokens, int32_t slot,
-                                                 uint32_t lane) {
-  const uint32_t full = num_tokens >> 2;
-  const int4* s4 = reinterpret_cast<const int4*>(slots);
-  bool later = false;
-#pragma unroll
-  for (int i = 0; i < kScanBatch; ++i) later |= group_hit(sc.v[i], (sc.base + lane + 32 * i) << 2, token, slot);
 #pragma unroll 1
-  for (uint32_t g = sc.base + 32 * kScanBatch + lane; g < full; g += 32)
-    later |= group_hit(__ldg(s4 + g), g << 2, token, slot);
+  for (uint32_t base = (token + 1) >> 2; base < full; base += 32 * kScanBatch) {
+    int4 v[kScanBatch];
+#pragma unroll
+    for (int i = 0; i < kScanBatch; ++i) {
+      const uint32_t g = base + lane + 32 * i;
+      v[i] = g < full ? __ldg(s4 + g) : make_int4(-1, -1, -1, -1);  // -1 equals no valid slot
+    }
+#pragma unroll
+    for (int i = 0; i < kScanBatch; ++i) {
+      const uint32_t idx = (base + lane + 32 * i) << 2;  // only the first group can hold earlier tokens
+      later |= (v[i].x == slot && idx > token) | (v[i].y == slot && idx + 1 > token) |
+               (v[i].z == slot && idx + 2 > token) | (v[i].w == slot && idx + 3 > token);
+    }
+  }
   const uint32_t tail = (full << 2) + lane;  // the last one to three slots
   if (lane < (num_tokens & 3u) && tail > token) later |= (__ldg(slots + tail) == slot);
-  return __any_sync(0xffffffffu, later);
-}
-
-__device__ __forceinline__ bool named_again_scalar(const int32_t* __restrict__ slots, uint32_t token,
-                                                   uint32_t num_tokens, int32_t slot, uint32_t lane) {
-  bool later = false;
-#pragma unroll 4
-  for (uint32_t t = token + 1 + lane; t < num_tokens; t += 32) later |= (__ldg(slots + t) == slot);
   return __any_sync(0xffffffffu, later);
 }
 
 constexpr int kDedupMaxTokens = 4096;
 
 // Row-per-warp kernel for rows that are whole 32-byte sectors (row_elems % 16 == 0): a warp
-// owns one token, every lane moves 32-byte pieces of the K row and of the V row.  All loads (the
-// slot, the rows, the slots of the later tokens) are issued before anything depends on them, so
-// one memory round trip covers them; stores are one full sector each.  kMaxPieces bounds the
+// owns one token, every lane moves 32-byte pieces of the K row and of the V row.  All loads
+// (including the slot) are issued before anything depends on them, so one DRAM round trip
+// covers them; stores are one full sector each.  kMaxPieces bounds the
 // pieces a lane holds.  (Giving a token's K row and V row to separate warps, and CTAs of 2, 8 or
 // 16 warps, were measured: slower or equal at a decode batch of 2048 tokens.)
 constexpr int kRowWarps = 4;
@@ -170,8 +154,6 @@ __global__ void __launch_bounds__(kRowWarps * 32) scatter_rows_kernel(ScatterPar
   const char* ks = reinterpret_cast<const char*>(p.key) + static_cast<size_t>(token) * p.row_elems * 2;
   const char* vs = reinterpret_cast<const char*>(p.value) + static_cast<size_t>(token) * p.row_elems * 2;
   const int32_t slot32 = p.slots[token];
-  SlotScan scan;
-  if (kDedup && p.slots_vec) scan_issue(scan, p.slots, token, p.num_tokens, lane);
   Vec256 kb[kMaxPieces], vb[kMaxPieces];
 #pragma unroll
   for (int i = 0; i < kMaxPieces; ++i) {
@@ -183,11 +165,7 @@ __global__ void __launch_bounds__(kRowWarps * 32) scatter_rows_kernel(ScatterPar
   }
   const int64_t slot = slot32;
   if (slot < 0 || slot >= p.num_slots) return;
-  if (kDedup) {
-    const bool again = p.slots_vec ? scan_named_again(scan, p.slots, token, p.num_tokens, slot32, lane)
-                                   : named_again_scalar(p.slots, token, p.num_tokens, slot32, lane);
-    if (again) return;
-  }
+  if (kDedup && named_again(p.slots, token, p.num_tokens, slot32, lane, p.slots_vec)) return;
   size_t base, stride;  // byte offset of piece 0 and distance between pieces in the cache
   uint32_t limit = pieces;
   if (kNz) {

@@ -21,11 +21,11 @@
 // 148 SMs take two waves), and a problem with fewer tiles than SMs leaves SMs idle while each
 // busy CTA streams its operands at the rate one SM can ingest.  If the caller passes a
 // workspace, every CTA derives the same decision from the tile count it computed on the device:
-// the (tile, k-block) units are cut into one contiguous range per CTA; whole tiles inside a range
-// are stored directly, the incomplete tiles at its ends go to the workspace as fp32 partial
-// tiles.  A counter per tile identifies the last CTA to publish a part; it alone sums the parts
-// in CTA order and writes the fp16 rows (with SwiGLU applied for the fused gate/up form).
-// Nobody waits on another CTA.
+// the full waves are handed out tile by tile as before, and the (tile, k-block) units of the
+// ragged last wave are cut into one contiguous range per CTA.  The parts of a cut tile go to the
+// workspace as fp32 partial tiles; a counter per tile identifies the last CTA to publish a part,
+// and it alone sums the parts in CTA order and writes the fp16 rows (with SwiGLU applied for the
+// fused gate/up form).  Nobody waits on another CTA.
 //
 // CTA pairs.  Problems of a wave of tiles or more run grouped_matmul_pair_kernel instead
 // (grouped_matmul_pair.cuh): clusters of two CTAs issue one 256 x 256 x 16 MMA (cta_group::2), each
@@ -221,29 +221,35 @@ __device__ __forceinline__ __half* output_row(const RowScatter& sc, __half* y, i
   return static_cast<__half*>(sc.peers.base[peer]) + (static_cast<size_t>(sc.my_rank) * sc.cap + off) * N;
 }
 
-// Work decomposition.  A unit is one k-block of one tile; tiles are numbered as locate_tile
-// numbers them.  Two schedules:
-//   by tiles    CTA c takes tiles c, c + G, ... whole (no workspace needed);
-//   balanced    the units are cut into G equal contiguous ranges, CTA c takes range c.  A range
-//               covers the end of one tile, whole tiles, and the start of another: whole tiles are
-//               stored directly, parts go through the workspace (see the epilogue).  Chosen when
-//               a workspace is given and the tile count leaves a ragged last wave that matters
-//               (see make_schedule): 160 tiles of a long k on 148 SMs are two waves by tiles, 1.08
-//               waves balanced.  With fewer tiles than CTAs this is split-K; ranges are kept at
-//               least kMinKBlocksPerSplit k-blocks long.
+// Work decomposition.  Tiles are numbered as locate_tile numbers them; a unit is one k-block
+// of one tile.  Two schedules:
+//   by tiles    CTA c takes tiles c, c + G, ... whole (no workspace needed).  CTAs that run at the
+//               same time work on neighbouring tiles, which share weight tiles through L2.
+//   balanced    the full waves of G tiles are handed out as above; the tiles of the ragged last
+//               wave are cut, as (tile, k-block) units, into equal contiguous ranges, one per CTA.
+//               A range covers the end of one tile and/or the start of the next: both are parts
+//               that go through the workspace (see the epilogue).  160 tiles of a long k on 148
+//               SMs are two waves by tiles, 1.08 balanced.  With fewer tiles than CTAs this is
+//               split-K.  Ranges are kept at least kMinKBlocksPerSplit k-blocks long.
+//               (Cutting ALL units into one range per CTA balances as well but lets every CTA walk
+//               its own stretch of the tile sequence: 148 weight tiles are then live at once,
+//               more than L2 holds, and the re-reads by a weight tile's other m-tiles go to HBM --
+//               measured 1.7 times slower on three experts of 350 rows.)
 struct Segment {
   int tile, kb0, kb1;
 };
 
 struct Schedule {
-  long long units;   // total_tiles * k_blocks
-  int k_blocks, total_tiles;
-  int ctas;          // CTAs that take part (balanced: ranges; by tiles: the grid)
+  int k_blocks, total_tiles, grid;
+  int whole_tiles;       // tiles [0, whole_tiles) are handed out whole, round-robin
+  long long tail_units;  // balanced: units of the tiles [whole_tiles, total_tiles)
+  int tail_ctas;         // balanced: CTAs that take a range of them
   bool balanced;
-  __device__ __forceinline__ long long first_unit(int c) const { return units * c / ctas; }
+  // Ranges of the tail, in units counted from the first tail tile.
+  __device__ __forceinline__ long long first_unit(int c) const { return tail_units * c / tail_ctas; }
   // The CTA whose range holds unit u: the largest c with first_unit(c) <= u.
   __device__ __forceinline__ int cta_of(long long u) const {
-    return static_cast<int>(((u + 1) * ctas + units - 1) / units) - 1;
+    return static_cast<int>(((u + 1) * tail_ctas + tail_units - 1) / tail_units) - 1;
   }
 };
 
@@ -252,8 +258,11 @@ __device__ __forceinline__ Schedule make_schedule(int total_tiles, int k_blocks,
   Schedule s;
   s.k_blocks = k_blocks;
   s.total_tiles = total_tiles;
-  s.units = static_cast<long long>(total_tiles) * k_blocks;
-  s.ctas = grid;
+  s.grid = grid;
+  s.whole_tiles = total_tiles;
+  s.tail_units = 0;
+  s.tail_ctas = 0;
+  const int tail = total_tiles % grid;
   // Fewer tiles than half the CTAs is split-K proper, whose publish-and-sum tail only pays for a
   // long k (kMinSplitK).  With more tiles the balanced schedule pays when CTAs run at their own
   // pace, i.e. when the tensor pipe is the limit: every weight tile (`weight_tiles` of them: one per
@@ -262,45 +271,43 @@ __device__ __forceinline__ Schedule make_schedule(int total_tiles, int k_blocks,
   // ragged last wave simply run faster, and cutting tiles only adds traffic.
   const bool split_k = 2 * total_tiles <= grid && k_blocks * BK >= kMinSplitK;
   const bool even_out = 2 * total_tiles > grid && total_tiles < 8 * grid && total_tiles >= 2 * weight_tiles;
-  s.balanced = have_workspace && total_tiles > 0 && total_tiles % grid != 0 && (split_k || even_out);
+  s.balanced = have_workspace && tail != 0 && (split_k || even_out);
   if (s.balanced) {
-    const long long most = s.units / kMinKBlocksPerSplit;
-    if (most < grid) s.ctas = most < 1 ? 1 : static_cast<int>(most);
+    s.whole_tiles = total_tiles - tail;
+    s.tail_units = static_cast<long long>(tail) * k_blocks;
+    const long long most = s.tail_units / kMinKBlocksPerSplit;
+    s.tail_ctas = most < grid ? (most < 1 ? 1 : static_cast<int>(most)) : grid;
   }
   return s;
 }
 
-// Workspace slot of a part: a CTA has at most one part that starts inside a tile (the first
-// segment of its range) and at most one that starts a tile without finishing it (the last).
+// Workspace slot of a part: a CTA's range has at most one part that starts inside a tile (its
+// first segment) and at most one that starts a tile without finishing it (its last).
 __device__ __forceinline__ int partial_slot(int cta, int kb0) { return 2 * cta + (kb0 == 0 ? 1 : 0); }
 
 struct Walk {
   const Schedule& s;
-  long long lo, hi;  // balanced: remaining units; by tiles: next tile, tile count
-  int stride;
-  __device__ __forceinline__ Walk(const Schedule& sched, int cta) : s(sched) {
-    if (s.balanced) {
-      lo = cta < s.ctas ? s.first_unit(cta) : 0;
-      hi = cta < s.ctas ? s.first_unit(cta + 1) : 0;
-      stride = 0;
-    } else {
-      lo = cta;
-      hi = s.total_tiles;
-      stride = s.ctas;
+  int tile;          // next whole tile of this CTA
+  long long lo, hi;  // remaining units of its tail range
+  __device__ __forceinline__ Walk(const Schedule& sched, int cta) : s(sched), tile(cta), lo(0), hi(0) {
+    if (s.balanced && cta < s.tail_ctas) {
+      lo = s.first_unit(cta);
+      hi = s.first_unit(cta + 1);
     }
   }
   __device__ __forceinline__ bool next(Segment& g) {
-    if (lo >= hi) return false;
-    if (!s.balanced) {
-      g.tile = static_cast<int>(lo);
+    if (tile < s.whole_tiles) {
+      g.tile = tile;
       g.kb0 = 0;
       g.kb1 = s.k_blocks;
-      lo += stride;
+      tile += s.grid;
       return true;
     }
-    g.tile = static_cast<int>(lo / s.k_blocks);
-    const long long t0 = static_cast<long long>(g.tile) * s.k_blocks;
+    if (lo >= hi) return false;
+    const int t = static_cast<int>(lo / s.k_blocks);
+    const long long t0 = static_cast<long long>(t) * s.k_blocks;
     const long long end = hi < t0 + s.k_blocks ? hi : t0 + s.k_blocks;
+    g.tile = s.whole_tiles + t;
     g.kb0 = static_cast<int>(lo - t0);
     g.kb1 = static_cast<int>(end - t0);
     lo = end;
@@ -666,14 +673,15 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
         // Publish this part; the CTA that finds all other parts of the tile already published
         // sums them (in CTA order, so the result does not depend on timing) and writes the rows.
         // Counters were zeroed by the host before the launch.  Nobody waits.
-        const int c_first = sched.cta_of(static_cast<long long>(sg.tile) * k_blocks);
-        const int c_last = sched.cta_of(static_cast<long long>(sg.tile + 1) * k_blocks - 1);
+        const long long tile_unit0 = static_cast<long long>(sg.tile - sched.whole_tiles) * k_blocks;
+        const int c_first = sched.cta_of(tile_unit0);
+        const int c_last = sched.cta_of(tile_unit0 + k_blocks - 1);
         const int parts = c_last - c_first + 1;
         __threadfence();
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (threadIdx.x == 64) ctl->split_rank = atomicAdd(&tile_counters[sg.tile], 1);
         for (int i = threadIdx.x - 64; i < parts; i += 128) {
-          const long long begin = sched.first_unit(c_first + i) - static_cast<long long>(sg.tile) * k_blocks;
+          const long long begin = sched.first_unit(c_first + i) - tile_unit0;
           ctl->part_slot[i] = partial_slot(c_first + i, begin > 0 ? static_cast<int>(begin) : 0);
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");

@@ -68,6 +68,9 @@ constexpr int kErrMmaWaitFull = 2;
 constexpr int kErrMmaWaitTmem = 3;
 constexpr int kErrEpilogueWait = 4;
 constexpr int kMinKBlocksPerSplit = 4;  // keep every k-slice long enough to fill the ring
+constexpr int kMaxPartsSplitK = 8;      // parts of one tile: few rows per tile, small partial tiles
+constexpr int kMaxPartsEvenOut = 4;     // parts of one tile when tiles are full (128 KB per part)
+constexpr int kEvenOutMinSavedKBlocks = 80;  // cut the last wave only if it saves more tensor time than this
 
 // Workspace layout (used by the balanced schedule): one counter per tile, then two fp32 partial
 // tiles of BM x BN per CTA (a CTA's range has at most two incomplete tiles, see partial_slot).
@@ -264,19 +267,28 @@ __device__ __forceinline__ Schedule make_schedule(int total_tiles, int k_blocks,
   s.tail_ctas = 0;
   const int tail = total_tiles % grid;
   // Fewer tiles than half the CTAs is split-K proper, whose publish-and-sum tail only pays for a
-  // long k (kMinSplitK).  With more tiles the balanced schedule pays when CTAs run at their own
-  // pace, i.e. when the tensor pipe is the limit: every weight tile (`weight_tiles` of them: one per
-  // group with rows and column block) is used by two m-tiles or more on average.  With one m-tile
-  // per weight tile (decode batches) the kernel streams weights at the HBM rate, the CTAs of a
-  // ragged last wave simply run faster, and cutting tiles only adds traffic.
+  // long k (kMinSplitK).  With more tiles, cutting the last wave pays when (a) CTAs run at their
+  // own pace, i.e. the tensor pipe is the limit: every weight tile (`weight_tiles` of them: one per
+  // group with rows and column block) is used by two m-tiles or more on average -- with one
+  // m-tile per weight tile (decode batches) the kernel streams weights at the HBM rate, the CTAs
+  // of a ragged last wave simply run faster, and cutting tiles only adds traffic -- and (b) the
+  // k-blocks saved exceed the price of summing a cut tile: the CTA that sums reads every part
+  // (128 KB each) at the rate of a chain of L2 round trips, about 4 us per part or 10 k-blocks'
+  // worth of tensor time.  Hence also the cap on the parts of a tile.
   const bool split_k = 2 * total_tiles <= grid && k_blocks * BK >= kMinSplitK;
-  const bool even_out = 2 * total_tiles > grid && total_tiles < 8 * grid && total_tiles >= 2 * weight_tiles;
+  const int parts_cap = split_k ? kMaxPartsSplitK : kMaxPartsEvenOut;
+  const long long want = static_cast<long long>(tail) * parts_cap;
+  int ctas = want < grid ? static_cast<int>(want) : grid;
+  const long long most = static_cast<long long>(tail) * k_blocks / kMinKBlocksPerSplit;
+  if (most < ctas) ctas = most < 1 ? 1 : static_cast<int>(most);
+  const int range = ctas > 0 ? static_cast<int>((static_cast<long long>(tail) * k_blocks + ctas - 1) / ctas) : k_blocks;
+  const bool even_out = 2 * total_tiles > grid && total_tiles < 8 * grid && total_tiles >= 2 * weight_tiles &&
+                        k_blocks - range > kEvenOutMinSavedKBlocks;
   s.balanced = have_workspace && tail != 0 && (split_k || even_out);
   if (s.balanced) {
     s.whole_tiles = total_tiles - tail;
     s.tail_units = static_cast<long long>(tail) * k_blocks;
-    const long long most = s.tail_units / kMinKBlocksPerSplit;
-    s.tail_ctas = most < grid ? (most < 1 ? 1 : static_cast<int>(most)) : grid;
+    s.tail_ctas = ctas;
   }
   return s;
 }

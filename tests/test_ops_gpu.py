@@ -751,12 +751,13 @@ def test_matmul_c_abi_any_shape(cabi, m, k, n):
 
 
 @pytest.mark.parametrize("counts,k,n", [
-    ([350, 340, 410], 2048, 4096),       # 160 tiles on 148 SMs: the ragged second wave is spread out
-    ([1024], 1024, 256 * 146),           # 7.9 waves: ranges of several whole tiles with cut ends
-    ([64] * 8, 14336, 4096),             # decode down projection: one m-tile per expert, stays tile by tile
-    ([200] * 4, 14336, 4096),            # 128 tiles of two m-tiles per expert: under one wave, evened out
+    ([350, 340, 410], 14336, 4096),      # 160 tiles on 148 SMs: the 12 tiles of the second wave are cut in four
+    ([380, 390, 400], 14336, 4096),      # 176 tiles: 28 cut
+    ([200] * 4, 14336, 4096),            # 128 tiles, nearly a full wave: cutting would save too little, stays whole
+    ([64] * 8, 14336, 4096),             # decode down projection: one m-tile per expert, stays whole
     ([40, 0, 3, 90, 7, 64, 1, 128], 8192, 1024),  # fewer tiles than half the SMs, long k: split-K proper
-    ([200, 100], 1024, 320),             # N tail (320 = 256 + 64) in cut tiles
+    ([200, 100], 8192, 320),             # N tail (320 = 256 + 64) in cut tiles
+    ([1024], 1024, 256 * 146),           # 7.9 waves of a short k: stays whole
 ])
 def test_grouped_matmul_balanced_schedule(cabi, counts, k, n):
     """With a workspace the kernel cuts the (tile, k-block) units into equal ranges per SM; tiles
@@ -778,7 +779,7 @@ def test_grouped_matmul_balanced_schedule(cabi, counts, k, n):
     close(balanced[rows], want.half())
 
 
-@pytest.mark.parametrize("counts,k,d", [([350, 340, 410], 1024, 1792), ([64] * 8, 4096, 2048), ([1, 127, 129], 2048, 640)])
+@pytest.mark.parametrize("counts,k,d", [([300] * 3, 14336, 1024), ([64] * 8, 4096, 2048), ([1, 127, 129], 8192, 640)])
 def test_grouped_matmul_swiglu_balanced_schedule(cabi, counts, k, d):
     """The fused gate/up form under the balanced schedule: the CTA that sums a cut tile applies
     SwiGLU to the rounded sums.  Against grouped_matmul followed by swiglu (whose 256-column

@@ -656,9 +656,11 @@ __device__ __forceinline__ bool wait_for_count(const uint32_t* p, uint32_t tag, 
   }
 }
 
+// kBatch > 0: route here (route_logits<kBatch>); kBatch == 0: the expert ids are given, and the
+// kernel needs a fraction of the registers, so that a large batch's CTAs are all resident at once.
 template <int kBatch>
 __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams p) {
-  __shared__ float logits[kMaxExperts];
+  __shared__ float logits[kBatch > 0 ? kMaxExperts : 1];
   __shared__ int32_t chosen[kMaxTopK];
   __shared__ float chosen_w[kMaxTopK];
   __shared__ int dest_peer[kMaxTopK];
@@ -669,7 +671,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams 
   const int token = blockIdx.x;
   const int tid = threadIdx.x;
   if (tid == 0) dropped = 0;
-  if (p.router_weight != nullptr) {
+  if constexpr (kBatch > 0) {
     route_logits<kBatch>(p.x, p.router_weight, logits, token, p.hidden, p.num_experts);
     __syncthreads();
     if (tid < 32) {
@@ -961,7 +963,9 @@ extern "C" int b200ops_moe_dispatch(const void* x, const void* router_weight, co
   p.cap = static_cast<int>(cap);
   p.world = static_cast<int>(world);
   p.my_rank = static_cast<int>(my_rank);
-  auto kern = num_experts <= 8 ? moe::moe_dispatch_kernel<16> : moe::moe_dispatch_kernel<8>;
+  auto kern = router_weight == nullptr ? moe::moe_dispatch_kernel<0>
+              : num_experts <= 8       ? moe::moe_dispatch_kernel<16>
+                                       : moe::moe_dispatch_kernel<8>;
   B200OPS_CUDA(launch_kernel(kern, dim3(static_cast<unsigned>(num_tokens)), dim3(256), 0, static_cast<cudaStream_t>(stream), p));
   return B200OPS_OK;
 }

@@ -743,6 +743,32 @@ def profile_case(name, ops, dev):
         x, ws, gl = w["x"].to(dev), w["w_storage"].to(dev).transpose(1, 2), w["group_list"].to(dev)
         fn = lambda: moe.grouped_matmul_swiglu(x, ws, gl)
         info = {"flops": 2 * 4096 * 4096 * 4096}
+    elif name == "grouped_matmul_balanced":  # one rank's down projection of the 4096-token MoE MLP at 8 GPUs
+        counts = [350, 340, 410]
+        g = torch.Generator(device=dev).manual_seed(4)
+        x = torch.randn(1408, 14336, generator=g, device=dev, dtype=torch.float16)  # rows past 1100 belong to no group
+        ws = (0.02 * torch.randn(3, 4096, 14336, generator=g, device=dev, dtype=torch.float16)).transpose(1, 2)
+        gl = torch.tensor(counts, device=dev).cumsum(0).to(torch.int64)
+        fn = lambda: ops.grouped_matmul(x, ws, gl)
+        info = {"flops": 2 * sum(counts) * 14336 * 4096, "tiles": 160}
+    elif name == "moe_exchange":  # the three exchange launches with one rank (its own peer): latency only
+        import ascend910a_extras.moe as moe
+
+        t, h, e, k, cap = 256, 4096, 8, 2, 512
+        g = torch.Generator(device=dev).manual_seed(4)
+        x = torch.randn(t, h, generator=g, device=dev, dtype=torch.float16)
+        wr = 0.02 * torch.randn(e, h, generator=g, device=dev, dtype=torch.float16)
+        z = lambda *shape, dt=torch.int32: torch.zeros(*shape, dtype=dt, device=dev)
+        recv, ret = z(e * cap, h, dt=torch.float16), z(e * cap, h, dt=torch.float16)
+        counts, flags, cursor, state, over = z(1, e), z(1), z(e), z(8), z(2)
+
+        def fn():
+            pos, ids, wts = moe.dispatch(x, wr, None, k, None, None, 0, [recv.data_ptr()], [counts.data_ptr()], cursor,
+                                         state, over, e, cap, 0)
+            grouped, back, gl, total = moe.gather(recv, counts, state, over, cap, t * k)
+            moe.push_rows(grouped, back, 1, total, t * k, [ret.data_ptr()], e * cap, 0)
+            return moe.combine(ret, pos, wts, [flags.data_ptr()], flags, state, 0)
+        info = {"tokens": t, "rows": t * k}
     elif name == "dense_projection":  # QKV projection of a 256-row decode batch: cluster split-K
         g = torch.Generator().manual_seed(4)
         x = torch.randn(256, 4096, generator=g).half().to(dev)
@@ -780,6 +806,46 @@ def profile_case(name, ops, dev):
         fn()
     torch.cuda.synchronize(dev)
     print(json.dumps({"profile_case": name, **info}))
+
+
+# --------------------------------------------------------------------------- per-kernel timeline
+def timeline(which, ops, dev, rank, world, group):
+    """Per-kernel timeline of one step on every rank (torch profiler; the step launched op by op,
+    so kernel durations are clean but the gaps are host launch gaps, not the graph's).  Rank r
+    writes gpurun_out/timeline_<which>_n<N>_r<r>.txt: start offset, duration, kernel name."""
+    from torch.profiler import ProfilerActivity, profile
+
+    if which == "layer":
+        cfg, layer, batch, k_cache, v_cache, _ = build_layer(ops, dev, rank, world, group)
+        names = ("x", "residual", "positions", "slots", "block_tables", "context_lens")
+        d = {n: batch[n].to(dev) for n in names}
+        step = lambda: layer.forward(*(d[n] for n in names), k_cache, v_cache)
+    else:
+        step = run_moe_mlp(ops, dev, rank, world, group, 0, 3, load_peaks())
+    for _ in range(5):
+        step()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        torch.distributed.barrier(group)
+    reps = 4
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        for _ in range(reps):
+            step()
+        torch.cuda.synchronize(dev)
+    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                 key=lambda e: e.time_range.start)
+    last = evs[-(len(evs) // reps):]
+    t0 = last[0].time_range.start
+    out = REPO / "gpurun_out"
+    out.mkdir(exist_ok=True)
+    with open(out / f"timeline_{which}_n{world}_r{rank}.txt", "w") as f:
+        f.write(f"# {which} step, {world} GPUs, rank {rank}, exchange {EXCHANGE}, "
+                f"B200OPS_PDL={os.environ.get('B200OPS_PDL', '1')}\n")
+        for e in last:
+            f.write(f"{e.time_range.start - t0:9.1f} +{e.time_range.elapsed_us():8.1f} us  {e.name[:110]}\n")
+        f.write(f"step span us: {last[-1].time_range.end - t0:.1f}\n")
+    if world > 1:
+        torch.distributed.barrier(group)
 
 
 # --------------------------------------------------------------------------- main
@@ -821,6 +887,8 @@ def main():
                     help="expert-parallel exchange: NVLink peer-memory pushes, or NCCL collectives")
     ap.add_argument("--profile-case", default=None,
                     help="run a small case of one operator (for ncu) and exit")
+    ap.add_argument("--timeline", default=None, choices=["layer", "mlp"],
+                    help="write a per-kernel timeline of one step per rank (torch profiler) and exit")
     ns = ap.parse_args()
     global EXCHANGE
     EXCHANGE = ns.exchange
@@ -871,6 +939,11 @@ def main():
 
     if ns.profile_case:
         profile_case(ns.profile_case, ops, dev)
+        return
+    if ns.timeline:
+        timeline(ns.timeline, ops, dev, rank, world, group)
+        if world > 1:
+            torch.distributed.destroy_process_group()
         return
 
     sampler = ClockSampler(local_rank)

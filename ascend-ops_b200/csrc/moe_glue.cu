@@ -728,7 +728,7 @@ __global__ void __launch_bounds__(256) moe_dispatch_kernel(const DispatchParams 
   if (tid == 0) {
     __threadfence_system();
     is_last = atomicAdd(&p.state[2], 1u) == gridDim.x - 1;
-    if (is_last) __threadfence_system();
+    if (is_last) __threadfence();  // acquire the other CTAs' arrivals; the count words below release at system scope
   }
   __syncthreads();
   if (!is_last) return;
@@ -864,10 +864,8 @@ __global__ void __launch_bounds__(128) moe_combine_kernel(const CombineParams p)
   const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.state);
   if (tid == 0) ticket = atomicAdd(&p.state[3], 1u);
   __syncthreads();
-  if (ticket == 0 && tid < p.world) {
-    __threadfence_system();
+  if (ticket == 0 && tid < p.world)  // the release orders the completed down projection's stores before the flag
     st_release_sys(static_cast<uint32_t*>(p.flags.base[tid]) + p.my_rank, step);
-  }
   if (tid < p.world && !wait_for_peer(p.my_flags + tid, step))
     atomicCAS(reinterpret_cast<unsigned int*>(p.state + 1), 0u, 100u + static_cast<unsigned>(tid));
   __syncthreads();

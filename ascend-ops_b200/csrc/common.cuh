@@ -67,7 +67,6 @@ int sm_count();
 enum Knob {
   kKnobGmmPair,         // B200OPS_GMM_PAIR: 0 never use CTA pairs, 2 always, otherwise by shape
   kKnobGmmKsplit,       // B200OPS_GMM_KSPLIT: 0 disables the cluster split-K kernel
-  kKnobGmmSwap,         // B200OPS_GMM_SWAP: 0 disables the weights-as-M decode kernel
   kKnobPaMode,          // B200OPS_PA_MODE: 2 forces the general attention kernel
   kKnobPaStages,        // B200OPS_PA_STAGES: ring depth of the TMA attention kernel (2, 3, 4, 6)
   kKnobPaChunkTokens,   // B200OPS_PA_CHUNK_TOKENS: base chunk length of the split context

@@ -1,6 +1,5 @@
 """Out-of-bounds guard: every operator writes its outputs into the middle of a larger buffer
-whose margins hold a canary pattern; the margins must be intact afterwards.  (The GPU pool
-offers no compute-sanitizer, so the tests carry their own red zones.)"""
+whose margins hold a canary pattern; the margins must be intact afterwards."""
 import ctypes
 
 import pytest

@@ -10,7 +10,7 @@ times the CPU oracle's layer step, `ep_check` (more than one GPU) compares the e
 with the single-GPU path, and `per_op` holds one short row per operator (columns in
 `per_op_cols`: device time, achieved rate, fraction of the measured peak, the CPU oracle's time
 on all host threads, and the GPU result's error against it).  Shapes, byte counts and the other
-details of every row go to gpurun_out/bench_detail_n<N>.json.
+details of every row go to bench_detail_n<N>.json in the side-file directory (OUT_DIR).
 """
 from __future__ import annotations
 
@@ -36,6 +36,9 @@ import decode_workloads as wl  # noqa: E402
 # algorithmic bytes in an ncu capture of a 16-sequence case; the traffic grows in proportion to
 # the context tokens, so the ratio carries over to the full batch).
 ATTENTION_TRAFFIC_RATIO = 1.05
+
+# Side files (row details, timelines) go here; the printed line never depends on them.
+OUT_DIR = REPO / "gpurun_out"
 
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 L2_BYTES = 126 * 1024 * 1024
@@ -812,7 +815,7 @@ def profile_case(name, ops, dev):
 def timeline(which, ops, dev, rank, world, group):
     """Per-kernel timeline of one step on every rank (torch profiler; the step launched op by op,
     so kernel durations are clean but the gaps are host launch gaps, not the graph's).  Rank r
-    writes gpurun_out/timeline_<which>_n<N>_r<r>.txt: start offset, duration, kernel name."""
+    writes timeline_<which>_n<N>_r<r>.txt into OUT_DIR: start offset, duration, kernel name."""
     from torch.profiler import ProfilerActivity, profile
 
     if which == "layer":
@@ -836,7 +839,7 @@ def timeline(which, ops, dev, rank, world, group):
                  key=lambda e: e.time_range.start)
     last = evs[-(len(evs) // reps):]
     t0 = last[0].time_range.start
-    out = REPO / "gpurun_out"
+    out = OUT_DIR
     out.mkdir(exist_ok=True)
     with open(out / f"timeline_{which}_n{world}_r{rank}.txt", "w") as f:
         f.write(f"# {which} step, {world} GPUs, rank {rank}, exchange {EXCHANGE}, "
@@ -860,9 +863,9 @@ def compact(rec):
 
 def write_detail(n_gpus, detail):
     """Everything the printed line leaves out (shapes, byte counts, group sizes, placement), as
-    gpurun_out/bench_detail_n<N>.json next to this file, if that directory can be written."""
+    bench_detail_n<N>.json in OUT_DIR, if that directory can be written."""
     try:
-        out = REPO / "gpurun_out"
+        out = OUT_DIR
         out.mkdir(exist_ok=True)
         path = out / f"bench_detail_n{n_gpus}.json"
         path.write_text(json.dumps(detail, indent=1))

@@ -46,19 +46,19 @@ __device__ __forceinline__ uint32_t partial_offset(int row, int c4) {
 }
 
 // Sum rows rank, rank + s, ... of the cluster's s partial tiles (in rank order) and store them.
-// 128 threads: a thread owns one 16-byte chunk (4 output columns) of kRows rows per iteration and
-// has all of their kPeers x kRows remote loads in flight before the first add: the step is a
+// All 192 threads: a thread owns one 16-byte chunk (4 output columns) of kRows rows per iteration
+// and has all of their kPeers x kRows remote loads in flight before the first add: the step is a
 // chain of distributed-shared-memory round trips of about 0.3 us otherwise.
 template <int kPeers, int kRows>
 __device__ __forceinline__ void reduce_rows(uint8_t* smem, int rank, int splits, int rows_here,
                                             const TileCoord& tc, __half* y, int N, const RowScatter& scatter) {
-  const int t = threadIdx.x - 64;          // 0..127
+  const int t = threadIdx.x;               // 0..191
   const int c4 = t & 63;                   // 16-byte chunk = 4 output columns
   const bool col_ok = tc.n0 + c4 * 4 < N;  // N is a multiple of 64: chunks are all-or-nothing
   uint32_t peer_base[kPeers];
 #pragma unroll
   for (int p = 0; p < kPeers; ++p) peer_base[p] = ptx::map_to_cta(smem, p < splits ? p : 0);
-  const int step = 2 * splits;             // threads 0-63 and 64-127 take alternate owned rows
+  const int step = (kThreads / 64) * splits;  // the three groups of 64 threads take owned rows in turn
   for (int row0 = rank + splits * (t >> 6); row0 < rows_here; row0 += kRows * step) {
     float4 v[kRows][kPeers];
 #pragma unroll
@@ -133,6 +133,8 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   // Set-up that needs no input runs before the wait for the previous kernel, so that it overlaps
   // that kernel's tail: the barriers, and the TMEM allocation (warp 1, in parallel).
   if (threadIdx.x == 0) {
+    ptx::prefetch_tensormap(&map_x);
+    ptx::prefetch_tensormap(&map_w);
     for (int s = 0; s < kSplitStages; ++s) {
       ptx::mbar_init(&ctl->full[s], 1);
       ptx::mbar_init(&ctl->empty[s], 1);
@@ -254,10 +256,14 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   __syncthreads();  // reconverges the single-lane roles before the warp-aligned cluster barrier
   ptx::cluster_sync();
 
-  if (active && warp >= 2) {
+  if (active) {
     const int rows_here = min(BM, tc.row_end - tc.row0);
-    if (splits <= 4)
+    if (splits <= 2)
+      reduce_rows<2, 8>(smem, rank, splits, rows_here, tc, y, N, scatter);
+    else if (splits <= 4)
       reduce_rows<4, 4>(smem, rank, splits, rows_here, tc, y, N, scatter);
+    else if (splits <= 6)
+      reduce_rows<6, 3>(smem, rank, splits, rows_here, tc, y, N, scatter);
     else
       reduce_rows<kMaxClusterSplit, 2>(smem, rank, splits, rows_here, tc, y, N, scatter);
   }

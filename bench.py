@@ -701,9 +701,11 @@ def run_moe_mlp(ops, dev, rank, world, group, steps, warmup, peaks):
 
 
 # --------------------------------------------------------------------------- CPU baseline
-def cpu_layer_sample(seqs=32, repeats=1):
+def cpu_layer_sample(seqs=32, repeats=1, warmup=0, budget_s=None):
     """The CPU oracle's layer on a bounded sample: the first `seqs` of the 256 sequences with
-    the full weights.  Returns (microseconds scaled to 256 sequences, seconds measured)."""
+    the full weights.  `warmup` untimed passes, then `repeats` timed ones; with `budget_s` both
+    stop early once that many seconds have gone (a slow host), and the passes done are returned.
+    Returns (microseconds scaled to 256 sequences, seconds per pass, sequences[, passes, warm-ups])."""
     import moe_decode_layer as mdl
     from oracle import decode_ops_oracle as oracle
 
@@ -718,15 +720,30 @@ def cpu_layer_sample(seqs=32, repeats=1):
     k_cache = block.repeat(reps, 1, 1, 1)[: batch["cache_shape"][0]].contiguous()
     v_cache = k_cache.flip(0).contiguous()
     cos, sin = oracle.cos_sin_cache(16385, cfg.head_dim, cfg.rope_theta)
-    times = []
-    for _ in range(repeats):
+    def one_pass():
         t0 = time.perf_counter()
         oracle.moe_decode_layer(w, batch, k_cache, v_cache, heads=cfg.heads, kv_heads=cfg.kv_heads,
                                 head_dim=cfg.head_dim, experts=cfg.experts, top_k=cfg.top_k, eps=cfg.eps,
                                 cos_cache=cos, sin_cache=sin)
-        times.append(time.perf_counter() - t0)
-    dt = statistics.median(times)
-    return dt * 1e6 * (256 / seqs), dt, seqs
+        return time.perf_counter() - t0
+
+    start = time.perf_counter()
+    warmed = 0
+    for _ in range(warmup):
+        if budget_s is not None and warmed >= 1 and time.perf_counter() - start > budget_s / 4:
+            break
+        one_pass()
+        warmed += 1
+    times = []
+    for _ in range(repeats):
+        if budget_s is not None and times and time.perf_counter() - start > budget_s:
+            break
+        times.append(one_pass())
+    if budget_s is None:
+        dt = statistics.median(times)
+        return dt * 1e6 * (256 / seqs), dt, seqs
+    dt = sum(times) / len(times)  # the timed passes back to back, as the GPU arm's steps are
+    return dt * 1e6 * (256 / seqs), dt, seqs, len(times), warmed
 
 
 def cpu_sample_text(seqs, dt):
@@ -939,10 +956,13 @@ def main():
         # here is the CPU golden path, timed with every host thread on a bounded sample.
         if rank != 0:
             return
-        us, dt, seqs = cpu_layer_sample(ns.cpu_seqs, repeats=max(1, min(ns.steps, 3)))
+        # K timed passes after W untimed ones, as asked; a host so slow that this would run for
+        # more than about three minutes stops early and reports the passes it made.
+        us, dt, seqs, done, warmed = cpu_layer_sample(ns.cpu_seqs, repeats=max(1, ns.steps), warmup=ns.warmup,
+                                                      budget_s=180.0)
         line = dict(base)
         line.update({
-            "impl": "reference", "value": round(us, 1), "steps": max(1, min(ns.steps, 3)), "warmup": 0,
+            "impl": "reference", "value": round(us, 1), "steps": done, "warmup": warmed,
             "ms_per_step": round(us / 1e3, 3),
             "cpu_baseline": {"value": round(us, 1), "unit": "us", "cores": cores, "kind": "port",
                              "sample": cpu_sample_text(seqs, dt)},

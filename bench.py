@@ -793,6 +793,16 @@ def profile_case(name, ops, dev):
         gl = torch.tensor(counts, device=dev).cumsum(0).to(torch.int64)
         fn = lambda: ops.grouped_matmul(x, ws, gl)
         info = {"flops": 2 * sum(counts) * 14336 * 4096, "tiles": 160}
+    elif name == "grouped_matmul_decode":  # the layer's expert gate/up projection: 8 experts x 64 rows, SwiGLU epilogue
+        import ascend910a_extras.moe as moe
+
+        counts = [64] * 8
+        g = torch.Generator(device=dev).manual_seed(4)
+        x = torch.randn(512, 4096, generator=g, device=dev, dtype=torch.float16)
+        ws = (0.02 * torch.randn(8, 28672, 4096, generator=g, device=dev, dtype=torch.float16)).transpose(1, 2)
+        gl = torch.tensor(counts, device=dev).cumsum(0).to(torch.int64)
+        fn = lambda: moe.grouped_matmul_swiglu(x, ws, gl)
+        info = {"bytes": 2 * (8 * 28672 * 4096 + 512 * 4096 + 512 * 14336), "tiles": 896}
     elif name == "moe_exchange":  # the three exchange launches with one rank (its own peer): latency only
         import ascend910a_extras.moe as moe
 

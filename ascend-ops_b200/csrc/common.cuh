@@ -67,6 +67,7 @@ int sm_count();
 enum Knob {
   kKnobGmmPair,         // B200OPS_GMM_PAIR: 0 never use CTA pairs, 2 always, otherwise by shape
   kKnobGmmKsplit,       // B200OPS_GMM_KSPLIT: 0 disables the cluster split-K kernel
+  kKnobGmmShort,        // B200OPS_GMM_SHORT: 0 never loads short activation tiles (decode-size grouped GEMMs)
   kKnobPaMode,          // B200OPS_PA_MODE: 2 forces the general attention kernel
   kKnobPaStages,        // B200OPS_PA_STAGES: ring depth of the TMA attention kernel (2, 3, 4, 6)
   kKnobPaChunkTokens,   // B200OPS_PA_CHUNK_TOKENS: base chunk length of the split context

@@ -9,7 +9,8 @@ namespace b200ops {
 
 namespace {
 const char* const kKnobNames[kKnobCount] = {
-    "B200OPS_GMM_PAIR",    "B200OPS_GMM_KSPLIT",        "B200OPS_PA_MODE",   "B200OPS_PA_STAGES", "B200OPS_PA_CHUNK_TOKENS",
+    "B200OPS_GMM_PAIR",    "B200OPS_GMM_KSPLIT",        "B200OPS_GMM_SHORT", "B200OPS_PA_MODE",
+    "B200OPS_PA_STAGES",   "B200OPS_PA_CHUNK_TOKENS",
     "B200OPS_RMSNORM_VPT", "B200OPS_RMSNORM_CTA_WARPS", "B200OPS_RAC_DEDUP", "B200OPS_PDL"};
 std::atomic<int> g_knob_state[kKnobCount];  // 0 not read yet, 1 unset, 2 set
 std::atomic<int> g_knob_value[kKnobCount];

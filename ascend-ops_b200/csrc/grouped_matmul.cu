@@ -151,7 +151,20 @@ inline bool balanced_possible(int64_t num_tokens, int64_t k, int64_t num_experts
   return k >= 1024 && max_tiles < static_cast<int64_t>(kBalancedWaves) * sms;
 }
 
+// Short activation tiles.  When no group has more than kShortRows rows (a decode batch: one
+// m-tile per expert, mostly half empty) the 256-column kernels load only kShortRows rows of x per
+// k-block and use the room for a fifth stage.  Such a problem streams its weights once and is
+// bound by the bytes a CTA has in flight (about 3 us pass between a load's issue and the release
+// of its stage): with 48 KB stages a third of them are the activation tile, an L2 hit, and the
+// weights stream at 6.0 TB/s; with 10 + 32 KB stages, five of them, 160 KB of weights are in
+// flight instead of 128.  The MMA still multiplies 128 rows: rows past the box are whatever the
+// next stage holds, and are never stored.  Decided on the device from the real group sizes.
+constexpr int kShortRows = 80;
+constexpr int kShortABytes = kShortRows * BK * 2;
+constexpr int kShortStages = 5;
+
 struct Control {
+  int short_tiles;  // this launch runs with short activation tiles
   uint64_t full[kMaxStages];
   uint64_t empty[kMaxStages];
   uint64_t tmem_full[2];
@@ -186,7 +199,13 @@ struct Cfg {
   static constexpr int kBBytes = BN_ * BK * 2;
   static constexpr int kStageBytes = kABytes + kBBytes;
   static constexpr int kTmemCols = 2 * BN_ < 32 ? 32 : 2 * BN_;  // a power of two >= 32
-  static constexpr size_t kSmemBytes = 1024 /* alignment slack */ + STAGES_ * kStageBytes + sizeof(Control);
+  static constexpr bool kShortCapable = BN_ == kWideBN;  // the narrow shape's stages are small already
+  static constexpr int kShortStageBytes = kShortABytes + kBBytes;
+  static constexpr int kRingBytes = (kShortCapable && kShortStages * kShortStageBytes > STAGES_ * kStageBytes)
+                                        ? kShortStages * kShortStageBytes
+                                        : STAGES_ * kStageBytes;
+  static constexpr size_t kSmemBytes = 1024 /* alignment slack */ + kRingBytes + sizeof(Control);
+  static_assert(kSmemBytes <= 227 * 1024, "shared memory per CTA");
 };
 using WideCfg = Cfg<kWideBN, 4>;
 using NarrowCfg = Cfg<kNarrowBN, 8>;
@@ -463,21 +482,20 @@ __device__ __forceinline__ void reduce_parts(const float* __restrict__ partials,
 template <class C>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
+                      const __grid_constant__ CUtensorMap map_x_short,
                       const __grid_constant__ CUtensorMap map_w,
                       const int64_t* __restrict__ group_list, __half* __restrict__ y, int M, int N,
                       int K, int E, int* __restrict__ tile_counters, float* __restrict__ partials,
-                      const RowScatter scatter) {
+                      const RowScatter scatter, const int allow_short) {
   constexpr int BN = C::BN;
   constexpr int kStages = C::kStages;
   constexpr int kBBytes = C::kBBytes;
-  constexpr int kStageBytes = C::kStageBytes;
   constexpr int kTmemCols = C::kTmemCols;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* a_tiles = smem;
-  uint8_t* b_tiles = smem + kStages * kABytes;
-  Control* ctl = reinterpret_cast<Control*>(smem + kStages * kStageBytes);
+  Control* ctl = reinterpret_cast<Control*>(smem + C::kRingBytes);
 
   constexpr bool kGlu = C::kGlu;
   constexpr int kOutBN = C::kOutBN;  // output columns per tile
@@ -489,7 +507,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
 
   pdl_trigger();
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < (kStages > kShortStages ? kStages : kShortStages); ++s) {
       ptx::mbar_init(&ctl->full[s], 1);
       ptx::mbar_init(&ctl->empty[s], 1);
     }
@@ -500,6 +518,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
     ctl->abort_flag = 0;
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&map_x);
+    ptx::prefetch_tensormap(&map_x_short);
     ptx::prefetch_tensormap(&map_w);
   }
   if (warp == 1) {
@@ -518,21 +537,30 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
   }
   __syncthreads();
   if (threadIdx.x == 0) {
-    int acc = 0, live = 0;
+    int acc = 0, live = 0, most = 0;
     ctl->tile_prefix[0] = 0;
     for (int e = 0; e < E; ++e) {
       const int rows = ctl->row_end[e] - ctl->row_start[e];
       acc += ((rows + BM - 1) / BM) * n_tiles;
       live += rows > 0;
+      most = rows > most ? rows : most;
       ctl->tile_prefix[e + 1] = acc;
     }
     ctl->live_groups = live;
+    ctl->short_tiles = C::kShortCapable && allow_short != 0 && most <= kShortRows;
   }
   ptx::tcgen05_fence_before();
   __syncthreads();
   ptx::tcgen05_fence_after();
 
   const int total_tiles = ctl->tile_prefix[E];
+  // Ring geometry of this launch (the same in every CTA: it follows from the group sizes).
+  const bool short_tiles = ctl->short_tiles != 0;
+  const int stages = short_tiles ? kShortStages : kStages;
+  const int a_bytes = short_tiles ? kShortABytes : kABytes;
+  const uint32_t stage_tx = static_cast<uint32_t>(a_bytes + kBBytes);
+  uint8_t* b_tiles = smem + stages * a_bytes;
+  const CUtensorMap* x_map = short_tiles ? &map_x_short : &map_x;
   const uint32_t tmem_base = ctl->tmem_base;
   volatile int* abort_flag = &ctl->abort_flag;
   // Every role walks the same sequence of segments (tile, k-blocks [kb0, kb1)); the schedule
@@ -557,8 +585,8 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
             ok = false;
             break;
           }
-          ptx::mbar_arrive_expect_tx(&ctl->full[stage], kStageBytes);
-          ptx::tma_load_2d(a_tiles + stage * kABytes, &map_x, &ctl->full[stage], kb * BK, tc.row0);
+          ptx::mbar_arrive_expect_tx(&ctl->full[stage], stage_tx);
+          ptx::tma_load_2d(a_tiles + stage * a_bytes, x_map, &ctl->full[stage], kb * BK, tc.row0);
           if (kGlu) {  // gate rows, then the up rows of the same outputs (boxes of BN / 2 rows)
             ptx::tma_load_3d(b_tiles + stage * kBBytes, &map_w, &ctl->full[stage], kb * BK, tc.n0, tc.group);
             ptx::tma_load_3d(b_tiles + stage * kBBytes + kBBytes / 2, &map_w, &ctl->full[stage], kb * BK,
@@ -566,7 +594,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
           } else
           ptx::tma_load_3d(b_tiles + stage * kBBytes, &map_w, &ctl->full[stage], kb * BK, tc.n0,
                            tc.group);
-          if (++stage == kStages) {
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -601,7 +629,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
             break;
           }
           ptx::tcgen05_fence_after();
-          const uint32_t a_addr = ptx::smem_u32(a_tiles + stage * kABytes);
+          const uint32_t a_addr = ptx::smem_u32(a_tiles + stage * a_bytes);
           const uint32_t b_addr = ptx::smem_u32(b_tiles + stage * kBBytes);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -611,7 +639,7 @@ grouped_matmul_kernel(const __grid_constant__ CUtensorMap map_x,
             ptx::umma_f16(d_tmem, a_desc, b_desc, idesc, (kb != sg.kb0 || k != 0) ? 1u : 0u);
           }
           ptx::umma_commit(&ctl->empty[stage]);  // frees the stage once these MMAs retire
-          if (++stage == kStages) {
+          if (++stage == stages) {
             stage = 0;
             phase ^= 1u;
           }
@@ -1053,6 +1081,7 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
               : narrow ? gmm::grouped_matmul_kernel<gmm::NarrowCfg>
                        : gmm::grouped_matmul_kernel<gmm::WideCfg>;
   const size_t smem = narrow ? gmm::NarrowCfg::kSmemBytes : gmm::WideCfg::kSmemBytes;
+  static_assert(gmm::WideCfg::kSmemBytes == gmm::GluCfg::kSmemBytes, "the gate/up form shares the wide shape's ring");
   const int variant = glu ? 2 : (narrow ? 1 : 0);
   static std::atomic<bool> attr_set[3][64];
   int dev = 0;
@@ -1077,9 +1106,19 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
     B200OPS_CUDA(cudaMemsetAsync(counters, 0, gmm::kCounterBytes, st));
     grid = sms;  // the schedule cuts the work into one range per SM; CTAs without one exit
   }
-  B200OPS_CUDA(launch_kernel(kern, dim3(grid), dim3(gmm::kThreads), smem, st, map_x, map_w, group_list,
+  CUtensorMap map_x_short = map_x;  // the narrow shape never uses it
+  if (!narrow) {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(num_tokens)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
+    const uint32_t box[2] = {gmm::BK, gmm::kShortRows};
+    const int rc = encode_f16_map(&map_x_short, x, 2, dims, strides, box, "grouped_matmul(x, short tiles)");
+    if (rc != B200OPS_OK) return rc;
+  }
+  const int allow_short = knob(kKnobGmmShort, 1) != 0 ? 1 : 0;
+  B200OPS_CUDA(launch_kernel(kern, dim3(grid), dim3(gmm::kThreads), smem, st, map_x, map_x_short, map_w, group_list,
                       static_cast<__half*>(y), static_cast<int>(num_tokens), static_cast<int>(n),
-                      static_cast<int>(k), static_cast<int>(num_experts), counters, partials, scatter));
+                      static_cast<int>(k), static_cast<int>(num_experts), counters, partials, scatter,
+                      allow_short));
   return B200OPS_OK;
 }
 

@@ -49,12 +49,12 @@ int b200ops_version(void);
 const char* b200ops_last_error(void);
 
 /*
- * Tuning variables (B200OPS_GMM_PAIR, B200OPS_GMM_KSPLIT, B200OPS_PA_MODE, B200OPS_PA_STAGES,
- * B200OPS_PA_CHUNK_TOKENS, B200OPS_RMSNORM_VPT, B200OPS_RMSNORM_CTA_WARPS, B200OPS_RAC_DEDUP,
- * B200OPS_PDL) are read from the environment once per process, at their first use; no launch
- * calls getenv after that.  This call forgets what was read, so that the next use looks at the environment again
- * (for tests and tuning sessions that change a variable mid-process).  No counterpart in the
- * reference.
+ * Tuning variables (B200OPS_GMM_PAIR, B200OPS_GMM_KSPLIT, B200OPS_GMM_SHORT, B200OPS_PA_MODE,
+ * B200OPS_PA_STAGES, B200OPS_PA_CHUNK_TOKENS, B200OPS_RMSNORM_VPT, B200OPS_RMSNORM_CTA_WARPS,
+ * B200OPS_RAC_DEDUP, B200OPS_PDL) are read from the environment once per process, at their
+ * first use; no launch calls getenv after that.  This call forgets what was read, so that the
+ * next use looks at the environment again (for tests and tuning sessions that change a
+ * variable mid-process).  No counterpart in the reference.
  */
 void b200ops_reload_options(void);
 

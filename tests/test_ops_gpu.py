@@ -503,6 +503,42 @@ def test_grouped_matmul_cluster_split_k(cabi, monkeypatch, counts, k, n):
     close(run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False), want)
 
 
+@pytest.mark.parametrize("counts,k,n", [
+    ([64] * 8, 512, 512),              # a decode batch: every group fits the short activation tile
+    ([80, 1, 0, 79, 33], 1024, 768),   # the limit itself, a single row, an empty group; 16 k-blocks wrap the 5-stage ring
+    ([81, 3], 512, 512),               # one row too many: the launch keeps the full tile
+    ([40, 70], 8192, 512),             # short tiles together with split-K through the workspace
+    ([17] * 100, 256, 256),            # a hundred small groups
+])
+def test_grouped_matmul_short_activation_tiles(cabi, monkeypatch, counts, k, n):
+    """When no group has more than 80 rows the kernel loads 80-row activation tiles into a
+    five-stage ring; the products are the same, in the same order: bit-equal to the full tile."""
+    g = torch.Generator().manual_seed(sum(counts) + k + n)
+    m = sum(counts)
+    x = torch.randn(m + 40, k, generator=g).half()  # rows past the last group: read by boxes, never used
+    w_storage = (torch.randn(len(counts), n, k, generator=g) * 0.05).half()
+    gl = torch.tensor(counts).cumsum(0).to(torch.int64)
+    want = oracle.grouped_matmul(x, w_storage.transpose(1, 2), gl)
+    knob(monkeypatch, "B200OPS_GMM_SHORT", None)
+    got = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0)
+    close(got[:m], want[:m])
+    assert (got[m:] == 5.0).all()
+    knob(monkeypatch, "B200OPS_GMM_SHORT", "0")
+    full = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0)
+    assert torch.equal(got, full)
+    # the same with SwiGLU in the epilogue
+    xd, wd, gld = x.to(DEV), w_storage.to(DEV), gl.to(DEV)
+    fused_full = torch.full((m + 40, n // 2), 3.0, dtype=torch.float16, device=DEV)
+    cabi.grouped_matmul_swiglu(xd, wd, gld, fused_full)
+    knob(monkeypatch, "B200OPS_GMM_SHORT", None)
+    fused = torch.full((m + 40, n // 2), 3.0, dtype=torch.float16, device=DEV)
+    cabi.grouped_matmul_swiglu(xd, wd, gld, fused)
+    torch.cuda.synchronize()
+    assert cabi.pipeline_status() == 0
+    assert torch.equal(fused, fused_full)
+    close(fused[:m].cpu(), oracle.swiglu(want[:m]))
+
+
 def test_grouped_matmul_cluster_split_k_fewer_rows_than_the_bound(cabi):
     """group_list may end before num_tokens: clusters whose tile does not exist do nothing, rows
     past the group's end stay untouched."""

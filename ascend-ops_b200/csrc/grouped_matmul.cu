@@ -964,7 +964,8 @@ static int fit_split_to_device(int splits, int64_t tiles) {
   return splits >= 2 ? splits : 0;
 }
 
-static int launch_ksplit(const CUtensorMap& map_x, const void* w, const int64_t* group_list, void* y,
+static int launch_ksplit(const CUtensorMap& map_x, const CUtensorMap& map_x_short, const void* w,
+                         const int64_t* group_list, void* y,
                          int64_t num_tokens, int64_t k, int64_t num_experts, int64_t n, int splits,
                          const RowScatter& scatter, cudaStream_t st) {
   CUtensorMap map_w;
@@ -986,10 +987,16 @@ static int launch_ksplit(const CUtensorMap& map_x, const void* w, const int64_t*
   }
   static_assert(kMaxClusterSplitHost == kMaxClusterSplit, "host and device agree on the cluster limit");
   const int64_t tiles = ((num_tokens + BM - 1) / BM) * ((n + kSplitBN - 1) / kSplitBN);
+  int tile_choice = kSplitTilesFull;
+  if (knob(kKnobGmmShort, 1) != 0) {
+    if (num_tokens <= kShortRows) tile_choice = kSplitTilesShort;
+    else if (num_tokens > kMaxClusterSplitRows && group_list != nullptr) tile_choice = kSplitTilesByRowCount;
+  }
   B200OPS_CUDA(launch_cluster(grouped_matmul_ksplit_kernel, dim3(static_cast<unsigned>(tiles * splits)),
-                              dim3(kThreads), kSplitSmemBytes, st, static_cast<unsigned>(splits), map_x, map_w,
-                              group_list, static_cast<__half*>(y), static_cast<int>(num_tokens),
-                              static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts), scatter));
+                              dim3(kThreads), kSplitSmemBytes, st, static_cast<unsigned>(splits), map_x, map_x_short,
+                              map_w, group_list, static_cast<__half*>(y), static_cast<int>(num_tokens),
+                              static_cast<int>(n), static_cast<int>(k), static_cast<int>(num_experts), scatter,
+                              tile_choice));
   return B200OPS_OK;
 }
 
@@ -1055,6 +1062,14 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
     const int rc = encode_f16_map(&map_x, x, 2, dims, strides, box, "grouped_matmul(x)");
     if (rc != B200OPS_OK) return rc;
   }
+  CUtensorMap map_x_short;  // the same rows in boxes of kShortRows (decode-size problems)
+  {
+    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(num_tokens)};
+    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
+    const uint32_t box[2] = {gmm::BK, gmm::kShortRows};
+    const int rc = encode_f16_map(&map_x_short, x, 2, dims, strides, box, "grouped_matmul(x, short tiles)");
+    if (rc != B200OPS_OK) return rc;
+  }
   const int sms = gmm::launch_sms();
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   // The fused gate/up form exists in the two throughput kernels only (its shapes have thousands
@@ -1063,7 +1078,7 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
   int s = glu ? 0 : gmm::cluster_split_factor(num_tokens, k, num_experts, n, sms, &resident_tiles);
   if (s) s = gmm::fit_split_to_device(s, resident_tiles);
   if (s)
-    return gmm::launch_ksplit(map_x, w, group_list, y, num_tokens, k, num_experts, n, s, scatter, st);
+    return gmm::launch_ksplit(map_x, map_x_short, w, group_list, y, num_tokens, k, num_experts, n, s, scatter, st);
   if (gmm::use_cta_pairs(num_tokens, num_experts, n, sms))
     return gmm::launch_pairs(map_x, w, group_list, y, num_tokens, k, num_experts, n, glu, scatter, st);
   const bool narrow = !glu && gmm::use_narrow_tiles(num_tokens, k, n, sms);
@@ -1105,14 +1120,6 @@ int b200ops::gmm::launch(const void* x, const void* w, const int64_t* group_list
     partials = reinterpret_cast<float*>(static_cast<char*>(workspace) + gmm::kCounterBytes);
     B200OPS_CUDA(cudaMemsetAsync(counters, 0, gmm::kCounterBytes, st));
     grid = sms;  // the schedule cuts the work into one range per SM; CTAs without one exit
-  }
-  CUtensorMap map_x_short = map_x;  // the narrow shape never uses it
-  if (!narrow) {
-    const uint64_t dims[2] = {static_cast<uint64_t>(k), static_cast<uint64_t>(num_tokens)};
-    const uint64_t strides[1] = {static_cast<uint64_t>(k) * 2};
-    const uint32_t box[2] = {gmm::BK, gmm::kShortRows};
-    const int rc = encode_f16_map(&map_x_short, x, 2, dims, strides, box, "grouped_matmul(x, short tiles)");
-    if (rc != B200OPS_OK) return rc;
   }
   const int allow_short = knob(kKnobGmmShort, 1) != 0 ? 1 : 0;
   B200OPS_CUDA(launch_kernel(kern, dim3(grid), dim3(gmm::kThreads), smem, st, map_x, map_x_short, map_w, group_list,

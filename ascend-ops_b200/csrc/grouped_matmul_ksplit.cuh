@@ -18,11 +18,22 @@ constexpr int kSplitBN = kWideBN;
 constexpr int kSplitStages = 4;
 constexpr int kSplitBBytes = kSplitBN * BK * 2;
 constexpr int kSplitStageBytes = kABytes + kSplitBBytes;
+// With at most kShortRows rows the ring holds kShortStages stages of a short activation tile and
+// the weight tile (see kShortRows): more weight bytes in flight per CTA.
+constexpr int kSplitShortStageBytes = kShortABytes + kSplitBBytes;
+constexpr int kSplitRingBytes = kShortStages * kSplitShortStageBytes > kSplitStages * kSplitStageBytes
+                                    ? kShortStages * kSplitShortStageBytes
+                                    : kSplitStages * kSplitStageBytes;
 constexpr int kSplitTmemCols = kSplitBN;                       // one accumulator
 constexpr int kSplitRowBytes = kSplitBN * 4;                   // an fp32 row of the partial tile
-constexpr size_t kSplitSmemBytes = 1024 + kSplitStages * kSplitStageBytes + sizeof(Control);
+constexpr size_t kSplitSmemBytes = 1024 + kSplitRingBytes + sizeof(Control);
 constexpr int kMaxClusterSplit = 8;                            // portable cluster size
 static_assert(BM * kSplitRowBytes <= kSplitStages * kSplitStageBytes, "partial tile must fit the ring");
+static_assert(kSplitSmemBytes <= 227 * 1024, "shared memory per CTA");
+// How the launch chooses the activation tile's height: the host knows (rows <= kShortRows by its
+// bound, or not), or the kernel reads the row count first (a loose bound: an expert-parallel
+// receive buffer), which costs a load's latency before the first TMA.
+constexpr int kSplitTilesFull = 0, kSplitTilesShort = 1, kSplitTilesByRowCount = 2;
 
 __device__ __forceinline__ uint32_t cluster_size_x() {
   uint32_t r;
@@ -94,15 +105,15 @@ __device__ __forceinline__ void reduce_rows(uint8_t* smem, int rank, int splits,
 
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
+                             const __grid_constant__ CUtensorMap map_x_short,
                              const __grid_constant__ CUtensorMap map_w,
                              const int64_t* __restrict__ group_list, __half* __restrict__ y, int M, int N,
-                             int K, int E, const RowScatter scatter) {
+                             int K, int E, const RowScatter scatter, const int tile_choice) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   uint8_t* a_tiles = smem;
-  uint8_t* b_tiles = smem + kSplitStages * kABytes;
-  Control* ctl = reinterpret_cast<Control*>(smem + kSplitStages * kSplitStageBytes);
+  Control* ctl = reinterpret_cast<Control*>(smem + kSplitRingBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -134,8 +145,9 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   // that kernel's tail: the barriers, and the TMEM allocation (warp 1, in parallel).
   if (threadIdx.x == 0) {
     ptx::prefetch_tensormap(&map_x);
+    ptx::prefetch_tensormap(&map_x_short);
     ptx::prefetch_tensormap(&map_w);
-    for (int s = 0; s < kSplitStages; ++s) {
+    for (int s = 0; s < kShortStages; ++s) {
       ptx::mbar_init(&ctl->full[s], 1);
       ptx::mbar_init(&ctl->empty[s], 1);
     }
@@ -149,17 +161,26 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   }
   pdl_wait();  // the row count and the loads below are inputs
   bool active = may_run;
-  if (m_tile > 0) {
+  bool short_tiles = tile_choice == kSplitTilesShort;
+  if (m_tile > 0 || tile_choice == kSplitTilesByRowCount) {
     long long rows = group_list ? group_list[0] : M;
-    active = active && tc.row0 < (rows > M ? M : rows);
+    rows = rows > M ? M : rows;
+    if (m_tile > 0) active = active && tc.row0 < rows;
+    if (tile_choice == kSplitTilesByRowCount) short_tiles = rows <= kShortRows;  // the same in every CTA
   }
-  const int prefill = active ? min(kSplitStages, kb1 - kb0) : 0;
+  // Ring geometry of this launch.
+  const int stages = short_tiles ? kShortStages : kSplitStages;
+  const int a_bytes = short_tiles ? kShortABytes : kABytes;
+  const uint32_t stage_tx = static_cast<uint32_t>(a_bytes + kSplitBBytes);
+  uint8_t* b_tiles = smem + stages * a_bytes;
+  const CUtensorMap* x_map = short_tiles ? &map_x_short : &map_x;
+  const int prefill = active ? min(stages, kb1 - kb0) : 0;
   if (threadIdx.x == 0) {
     // The first ring-full of loads needs nobody else: issue it before the CTA-wide barrier so
     // that its latency (about 2 us from HBM) overlaps it.
     for (int i = 0; i < prefill; ++i) {
-      ptx::mbar_arrive_expect_tx(&ctl->full[i], kSplitStageBytes);
-      ptx::tma_load_2d(a_tiles + i * kABytes, &map_x, &ctl->full[i], (kb0 + i) * BK, tc.row0);
+      ptx::mbar_arrive_expect_tx(&ctl->full[i], stage_tx);
+      ptx::tma_load_2d(a_tiles + i * a_bytes, x_map, &ctl->full[i], (kb0 + i) * BK, tc.row0);
       ptx::tma_load_3d(b_tiles + i * kSplitBBytes, &map_w, &ctl->full[i], (kb0 + i) * BK, tc.n0, 0);
     }
   }
@@ -178,18 +199,18 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
   if (active && warp == 0) {
     // ---------------- TMA producer (the rest of the k-slice) ----------------
     if (lane == 0) {
-      int stage = prefill == kSplitStages ? 0 : prefill;
-      uint32_t phase = prefill == kSplitStages ? 1u : 0u;
+      int stage = prefill == stages ? 0 : prefill;
+      uint32_t phase = prefill == stages ? 1u : 0u;
       for (int kb = kb0 + prefill; kb < kb1; ++kb) {
         if (!ptx::mbar_wait(&ctl->empty[stage], phase ^ 1u, abort_flag)) {
           *abort_flag = 1;
           atomicCAS(&g_pipeline_status, 0, kErrProducerWait);
           break;
         }
-        ptx::mbar_arrive_expect_tx(&ctl->full[stage], kSplitStageBytes);
-        ptx::tma_load_2d(a_tiles + stage * kABytes, &map_x, &ctl->full[stage], kb * BK, tc.row0);
+        ptx::mbar_arrive_expect_tx(&ctl->full[stage], stage_tx);
+        ptx::tma_load_2d(a_tiles + stage * a_bytes, x_map, &ctl->full[stage], kb * BK, tc.row0);
         ptx::tma_load_3d(b_tiles + stage * kSplitBBytes, &map_w, &ctl->full[stage], kb * BK, tc.n0, 0);
-        if (++stage == kSplitStages) {
+        if (++stage == stages) {
           stage = 0;
           phase ^= 1u;
         }
@@ -210,7 +231,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
           break;
         }
         ptx::tcgen05_fence_after();
-        const uint32_t a_addr = ptx::smem_u32(a_tiles + stage * kABytes);
+        const uint32_t a_addr = ptx::smem_u32(a_tiles + stage * a_bytes);
         const uint32_t b_addr = ptx::smem_u32(b_tiles + stage * kSplitBBytes);
 #pragma unroll
         for (int k = 0; k < BK / UMMA_K; ++k) {
@@ -219,7 +240,7 @@ grouped_matmul_ksplit_kernel(const __grid_constant__ CUtensorMap map_x,
           ptx::umma_f16(tmem_base, a_desc, b_desc, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
         }
         ptx::umma_commit(&ctl->empty[stage]);
-        if (++stage == kSplitStages) {
+        if (++stage == stages) {
           stage = 0;
           phase ^= 1u;
         }

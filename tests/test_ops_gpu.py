@@ -499,6 +499,9 @@ def test_grouped_matmul_cluster_split_k(cabi, monkeypatch, counts, k, n):
     close(got, want)
     again = run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False)
     assert torch.equal(got, again)  # fixed summation order: bitwise repeatable
+    knob(monkeypatch, "B200OPS_GMM_SHORT", "0")  # full activation tiles also for up to 80 rows: the same bits
+    assert torch.equal(run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False), got)
+    knob(monkeypatch, "B200OPS_GMM_SHORT", None)
     knob(monkeypatch, "B200OPS_GMM_KSPLIT", "0")
     close(run_grouped_matmul(cabi, x, w_storage, gl, fill=5.0, split_k=False), want)
 
@@ -590,10 +593,12 @@ def test_grouped_matmul_swiglu_rejects_odd_widths(cabi):
     assert e.value.code == cabi.EINVAL
 
 
-@pytest.mark.parametrize("rows", [0, 100, 128, 300, 512])
-def test_grouped_matmul_cluster_split_k_loose_row_bound(cabi, rows):
+@pytest.mark.parametrize("rows", [0, 64, 80, 81, 100, 128, 300, 512])
+def test_grouped_matmul_cluster_split_k_loose_row_bound(cabi, monkeypatch, rows):
     """One expert, a 512-row buffer, K = 8192: the cluster size is chosen for one m-tile of rows;
-    clusters of m-tiles without rows leave at once, those with rows run as further waves."""
+    clusters of m-tiles without rows leave at once, those with rows run as further waves.  The
+    kernel reads the row count first and loads short activation tiles for up to 80 rows: the
+    same products in the same order."""
     g = torch.Generator().manual_seed(rows + 5)
     x = torch.randn(512, 8192, generator=g).half()
     w_storage = (torch.randn(1, 512, 8192, generator=g) * 0.03).half()
@@ -602,6 +607,8 @@ def test_grouped_matmul_cluster_split_k_loose_row_bound(cabi, rows):
     got = run_grouped_matmul(cabi, x, w_storage, gl, fill=9.0, split_k=True)
     close(got[:rows], want[:rows])
     assert (got[rows:] == 9.0).all()
+    knob(monkeypatch, "B200OPS_GMM_SHORT", "0")
+    assert torch.equal(run_grouped_matmul(cabi, x, w_storage, gl, fill=9.0, split_k=True), got)
 
 
 def test_paged_attention_nz_layout_fast_and_general_paths_agree(cabi, monkeypatch):

@@ -35,13 +35,17 @@
 // runs grouped_matmul_ksplit_kernel (grouped_matmul_ksplit.cuh): the CTAs of a cluster share one
 // output tile and reduce their k-slices through distributed shared memory, without a workspace.
 //
+// Short activation tiles.  When no group has more than 80 rows (a decode batch) the x tile is
+// loaded 80 rows high and the ring has five stages of 42 KB: such problems are bound by the
+// weight bytes a CTA has in flight (see kShortRows).
+//
 // SwiGLU epilogue.  Cfg<.., true> and grouped_matmul_pair_kernel<true> compute the gate/up
 // projection of a gated MLP and apply SwiGLU before storing (b200ops_grouped_matmul_swiglu).
 //
 // Tiles are enumerated group by group, m-tile fastest, so that CTAs running at the same
 // time share the same w tile (read from HBM once, then from L2) while the group's x rows
 // stay L2-resident.  Work is 2*M*K*N flops; at the sizes of interest the kernel is bound by
-// the tensor pipe, at decode sizes (few rows per expert) by streaming w from HBM.
+// the tensor pipe, at decode sizes (few rows per expert) by streaming w from HBM once.
 #include <atomic>
 
 #include "common.cuh"
